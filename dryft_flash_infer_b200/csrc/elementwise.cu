@@ -1,0 +1,328 @@
+// Row-wise kernels of the step: embedding gather, RMSNorm with and without the fused
+// residual add, SwiGLU, row gather, and the fused per-head norm + rotary embedding +
+// cache write.  Formulas follow the reference engine's plain-torch statement of its
+// fused kernels (engine/kernels/reference.py:13-23, :31-71, :74-79) with one
+// difference: values stay float32 inside a kernel and round once on store.
+#include "common.cuh"
+
+namespace dfi {
+
+// ------------------------------------------------------------------ embedding
+template <typename T, bool VEC>
+__global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids, T* __restrict__ out,
+                                 int hidden, int vocab) {
+    const int row = blockIdx.x;
+    int id = ids[row];
+    id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+    const T* src = table + (size_t)id * hidden;
+    T* dst = out + (size_t)row * hidden;
+    if (VEC) {
+        constexpr int n = Vec16<T>::n;
+        for (int i = threadIdx.x * n; i < hidden; i += blockDim.x * n)
+            *reinterpret_cast<uint4*>(dst + i) = *reinterpret_cast<const uint4*>(src + i);
+    } else {
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = src[i];
+    }
+}
+
+// ------------------------------------------------------------------ gather rows
+template <typename T, bool VEC>
+__global__ void gather_rows_kernel(const T* __restrict__ x, const int* __restrict__ rows, T* __restrict__ out, int dim) {
+    const T* src = x + (size_t)rows[blockIdx.x] * dim;
+    T* dst = out + (size_t)blockIdx.x * dim;
+    if (VEC) {
+        constexpr int n = Vec16<T>::n;
+        for (int i = threadIdx.x * n; i < dim; i += blockDim.x * n)
+            *reinterpret_cast<uint4*>(dst + i) = *reinterpret_cast<const uint4*>(src + i);
+    } else {
+        for (int i = threadIdx.x; i < dim; i += blockDim.x) dst[i] = src[i];
+    }
+}
+
+// ------------------------------------------------------------------ RMSNorm (+ residual add)
+// ADD: residual[row] += delta[row] (float32 sum, rounded to T), then out = norm(residual) * w.
+// else: out = norm(x) * w with x = residual (read only).
+template <typename T, bool VEC, bool ADD>
+__global__ void rmsnorm_kernel(T* __restrict__ residual, const T* __restrict__ delta,
+                               const float* __restrict__ weight, T* __restrict__ out, int dim, float eps) {
+    __shared__ float scratch[32];
+    T* x = residual + (size_t)blockIdx.x * dim;
+    const T* d = ADD ? delta + (size_t)blockIdx.x * dim : nullptr;
+    T* y = out + (size_t)blockIdx.x * dim;
+    float ssq = 0.f;
+    if (VEC) {
+        constexpr int n = Vec16<T>::n;
+        for (int i = threadIdx.x * n; i < dim; i += blockDim.x * n) {
+            float a[n];
+            load16(x + i, a);
+            if (ADD) {
+                float b[n];
+                load16(d + i, b);
+#pragma unroll
+                for (int j = 0; j < n; ++j) a[j] = to_float(from_float<T>(a[j] + b[j]));
+                store16(x + i, a);
+            }
+#pragma unroll
+            for (int j = 0; j < n; ++j) ssq += a[j] * a[j];
+        }
+    } else {
+        for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+            float a = to_float(x[i]);
+            if (ADD) {
+                T r = from_float<T>(a + to_float(d[i]));
+                x[i] = r;
+                a = to_float(r);
+            }
+            ssq += a * a;
+        }
+    }
+    ssq = block_sum(ssq, scratch);
+    const float scale = 1.0f / sqrtf(ssq / (float)dim + eps);
+    // each thread re-reads exactly the elements it wrote above, so no barrier is needed
+    if (VEC) {
+        constexpr int n = Vec16<T>::n;
+        for (int i = threadIdx.x * n; i < dim; i += blockDim.x * n) {
+            float a[n];
+            load16(x + i, a);
+#pragma unroll
+            for (int j = 0; j < n; ++j) a[j] = a[j] * scale * weight[i + j];
+            store16(y + i, a);
+        }
+    } else {
+        for (int i = threadIdx.x; i < dim; i += blockDim.x)
+            y[i] = from_float<T>(to_float(x[i]) * scale * weight[i]);
+    }
+}
+
+// ------------------------------------------------------------------ SwiGLU
+// gate_up [rows, 2*inter] (gate first), out [rows, inter] = silu(gate) * up.
+template <typename T, bool VEC>
+__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter) {
+    const T* g = gate_up + (size_t)blockIdx.y * 2 * inter;
+    const T* u = g + inter;
+    T* y = out + (size_t)blockIdx.y * inter;
+    if (VEC) {
+        constexpr int n = Vec16<T>::n;
+        const int i = (blockIdx.x * blockDim.x + threadIdx.x) * n;
+        if (i < inter) {
+            float a[n], b[n];
+            load16(g + i, a);
+            load16(u + i, b);
+#pragma unroll
+            for (int j = 0; j < n; ++j) a[j] = a[j] / (1.0f + expf(-a[j])) * b[j];
+            store16(y + i, a);
+        }
+    } else {
+        const int i = blockIdx.x * blockDim.x + threadIdx.x;
+        if (i < inter) {
+            const float a = to_float(g[i]);
+            y[i] = from_float<T>(a / (1.0f + expf(-a)) * to_float(u[i]));
+        }
+    }
+}
+
+// ------------------------------------------------------------------ per-head norm + rotary + cache write
+// One warp per (row, head).  Heads 0..n_q-1 are queries (normalised and rotated in place
+// in `qkv`), the next n_kv are keys (normalised, rotated, written to the key cache), the
+// last n_kv are values (copied to the value cache).  A head vector pairs element i with
+// i + D/2 (engine/kernels/reference.py:31-46).  q_w / k_w may be null (no per-head norm),
+// cos may be null (no rotation).  cos/sin are [max_positions, D/2] float32.
+constexpr int kMaxPairsPerLane = 4;  // D <= 256
+
+template <typename T>
+__global__ void qk_norm_rope_write_kernel(T* __restrict__ qkv, int row_stride, int n_q, int n_kv, int D,
+                                          const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
+                                          const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                          const int* __restrict__ row_pos, const int* __restrict__ row_seq,
+                                          T* __restrict__ k_cache, T* __restrict__ v_cache,
+                                          const int* __restrict__ block_table, int table_width, int page_size,
+                                          int ring_tokens, int write_cache) {
+    const int lane = threadIdx.x & 31;
+    const int head = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int total_heads = n_q + 2 * n_kv;
+    if (head >= total_heads) return;
+    const int row = blockIdx.x;
+    const bool is_q = head < n_q;
+    const bool is_k = !is_q && head < n_q + n_kv;
+    if (!is_q && !write_cache) return;
+    const int half = D >> 1;
+    T* src = qkv + (size_t)row * row_stride + (size_t)head * D;
+
+    T* dst = src;
+    if (!is_q) {
+        const int pos = row_pos[row];
+        const int place = place_of(pos, ring_tokens);
+        const int page = block_table[(size_t)row_seq[row] * table_width + place / page_size];
+        const int kv_head = is_k ? head - n_q : head - n_q - n_kv;
+        T* cache = is_k ? k_cache : v_cache;
+        dst = cache + (((size_t)page * n_kv + kv_head) * page_size + place % page_size) * D;
+    }
+
+    float lo[kMaxPairsPerLane], hi[kMaxPairsPerLane];
+    float ssq = 0.f;
+#pragma unroll
+    for (int j = 0; j < kMaxPairsPerLane; ++j) {
+        const int i = lane + 32 * j;
+        if (i < half) {
+            lo[j] = to_float(src[i]);
+            hi[j] = to_float(src[i + half]);
+            ssq += lo[j] * lo[j] + hi[j] * hi[j];
+        }
+    }
+    const float* w = is_q ? q_w : (is_k ? k_w : nullptr);
+    if (w != nullptr) {
+        ssq = warp_sum(ssq);
+        const float scale = 1.0f / sqrtf(ssq / (float)D + eps);
+#pragma unroll
+        for (int j = 0; j < kMaxPairsPerLane; ++j) {
+            const int i = lane + 32 * j;
+            if (i < half) {
+                lo[j] = lo[j] * scale * w[i];
+                hi[j] = hi[j] * scale * w[i + half];
+            }
+        }
+    }
+    const bool rotate = (is_q || is_k) && cos_t != nullptr;
+    const float* c = rotate ? cos_t + (size_t)row_pos[row] * half : nullptr;
+    const float* s = rotate ? sin_t + (size_t)row_pos[row] * half : nullptr;
+#pragma unroll
+    for (int j = 0; j < kMaxPairsPerLane; ++j) {
+        const int i = lane + 32 * j;
+        if (i < half) {
+            float a = lo[j], b = hi[j];
+            if (rotate) {
+                const float cv = c[i], sv = s[i];
+                a = lo[j] * cv - hi[j] * sv;
+                b = hi[j] * cv + lo[j] * sv;
+            }
+            dst[i] = from_float<T>(a);
+            dst[i + half] = from_float<T>(b);
+        }
+    }
+}
+
+template <typename T>
+static int launch_embedding(const void* table, const int* ids, void* out, int rows, int hidden, int vocab,
+                            cudaStream_t st) {
+    const bool vec = hidden % Vec16<T>::n == 0 && aligned16(table) && aligned16(out);
+    const int threads = 128;
+    if (vec) embedding_kernel<T, true><<<rows, threads, 0, st>>>((const T*)table, ids, (T*)out, hidden, vocab);
+    else embedding_kernel<T, false><<<rows, threads, 0, st>>>((const T*)table, ids, (T*)out, hidden, vocab);
+    return DFI_OK;
+}
+
+template <typename T>
+static int launch_gather(const void* x, const int* rows_idx, void* out, int rows, int dim, cudaStream_t st) {
+    const bool vec = dim % Vec16<T>::n == 0 && aligned16(x) && aligned16(out);
+    if (vec) gather_rows_kernel<T, true><<<rows, 128, 0, st>>>((const T*)x, rows_idx, (T*)out, dim);
+    else gather_rows_kernel<T, false><<<rows, 128, 0, st>>>((const T*)x, rows_idx, (T*)out, dim);
+    return DFI_OK;
+}
+
+template <typename T>
+static int launch_rmsnorm(void* residual, const void* delta, const float* weight, void* out, int rows, int dim,
+                          float eps, cudaStream_t st) {
+    const bool vec = dim % Vec16<T>::n == 0 && aligned16(residual) && aligned16(out) &&
+                     (delta == nullptr || aligned16(delta));
+    int threads = 32;
+    const int per = vec ? Vec16<T>::n : 1;
+    while (threads < 512 && threads * per < dim) threads <<= 1;
+    if (delta != nullptr) {
+        if (vec) rmsnorm_kernel<T, true, true><<<rows, threads, 0, st>>>((T*)residual, (const T*)delta, weight, (T*)out, dim, eps);
+        else rmsnorm_kernel<T, false, true><<<rows, threads, 0, st>>>((T*)residual, (const T*)delta, weight, (T*)out, dim, eps);
+    } else {
+        if (vec) rmsnorm_kernel<T, true, false><<<rows, threads, 0, st>>>((T*)residual, nullptr, weight, (T*)out, dim, eps);
+        else rmsnorm_kernel<T, false, false><<<rows, threads, 0, st>>>((T*)residual, nullptr, weight, (T*)out, dim, eps);
+    }
+    return DFI_OK;
+}
+
+template <typename T>
+static int launch_swiglu(const void* gate_up, void* out, int rows, int inter, cudaStream_t st) {
+    const bool vec = inter % Vec16<T>::n == 0 && aligned16(gate_up) && aligned16(out);
+    const int per = vec ? Vec16<T>::n : 1;
+    const int threads = 256;
+    dim3 grid((inter + threads * per - 1) / (threads * per), rows);
+    if (vec) swiglu_kernel<T, true><<<grid, threads, 0, st>>>((const T*)gate_up, (T*)out, inter);
+    else swiglu_kernel<T, false><<<grid, threads, 0, st>>>((const T*)gate_up, (T*)out, inter);
+    return DFI_OK;
+}
+
+}  // namespace dfi
+
+using namespace dfi;
+
+DFI_EXPORT int dfi_embedding(const void* table, const int* ids, void* out, int rows, int hidden, int vocab,
+                             int dtype, void* stream) {
+    if (rows <= 0) return DFI_OK;
+    if (hidden <= 0 || vocab <= 0) return DFI_ERR_SHAPE;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == DFI_DTYPE_F32) launch_embedding<float>(table, ids, out, rows, hidden, vocab, st);
+    else if (dtype == DFI_DTYPE_BF16) launch_embedding<bf16>(table, ids, out, rows, hidden, vocab, st);
+    else return DFI_ERR_DTYPE;
+    DFI_CHECK_LAUNCH();
+    return DFI_OK;
+}
+
+DFI_EXPORT int dfi_gather_rows(const void* x, const int* rows_idx, void* out, int rows, int dim, int dtype,
+                               void* stream) {
+    if (rows <= 0) return DFI_OK;
+    if (dim <= 0) return DFI_ERR_SHAPE;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == DFI_DTYPE_F32) launch_gather<float>(x, rows_idx, out, rows, dim, st);
+    else if (dtype == DFI_DTYPE_BF16) launch_gather<bf16>(x, rows_idx, out, rows, dim, st);
+    else return DFI_ERR_DTYPE;
+    DFI_CHECK_LAUNCH();
+    return DFI_OK;
+}
+
+// delta == nullptr: out = rmsnorm(residual) * weight.  Otherwise residual += delta first (in place).
+DFI_EXPORT int dfi_rmsnorm(void* residual, const void* delta, const float* weight, void* out, int rows, int dim,
+                           float eps, int dtype, void* stream) {
+    if (rows <= 0) return DFI_OK;
+    if (dim <= 0) return DFI_ERR_SHAPE;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == DFI_DTYPE_F32) launch_rmsnorm<float>(residual, delta, weight, out, rows, dim, eps, st);
+    else if (dtype == DFI_DTYPE_BF16) launch_rmsnorm<bf16>(residual, delta, weight, out, rows, dim, eps, st);
+    else return DFI_ERR_DTYPE;
+    DFI_CHECK_LAUNCH();
+    return DFI_OK;
+}
+
+DFI_EXPORT int dfi_swiglu(const void* gate_up, void* out, int rows, int inter, int dtype, void* stream) {
+    if (rows <= 0) return DFI_OK;
+    if (inter <= 0) return DFI_ERR_SHAPE;
+    if (rows > 65535) return DFI_ERR_LIMIT;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == DFI_DTYPE_F32) launch_swiglu<float>(gate_up, out, rows, inter, st);
+    else if (dtype == DFI_DTYPE_BF16) launch_swiglu<bf16>(gate_up, out, rows, inter, st);
+    else return DFI_ERR_DTYPE;
+    DFI_CHECK_LAUNCH();
+    return DFI_OK;
+}
+
+DFI_EXPORT int dfi_qk_norm_rope_write(void* qkv, int rows, int row_stride, int n_q, int n_kv, int head_dim,
+                                      const float* q_w, const float* k_w, float eps, const float* cos_t,
+                                      const float* sin_t, const int* row_pos, const int* row_seq, void* k_cache,
+                                      void* v_cache, const int* block_table, int table_width, int page_size,
+                                      int ring_tokens, int write_cache, int dtype, void* stream) {
+    if (rows <= 0) return DFI_OK;
+    if (head_dim <= 0 || head_dim % 2 || head_dim > 64 * kMaxPairsPerLane) return DFI_ERR_SHAPE;
+    if (n_q < 0 || n_kv < 0 || page_size <= 0 || table_width <= 0) return DFI_ERR_SHAPE;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int warps = 4;
+    const int heads = n_q + 2 * n_kv;
+    dim3 grid(rows, (heads + warps - 1) / warps);
+    if (grid.y > 65535) return DFI_ERR_LIMIT;
+    if (dtype == DFI_DTYPE_F32)
+        qk_norm_rope_write_kernel<float><<<grid, warps * 32, 0, st>>>(
+            (float*)qkv, row_stride, n_q, n_kv, head_dim, q_w, k_w, eps, cos_t, sin_t, row_pos, row_seq,
+            (float*)k_cache, (float*)v_cache, block_table, table_width, page_size, ring_tokens, write_cache);
+    else if (dtype == DFI_DTYPE_BF16)
+        qk_norm_rope_write_kernel<bf16><<<grid, warps * 32, 0, st>>>(
+            (bf16*)qkv, row_stride, n_q, n_kv, head_dim, q_w, k_w, eps, cos_t, sin_t, row_pos, row_seq,
+            (bf16*)k_cache, (bf16*)v_cache, block_table, table_width, page_size, ring_tokens, write_cache);
+    else return DFI_ERR_DTYPE;
+    DFI_CHECK_LAUNCH();
+    return DFI_OK;
+}

@@ -1,0 +1,143 @@
+"""Compiles the CUDA sources under ``csrc/`` for sm_100a with nvcc and loads the result.
+
+The kernels are plain ``extern "C"`` entry points in one shared library, called through
+ctypes with raw device pointers: no Python headers are involved, so a build takes
+seconds per file.  A library is named after a hash of its sources and flags and kept
+in ``csrc/_build`` (or, when the package folder is read-only, in a per-user folder
+under the system's temporary directory), so the first call in a fresh checkout
+compiles and later calls only load.  While compiling it reports progress on stderr.
+There is no fallback: if nvcc or a source is missing, or a compile fails, the error
+is raised.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+CSRC = Path(__file__).resolve().parent.parent / "csrc"
+
+ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
+COMMON_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
+
+#: sources of the core library; further modules (built per head size) name their own
+CORE_SOURCES = ["elementwise.cu", "attention_generic.cu", "sampling.cu"]
+
+
+class BuildError(RuntimeError):
+    pass
+
+
+def _say(message: str) -> None:
+    print(f"[dryft-flash-infer_b200] {message}", file=sys.stderr, flush=True)
+
+
+def find_nvcc() -> str:
+    for candidate in (os.environ.get("DFI_NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if candidate and Path(candidate).is_file():
+            return candidate
+    raise BuildError("nvcc not found (looked at $DFI_NVCC, PATH and /usr/local/cuda/bin): "
+                     "the CUDA kernels cannot be compiled and there is no fallback")
+
+
+def build_dir() -> Path:
+    override = os.environ.get("DFI_BUILD_DIR")
+    candidates = [Path(override)] if override else []
+    candidates.append(CSRC / "_build")
+    candidates.append(Path(tempfile.gettempdir()) / f"dryft_flash_infer_b200_build_{os.getuid()}")
+    for folder in candidates:
+        try:
+            folder.mkdir(parents=True, exist_ok=True)
+            probe = folder / f".probe_{os.getpid()}"
+            probe.write_text("")
+            probe.unlink()
+            return folder
+        except OSError:
+            continue
+    raise BuildError("no writable folder for compiled kernels; set DFI_BUILD_DIR")
+
+
+def _headers() -> list[Path]:
+    return sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h"))
+
+
+def _digest(sources: list[str], defines: list[str]) -> str:
+    h = hashlib.sha256()
+    for path in [CSRC / s for s in sources] + _headers():
+        if not path.is_file():
+            raise BuildError(f"kernel source missing: {path}")
+        h.update(path.name.encode())
+        h.update(path.read_bytes())
+    h.update(" ".join(ARCH_FLAGS + COMMON_FLAGS + defines).encode())
+    return h.hexdigest()[:16]
+
+
+def library_file(name: str, sources: list[str], defines: list[str]) -> Path:
+    return build_dir() / f"{name}_{_digest(sources, defines)}.so"
+
+
+def compile_library(name: str, sources: list[str], defines: list[str] | None = None) -> Path:
+    """Builds (if not built yet) and returns the shared library of ``sources``."""
+    defines = list(defines or [])
+    target = library_file(name, sources, defines)
+    if target.is_file():
+        return target
+    nvcc = find_nvcc()
+    work = Path(tempfile.mkdtemp(prefix=f"{name}_", dir=target.parent))
+    started = time.time()
+    _say(f"compiling {len(sources)} CUDA source files for sm_100a ({name}); this happens once")
+    done = threading.Event()
+
+    def ticker():
+        while not done.wait(10.0):
+            _say(f"  ... still compiling {name} ({time.time() - started:.0f} s)")
+
+    threading.Thread(target=ticker, daemon=True).start()
+
+    def one(source: str) -> Path:
+        obj = work / (Path(source).stem + ".o")
+        cmd = [nvcc, *ARCH_FLAGS, *COMMON_FLAGS, *defines, "-I", str(CSRC), "-c", str(CSRC / source), "-o", str(obj)]
+        proc = subprocess.run(cmd, capture_output=True, text=True)
+        if proc.returncode != 0:
+            raise BuildError(f"nvcc failed on {source}:\n{proc.stdout}\n{proc.stderr}")
+        _say(f"  compiled {source} ({time.time() - started:.0f} s)")
+        return obj
+
+    try:
+        with ThreadPoolExecutor(max_workers=min(len(sources), os.cpu_count() or 1)) as pool:
+            objects = list(pool.map(one, sources))
+        partial = work / "out.so"
+        cmd = [nvcc, *ARCH_FLAGS, "-shared", "-o", str(partial), *map(str, objects), "-lcuda"]
+        proc = subprocess.run(cmd, capture_output=True, text=True)
+        if proc.returncode != 0:
+            raise BuildError(f"linking {name} failed:\n{proc.stdout}\n{proc.stderr}")
+        os.replace(partial, target)  # atomic: a concurrent builder ends with the same file
+    finally:
+        done.set()
+        shutil.rmtree(work, ignore_errors=True)
+    _say(f"built {target.name} in {time.time() - started:.0f} s")
+    return target
+
+
+def all_libraries() -> list[tuple[str, list[str], list[str]]]:
+    """Every library the package can load: ``(name, sources, defines)``."""
+    return [("dfi_core", CORE_SOURCES, [])]
+
+
+_LOADED: dict[str, ctypes.CDLL] = {}
+
+
+def load_library(name: str, sources: list[str], defines: list[str] | None = None) -> ctypes.CDLL:
+    key = name + "|" + " ".join(defines or [])
+    if key not in _LOADED:
+        _LOADED[key] = ctypes.CDLL(str(compile_library(name, sources, defines)))
+    return _LOADED[key]

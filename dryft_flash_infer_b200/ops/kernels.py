@@ -1,0 +1,208 @@
+"""Python faces of the CUDA entry points: argument checks, the launch, the error.
+
+Every function here runs a hand-written kernel on the current CUDA stream.  There is no
+CPU or library fallback: tensors that are not on a CUDA device, or sizes that a kernel
+does not take, raise ``KernelError`` with the reason.
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from .build import CORE_SOURCES, load_library
+
+_ERRORS = {
+    1: "unsupported dtype (kernels take float32 and bfloat16)",
+    2: "a size this kernel does not take",
+    3: "a pointer or stride is not aligned as the kernel needs",
+    4: "the CUDA launch failed",
+    5: "a size beyond the kernel's stated maximum",
+}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
+
+
+def _core():
+    return load_library("dfi_core", CORE_SOURCES)
+
+
+def _code(t: torch.Tensor) -> int:
+    if t.dtype not in _DTYPE_CODE:
+        raise KernelError(f"unsupported dtype {t.dtype}: kernels take float32 and bfloat16")
+    return _DTYPE_CODE[t.dtype]
+
+
+def _need_cuda(*tensors: torch.Tensor) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("the kernels run on a CUDA device only (tensor is on %s); there is no CPU path" % t.device)
+
+
+def _ptr(t: torch.Tensor | None):
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _check(rc: int, what: str, detail: str = "") -> None:
+    if rc != 0:
+        raise KernelError(f"{what}: {_ERRORS.get(rc, f'error {rc}')}{' (' + detail + ')' if detail else ''}")
+
+
+def _f(x: float):
+    return ctypes.c_float(x)
+
+
+def embedding(table: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+    """``table[ids]`` for int32 ``ids [rows]``."""
+    _need_cuda(table, ids)
+    assert ids.dtype == torch.int32 and table.is_contiguous()
+    rows, (vocab, hidden) = ids.numel(), table.shape
+    out = torch.empty((rows, hidden), dtype=table.dtype, device=table.device)
+    _check(_core().dfi_embedding(_ptr(table), _ptr(ids), _ptr(out), rows, hidden, vocab, _code(table), _stream()),
+           "embedding")
+    return out
+
+
+def gather_rows(x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
+    """``x[rows]`` for int32 ``rows`` on the device."""
+    _need_cuda(x, rows)
+    assert rows.dtype == torch.int32 and x.is_contiguous() and x.dim() == 2
+    out = torch.empty((rows.numel(), x.shape[1]), dtype=x.dtype, device=x.device)
+    _check(_core().dfi_gather_rows(_ptr(x), _ptr(rows), _ptr(out), rows.numel(), x.shape[1], _code(x), _stream()),
+           "gather_rows")
+    return out
+
+
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """``x * rsqrt(mean(x^2) + eps) * weight`` per row; ``weight`` is float32."""
+    _need_cuda(x, weight)
+    assert x.is_contiguous() and x.dim() == 2 and weight.dtype == torch.float32 and weight.numel() == x.shape[1]
+    out = torch.empty_like(x)
+    _check(_core().dfi_rmsnorm(_ptr(x), _ptr(None), _ptr(weight), _ptr(out), x.shape[0], x.shape[1], _f(eps),
+                               _code(x), _stream()), "rms_norm")
+    return out
+
+
+def add_rms_norm(residual: torch.Tensor, delta: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """``residual += delta`` in place (float32 sum), then the RMSNorm of the new residual."""
+    _need_cuda(residual, delta, weight)
+    assert residual.is_contiguous() and delta.is_contiguous() and residual.shape == delta.shape
+    assert residual.dtype == delta.dtype and weight.dtype == torch.float32 and weight.numel() == residual.shape[1]
+    out = torch.empty_like(residual)
+    _check(_core().dfi_rmsnorm(_ptr(residual), _ptr(delta), _ptr(weight), _ptr(out), residual.shape[0],
+                               residual.shape[1], _f(eps), _code(residual), _stream()), "add_rms_norm")
+    return out
+
+
+def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
+    """``silu(gate) * up`` for ``gate_up [rows, 2*inter]`` with the gate half first."""
+    _need_cuda(gate_up)
+    assert gate_up.is_contiguous() and gate_up.dim() == 2 and gate_up.shape[1] % 2 == 0
+    rows, inter = gate_up.shape[0], gate_up.shape[1] // 2
+    out = torch.empty((rows, inter), dtype=gate_up.dtype, device=gate_up.device)
+    for start in range(0, rows, 65535):
+        part = gate_up[start:start + 65535]
+        _check(_core().dfi_swiglu(_ptr(part), _ptr(out[start:start + 65535]), part.shape[0], inter,
+                                  _code(gate_up), _stream()), "swiglu")
+    return out
+
+
+def qk_norm_rope_write(qkv: torch.Tensor, n_q: int, n_kv: int, head_dim: int, q_weight, k_weight, eps: float,
+                       cos, sin, row_pos: torch.Tensor, row_seq: torch.Tensor, cache) -> torch.Tensor:
+    """Per-head RMSNorm (if weights are given) and rotation (if tables are given) of the
+    query and key heads of ``qkv [rows, (n_q + 2 n_kv) * head_dim]``; queries are
+    rewritten in place, keys and values go to ``cache`` (a ``LayerCache``) at each row's
+    position unless ``cache.writes`` is false.  Returns the query view ``[rows, n_q * head_dim]``.
+    """
+    _need_cuda(qkv, row_pos, row_seq, cache.k, cache.v, cache.block_table)
+    rows, width = qkv.shape
+    assert qkv.is_contiguous() and width == (n_q + 2 * n_kv) * head_dim
+    assert row_pos.dtype == torch.int32 and row_seq.dtype == torch.int32
+    assert cache.k.dtype == qkv.dtype and cache.k.is_contiguous() and cache.v.is_contiguous()
+    assert cache.k.shape[1] == n_kv and cache.k.shape[3] == head_dim and cache.k.shape[2] == cache.page_size
+    if head_dim % 2 or head_dim > 256:
+        raise KernelError(f"qk_norm_rope_write: head_dim {head_dim} must be even and at most 256")
+    for w in (q_weight, k_weight):
+        assert w is None or (w.dtype == torch.float32 and w.numel() == head_dim)
+    if cos is not None:
+        assert cos.dtype == torch.float32 and sin.dtype == torch.float32 and cos.shape[1] == head_dim // 2
+    _check(_core().dfi_qk_norm_rope_write(
+        _ptr(qkv), rows, width, n_q, n_kv, head_dim, _ptr(q_weight), _ptr(k_weight), _f(eps), _ptr(cos), _ptr(sin),
+        _ptr(row_pos), _ptr(row_seq), _ptr(cache.k), _ptr(cache.v), _ptr(cache.block_table),
+        cache.block_table.shape[1], cache.page_size, cache.ring_tokens, 1 if cache.writes else 0, _code(qkv),
+        _stream()), "qk_norm_rope_write", f"head_dim {head_dim}")
+    return qkv[:, : n_q * head_dim]
+
+
+def attention_generic(q: torch.Tensor, cache, row_seq: torch.Tensor, row_pos: torch.Tensor, n_q: int, n_kv: int,
+                      head_dim: int, scale: float, window: int = 0) -> torch.Tensor:
+    """Causal attention of every query row over its sequence's cached keys up to the
+    row's own position (and not further back than ``window`` keys, if given).
+    ``q`` may be a column slice of a wider matrix (its row stride is passed on)."""
+    _need_cuda(q, cache.k, row_seq, row_pos)
+    rows = q.shape[0]
+    assert q.stride(1) == 1 and q.shape[1] == n_q * head_dim
+    vec = 4 if q.dtype == torch.float32 else 8
+    if head_dim % vec or head_dim > 256:
+        raise KernelError(f"attention: head_dim {head_dim} must be a multiple of {vec} and at most 256")
+    if n_q % n_kv:
+        raise KernelError(f"attention: {n_q} query heads are not a multiple of {n_kv} key/value heads")
+    out = torch.empty((rows, n_q * head_dim), dtype=q.dtype, device=q.device)
+    _check(_core().dfi_attention_generic(
+        _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cache.k), _ptr(cache.v), _ptr(cache.block_table),
+        cache.block_table.shape[1], _ptr(row_seq), _ptr(row_pos), rows, n_q, n_kv, head_dim, cache.page_size,
+        cache.ring_tokens, window, _f(scale), _code(q), _stream()), "attention", f"head_dim {head_dim}")
+    return out
+
+
+def attention(q: torch.Tensor, cache, ctx, n_q: int, n_kv: int, head_dim: int, scale: float,
+              window: int = 0) -> torch.Tensor:
+    """Attention of a step's query rows over the cache, by the kernel that fits the shapes."""
+    return attention_generic(q, cache, ctx.row_seq, ctx.row_pos, n_q, n_kv, head_dim, scale, window)
+
+
+def argmax(logits: torch.Tensor) -> torch.Tensor:
+    """Index of the largest float32 logit per row (lowest index on ties), int32."""
+    _need_cuda(logits)
+    assert logits.dtype == torch.float32 and logits.dim() == 2 and logits.stride(1) == 1
+    out = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
+    _check(_core().dfi_argmax(_ptr(logits), logits.shape[0], logits.stride(0), logits.shape[1], _ptr(out), _stream()),
+           "argmax")
+    return out
+
+
+def sample_temperature(logits: torch.Tensor, uniforms: torch.Tensor, temperature: float) -> torch.Tensor:
+    """One draw per row from ``softmax(logits / temperature)`` by inverse CDF at ``uniforms [rows]``."""
+    _need_cuda(logits, uniforms)
+    assert logits.dtype == torch.float32 and logits.dim() == 2 and logits.stride(1) == 1
+    assert uniforms.dtype == torch.float32 and uniforms.numel() == logits.shape[0]
+    if not temperature > 0:
+        raise KernelError("sample_temperature: temperature must be positive (use argmax for greedy)")
+    out = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
+    _check(_core().dfi_sample_temperature(_ptr(logits), logits.shape[0], logits.stride(0), logits.shape[1],
+                                          _ptr(uniforms), _f(temperature), _ptr(out), _stream()),
+           "sample_temperature")
+    return out
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """``x @ weight.T`` for ``weight [out, in]`` as stored in the model file.
+
+    float32 operands take the library's float32 product with no reduced-precision mode.
+    ``out_dtype=torch.float32`` keeps bfloat16 products unrounded (used for logits).
+    """
+    _need_cuda(x, weight)
+    assert x.dim() == 2 and weight.dim() == 2 and x.shape[1] == weight.shape[1] and x.dtype == weight.dtype
+    if out_dtype is not None and out_dtype != x.dtype:
+        return torch.mm(x, weight.t(), out_dtype=out_dtype)
+    return torch.mm(x, weight.t())

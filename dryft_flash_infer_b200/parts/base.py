@@ -1,0 +1,158 @@
+"""Interfaces of the parts a layer is made of, and the registries that hold their kinds.
+
+A part is built from its own parameters only (sizes, constants); it does not know
+which model it is in.  It declares its tensors by a local name; the
+architecture's builder maps local names to names in the model file.
+
+Interfaces
+----------
+Norm          ``forward(x) -> normed``; ``add_forward(residual, delta) -> normed``
+              (adds ``delta`` into ``residual`` in place first).
+Position      ``prepare(max_positions, device)``; what the mixer reads from it is
+              between the two of them (rotary: ``cos``/``sin`` tables).
+Mixer         ``cache_need()``, ``state_need()``, ``forward(x, ctx, cache, state)``.
+FeedForward   ``forward(x, ctx)``.
+Block         ``forward(residual, pending, ctx, cache, state) -> (residual, pending)``.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable
+
+import torch
+
+from .spec import PartSpec
+
+
+@dataclass(frozen=True)
+class TensorDecl:
+    """One tensor a part wants from the model file.
+
+    It lands in rows ``row_start ...`` of the part's device buffer ``buffer``, so
+    that several file tensors can share one fused matrix without a second copy.
+    ``init`` picks the random-weights rule: ``matrix`` or ``norm``.  ``precision``
+    is ``compute`` (held in the engine's dtype) or ``float32`` (always 32-bit).
+    """
+
+    shape: tuple[int, ...]
+    buffer: str
+    row_start: int = 0
+    init: str = "matrix"
+    precision: str = "compute"
+
+
+@dataclass(frozen=True)
+class KVNeed:
+    """A mixer that keeps keys and values per token: heads, head size and, if not 0,
+    the window of latest tokens that it ever reads."""
+
+    n_kv_heads: int
+    head_dim: int
+    window: int = 0
+
+
+@dataclass(frozen=True)
+class StateNeed:
+    """A mixer that keeps a fixed-size float32 state per sequence, zero at the start."""
+
+    shape: tuple[int, ...]
+
+
+class Part:
+    kind = ""
+
+    def tensors(self) -> dict[str, TensorDecl]:
+        return {}
+
+    def bind(self, buffers: dict[str, torch.Tensor]) -> None:
+        """Receives the device buffers named in ``tensors()`` once they are filled."""
+        for name, tensor in buffers.items():
+            setattr(self, name, tensor)
+
+    def buffer_shapes(self) -> dict[str, tuple[tuple[int, ...], str]]:
+        out: dict[str, tuple[tuple[int, ...], str]] = {}
+        for decl in self.tensors().values():
+            rows = decl.row_start + decl.shape[0]
+            shape, precision = out.get(decl.buffer, ((0,) + decl.shape[1:], decl.precision))
+            if shape[1:] != decl.shape[1:] or precision != decl.precision:
+                raise ValueError(f"tensors sharing buffer '{decl.buffer}' disagree on shape or precision")
+            out[decl.buffer] = ((max(shape[0], rows),) + decl.shape[1:], precision)
+        return out
+
+
+class Norm(Part):
+    def forward(self, x):
+        raise NotImplementedError
+
+    def add_forward(self, residual, delta):
+        residual.add_(delta)
+        return self.forward(residual)
+
+
+class PositionEncoding(Part):
+    def prepare(self, max_positions: int, device) -> None:
+        pass
+
+
+class Mixer(Part):
+    def cache_need(self) -> KVNeed | None:
+        return None
+
+    def state_need(self) -> StateNeed | None:
+        return None
+
+    def prepare(self, max_positions: int, device) -> None:
+        pass
+
+    def forward(self, x, ctx, cache, state):
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, x, ctx):
+        raise NotImplementedError
+
+
+class Block:
+    """An arrangement of a mixer, a feed-forward and their norms around the residual stream.
+
+    The residual stream travels between blocks as ``(residual, pending)``: ``pending``
+    is a delta not yet added, so that the next norm can add and normalise in one pass.
+    """
+
+    kind = ""
+
+    def __init__(self, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm, ffn_norm: Norm):
+        self.mixer, self.feed_forward = mixer, feed_forward
+        self.mixer_norm, self.ffn_norm = mixer_norm, ffn_norm
+
+    def parts(self) -> dict[str, Part]:
+        return {"mixer": self.mixer, "feed_forward": self.feed_forward,
+                "mixer_norm": self.mixer_norm, "ffn_norm": self.ffn_norm}
+
+    def forward(self, residual, pending, ctx, cache, state):
+        raise NotImplementedError
+
+
+_REGISTRIES: dict[str, dict[str, Callable]] = {
+    "mixer": {}, "feed_forward": {}, "norm": {}, "position": {}, "block": {},
+}
+
+
+def register_part(category: str, kind: str, factory: Callable) -> None:
+    """Registers ``factory(hidden_size=..., **params)`` (for blocks: the class) under ``kind``."""
+    if category not in _REGISTRIES:
+        raise ValueError(f"unknown part category '{category}'; known: {', '.join(_REGISTRIES)}")
+    _REGISTRIES[category][kind] = factory
+
+
+def part_factory(category: str, kind: str) -> Callable:
+    table = _REGISTRIES[category]
+    if kind not in table:
+        raise ValueError(f"unknown {category} kind '{kind}'; known: {', '.join(sorted(table)) or 'none'}")
+    return table[kind]
+
+
+def build_part(category: str, spec: PartSpec, hidden_size: int):
+    return part_factory(category, spec.kind)(hidden_size=hidden_size, **spec.params)

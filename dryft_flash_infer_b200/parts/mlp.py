@@ -1,0 +1,35 @@
+"""The dense SwiGLU feed-forward."""
+
+from __future__ import annotations
+
+from ..ops import kernels
+from .base import FeedForward, TensorDecl, register_part
+
+
+class SwiGLU(FeedForward):
+    """``down(silu(gate(x)) * up(x))`` without biases; gate and up share one fused matrix
+    ``[2*inter, hidden]`` with the gate rows first (engine/engine.py:173-176;
+    engine/kernels/reference.py:74-79)."""
+
+    kind = "swiglu"
+
+    def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "silu"):
+        if activation != "silu":
+            raise ValueError(f"SwiGLU feed-forward knows the 'silu' activation only, got {activation!r}")
+        self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
+        self.gate_up = self.down = None
+
+    def tensors(self):
+        inter, hidden = self.intermediate_size, self.hidden_size
+        return {
+            "gate_proj": TensorDecl((inter, hidden), "gate_up", 0),
+            "up_proj": TensorDecl((inter, hidden), "gate_up", inter),
+            "down_proj": TensorDecl((hidden, inter), "down"),
+        }
+
+    def forward(self, x, ctx):
+        inner = kernels.swiglu(kernels.linear(x, self.gate_up))
+        return kernels.linear(inner, self.down)
+
+
+register_part("feed_forward", SwiGLU.kind, SwiGLU)
