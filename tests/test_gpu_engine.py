@@ -1,0 +1,262 @@
+"""The engine on a GPU against the plain implementation, in float32 and in bfloat16."""
+
+import math
+
+import pytest
+import torch
+
+import plain_model
+from helpers import CONFIGS, assert_close, bf16_weights, prompts_for, write_model
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = ["float32", "bfloat16"]
+
+
+def reference_weights(weights, dtype):
+    return weights if dtype == "float32" else bf16_weights(weights)
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    out = {}
+    for name, cfg in CONFIGS.items():
+        weights = plain_model.random_weights(cfg, seed=31 + len(name), matrix_std=0.06, norm_std=0.1)
+        out[name] = (write_model(tmp_path_factory.mktemp(f"tiny_{name}"), cfg, weights), cfg, weights)
+    return out
+
+
+def make_engine(folder, dtype, max_tokens=2048, **kw):
+    from dryft_flash_infer_b200 import Engine
+
+    engine = Engine(folder, dtype=dtype, max_tokens=max_tokens, **kw)
+    for group in engine.cache.groups:       # anything read beyond what was written shows as NaN
+        group.k.fill_(float("nan"))
+        group.v.fill_(float("nan"))
+    return engine
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_each_request_alone_and_whole(folders, name, dtype):
+    from dryft_flash_infer_b200 import StepEntry
+
+    folder, cfg, weights = folders[name]
+    engine = make_engine(folder, dtype)
+    for prompt in prompts_for(cfg, [1, 2, 17, 64, 65, 150], seed=1):
+        slot = engine.open_slot()
+        logits = engine.step([StepEntry(slot, prompt, list(range(len(prompt))))])
+        engine.close_slot(slot)
+        assert_close(logits, plain_model.forward(cfg, reference_weights(weights, dtype), prompt), dtype,
+                     f"prompt of {len(prompt)}")
+    engine.cache.book.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_last_32_tokens_one_by_one(folders, name, dtype):
+    from dryft_flash_infer_b200 import StepEntry
+
+    folder, cfg, weights = folders[name]
+    engine = make_engine(folder, dtype)
+    for prompt in prompts_for(cfg, [33, 100], seed=2):
+        want = plain_model.forward(cfg, reference_weights(weights, dtype), prompt)
+        slot = engine.open_slot()
+        head = len(prompt) - 32
+        first = engine.step([StepEntry(slot, prompt[:head], [head - 1])])
+        rows = [first[0]]
+        for t in range(head, len(prompt)):
+            rows.append(engine.step([StepEntry(slot, [prompt[t]], [0])])[0])
+        engine.close_slot(slot)
+        assert_close(torch.stack(rows), want[head - 1:], dtype, f"decode after {head}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_unequal_batches_one_after_another(folders, name, dtype):
+    """Batches of unequal lengths; shorter requests end earlier; the next batch takes the
+    freed slots and pages, which still hold the earlier batch's keys."""
+    from dryft_flash_infer_b200 import StepEntry
+
+    folder, cfg, weights = folders[name]
+    engine = make_engine(folder, dtype, max_tokens=64 * 8)
+    ref_w = reference_weights(weights, dtype)
+    seen_slots = []
+    for round_, lengths in enumerate([(5, 9, 17, 70), (23, 1, 4, 11), (66, 3)]):
+        prompts = prompts_for(cfg, lengths, seed=10 + round_)
+        decode = [3 + i for i in range(len(prompts))]          # the first request ends first
+        full = [p + prompts_for(cfg, [d], seed=50 + i)[0] for i, (p, d) in enumerate(zip(prompts, decode))]
+        want = [plain_model.forward(cfg, ref_w, seq) for seq in full]
+        slots = [engine.open_slot() for _ in prompts]
+        seen_slots.append(list(slots))
+        logits = engine.step([StepEntry(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)])
+        for i, p in enumerate(prompts):
+            assert_close(logits[i], want[i][len(p) - 1], dtype, f"round {round_} prefill {i}")
+        live = list(range(len(prompts)))
+        for t in range(max(decode)):
+            live = [i for i in live if t < decode[i]]
+            logits = engine.step([StepEntry(slots[i], [full[i][len(prompts[i]) + t]], [0]) for i in live])
+            for row, i in enumerate(live):
+                assert_close(logits[row], want[i][len(prompts[i]) + t], dtype, f"round {round_} seq {i} step {t}")
+            for i in live:
+                if t + 1 == decode[i]:
+                    engine.close_slot(slots[i])
+        engine.cache.book.check()
+        assert engine.cache.live_slots == 0
+    assert seen_slots[1][0] == seen_slots[0][0]                  # slots are used again
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_decoding_and_the_first_tokens(folders, dtype):
+    from dryft_flash_infer_b200 import StepEntry
+
+    folder, cfg, weights = folders["B"]
+    engine = make_engine(folder, dtype)
+    seq = prompts_for(cfg, [200], seed=3)[0]
+    want = plain_model.forward(cfg, reference_weights(weights, dtype), seq)
+    slot = engine.open_slot()
+    rows = [engine.step([StepEntry(slot, [t], [0])])[0] for t in seq]     # from the very first token on
+    engine.close_slot(slot)
+    got = torch.stack(rows)
+    assert_close(got[:4], want[:4], dtype, "first tokens")
+    assert_close(got, want, dtype, "200 single-token steps")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_chunks_of_any_size_agree(folders, dtype):
+    from dryft_flash_infer_b200 import StepEntry
+
+    folder, cfg, weights = folders["A"]
+    engine = make_engine(folder, dtype)
+    seq = prompts_for(cfg, [131], seed=4)[0]
+    want = plain_model.forward(cfg, reference_weights(weights, dtype), seq)
+    slot = engine.open_slot()
+    rows, at = [], 0
+    for size in (1, 63, 1, 2, 64):
+        piece = seq[at:at + size]
+        rows.append(engine.step([StepEntry(slot, piece, list(range(len(piece))))]))
+        at += size
+    engine.close_slot(slot)
+    assert at == len(seq)
+    assert_close(torch.cat(rows), want, dtype, "chunked prompt")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_far_key_among_hundreds(tmp_path, dtype):
+    """One key far back is made to stand out: the query of the last token is scaled so that it
+    matches the key at position 3 much better than the other 400.  A kernel that drops, repeats or
+    misplaces a page of keys gives other logits than the plain implementation."""
+    from dryft_flash_infer_b200 import Engine, StepEntry
+
+    cfg = dict(plain_model.TINY_B, num_hidden_layers=1)
+    weights = plain_model.random_weights(cfg, seed=77, matrix_std=0.05)
+    p = "model.layers.0.self_attn."
+    weights[p + "q_norm.weight"] = weights[p + "q_norm.weight"] * 6.0    # sharp attention
+    weights[p + "v_proj.weight"] = weights[p + "v_proj.weight"] * 4.0    # and values that matter
+    seq = prompts_for(cfg, [401], seed=5)[0]
+    seq[-1] = seq[3]                     # same token: same direction of q and k up to the rotation
+    folder = write_model(tmp_path, cfg, weights)
+    ref_w = reference_weights(weights, dtype)
+    want = plain_model.forward(cfg, ref_w, seq)
+    engine = Engine(folder, dtype=dtype, max_tokens=1024)
+    slot = engine.open_slot()
+    whole = engine.step([StepEntry(slot, seq, [len(seq) - 1])])
+    engine.close_slot(slot)
+    slot = engine.open_slot()
+    engine.step([StepEntry(slot, seq[:-1], [])])
+    single = engine.step([StepEntry(slot, seq[-1:], [0])])
+    engine.close_slot(slot)
+    assert_close(whole[0], want[-1], dtype, "far key, whole")
+    assert_close(single[0], want[-1], dtype, "far key, decode")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_generation_through_the_entry_point(folders, name, dtype):
+    from dryft_flash_infer_b200 import Engine
+
+    folder, cfg, weights = folders[name]
+    engine = Engine(folder, dtype=dtype)
+    prompts = prompts_for(cfg, [5, 9, 17] if name == "A" else [1, 4, 11, 23], seed=6)
+    steps = 8 if name == "A" else 12
+    rows = list(engine.generate(prompts, steps))
+    assert len(rows) == steps and all(len(r) == len(prompts) for r in rows)
+    ref_w = reference_weights(weights, dtype)
+    for i, prompt in enumerate(prompts):
+        got = [r[i] for r in rows]
+        if dtype == "float32":
+            assert got == plain_model.greedy_continue(cfg, ref_w, prompt, steps)
+        else:
+            # bfloat16 may pick another token where two logits are close: follow the engine's own tokens
+            seq = list(prompt)
+            for token in got:
+                logits = plain_model.forward(cfg, ref_w, seq)[-1]
+                gap = float(logits.max() - logits[token])
+                assert gap <= 2 * 0.03 * max(1.0, float(logits.abs().max())), f"token {token} is {gap} below the best"
+                seq.append(token)
+    # a second call shares nothing with the first, and freed slots were all returned
+    again = list(engine.generate(prompts, steps))
+    assert again == rows and engine.cache.live_slots == 0
+    assert list(engine.generate(prompts, 0)) == []
+    with pytest.raises(ValueError):
+        list(engine.generate(prompts, -1))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_temperature_sampling_does_not_depend_on_the_batch(folders, dtype):
+    from dryft_flash_infer_b200 import Engine, Request
+
+    folder, cfg, weights = folders["B"]
+    engine = Engine(folder, dtype=dtype)
+    prompts = prompts_for(cfg, [1, 4, 11, 23], seed=7)
+    together = list(engine.generate(prompts, 12, temperature=0.8, seed=5))
+    assert any(len({r[i] for r in together}) > 1 for i in range(4))
+    requests = [Request(p, 12, request_id=i) for i, p in enumerate(prompts)]
+    engine.generate_requests(requests, max_batch=1, temperature=0.8, seed=5)       # one batch after another
+    if dtype == "float32":
+        for i, r in enumerate(requests):
+            assert r.output == [row[i] for row in together]
+    # stop tokens end a sequence early
+    stop = together[2][0]
+    rows = list(engine.generate(prompts, 12, temperature=0.8, seed=5, stop_token_ids=(stop,)))
+    assert rows[2][0] == stop and all(r[0] is None for r in rows[3:])
+    assert engine.cache.live_slots == 0
+
+
+def test_sampled_tokens_follow_the_distribution(folders):
+    """Each sampled token lies where the inverse CDF of the plain softmax puts its uniform number."""
+    from dryft_flash_infer_b200 import Engine
+    from dryft_flash_infer_b200.sampling import uniform_for
+
+    folder, cfg, weights = folders["B"]
+    engine = Engine(folder, dtype="float32")
+    prompt = prompts_for(cfg, [9], seed=8)[0]
+    got = [r[0] for r in engine.generate([prompt], 10, temperature=0.8, seed=11)]
+    seq = list(prompt)
+    for step, token in enumerate(got):
+        probs = plain_model.temperature_probabilities(plain_model.forward(cfg, weights, seq)[-1], 0.8)
+        cdf = torch.cumsum(probs, 0)
+        u = uniform_for(11, 0, step)
+        low = float(cdf[token - 1]) if token else 0.0
+        assert low - 1e-5 <= u <= float(cdf[token]) + 1e-5, f"step {step}: u={u} not in [{low}, {float(cdf[token])}]"
+        seq.append(token)
+
+
+def test_engine_errors_are_loud(folders):
+    from dryft_flash_infer_b200 import Engine, StepEntry
+    from dryft_flash_infer_b200.cache import CacheError
+
+    folder, cfg, _ = folders["A"]
+    engine = Engine(folder, dtype="float32", max_tokens=128)
+    a, b = engine.open_slot(), engine.open_slot()
+    with pytest.raises(CacheError, match="out of slots"):
+        engine.open_slot()
+    with pytest.raises(CacheError, match="out of cache pages"):
+        engine.step([StepEntry(a, [1] * 65, []), StepEntry(b, [1] * 65, [])])
+    with pytest.raises(ValueError, match="vocabulary"):
+        engine.step([StepEntry(a, [cfg["vocab_size"]], [0])])
+    with pytest.raises(ValueError, match="twice"):
+        engine.step([StepEntry(a, [1], [0]), StepEntry(a, [2], [0])])
+    engine.close_slot(a)
+    with pytest.raises(CacheError, match="freed twice"):
+        engine.close_slot(a)

@@ -1,0 +1,238 @@
+"""Each CUDA kernel alone against a plain float32 statement of the same operation,
+at sizes other than the engine's tiny models use."""
+
+import math
+
+import pytest
+import torch
+
+import plain_model
+from dryft_flash_infer_b200.cache import LayerCache
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype, scale=1.0):
+    return (2e-5 if dtype == torch.float32 else 1.6e-2) * scale
+
+
+def rounded(x, dtype):
+    return x.to(dtype).float()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows, dim", [(1, 8), (7, 100), (33, 2560), (5, 3001)])
+def test_rms_norm_and_add(dtype, rows, dim):
+    from dryft_flash_infer_b200.ops import kernels
+
+    g = torch.Generator().manual_seed(rows * dim)
+    x = rounded(torch.randn(rows, dim, generator=g) * 3, dtype)
+    d = rounded(torch.randn(rows, dim, generator=g), dtype)
+    w = 1 + 0.2 * torch.randn(dim, generator=g)
+    eps = 1e-5
+    got = kernels.rms_norm(x.to(dtype).cuda(), w.cuda(), eps)
+    assert torch.allclose(got.float().cpu(), plain_model.rms_norm(x, w, eps), atol=tol(dtype, 4), rtol=tol(dtype))
+    res = x.to(dtype).cuda()
+    got = kernels.add_rms_norm(res, d.to(dtype).cuda(), w.cuda(), eps)
+    summed = rounded(x + d, dtype)
+    assert torch.equal(res.float().cpu(), summed)                       # the residual is the rounded float32 sum
+    assert torch.allclose(got.float().cpu(), plain_model.rms_norm(summed, w, eps), atol=tol(dtype, 4), rtol=tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows, inter", [(3, 200), (1, 9728), (9, 37)])
+def test_swiglu(dtype, rows, inter):
+    from dryft_flash_infer_b200.ops import kernels
+
+    g = torch.Generator().manual_seed(inter)
+    gu = rounded(torch.randn(rows, 2 * inter, generator=g) * 2, dtype)
+    want = gu[:, :inter] / (1 + torch.exp(-gu[:, :inter])) * gu[:, inter:]
+    got = kernels.swiglu(gu.to(dtype).cuda())
+    assert torch.allclose(got.float().cpu(), want, atol=tol(dtype, 2), rtol=tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embedding_and_gather(dtype):
+    from dryft_flash_infer_b200.ops import kernels
+
+    table = torch.randn(321, 100).to(dtype)
+    ids = torch.tensor([0, 320, 17, 17, 5], dtype=torch.int32)
+    got = kernels.embedding(table.cuda(), ids.cuda())
+    assert torch.equal(got.cpu(), table[ids.long()])
+    rows = torch.tensor([4, 0, 2], dtype=torch.int32)
+    assert torch.equal(kernels.gather_rows(got, rows.cuda()).cpu(), table[ids.long()][rows.long()])
+    odd = torch.randn(9, 33).to(dtype)                                  # a width with no 16-byte rows
+    assert torch.equal(kernels.gather_rows(odd.cuda(), rows.cuda()).cpu(), odd[rows.long()])
+
+
+def paged_cache(n_seqs, lengths, n_kv, dim, dtype, ring_tokens=0, seed=0, page_size=64):
+    """A cache with pages handed out in a scrambled order, NaN everywhere nothing was written."""
+    width = max(-(-(ring_tokens or n) // page_size) for n in lengths)
+    n_pages = 1 + n_seqs * width
+    g = torch.Generator().manual_seed(seed)
+    order = (1 + torch.randperm(n_pages - 1, generator=g)).tolist()
+    table = torch.zeros(n_seqs, width, dtype=torch.int32)
+    for s in range(n_seqs):
+        need = -(-(ring_tokens or lengths[s]) // page_size)
+        table[s, :need] = torch.tensor([order.pop() for _ in range(need)], dtype=torch.int32)
+    k = torch.full((n_pages, n_kv, page_size, dim), float("nan"), dtype=dtype)
+    v = torch.full((n_pages, n_kv, page_size, dim), float("nan"), dtype=dtype)
+    return LayerCache(k.cuda(), v.cuda(), table.cuda(), page_size, ring_tokens, True), table
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n_q, n_kv, dim", [(6, 3, 48), (4, 4, 16), (16, 2, 128), (5, 1, 256)])
+def test_qk_norm_rope_write(dtype, n_q, n_kv, dim):
+    from dryft_flash_infer_b200.ops import kernels
+    from dryft_flash_infer_b200.parts.rotary import RotaryEmbedding
+
+    lengths = [70, 3, 130]
+    starts = [60, 0, 127]                                               # the new rows cross page borders
+    new = [l - s for l, s in zip(lengths, starts)]
+    rows = sum(new)
+    g = torch.Generator().manual_seed(dim)
+    qkv = rounded(torch.randn(rows, (n_q + 2 * n_kv) * dim, generator=g), dtype)
+    qw, kw = 1 + 0.3 * torch.randn(dim, generator=g), 1 + 0.3 * torch.randn(dim, generator=g)
+    eps, theta = 1e-5, 12345.0
+    row_seq = torch.cat([torch.full((n,), i) for i, n in enumerate(new)]).int()
+    row_pos = torch.cat([torch.arange(s, l) for s, l in zip(starts, lengths)]).int()
+    cache, table = paged_cache(3, lengths, n_kv, dim, dtype, seed=dim)
+    rotary = RotaryEmbedding(0, dim, theta)
+    rotary.prepare(256, "cuda")
+    dev = qkv.to(dtype).cuda()
+    q = kernels.qk_norm_rope_write(dev, n_q, n_kv, dim, qw.cuda(), kw.cuda(), eps, rotary.cos, rotary.sin,
+                                   row_pos.cuda(), row_seq.cuda(), cache)
+    x = qkv.view(rows, n_q + 2 * n_kv, dim)
+    angles = plain_model.rope_angles(row_pos, dim, theta)
+    want_q = plain_model.apply_rope(plain_model.head_norm(x[:, :n_q], qw, eps), angles)
+    want_k = plain_model.apply_rope(plain_model.head_norm(x[:, n_q:n_q + n_kv], kw, eps), angles)
+    want_v = x[:, n_q + n_kv:]
+    t = tol(dtype, 4)
+    assert torch.allclose(q.float().cpu().view(rows, n_q, dim), want_q, atol=t, rtol=tol(dtype))
+    k_cache, v_cache = cache.k.float().cpu(), cache.v.float().cpu()
+    written = torch.zeros(k_cache.shape[0], 64, dtype=torch.bool)
+    for r in range(rows):
+        page = int(table[row_seq[r], row_pos[r] // 64])
+        assert torch.allclose(k_cache[page, :, row_pos[r] % 64], want_k[r], atol=t, rtol=tol(dtype))
+        assert torch.equal(v_cache[page, :, row_pos[r] % 64], want_v[r])
+        written[page, row_pos[r] % 64] = True
+    assert torch.isnan(k_cache.transpose(1, 2)[~written]).all() and torch.isnan(v_cache.transpose(1, 2)[~written]).all()   # nothing else was touched
+    # without weights and tables the heads pass through unchanged, and writes=False leaves the cache alone
+    cache2, _ = paged_cache(3, lengths, n_kv, dim, dtype, seed=dim)
+    cache2.writes = False
+    dev = qkv.to(dtype).cuda()
+    q = kernels.qk_norm_rope_write(dev, n_q, n_kv, dim, None, None, eps, None, None, row_pos.cuda(), row_seq.cuda(), cache2)
+    assert torch.equal(q.float().cpu(), qkv[:, :n_q * dim]) and torch.isnan(cache2.k).all()
+
+
+def plain_attention_rows(q, keys, values, positions, starts, scale, window):
+    """q [rows, n_q, D] of one sequence at ``positions``; keys/values [len, n_kv, D]."""
+    n_q, n_kv = q.shape[1], keys.shape[1]
+    out = torch.empty_like(q)
+    for r, pos in enumerate(positions):
+        first = max(0, pos - window + 1) if window else 0
+        for h in range(n_q):
+            s = (keys[first:pos + 1, h // (n_q // n_kv)] @ q[r, h]) * scale
+            out[r, h] = torch.softmax(s, 0) @ values[first:pos + 1, h // (n_q // n_kv)]
+    return out
+
+
+def attention_case(dtype, n_q, n_kv, dim, lengths, new, window=0, ring_tokens=0, seed=0, sharp=None):
+    g = torch.Generator().manual_seed(seed)
+    keys = [rounded(torch.randn(l, n_kv, dim, generator=g), dtype) for l in lengths]
+    values = [rounded(torch.randn(l, n_kv, dim, generator=g), dtype) for l in lengths]
+    qs = [rounded(torch.randn(n, n_q, dim, generator=g), dtype) for n in new]
+    if sharp is not None:                          # the last query of sequence 0 looks for one far key
+        qs[0][-1] = keys[0][sharp].repeat_interleave(n_q // n_kv, 0) * 4.0
+    cache, table = paged_cache(len(lengths), lengths, n_kv, dim, dtype, ring_tokens, seed)
+    k_host, v_host = cache.k.cpu(), cache.v.cpu()
+    for s, l in enumerate(lengths):
+        first = max(0, l - ring_tokens) if ring_tokens else 0
+        for p in range(first, l):
+            place = p % ring_tokens if ring_tokens else p
+            page = int(table[s, place // 64])
+            k_host[page, :, place % 64] = keys[s][p].to(dtype)
+            v_host[page, :, place % 64] = values[s][p].to(dtype)
+    cache.k.copy_(k_host)
+    cache.v.copy_(v_host)
+    row_seq = torch.cat([torch.full((n,), i) for i, n in enumerate(new)]).int().cuda()
+    row_pos = torch.cat([torch.arange(l - n, l) for l, n in zip(lengths, new)]).int().cuda()
+    q = torch.cat(qs).reshape(sum(new), n_q * dim).to(dtype).cuda()
+    scale = dim ** -0.5
+    want = torch.cat([plain_attention_rows(qs[s], keys[s], values[s], list(range(l - n, l)), None, scale, window)
+                      for s, (l, n) in enumerate(zip(lengths, new))]).reshape(sum(new), n_q * dim)
+    return q, cache, row_seq, row_pos, scale, want
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n_q, n_kv, dim", [(6, 3, 48), (4, 4, 16), (8, 2, 128), (3, 1, 256)])
+def test_attention_generic_prefill_and_decode(dtype, n_q, n_kv, dim):
+    from dryft_flash_infer_b200.ops import kernels
+
+    for lengths, new in (([70, 3, 130], [70, 3, 130]), ([70, 3, 130], [10, 3, 3]), ([257, 64, 1], [1, 1, 1])):
+        q, cache, row_seq, row_pos, scale, want = attention_case(dtype, n_q, n_kv, dim, lengths, new, seed=dim)
+        got = kernels.attention_generic(q, cache, row_seq, row_pos, n_q, n_kv, dim, scale)
+        assert torch.isfinite(got).all()
+        assert torch.allclose(got.float().cpu(), want, atol=tol(dtype, 2), rtol=tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_generic_far_key_and_window_edge(dtype):
+    from dryft_flash_infer_b200.ops import kernels
+
+    # one key at position 5 of 600 takes nearly all the weight
+    q, cache, row_seq, row_pos, scale, want = attention_case(dtype, 8, 2, 64, [600, 90], [1, 1], seed=3, sharp=5)
+    got = kernels.attention_generic(q, cache, row_seq, row_pos, 8, 2, 64, scale)
+    assert torch.allclose(got.float().cpu(), want, atol=tol(dtype, 2), rtol=tol(dtype))
+    # a window of 100 over a ring of 192 places: the key just outside must not count, the one just inside must
+    for window, ring in ((100, 192), (64, 128), (1, 64)):
+        q, cache, row_seq, row_pos, scale, want = attention_case(
+            dtype, 4, 2, 32, [500, 131, 40], [3, 2, 40], window=window, ring_tokens=ring, seed=window)
+        got = kernels.attention_generic(q, cache, row_seq, row_pos, 4, 2, 32, scale, window)
+        assert torch.isfinite(got).all()
+        assert torch.allclose(got.float().cpu(), want, atol=tol(dtype, 2), rtol=tol(dtype))
+
+
+def test_argmax_and_sampling():
+    from dryft_flash_infer_b200.ops import kernels
+
+    g = torch.Generator().manual_seed(0)
+    logits = torch.randn(5, 151936, generator=g)
+    logits[1, 7] = logits[1, 90000] = 50.0                              # a tie: the lowest index wins
+    logits[2, 151935] = 60.0
+    got = kernels.argmax(logits.cuda()).cpu()
+    assert got.tolist() == [int(logits[0].argmax()), 7, 151935, int(logits[3].argmax()), int(logits[4].argmax())]
+    small = torch.randn(3, 37, generator=g)
+    assert kernels.argmax(small.cuda()).cpu().tolist() == small.argmax(-1).tolist()
+    wide = torch.randn(4, 1000, generator=g)[:, :700]                   # rows with a stride
+    assert kernels.argmax(wide.cuda()[:, :700]).cpu().tolist() == wide.argmax(-1).tolist()
+    # sampling: the token's CDF interval holds its uniform number
+    for vocab, temperature in ((320, 0.8), (151936, 1.3), (5, 0.1)):
+        logits = torch.randn(64, vocab, generator=g) * 3
+        u = torch.rand(64, generator=g)
+        u[0], u[1] = 0.0, 1.0 - 2 ** -24
+        got = kernels.sample_temperature(logits.cuda(), u.cuda(), temperature).cpu()
+        cdf = torch.cumsum(plain_model.temperature_probabilities(logits, temperature), -1)
+        for r in range(64):
+            t = int(got[r])
+            low = float(cdf[r, t - 1]) if t else 0.0
+            assert low - 2e-5 <= float(u[r]) <= float(cdf[r, t]) + 2e-5, (vocab, r, t)
+    # a row's draw does not depend on the other rows
+    alone = kernels.sample_temperature(logits[5:6].cuda(), u[5:6].cuda(), temperature).cpu()
+    assert int(alone[0]) == int(got[5])
+
+
+def test_sizes_a_kernel_does_not_take_are_refused():
+    from dryft_flash_infer_b200.ops import KernelError, kernels
+
+    cache, _ = paged_cache(1, [10], 1, 20, torch.bfloat16)
+    q = torch.zeros(1, 20, dtype=torch.bfloat16).cuda()
+    pos = torch.zeros(1, dtype=torch.int32).cuda()
+    with pytest.raises(KernelError, match="head_dim"):
+        kernels.attention_generic(q, cache, pos, pos, 1, 1, 20, 1.0)
+    with pytest.raises(KernelError, match="CUDA device"):
+        kernels.rms_norm(torch.zeros(2, 8), torch.ones(8), 1e-6)
+    with pytest.raises(KernelError, match="dtype"):
+        kernels.rms_norm(torch.zeros(2, 8, dtype=torch.float16).cuda(), torch.ones(8).cuda(), 1e-6)

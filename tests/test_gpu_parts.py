@@ -1,0 +1,231 @@
+"""Each part of a layer alone, and a toy architecture whose mixer keeps a state of its own,
+registered from here without a change to the package."""
+
+from dataclasses import dataclass
+from typing import ClassVar
+
+import pytest
+import torch
+
+import plain_model
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def fill(part, dtype, seed, std=0.05):
+    g = torch.Generator().manual_seed(seed)
+    host, dev = {}, {}
+    for name, (shape, precision) in part.buffer_shapes().items():
+        t = torch.randn(shape, generator=g) * std if len(shape) > 1 else 1 + 0.2 * torch.randn(shape, generator=g)
+        kept = t if precision == "float32" else t.to(dtype).float()
+        host[name] = kept
+        dev[name] = kept.to(torch.float32 if precision == "float32" else dtype).cuda()
+    part.bind(dev)
+    return host
+
+
+def close(got, want, dtype, scale=1.0):
+    t = (3e-5 if dtype == torch.float32 else 2e-2) * scale
+    err = float((got.float().cpu() - want).abs().max())
+    assert err <= t * max(1.0, float(want.abs().max())), err
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_norm_and_feed_forward_alone(dtype):
+    from dryft_flash_infer_b200.parts import PartSpec, build_part
+
+    norm = build_part("norm", PartSpec("rms_norm", {"eps": 1e-4}), hidden_size=72)
+    w = fill(norm, dtype, 1)
+    x = (torch.randn(5, 72) * 2).to(dtype)
+    close(norm.forward(x.cuda()), plain_model.rms_norm(x.float(), w["weight"], 1e-4), dtype)
+    ffn = build_part("feed_forward", PartSpec("swiglu", {"intermediate_size": 136}), hidden_size=72)
+    w = fill(ffn, dtype, 2)
+    names = {"g.gate_proj.weight": w["gate_up"][:136], "g.up_proj.weight": w["gate_up"][136:],
+             "g.down_proj.weight": w["down"]}
+    close(ffn.forward(x.cuda(), None), plain_model.swiglu_mlp(x.float(), names, "g."), dtype)
+    with pytest.raises(ValueError, match="silu"):
+        build_part("feed_forward", PartSpec("swiglu", {"intermediate_size": 8, "activation": "relu"}), hidden_size=8)
+    with pytest.raises(ValueError, match="unknown mixer kind"):
+        build_part("mixer", PartSpec("no_such_mixer"), hidden_size=8)
+
+
+def one_layer_setup(mixer, dtype, lengths, hidden, max_tokens=1024):
+    from dryft_flash_infer_b200.cache import SequenceCache
+    from dryft_flash_infer_b200.engine import StepContext, StepEntry
+
+    cache = SequenceCache({0: mixer.cache_need()}, {}, max_tokens=max_tokens, max_seqs=len(lengths),
+                          max_context=max_tokens, step_tokens=256, dtype=dtype, device="cuda")   # one pass gives a sequence up to 145 rows
+    for g in cache.groups:
+        g.k.fill_(float("nan"))
+        g.v.fill_(float("nan"))
+    return cache
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("window, qk_norm, rotary", [(0, True, True), (0, False, False), (40, True, True)])
+def test_attention_mixer_alone(dtype, window, qk_norm, rotary):
+    """The mixer with its options switched one by one, prompt then single tokens, two sequences."""
+    from dryft_flash_infer_b200.engine import StepContext, StepEntry
+    from dryft_flash_infer_b200.parts import PartSpec, build_part
+
+    hidden, n_q, n_kv, dim, theta, eps = 72, 6, 2, 48, 5000.0, 1e-5
+    params = {"n_heads": n_q, "n_kv_heads": n_kv, "head_dim": dim, "qk_norm": qk_norm, "qk_norm_eps": eps,
+              "window": window}
+    if rotary:
+        params["position"] = PartSpec("rotary", {"head_dim": dim, "theta": theta})
+    mixer = build_part("mixer", PartSpec("attention", params), hidden_size=hidden)
+    w = fill(mixer, dtype, 3, std=0.15)
+    mixer.prepare(512, "cuda")
+    lengths = [150, 67]
+    cache = one_layer_setup(mixer, dtype, lengths, hidden)
+    xs = [(torch.randn(n, hidden)).to(dtype) for n in lengths]
+
+    def plain(x):
+        t = x.shape[0]
+        q = (x @ w["qkv"][: n_q * dim].T).view(t, n_q, dim)
+        k = (x @ w["qkv"][n_q * dim: (n_q + n_kv) * dim].T).view(t, n_kv, dim)
+        v = (x @ w["qkv"][(n_q + n_kv) * dim:].T).view(t, n_kv, dim)
+        if qk_norm:
+            q, k = plain_model.head_norm(q, w["q_norm"], eps), plain_model.head_norm(k, w["k_norm"], eps)
+        if rotary:
+            ang = plain_model.rope_angles(torch.arange(t), dim, theta)
+            q, k = plain_model.apply_rope(q, ang), plain_model.apply_rope(k, ang)
+        return plain_model.causal_attention(q, k, v, window=window).reshape(t, -1) @ w["o"].T
+
+    want = [plain(x.float()) for x in xs]
+    slots = [cache.open_slot() for _ in lengths]
+    heads = [n - 5 for n in lengths]
+    pieces = [[] for _ in lengths]
+
+    def run(parts):
+        entries = [StepEntry(s, [0] * p.shape[0]) for s, p in zip(slots, parts)]
+        for e in entries:
+            cache.book.reserve(e.slot, len(e.tokens))
+        ctx = StepContext(entries, cache, "cuda")
+        out = mixer.forward(torch.cat(parts).cuda(), ctx, cache.layer_view(0, ctx.block_tables, True), None)
+        at = 0
+        for i, e in enumerate(entries):
+            cache.book.advance(e.slot, len(e.tokens))
+            pieces[i].append(out[at: at + len(e.tokens)].float().cpu())
+            at += len(e.tokens)
+
+    run([x[:h] for x, h in zip(xs, heads)])
+    for t in range(5):
+        run([x[h + t: h + t + 1] for x, h in zip(xs, heads)])
+    for i in range(len(lengths)):
+        close(torch.cat(pieces[i]), want[i], dtype, scale=2.0)
+
+
+# --------------------------------------------------------------------------- a toy architecture
+
+
+def register_toy():
+    """A mixer with a fixed-size state per sequence (a running mean of its inputs), a block that
+    uses it, a configuration and an architecture: all defined here, all registered through the
+    package's public registries."""
+    from dryft_flash_infer_b200.config import ModelConfig, register_architecture
+    from dryft_flash_infer_b200.parts import (LayerSpec, Mixer, ModelSpec, PartSpec, ScheduleEntry, StateNeed,
+                                              TensorDecl, register_part)
+
+    class RunningMean(Mixer):
+        kind = "toy_running_mean"
+
+        def __init__(self, hidden_size: int, decay: float):
+            self.hidden_size, self.decay = hidden_size, decay
+            self.proj = None
+
+        def tensors(self):
+            return {"proj": TensorDecl((self.hidden_size, self.hidden_size), "proj")}
+
+        def state_need(self):
+            return StateNeed((self.hidden_size + 1,))        # running sum and running weight
+
+        def forward(self, x, ctx, cache, state):
+            out = torch.empty_like(x)
+            at = 0
+            for slot, n in zip(ctx.slots, ctx.q_lens):
+                total, weight = state[slot, :-1].clone(), state[slot, -1].clone()
+                for r in range(at, at + n):
+                    total = total * self.decay + x[r].float()
+                    weight = weight * self.decay + 1.0
+                    out[r] = (total / weight).to(x.dtype)
+                state[slot, :-1], state[slot, -1] = total, weight
+                at += n
+            return out @ self.proj.t()
+
+    register_part("mixer", RunningMean.kind, RunningMean)
+
+    @dataclass(frozen=True)
+    class ToyConfig(ModelConfig):
+        vocab_size: int
+        hidden_size: int
+        intermediate_size: int
+        num_hidden_layers: int
+        decay: float
+        architecture: ClassVar[str] = "ToyStateForCausalLM"
+
+        @classmethod
+        def from_dict(cls, raw):
+            return cls(raw["vocab_size"], raw["hidden_size"], raw["intermediate_size"], raw["num_hidden_layers"],
+                       raw["decay"])
+
+    def build(config):
+        norm = PartSpec("rms_norm", {"eps": 1e-5})
+        layers = []
+        for i in range(config.num_hidden_layers):
+            # even layers: the toy mixer; odd layers: attention without rotary or head norms
+            mixer = PartSpec("toy_running_mean", {"decay": config.decay}) if i % 2 == 0 else \
+                PartSpec("attention", {"n_heads": 2, "n_kv_heads": 1, "head_dim": 16, "qk_norm": False})
+            names = {"mixer_norm.weight": f"l{i}.n1", "ffn_norm.weight": f"l{i}.n2",
+                     "feed_forward.gate_proj": f"l{i}.gate", "feed_forward.up_proj": f"l{i}.up",
+                     "feed_forward.down_proj": f"l{i}.down"}
+            if i % 2 == 0:
+                names["mixer.proj"] = f"l{i}.proj"
+            else:
+                names.update({"mixer.q_proj": f"l{i}.q", "mixer.k_proj": f"l{i}.k", "mixer.v_proj": f"l{i}.v",
+                              "mixer.o_proj": f"l{i}.o"})
+            layers.append(LayerSpec("pre_norm", mixer, PartSpec("swiglu", {"intermediate_size": config.intermediate_size}),
+                                    norm, norm, names))
+        # the order of layers is data: layer 0 runs twice (each time with a state of its own), and the
+        # second pass of layer 1 reads the keys and values that its first pass wrote
+        schedule = (ScheduleEntry(0, cache=0), ScheduleEntry(1, cache=1), ScheduleEntry(0, cache=2),
+                    ScheduleEntry(1, cache=1, writes_cache=False))
+        return ModelSpec(config.architecture, config.vocab_size, config.hidden_size, 4096, tuple(layers), schedule,
+                         norm, "emb", {"weight": "final"}, None)
+
+    register_architecture(ToyConfig.architecture, ToyConfig, build)
+    return ToyConfig
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_toy_mixer_with_state_is_registered_built_and_stepped(dtype):
+    from dryft_flash_infer_b200 import Engine, StepEntry
+
+    ToyConfig = register_toy()
+    raw = {"architectures": ["ToyStateForCausalLM"], "vocab_size": 50, "hidden_size": 32, "intermediate_size": 48,
+           "num_hidden_layers": 2, "decay": 0.9}
+    engine = Engine(config=raw, random_weights=True, seed=4, dtype=dtype, max_tokens=512)
+    assert isinstance(engine.config, ToyConfig)
+    assert sorted(engine.cache.state) == [0, 2] and len(engine.cache.groups) == 1
+    seqs = [[3, 1, 4, 1, 5, 9, 2, 6, 5, 3], [8, 9, 7]]
+    slots = [engine.open_slot() for _ in seqs]
+    whole = engine.step([StepEntry(s, q, list(range(len(q)))) for s, q in zip(slots, seqs)])
+    for s in slots:
+        engine.close_slot(s)
+    slots = [engine.open_slot() for _ in seqs]          # the same slots again: their state starts at zero
+    rows = {0: [], 1: []}
+    for t in range(max(map(len, seqs))):
+        live = [i for i, q in enumerate(seqs) if t < len(q)]
+        out = engine.step([StepEntry(slots[i], [seqs[i][t]], [0]) for i in live])
+        for row, i in enumerate(live):
+            rows[i].append(out[row])
+    stepped = torch.cat([torch.stack(rows[0]), torch.stack(rows[1])])
+    tol = 1e-4 if dtype == "float32" else 0.05 * max(1.0, float(whole.abs().max()))
+    assert torch.isfinite(whole).all() and float((whole - stepped).abs().max()) <= tol
+    # the state did something: another decay gives other logits
+    other = Engine(config={**raw, "decay": 0.5}, random_weights=True, seed=4, dtype=dtype, max_tokens=512)
+    slot = other.open_slot()
+    changed = other.step([StepEntry(slot, seqs[0], list(range(len(seqs[0]))))])
+    assert float((changed - whole[: len(seqs[0])]).abs().max()) > 10 * tol or dtype == "bfloat16"
