@@ -1,0 +1,481 @@
+// bfloat16 attention over the paged cache on the tensor cores, for one head size per
+// build (-DDFI_HEAD_DIM=..., a multiple of 16 up to 128).
+//
+//   dfi_attention_prefill   any number of query rows per sequence (a whole prompt, a chunk
+//                           of one): flash attention with causal mask, grouped-query heads,
+//                           optional window.  One CTA per (64 query rows, query head).
+//   dfi_attention_decode    one query row per sequence: the G query heads of a key/value
+//                           head are the rows of one MMA tile, the key range is cut into
+//                           splits that run in parallel, and a second kernel merges them.
+//
+// Both follow the online softmax of the reference's split kernel
+// (engine/kernels/attention.py:40-137; merge :140-177): float32 scores, maximum, sum and
+// accumulator; probabilities rounded to bfloat16 for the product with V.  Keys and values
+// come one page (64 tokens) at a time through cp.async into padded shared memory; the
+// tensor-core instruction is mma.sync m16n8k16 (operands in registers via ldmatrix).
+//
+// Places of the cache that no token was written to may hold anything (NaN included):
+// scores of masked keys are replaced, not added to, and value rows past the sequence's
+// end are zero-filled on load, so such places never reach a result.
+#include "common.cuh"
+
+#ifndef DFI_HEAD_DIM
+#define DFI_HEAD_DIM 128
+#endif
+
+namespace dfi {
+
+constexpr int D = DFI_HEAD_DIM;
+static_assert(D % 16 == 0 && D >= 16 && D <= 128, "head size must be a multiple of 16 up to 128");
+constexpr int kStride = D + 8;      // padded row: 16-byte chunks at an odd stride are conflict-free for ldmatrix
+constexpr int kPage = 64;           // keys per tile = tokens per cache page
+constexpr int kChunks = D / 8;      // 16-byte chunks per row
+constexpr int kThreads = 128;
+constexpr float kLog2e = 1.4426950408889634f;
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+    const int bytes = valid ? 16 : 0;   // 0: the 16 bytes are filled with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_addr(dst)), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Copies one page of one key/value head ([64][D], contiguous) into padded shared memory.
+// Rows whose key index is not below `live_keys` are zero-filled when `zero_dead` is set.
+__device__ __forceinline__ void load_page(bf16* dst, const bf16* src, int first_key, int live_keys, bool zero_dead) {
+    for (int i = threadIdx.x; i < kPage * kChunks; i += kThreads) {
+        const int row = i / kChunks, c = i % kChunks;
+        const bool valid = !zero_dead || first_key + row < live_keys;
+        cp_async16(dst + row * kStride + c * 8, src + (size_t)row * D + c * 8, valid);
+    }
+}
+
+__device__ __forceinline__ const bf16* page_ptr(const bf16* cache, const int* table, int tile, int ring_tokens,
+                                                int n_kv, int kv_head) {
+    const int place = place_of(tile * kPage, ring_tokens);
+    const int page = table[place / kPage];
+    return cache + ((size_t)page * n_kv + kv_head) * kPage * D;
+}
+
+// S[16 x 8*NT] += Q[16 x D] . K[keys x D]^T for the NT key tiles starting at row `key0` of k_s.
+template <int NT>
+__device__ __forceinline__ void scores(float (&s)[NT][4], const uint32_t (&qf)[D / 16][4], const bf16* k_s, int key0,
+                                       int lane) {
+    static_assert(NT % 2 == 0, "key tiles come in pairs");
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[j][e] = 0.f;
+    const int mi = lane >> 3, r = lane & 7;
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+#pragma unroll
+        for (int j = 0; j < NT; j += 2) {
+            uint32_t b[4];
+            ldmatrix_x4(b, k_s + (key0 + j * 8 + r + (mi >> 1) * 8) * kStride + kk * 16 + (mi & 1) * 8);
+            mma_bf16(s[j], qf[kk], b[0], b[1]);
+            mma_bf16(s[j + 1], qf[kk], b[2], b[3]);
+        }
+    }
+}
+
+// O[16 x D] += P[16 x 8*NT] . V[keys x D] for the keys starting at row `key0` of v_s.
+template <int NT>
+__device__ __forceinline__ void weighted_values(float (&o)[D / 8][4], const float (&p)[NT][4], const bf16* v_s, int key0,
+                                                int lane) {
+    const int mi = lane >> 3, r = lane & 7;
+#pragma unroll
+    for (int c = 0; c < NT / 2; ++c) {
+        uint32_t a[4];
+        a[0] = pack_bf16(p[2 * c][0], p[2 * c][1]);
+        a[1] = pack_bf16(p[2 * c][2], p[2 * c][3]);
+        a[2] = pack_bf16(p[2 * c + 1][0], p[2 * c + 1][1]);
+        a[3] = pack_bf16(p[2 * c + 1][2], p[2 * c + 1][3]);
+#pragma unroll
+        for (int n = 0; n < D / 8; n += 2) {
+            uint32_t b[4];
+            ldmatrix_x4_trans(b, v_s + (key0 + c * 16 + r + (mi & 1) * 8) * kStride + n * 8 + (mi >> 1) * 8);
+            mma_bf16(o[n], a, b[0], b[1]);
+            mma_bf16(o[n + 1], a, b[2], b[3]);
+        }
+    }
+}
+
+// One online-softmax update of the two rows (g, g+8) a thread holds, over NT key tiles.
+// `s` holds scores in the log2 domain (already scaled); masked entries are -inf.
+template <int NT>
+__device__ __forceinline__ void softmax_update(float (&s)[NT][4], float (&m)[2], float (&l)[2], float (&o)[D / 8][4]) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        float mx = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < NT; ++j) mx = fmaxf(mx, fmaxf(s[j][2 * h], s[j][2 * h + 1]));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m[h], mx);
+        const float m_use = m_new == -INFINITY ? 0.f : m_new;   // a row with nothing to see yet
+        const float corr = exp2f(m[h] - m_use);
+        float sum = 0.f;
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+            s[j][2 * h] = exp2f(s[j][2 * h] - m_use);
+            s[j][2 * h + 1] = exp2f(s[j][2 * h + 1] - m_use);
+            sum += s[j][2 * h] + s[j][2 * h + 1];
+        }
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        l[h] = l[h] * corr + sum;
+        m[h] = m_new;
+#pragma unroll
+        for (int n = 0; n < D / 8; ++n) {
+            o[n][2 * h] *= corr;
+            o[n][2 * h + 1] *= corr;
+        }
+    }
+}
+
+// ------------------------------------------------------------------ prefill
+__global__ void __launch_bounds__(kThreads)
+attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, int out_stride,
+                         const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
+                         const int* __restrict__ block_table, int table_width, const int* __restrict__ cu_rows,
+                         const int* __restrict__ seq_start, int n_q, int n_kv, int ring_tokens, int window,
+                         float scale_log2) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* q_s = reinterpret_cast<bf16*>(smem_raw);   // [64][kStride]
+    bf16* k_s = q_s + kPage * kStride;               // [2][64][kStride]
+    bf16* v_s = k_s + 2 * kPage * kStride;           // [2][64][kStride]
+
+    const int seq = blockIdx.z, head = blockIdx.y;
+    const int row0 = cu_rows[seq], q_len = cu_rows[seq + 1] - row0;
+    const int r0 = blockIdx.x * 64;
+    if (r0 >= q_len) return;
+    const int rows_here = min(64, q_len - r0);
+    const int start = seq_start[seq];
+    const int kv_len = start + q_len;
+    const int kv_head = head / (n_q / n_kv);
+    const int* table = block_table + (size_t)seq * table_width;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t4 = lane & 3;
+
+    // the query tile; rows past the sequence's share are zeros
+    for (int i = threadIdx.x; i < 64 * kChunks; i += kThreads) {
+        const int row = i / kChunks, c = i % kChunks;
+        const bool valid = row < rows_here;
+        const bf16* src = q + (size_t)(row0 + r0 + (valid ? row : 0)) * q_stride + (size_t)head * D + c * 8;
+        cp_async16(q_s + row * kStride + c * 8, src, valid);
+    }
+    const int last_key = start + r0 + rows_here - 1;
+    const int first_key = window > 0 ? max(0, start + r0 - window + 1) : 0;
+    const int t_begin = first_key / kPage, t_end = last_key / kPage;
+    load_page(k_s, page_ptr(k_cache, table, t_begin, ring_tokens, n_kv, kv_head), t_begin * kPage, kv_len, false);
+    load_page(v_s, page_ptr(v_cache, table, t_begin, ring_tokens, n_kv, kv_head), t_begin * kPage, kv_len, true);
+    cp_async_commit();
+
+    uint32_t qf[D / 16][4];
+    float o[D / 8][4];
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[n][e] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    // positions of the two query rows this thread holds
+    const int pos_lo = start + r0 + warp * 16 + g, pos_hi = pos_lo + 8;
+
+    for (int t = t_begin; t <= t_end; ++t) {
+        const int stage = (t - t_begin) & 1;
+        if (t < t_end) {
+            bf16* k_next = k_s + (stage ^ 1) * kPage * kStride;
+            bf16* v_next = v_s + (stage ^ 1) * kPage * kStride;
+            load_page(k_next, page_ptr(k_cache, table, t + 1, ring_tokens, n_kv, kv_head), (t + 1) * kPage, kv_len, false);
+            load_page(v_next, page_ptr(v_cache, table, t + 1, ring_tokens, n_kv, kv_head), (t + 1) * kPage, kv_len, true);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        if (t == t_begin) {
+            const int mi = lane >> 3, r = lane & 7;
+#pragma unroll
+            for (int kk = 0; kk < D / 16; ++kk)
+                ldmatrix_x4(qf[kk], q_s + (warp * 16 + r + (mi & 1) * 8) * kStride + kk * 16 + (mi >> 1) * 8);
+        }
+        const bf16* k_t = k_s + stage * kPage * kStride;
+        const bf16* v_t = v_s + stage * kPage * kStride;
+        float s[8][4];
+        scores<8>(s, qf, k_t, 0, lane);
+        const int key_base = t * kPage;
+        // the tile needs masking if any of its keys is hidden from any row of this warp
+        const bool partial = key_base + kPage - 1 > start + r0 + warp * 16 ||
+                             (window > 0 && key_base < start + r0 + warp * 16 + 15 - window + 1);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                float v = s[j][e] * scale_log2;
+                if (partial) {
+                    const int key = key_base + j * 8 + t4 * 2 + (e & 1);
+                    const int pos = (e & 2) ? pos_hi : pos_lo;
+                    const bool seen = key <= pos && (window <= 0 || key > pos - window);
+                    v = seen ? v : -INFINITY;
+                }
+                s[j][e] = v;
+            }
+        }
+        softmax_update<8>(s, m, l, o);
+        weighted_values<8>(o, s, v_t, 0, lane);
+        __syncthreads();   // everyone is done with this stage before the next load overwrites it
+    }
+
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int row = warp * 16 + g + h * 8;
+        if (row < rows_here) {
+            const float inv = l[h] > 0.f ? 1.0f / l[h] : 0.f;
+            bf16* dst = out + (size_t)(row0 + r0 + row) * out_stride + (size_t)head * D;
+#pragma unroll
+            for (int n = 0; n < D / 8; ++n)
+                *reinterpret_cast<uint32_t*>(dst + n * 8 + t4 * 2) = pack_bf16(o[n][2 * h] * inv, o[n][2 * h + 1] * inv);
+        }
+    }
+}
+
+// ------------------------------------------------------------------ decode
+// grid (sequences * kv heads, splits).  part_o [seq*n_q + head][split][D] float32 holds the
+// unnormalised accumulators, part_ml [..][split][2] their (maximum, sum); unused when splits == 1.
+__global__ void __launch_bounds__(kThreads)
+attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, int out_stride,
+                        const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
+                        const int* __restrict__ block_table, int table_width, const int* __restrict__ seq_start,
+                        int n_q, int n_kv, int ring_tokens, int window, float scale_log2, int n_splits,
+                        float* __restrict__ part_o, float* __restrict__ part_ml) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* q_s = reinterpret_cast<bf16*>(smem_raw);   // [16][kStride]
+    bf16* k_s = q_s + 16 * kStride;                  // [2][64][kStride]
+    bf16* v_s = k_s + 2 * kPage * kStride;           // [2][64][kStride]
+
+    const int seq = blockIdx.x / n_kv, kv_head = blockIdx.x % n_kv, split = blockIdx.y;
+    const int group = n_q / n_kv;
+    const int pos = seq_start[seq];                  // the new token's position: keys 0..pos are live
+    const int kv_len = pos + 1;
+    const int* table = block_table + (size_t)seq * table_width;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t4 = lane & 3;
+
+    const int first_key = window > 0 ? max(0, pos - window + 1) : 0;
+    const int t_first = first_key / kPage, t_last = pos / kPage;
+    const int per = (t_last - t_first + n_splits) / n_splits;
+    const int t_begin = t_first + split * per, t_end = min(t_last, t_begin + per - 1);
+
+    float o[D / 8][4];
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[n][e] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+    if (t_begin <= t_end) {
+        for (int i = threadIdx.x; i < 16 * kChunks; i += kThreads) {
+            const int row = i / kChunks, c = i % kChunks;
+            const bool valid = row < group;
+            const bf16* src = q + (size_t)seq * q_stride + (size_t)(kv_head * group + (valid ? row : 0)) * D + c * 8;
+            cp_async16(q_s + row * kStride + c * 8, src, valid);
+        }
+        load_page(k_s, page_ptr(k_cache, table, t_begin, ring_tokens, n_kv, kv_head), t_begin * kPage, kv_len, false);
+        load_page(v_s, page_ptr(v_cache, table, t_begin, ring_tokens, n_kv, kv_head), t_begin * kPage, kv_len, true);
+        cp_async_commit();
+        uint32_t qf[D / 16][4];
+        for (int t = t_begin; t <= t_end; ++t) {
+            const int stage = (t - t_begin) & 1;
+            if (t < t_end) {
+                bf16* k_next = k_s + (stage ^ 1) * kPage * kStride;
+                bf16* v_next = v_s + (stage ^ 1) * kPage * kStride;
+                load_page(k_next, page_ptr(k_cache, table, t + 1, ring_tokens, n_kv, kv_head), (t + 1) * kPage, kv_len, false);
+                load_page(v_next, page_ptr(v_cache, table, t + 1, ring_tokens, n_kv, kv_head), (t + 1) * kPage, kv_len, true);
+                cp_async_commit();
+                cp_async_wait<1>();
+            } else {
+                cp_async_wait<0>();
+            }
+            __syncthreads();
+            if (t == t_begin) {
+                const int mi = lane >> 3, r = lane & 7;
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk)
+                    ldmatrix_x4(qf[kk], q_s + (r + (mi & 1) * 8) * kStride + kk * 16 + (mi >> 1) * 8);
+            }
+            const bf16* k_t = k_s + stage * kPage * kStride;
+            const bf16* v_t = v_s + stage * kPage * kStride;
+            // each warp takes 16 of the tile's 64 keys
+            float s[2][4];
+            scores<2>(s, qf, k_t, warp * 16, lane);
+            const int key_base = t * kPage + warp * 16;
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int key = key_base + j * 8 + t4 * 2 + (e & 1);
+                    const bool seen = key <= pos && key >= first_key;
+                    s[j][e] = seen ? s[j][e] * scale_log2 : -INFINITY;
+                }
+            softmax_update<2>(s, m, l, o);
+            weighted_values<2>(o, s, v_t, warp * 16, lane);
+            __syncthreads();
+        }
+    }
+
+    // merge the four warps' partial results: the tile buffers are free now
+    float* red_o = reinterpret_cast<float*>(k_s);        // [4][16][D]
+    float* red_ml = red_o + 4 * 16 * D;                  // [4][16][2]
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int row = g + h * 8;
+#pragma unroll
+        for (int n = 0; n < D / 8; ++n) {
+            red_o[(warp * 16 + row) * D + n * 8 + t4 * 2] = o[n][2 * h];
+            red_o[(warp * 16 + row) * D + n * 8 + t4 * 2 + 1] = o[n][2 * h + 1];
+        }
+        if (t4 == 0) {
+            red_ml[(warp * 16 + row) * 2] = m[h];
+            red_ml[(warp * 16 + row) * 2 + 1] = l[h];
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < group * D; i += kThreads) {
+        const int row = i / D, d = i % D;
+        float mx = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) mx = fmaxf(mx, red_ml[(w * 16 + row) * 2]);
+        const float m_use = mx == -INFINITY ? 0.f : mx;
+        float acc = 0.f, sum = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float c = exp2f(red_ml[(w * 16 + row) * 2] - m_use);
+            acc += c * red_o[(w * 16 + row) * D + d];
+            sum += c * red_ml[(w * 16 + row) * 2 + 1];
+        }
+        const int head = kv_head * group + row;
+        if (n_splits == 1) {
+            out[(size_t)seq * out_stride + (size_t)head * D + d] = __float2bfloat16_rn(sum > 0.f ? acc / sum : 0.f);
+        } else {
+            const size_t slot = ((size_t)seq * n_q + head) * n_splits + split;
+            part_o[slot * D + d] = acc;
+            if (d == 0) {
+                part_ml[slot * 2] = mx;
+                part_ml[slot * 2 + 1] = sum;
+            }
+        }
+    }
+}
+
+// grid (sequences * query heads); merges the splits by their log-sum-exp (attention.py:140-177).
+__global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                       bf16* __restrict__ out, int out_stride, int n_q, int n_splits) {
+    const int seq = blockIdx.x / n_q, head = blockIdx.x % n_q;
+    const size_t base = (size_t)blockIdx.x * n_splits;
+    float mx = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) mx = fmaxf(mx, part_ml[(base + s) * 2]);
+    const float m_use = mx == -INFINITY ? 0.f : mx;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float acc = 0.f, sum = 0.f;
+        for (int s = 0; s < n_splits; ++s) {
+            const float c = exp2f(part_ml[(base + s) * 2] - m_use);
+            acc += c * part_o[(base + s) * D + d];
+            sum += c * part_ml[(base + s) * 2 + 1];
+        }
+        out[(size_t)seq * out_stride + (size_t)head * D + d] = __float2bfloat16_rn(sum > 0.f ? acc / sum : 0.f);
+    }
+}
+
+constexpr int kPrefillSmem = (64 + 4 * kPage) * kStride * (int)sizeof(bf16);
+constexpr int kDecodeTiles = (16 + 4 * kPage) * kStride * (int)sizeof(bf16);
+constexpr int kDecodeReduce = 16 * kStride * (int)sizeof(bf16) + (4 * 16 * D + 4 * 16 * 2) * (int)sizeof(float);
+constexpr int kDecodeSmem = kDecodeTiles > kDecodeReduce ? kDecodeTiles : kDecodeReduce;
+
+}  // namespace dfi
+
+using namespace dfi;
+
+DFI_EXPORT int dfi_attention_head_dim() { return D; }
+
+// Scratch the decode kernel needs for `n_splits` > 1: floats for part_o, then for part_ml.
+DFI_EXPORT long long dfi_attention_decode_scratch_floats(int n_seqs, int n_q, int n_splits) {
+    return (long long)n_seqs * n_q * n_splits * (D + 2);
+}
+
+DFI_EXPORT int dfi_attention_prefill(const void* q, int q_stride, void* out, int out_stride, const void* k_cache,
+                                     const void* v_cache, const int* block_table, int table_width,
+                                     const int* cu_rows, const int* seq_start, int n_seqs, int max_q_len, int n_q,
+                                     int n_kv, int page_size, int ring_tokens, int window, float scale,
+                                     void* stream) {
+    if (n_seqs <= 0 || max_q_len <= 0) return DFI_OK;
+    if (page_size != kPage || n_q <= 0 || n_kv <= 0 || n_q % n_kv || ring_tokens % kPage) return DFI_ERR_SHAPE;
+    if (q_stride % 8 || !aligned16(q) || !aligned16(k_cache) || !aligned16(v_cache)) return DFI_ERR_ALIGN;
+    if (n_q > 65535 || n_seqs > 65535) return DFI_ERR_LIMIT;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(attention_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrefillSmem) != cudaSuccess)
+            return DFI_ERR_LAUNCH;
+        configured = true;
+    }
+    dim3 grid((max_q_len + 63) / 64, n_q, n_seqs);
+    attention_prefill_kernel<<<grid, kThreads, kPrefillSmem, (cudaStream_t)stream>>>(
+        (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_cache, (const bf16*)v_cache, block_table,
+        table_width, cu_rows, seq_start, n_q, n_kv, ring_tokens, window, scale * kLog2e);
+    DFI_CHECK_LAUNCH();
+    return DFI_OK;
+}
+
+// One query row per sequence (row i belongs to sequence i).  `scratch` holds at least
+// dfi_attention_decode_scratch_floats(...) floats when n_splits > 1.
+DFI_EXPORT int dfi_attention_decode(const void* q, int q_stride, void* out, int out_stride, const void* k_cache,
+                                    const void* v_cache, const int* block_table, int table_width,
+                                    const int* seq_start, int n_seqs, int n_q, int n_kv, int page_size,
+                                    int ring_tokens, int window, float scale, int n_splits, float* scratch,
+                                    void* stream) {
+    if (n_seqs <= 0) return DFI_OK;
+    if (page_size != kPage || n_q <= 0 || n_kv <= 0 || n_q % n_kv || n_q / n_kv > 16 || ring_tokens % kPage)
+        return DFI_ERR_SHAPE;
+    if (n_splits < 1 || n_splits > 65535 || (n_splits > 1 && scratch == nullptr)) return DFI_ERR_SHAPE;
+    if (q_stride % 8 || !aligned16(q) || !aligned16(k_cache) || !aligned16(v_cache)) return DFI_ERR_ALIGN;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecodeSmem) != cudaSuccess)
+            return DFI_ERR_LAUNCH;
+        configured = true;
+    }
+    float* part_o = scratch;
+    float* part_ml = scratch == nullptr ? nullptr : scratch + (size_t)n_seqs * n_q * n_splits * D;
+    dim3 grid(n_seqs * n_kv, n_splits);
+    attention_decode_kernel<<<grid, kThreads, kDecodeSmem, (cudaStream_t)stream>>>(
+        (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_cache, (const bf16*)v_cache, block_table,
+        table_width, seq_start, n_q, n_kv, ring_tokens, window, scale * kLog2e, n_splits, part_o, part_ml);
+    DFI_CHECK_LAUNCH();
+    if (n_splits > 1) {
+        attention_merge_kernel<<<n_seqs * n_q, D < 32 ? 32 : D, 0, (cudaStream_t)stream>>>(
+            part_o, part_ml, (bf16*)out, out_stride, n_q, n_splits);
+        DFI_CHECK_LAUNCH();
+    }
+    return DFI_OK;
+}

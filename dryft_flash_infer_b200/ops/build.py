@@ -31,6 +31,10 @@ COMMON_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcomp
 
 #: sources of the core library; further modules (built per head size) name their own
 CORE_SOURCES = ["elementwise.cu", "attention_generic.cu", "sampling.cu"]
+#: the tensor-core attention, built once per head size (-DDFI_HEAD_DIM=...)
+ATTENTION_SOURCES = ["attention_mma.cu"]
+#: head sizes compiled ahead by ``all_libraries`` (others compile at first use)
+PREBUILT_HEAD_DIMS = (16, 32, 128)
 
 
 class BuildError(RuntimeError):
@@ -130,7 +134,10 @@ def compile_library(name: str, sources: list[str], defines: list[str] | None = N
 
 def all_libraries() -> list[tuple[str, list[str], list[str]]]:
     """Every library the package can load: ``(name, sources, defines)``."""
-    return [("dfi_core", CORE_SOURCES, [])]
+    out = [("dfi_core", CORE_SOURCES, [])]
+    for dim in PREBUILT_HEAD_DIMS:
+        out.append((f"dfi_attention_d{dim}", ATTENTION_SOURCES, [f"-DDFI_HEAD_DIM={dim}"]))
+    return out
 
 
 _LOADED: dict[str, ctypes.CDLL] = {}

@@ -11,7 +11,7 @@ import ctypes
 
 import torch
 
-from .build import CORE_SOURCES, load_library
+from .build import ATTENTION_SOURCES, CORE_SOURCES, load_library
 
 _ERRORS = {
     1: "unsupported dtype (kernels take float32 and bfloat16)",
@@ -165,9 +165,64 @@ def attention_generic(q: torch.Tensor, cache, row_seq: torch.Tensor, row_pos: to
     return out
 
 
+_SM_TARGET_CTAS = 4 * 148   # a few CTAs for each of the 148 SMs
+
+
+def _attention_library(head_dim: int):
+    return load_library(f"dfi_attention_d{head_dim}", ATTENTION_SOURCES, [f"-DDFI_HEAD_DIM={head_dim}"])
+
+
+def decode_splits(n_seqs: int, n_kv: int, max_kv_len: int) -> int:
+    """How many parts the key range of a decode step is cut into: enough CTAs to fill the
+    GPU, but at least two pages of keys per part."""
+    tiles = max(1, -(-max_kv_len // 64))
+    return max(1, min(_SM_TARGET_CTAS // max(1, n_seqs * n_kv), tiles // 2))
+
+
+def attention_prefill(q, cache, ctx, n_q: int, n_kv: int, head_dim: int, scale: float, window: int = 0):
+    """Tensor-core flash attention (bfloat16) for any number of query rows per sequence."""
+    _need_cuda(q, cache.k)
+    assert q.dtype == torch.bfloat16 and q.stride(1) == 1 and q.shape[1] == n_q * head_dim
+    out = torch.empty((q.shape[0], n_q * head_dim), dtype=q.dtype, device=q.device)
+    _check(_attention_library(head_dim).dfi_attention_prefill(
+        _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cache.k), _ptr(cache.v), _ptr(cache.block_table),
+        cache.block_table.shape[1], _ptr(ctx.cu_rows), _ptr(ctx.seq_start), ctx.n_seqs, ctx.max_q_len, n_q, n_kv,
+        cache.page_size, cache.ring_tokens, window, _f(scale), _stream()), "attention_prefill",
+        f"head_dim {head_dim}, {n_q}/{n_kv} heads")
+    return out
+
+
+def attention_decode(q, cache, ctx, n_q: int, n_kv: int, head_dim: int, scale: float, window: int = 0,
+                     n_splits: int | None = None):
+    """Split-KV tensor-core attention (bfloat16) for steps with one query row per sequence."""
+    _need_cuda(q, cache.k)
+    assert q.dtype == torch.bfloat16 and q.stride(1) == 1 and q.shape == (ctx.n_seqs, n_q * head_dim)
+    if n_splits is None:
+        n_splits = getattr(ctx, "decode_splits", None) or decode_splits(ctx.n_seqs, n_kv, ctx.max_kv_len)
+    lib = _attention_library(head_dim)
+    out = torch.empty((q.shape[0], n_q * head_dim), dtype=q.dtype, device=q.device)
+    scratch = None
+    if n_splits > 1:
+        lib.dfi_attention_decode_scratch_floats.restype = ctypes.c_longlong
+        scratch = torch.empty(lib.dfi_attention_decode_scratch_floats(ctx.n_seqs, n_q, n_splits),
+                              dtype=torch.float32, device=q.device)
+    _check(lib.dfi_attention_decode(
+        _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cache.k), _ptr(cache.v), _ptr(cache.block_table),
+        cache.block_table.shape[1], _ptr(ctx.seq_start), ctx.n_seqs, n_q, n_kv, cache.page_size, cache.ring_tokens,
+        window, _f(scale), n_splits, _ptr(scratch), _stream()), "attention_decode",
+        f"head_dim {head_dim}, {n_q}/{n_kv} heads")
+    return out
+
+
 def attention(q: torch.Tensor, cache, ctx, n_q: int, n_kv: int, head_dim: int, scale: float,
               window: int = 0) -> torch.Tensor:
-    """Attention of a step's query rows over the cache, by the kernel that fits the shapes."""
+    """Attention of a step's query rows over the cache, by the kernel that fits: the
+    tensor-core kernels for bfloat16 and head sizes in steps of 16 up to 128, the plain
+    kernel for float32 and for head sizes up to 256."""
+    if q.dtype == torch.bfloat16 and head_dim % 16 == 0 and head_dim <= 128:
+        if ctx.all_decode and n_q // n_kv <= 16:
+            return attention_decode(q, cache, ctx, n_q, n_kv, head_dim, scale, window)
+        return attention_prefill(q, cache, ctx, n_q, n_kv, head_dim, scale, window)
     return attention_generic(q, cache, ctx.row_seq, ctx.row_pos, n_q, n_kv, head_dim, scale, window)
 
 

@@ -236,3 +236,61 @@ def test_sizes_a_kernel_does_not_take_are_refused():
         kernels.rms_norm(torch.zeros(2, 8), torch.ones(8), 1e-6)
     with pytest.raises(KernelError, match="dtype"):
         kernels.rms_norm(torch.zeros(2, 8, dtype=torch.float16).cuda(), torch.ones(8).cuda(), 1e-6)
+
+
+def step_like(lengths, new):
+    """The few per-step numbers the tensor-core attention reads from a StepContext."""
+    from types import SimpleNamespace
+
+    cu = torch.tensor([0] + list(torch.tensor(new).cumsum(0)), dtype=torch.int32)
+    return SimpleNamespace(cu_rows=cu.cuda(), seq_start=torch.tensor([l - n for l, n in zip(lengths, new)],
+                                                                   dtype=torch.int32).cuda(),
+                           n_seqs=len(lengths), max_q_len=max(new), max_kv_len=max(lengths),
+                           all_decode=all(n == 1 for n in new))
+
+
+@pytest.mark.parametrize("n_q, n_kv, dim", [(6, 3, 48), (4, 4, 16), (8, 2, 128), (3, 1, 64), (16, 1, 32), (5, 5, 112)])
+def test_attention_tensor_core_prefill(n_q, n_kv, dim):
+    from dryft_flash_infer_b200.ops import kernels
+
+    dtype = torch.bfloat16
+    for lengths, new in (([70, 3, 130], [70, 3, 130]), ([70, 3, 200], [10, 3, 67]), ([257, 64, 1], [1, 1, 1]),
+                         ([300], [300])):
+        q, cache, row_seq, row_pos, scale, want = attention_case(dtype, n_q, n_kv, dim, lengths, new, seed=dim)
+        got = kernels.attention_prefill(q, cache, step_like(lengths, new), n_q, n_kv, dim, scale)
+        assert torch.isfinite(got).all()
+        assert torch.allclose(got.float().cpu(), want, atol=tol(dtype, 2), rtol=tol(dtype)), (lengths, new)
+
+
+@pytest.mark.parametrize("n_q, n_kv, dim", [(6, 3, 48), (4, 4, 16), (8, 2, 128), (32, 8, 128), (16, 1, 32), (3, 1, 64)])
+def test_attention_tensor_core_decode_with_splits(n_q, n_kv, dim):
+    from dryft_flash_infer_b200.ops import kernels
+
+    dtype = torch.bfloat16
+    lengths, new = [257, 64, 1, 1000, 65], [1, 1, 1, 1, 1]
+    q, cache, row_seq, row_pos, scale, want = attention_case(dtype, n_q, n_kv, dim, lengths, new, seed=dim, sharp=5)
+    ctx = step_like(lengths, new)
+    for splits in (None, 1, 2, 3, 16, 40):             # 40 parts of 16 pages: most are empty
+        got = kernels.attention_decode(q, cache, ctx, n_q, n_kv, dim, scale, n_splits=splits)
+        assert torch.isfinite(got).all()
+        assert torch.allclose(got.float().cpu(), want, atol=tol(dtype, 2), rtol=tol(dtype)), splits
+
+
+def test_attention_tensor_core_window_edges():
+    from dryft_flash_infer_b200.ops import kernels
+
+    dtype = torch.bfloat16
+    for window, ring in ((100, 192), (64, 128), (1, 64), (130, 320)):
+        lengths, new = [500, 131, 40], [3, 2, 40]
+        q, cache, row_seq, row_pos, scale, want = attention_case(dtype, 4, 2, 32, lengths, new, window=window,
+                                                                 ring_tokens=ring, seed=window)
+        got = kernels.attention_prefill(q, cache, step_like(lengths, new), 4, 2, 32, scale, window)
+        assert torch.isfinite(got).all()
+        assert torch.allclose(got.float().cpu(), want, atol=tol(dtype, 2), rtol=tol(dtype)), window
+        lengths, new = [500, 131, 40, 1], [1, 1, 1, 1]
+        q, cache, row_seq, row_pos, scale, want = attention_case(dtype, 4, 2, 32, lengths, new, window=window,
+                                                                 ring_tokens=ring, seed=window + 1)
+        for splits in (1, 3):
+            got = kernels.attention_decode(q, cache, step_like(lengths, new), 4, 2, 32, scale, window, n_splits=splits)
+            assert torch.isfinite(got).all()
+            assert torch.allclose(got.float().cpu(), want, atol=tol(dtype, 2), rtol=tol(dtype)), (window, splits)
