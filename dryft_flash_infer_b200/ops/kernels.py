@@ -250,14 +250,77 @@ def sample_temperature(logits: torch.Tensor, uniforms: torch.Tensor, temperature
     return out
 
 
+_GEMM_SCRATCH: dict = {}
+_GEMM_TARGET_CTAS = 8 * 148
+SKINNY_MAX_ROWS = 64
+
+
+def _gemm_scratch(device, partial_floats: int, counters: int):
+    """The split-K scratch of a device: partial sums (grown on demand) and zeroed counters."""
+    held = _GEMM_SCRATCH.get(device)
+    if held is None or held[0].numel() < partial_floats or held[1].numel() < counters:
+        partials = torch.empty(max(partial_floats, 1 << 20, held[0].numel() if held else 0), dtype=torch.float32,
+                               device=device)
+        count = torch.zeros(max(counters, 8192, held[1].numel() if held else 0), dtype=torch.int32, device=device)
+        _GEMM_SCRATCH[device] = held = (partials, count)
+    return held
+
+
+def skinny_splits(m: int, n_blocks: int, k: int) -> int:
+    """Slices of K that run in parallel: enough CTAs to fill the GPU, slices of at least 256,
+    and partial sums that stay small beside the weights."""
+    m_pad = -(-m // 8) * 8
+    want = max(1, min(round(_GEMM_TARGET_CTAS / n_blocks), k // 256, max(1, k // (8 * m_pad))))
+    per = -(-(-(-k // want)) // 32) * 32
+    return -(-k // per)
+
+
+def skinny_linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None,
+                  swiglu: bool = False, n_splits: int | None = None) -> torch.Tensor:
+    """``x @ weight.T`` (or, with ``swiglu``, ``silu(x @ gate.T) * (x @ up.T)`` for ``weight = [gate; up]``)
+    for at most 64 rows of bfloat16 ``x``: the decode step's matrix product, bound by reading ``weight`` once."""
+    _need_cuda(x, weight)
+    m, k = x.shape
+    assert x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and weight.shape[1] == k
+    assert x.is_contiguous() and weight.is_contiguous()
+    if m > SKINNY_MAX_ROWS or k % 8:
+        raise KernelError(f"skinny_linear takes at most {SKINNY_MAX_ROWS} rows and K in steps of 8, got {m} x {k}")
+    n = weight.shape[0] // 2 if swiglu else weight.shape[0]
+    out_dtype = out_dtype or x.dtype
+    lib = _core()
+    lib.dfi_skinny_gemm_partial_floats.restype = ctypes.c_longlong
+    n_blocks = lib.dfi_skinny_gemm_counters(n, int(swiglu))
+    if n_splits is None:
+        n_splits = skinny_splits(m, n_blocks, k)
+    partials, counters = _gemm_scratch(x.device, lib.dfi_skinny_gemm_partial_floats(m, n, int(swiglu), n_splits), n_blocks)
+    out = torch.empty((m, n), dtype=out_dtype, device=x.device)
+    _check(lib.dfi_skinny_gemm(_ptr(x), _ptr(weight), _ptr(out), m, n, k, int(swiglu), n_splits, _ptr(partials),
+                               _ptr(counters), _DTYPE_CODE[out_dtype], _stream()), "skinny_linear",
+           f"{m} x {k} by {weight.shape[0]} x {k}")
+    return out
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
     """``x @ weight.T`` for ``weight [out, in]`` as stored in the model file.
 
-    float32 operands take the library's float32 product with no reduced-precision mode.
-    ``out_dtype=torch.float32`` keeps bfloat16 products unrounded (used for logits).
+    bfloat16 with at most 64 rows (decoding) runs the hand-written skinny kernel; larger
+    products go to the library's GEMM, as the reference's prefill does
+    (engine/engine.py:881-884).  float32 operands take the library's float32 product with
+    no reduced-precision mode.  ``out_dtype=torch.float32`` keeps bfloat16 products
+    unrounded (used for logits).
     """
     _need_cuda(x, weight)
     assert x.dim() == 2 and weight.dim() == 2 and x.shape[1] == weight.shape[1] and x.dtype == weight.dtype
+    if x.dtype == torch.bfloat16 and x.shape[0] <= SKINNY_MAX_ROWS and x.shape[1] % 8 == 0 and x.is_contiguous():
+        return skinny_linear(x, weight, out_dtype)
     if out_dtype is not None and out_dtype != x.dtype:
         return torch.mm(x, weight.t(), out_dtype=out_dtype)
     return torch.mm(x, weight.t())
+
+
+def linear_swiglu(x: torch.Tensor, gate_up: torch.Tensor) -> torch.Tensor:
+    """``silu(x @ gate.T) * (x @ up.T)`` for the fused matrix ``gate_up = [gate; up]``: one kernel
+    when decoding in bfloat16, else the product followed by the SwiGLU kernel."""
+    if x.dtype == torch.bfloat16 and x.shape[0] <= SKINNY_MAX_ROWS and x.shape[1] % 8 == 0 and x.is_contiguous():
+        return skinny_linear(x, gate_up, swiglu=True)
+    return swiglu(linear(x, gate_up))

@@ -28,7 +28,7 @@ class SwiGLU(FeedForward):
         }
 
     def forward(self, x, ctx):
-        inner = kernels.swiglu(kernels.linear(x, self.gate_up))
+        inner = kernels.linear_swiglu(x, self.gate_up)
         return kernels.linear(inner, self.down)
 
 

@@ -294,3 +294,42 @@ def test_attention_tensor_core_window_edges():
             got = kernels.attention_decode(q, cache, step_like(lengths, new), 4, 2, 32, scale, window, n_splits=splits)
             assert torch.isfinite(got).all()
             assert torch.allclose(got.float().cpu(), want, atol=tol(dtype, 2), rtol=tol(dtype)), (window, splits)
+
+
+@pytest.mark.parametrize("m", [1, 3, 8, 9, 17, 33, 64])
+@pytest.mark.parametrize("n, k", [(64, 96), (100, 200), (2560, 4096), (320, 2560), (37, 72)])
+def test_skinny_gemm(m, n, k):
+    from dryft_flash_infer_b200.ops import kernels
+
+    g = torch.Generator().manual_seed(m * n + k)
+    x = (torch.randn(m, k, generator=g)).to(torch.bfloat16)
+    w = (torch.randn(n, k, generator=g) * 0.05).to(torch.bfloat16)
+    want = x.float() @ w.float().T
+    for splits in (None, 1, 2, 3):
+        if splits and splits > 1 and -(-k // (-(-(-(-k // splits)) // 32) * 32)) != splits:
+            continue                                   # this many slices would leave one empty
+        got = kernels.skinny_linear(x.cuda(), w.cuda(), torch.float32, n_splits=splits)
+        assert torch.allclose(got.cpu(), want, atol=2e-3, rtol=1e-3), (splits, float((got.cpu() - want).abs().max()))
+        again = kernels.skinny_linear(x.cuda(), w.cuda(), torch.float32, n_splits=splits)
+        assert torch.equal(again, got)                 # counters were left ready, and the order of sums is fixed
+    got = kernels.skinny_linear(x.cuda(), w.cuda())
+    assert got.dtype == torch.bfloat16 and torch.allclose(got.float().cpu(), want, atol=2e-2, rtol=1e-2)
+
+
+@pytest.mark.parametrize("m", [1, 8, 20, 64])
+@pytest.mark.parametrize("inter, k", [(200, 96), (128, 64), (9728, 2560), (33, 40)])
+def test_skinny_gemm_with_swiglu(m, inter, k):
+    from dryft_flash_infer_b200.ops import kernels
+
+    g = torch.Generator().manual_seed(m + inter)
+    x = (torch.randn(m, k, generator=g)).to(torch.bfloat16)
+    w = (torch.randn(2 * inter, k, generator=g) * 0.1).to(torch.bfloat16)
+    gu = x.float() @ w.float().T
+    want = gu[:, :inter] / (1 + torch.exp(-gu[:, :inter])) * gu[:, inter:]
+    for splits in (None, 1, 2):
+        if splits == 2 and k < 64:
+            continue
+        got = kernels.skinny_linear(x.cuda(), w.cuda(), torch.float32, swiglu=True, n_splits=splits)
+        assert torch.allclose(got.cpu(), want, atol=3e-3, rtol=2e-3), (splits, float((got.cpu() - want).abs().max()))
+    got = kernels.linear_swiglu(x.cuda(), w.cuda())
+    assert got.dtype == torch.bfloat16 and torch.allclose(got.float().cpu(), want, atol=3e-2, rtol=1e-2)
