@@ -1,0 +1,254 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the engine at Qwen3-4B sizes with random weights, on one GPU.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--layers L]
+
+Prints one JSON line.  ``value`` is decoded tokens per second at batch 8 with every
+sequence at the benchmark context length (the last timed step ends there), timed on the
+device over K decode steps after W warm-up steps.  ``e2e`` is the same through
+``Engine.generate`` with host token lists in and out.  ``prefill`` is one prompt of 2,048
+tokens; ``points`` are decode at batch 1 and 64; ``roofline`` compares the bytes a decode
+step has to read (every weight once, the live requests' cache) with the HBM peak.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+# the sizes of the Qwen3-4B configuration named in BASELINE.json (configs[2])
+QWEN3_4B = {
+    "architectures": ["Qwen3ForCausalLM"], "num_hidden_layers": 36, "hidden_size": 2560,
+    "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 9728,
+    "vocab_size": 151936, "rope_theta": 5000000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": True,
+    "max_position_embeddings": 40960, "hidden_act": "silu", "torch_dtype": "bfloat16",
+}
+CONTEXT = 4096
+BATCH = 8
+PREFILL_TOKENS = 2048
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.is_file():
+        try:
+            raw = json.loads(path.read_text())
+            return {"hbm_gbs": float(raw["hbm_gbs"]), "bf16_tflops": float(raw["bf16_tflops"]), "source": "measured"}
+        except (KeyError, ValueError):
+            pass
+    return dict(FALLBACK_PEAKS, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.lines: list[str] = []
+        self.proc = None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self) -> dict:
+        mhz, top, reasons = [], 0, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7 or not parts[0].isdigit():
+                continue
+            mhz.append(int(parts[0]))
+            top = max(top, int(parts[1]))
+            for name, value in zip(names, parts[3:7]):
+                if value.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": int(statistics.median(mhz)) if mhz else None, "sm_max_mhz": top or None,
+                "reasons": sorted(reasons), "samples": len(mhz)}
+
+
+def model_numbers(cfg: dict, layers: int) -> dict:
+    h, inter, d = cfg["hidden_size"], cfg["intermediate_size"], cfg["head_dim"]
+    nq, nkv, vocab = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["vocab_size"]
+    per_layer = (nq + 2 * nkv) * d * h + h * nq * d + 3 * inter * h
+    return {"layer_params": per_layer, "weight_bytes": 2 * (layers * per_layer + vocab * h),
+            "kv_bytes_per_token": 2 * 2 * nkv * d * layers, "head_params": vocab * h}
+
+
+def prefill_flops(cfg: dict, layers: int, tokens: int) -> float:
+    nums = model_numbers(cfg, layers)
+    linear = 2.0 * tokens * layers * nums["layer_params"]
+    attention = layers * 4.0 * cfg["num_attention_heads"] * cfg["head_dim"] * tokens * tokens / 2
+    return linear + attention + 2.0 * nums["head_params"]
+
+
+def fill_context(engine, n_seqs: int, length: int):
+    """Opens ``n_seqs`` slots holding ``length`` tokens each of synthetic keys and values."""
+    slots = []
+    for _ in range(n_seqs):
+        slot = engine.open_slot()
+        engine.cache.book.reserve(slot, length)
+        engine.cache.book.advance(slot, length)
+        slots.append(slot)
+    return slots
+
+
+def time_decode(engine, n_seqs: int, context: int, steps: int, warmup: int, sampler=None):
+    import torch
+    from dryft_flash_infer_b200.ops import kernels
+    from dryft_flash_infer_b200.sampling import SamplingParams
+
+    params = SamplingParams()
+    slots = fill_context(engine, n_seqs, context - steps - warmup - 1)
+    tokens = [(17 * i + 3) % engine.config.vocab_size for i in range(n_seqs)]
+    for i in range(warmup):
+        tokens = engine.decode(slots, tokens, list(range(n_seqs)), 1 + i, params)
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches_before = kernels.LAUNCHES
+    start.record()
+    for i in range(steps):
+        tokens = engine.decode(slots, tokens, list(range(n_seqs)), 1 + warmup + i, params)
+    end.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(end) / steps
+    batch = next(iter(b for b in engine.decoder.batches.values() if b.n == n_seqs))
+    per_step = batch.launches_per_step if batch.graph else (kernels.LAUNCHES - launches_before) // max(1, steps)
+    for slot in slots:
+        engine.close_slot(slot)
+    return ms, per_step
+
+
+def main() -> int:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=64)
+    parser.add_argument("--warmup", type=int, default=4)
+    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--layers", type=int, default=QWEN3_4B["num_hidden_layers"],
+                        help="fewer layers than the configuration has (both numbers are reported)")
+    parser.add_argument("--quick", action="store_true", help="skip the batch 1/64 points and the end-to-end run")
+    args = parser.parse_args()
+    if args.gpus != 1:
+        print(f"bench.py measures a single-GPU engine: --gpus {args.gpus} is not supported, run it with --gpus 1")
+        return 2
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference is not an installable package (pip: neither setup.py nor pyproject.toml), "
+                          "and its engine loads a checkpoint through Transformers, which this box does not hold"}))
+        return 0
+    warmup = max(3, args.warmup)
+    steps = max(1, args.steps)
+
+    import torch
+    from dryft_flash_infer_b200 import Engine, StepEntry
+
+    cfg = dict(QWEN3_4B, num_hidden_layers=args.layers)
+    nums = model_numbers(cfg, args.layers)
+    peak = peaks()
+    max_seqs = 64
+    engine = Engine(config=cfg, random_weights=True, seed=0, dtype="bfloat16", max_tokens=max_seqs * CONTEXT,
+                    max_seqs=max_seqs, max_context=CONTEXT)
+    for group in engine.cache.groups:            # synthetic cache content, the same for every run
+        group.k.normal_(0.0, 1.0)
+        group.v.normal_(0.0, 1.0)
+    g = torch.Generator().manual_seed(0)
+
+    # ---- prefill: one prompt of 2,048 tokens, logits at its last place
+    prompt = torch.randint(0, cfg["vocab_size"], (PREFILL_TOKENS,), generator=g).tolist()
+    times = []
+    for i in range(2 + 3):
+        slot = engine.open_slot()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        engine.step([StepEntry(slot, prompt, [PREFILL_TOKENS - 1])])
+        b.record()
+        torch.cuda.synchronize()
+        engine.close_slot(slot)
+        if i >= 2:
+            times.append(a.elapsed_time(b))
+    prefill_ms = statistics.median(times)
+    flops = prefill_flops(cfg, args.layers, PREFILL_TOKENS)
+    prefill = {"value": round(PREFILL_TOKENS / prefill_ms * 1e3, 1), "tokens": PREFILL_TOKENS, "ms": round(prefill_ms, 3),
+               "frac": round(flops / (prefill_ms * 1e-3) / (peak["bf16_tflops"] * 1e12), 4)}
+
+    # ---- decode at batch 8, context 4,096: the headline
+    with ClockSampler() as clocks:
+        ms, launches = time_decode(engine, BATCH, CONTEXT, steps, warmup)
+    value = BATCH / ms * 1e3
+    step_bytes = nums["weight_bytes"] + BATCH * (CONTEXT - steps / 2) * nums["kv_bytes_per_token"]
+    achieved = step_bytes / (ms * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak["hbm_gbs"], "unit": "GB/s",
+                "frac": round(achieved / peak["hbm_gbs"], 4), "peaks": peak["source"]}
+
+    points, e2e = {}, None
+    if not args.quick:
+        for name, n in (("decode_b1", 1), ("decode_b64", 64)):
+            point_ms, _ = time_decode(engine, n, CONTEXT, max(8, steps // 4), warmup)
+            points[name] = round(n / point_ms * 1e3, 1)
+        # ---- end to end through Engine.generate: host token lists in, host token lists out
+        prompts = [torch.randint(0, cfg["vocab_size"], (CONTEXT - steps - 1,), generator=g).tolist() for _ in range(BATCH)]
+        stream = engine.generate(prompts, steps + 1)
+        next(stream)                                   # the prefill and the first token
+        torch.cuda.synchronize()
+        begin = time.perf_counter()
+        produced = sum(1 for _ in stream)
+        torch.cuda.synchronize()
+        elapsed = time.perf_counter() - begin
+        batch = next(iter(b for b in engine.decoder.batches.values() if b.n == BATCH))
+        e2e = {"value": round(BATCH * produced / elapsed, 1), "unit": "tokens/s",
+               "h2d_bytes_per_step": int((batch.host.numel() - batch.first_refreshed) * 4),
+               "d2h_bytes_per_step": BATCH * 4}
+
+    line = {
+        "metric": "decode tokens/s at batch 8 (Qwen3-4B sizes, bf16, random weights)",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: random weights, random token ids, random cache content",
+        "impl": "ours",
+        "config": {"model": "Qwen3-4B sizes", "layers": args.layers, "layers_of_config": QWEN3_4B["num_hidden_layers"],
+                   "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+                   "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
+                   "global_batch": BATCH, "seq_len": CONTEXT, "prefill_tokens": PREFILL_TOKENS, "parallelism": "none",
+                   "cuda_graph": True, "l2": "weights read per step (8 GB) exceed L2 (126 MB)"},
+        "prefill": prefill, "roofline": roofline, "points": points, "e2e": e2e,
+        "gpu_launches": int(launches * steps), "clocks": clocks.summary(),
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

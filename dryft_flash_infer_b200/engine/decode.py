@@ -1,0 +1,166 @@
+"""The decode step on fixed device addresses, captured in a CUDA graph.
+
+A decode step gives every sequence of a batch one token.  Its shapes depend only on
+the number of sequences, so its buffers can stay where they are from step to step: the
+step's numbers (positions, block tables, random numbers for sampling) are written into
+one fixed device buffer before each step, the tokens are left there by the sampler of
+the step before, and the kernels between are replayed as one CUDA graph, as the
+reference replays its decode step (engine/engine.py:835-863, :1031-1049).  The same
+code runs without a graph when graphs are switched off or a mixer cannot be captured.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from ..ops import kernels
+from ..sampling import SamplingParams, uniform_for
+
+
+def _pad4(n: int) -> int:
+    return (n + 3) & ~3
+
+
+class DecodeBatch:
+    """Fixed buffers (and the graph) for decode steps of ``n`` sequences.
+
+    It looks like a ``StepContext`` to the model: the same attributes, all views of one
+    device buffer.  ``run`` refreshes the numbers that change and runs one step; the
+    chosen tokens stay on the device as the next step's input and come back as a list.
+    """
+
+    all_decode = True
+    wants_every_row = True
+    max_q_len = 1
+
+    def __init__(self, model, cache, n: int, table_widths: list[int], max_context: int, temperature: float,
+                 use_graph: bool):
+        self.model, self.cache, self.n = model, cache, n
+        self.n_seqs = self.n_rows = self.n_wanted = n
+        self.table_widths = table_widths
+        self.temperature = temperature
+        self.use_graph = use_graph
+        self.q_lens = [1] * n
+        self.max_kv_len = max_context
+        n_kv = max((g.need.n_kv_heads for g in cache.groups), default=1)
+        self.decode_splits = kernels.decode_splits(n, n_kv, max_context)
+        device = model.device
+        sections = {"tokens": n, "row_seq": n, "row_pos": n, "seq_start": n, "seq_qlen": n, "seq_slot": n,
+                    "cu_rows": n + 1, "wanted_rows": n, "uniforms": n}
+        for g, width in enumerate(table_widths):
+            sections[f"table{g}"] = n * width
+        self.offsets, total = {}, 0
+        for name, size in sections.items():
+            self.offsets[name] = total
+            total += _pad4(size)
+        self.host = torch.zeros(total, dtype=torch.int32).pin_memory()
+        self.host_np = self.host.numpy()
+        self.device_buffer = torch.zeros(total, dtype=torch.int32, device=device)
+        self.tokens_host = torch.zeros(n, dtype=torch.int32).pin_memory()
+
+        def dev(name, size):
+            return self.device_buffer[self.offsets[name]: self.offsets[name] + size]
+
+        self.tokens, self.row_seq, self.row_pos = dev("tokens", n), dev("row_seq", n), dev("row_pos", n)
+        self.seq_start, self.seq_qlen, self.seq_slot = dev("seq_start", n), dev("seq_qlen", n), dev("seq_slot", n)
+        self.cu_rows, self.wanted_rows = dev("cu_rows", n + 1), dev("wanted_rows", n)
+        self.uniforms = dev("uniforms", n).view(torch.float32)
+        self.block_tables = [dev(f"table{g}", n * w).view(n, w) for g, w in enumerate(table_widths)]
+        h = self.host_np
+        h[self.offsets["row_seq"]: self.offsets["row_seq"] + n] = np.arange(n)
+        h[self.offsets["seq_qlen"]: self.offsets["seq_qlen"] + n] = 1
+        h[self.offsets["cu_rows"]: self.offsets["cu_rows"] + n + 1] = np.arange(n + 1)
+        h[self.offsets["wanted_rows"]: self.offsets["wanted_rows"] + n] = np.arange(n)
+        self.first_refreshed = self.offsets["row_seq"]
+        self.graph = None
+        self.slots: list[int] = []
+        self.starts: list[int] = []
+        self.launches_per_step = 0
+        self.last_out: list[int] | None = None
+
+    def _body(self) -> None:
+        logits = self.model.forward(self, self.cache)
+        if self.temperature == 0.0:
+            kernels.argmax(logits, out=self.tokens)
+        else:
+            kernels.sample_temperature(logits, self.uniforms, self.temperature, out=self.tokens)
+
+    def _refresh(self, slots: list[int], uniforms) -> None:
+        n, h, off = self.n, self.host_np, self.offsets
+        self.slots = slots
+        self.starts = starts = [self.cache.length(s) for s in slots]
+        h[off["row_pos"]: off["row_pos"] + n] = starts
+        h[off["seq_start"]: off["seq_start"] + n] = starts
+        h[off["seq_slot"]: off["seq_slot"] + n] = slots
+        if uniforms is not None:
+            h[off["uniforms"]: off["uniforms"] + n] = np.asarray(uniforms, dtype=np.float32).view(np.int32)
+        for g, width in enumerate(self.table_widths):
+            self.cache.fill_block_table(h[off[f"table{g}"]: off[f"table{g}"] + n * width].reshape(n, width),
+                                        slots, g, width)
+        first = self.first_refreshed
+        self.device_buffer[first:].copy_(self.host[first:], non_blocking=True)
+
+    def run(self, slots: list[int], tokens: list[int] | None, uniforms=None) -> list[int]:
+        """One decode step for ``slots``.  ``tokens`` None means: the tokens the last step chose."""
+        book = self.cache.book
+        for slot in slots:
+            book.reserve(slot, 1)
+        if tokens is not None:
+            self.tokens_host[:] = torch.tensor(tokens, dtype=torch.int32)
+            self.tokens.copy_(self.tokens_host, non_blocking=True)
+        self._refresh(slots, uniforms)
+        if not self.use_graph:
+            self._body()
+        elif self.graph is None:
+            # the first step runs as it is (it also sizes every scratch buffer); the second is captured
+            before = kernels.LAUNCHES
+            self._body()
+            self.launches_per_step = kernels.LAUNCHES - before
+            self.graph = False
+        elif self.graph is False:
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                self._body()
+            # capturing does not run the kernels: replay once for this step
+            graph.replay()
+            self.graph = graph
+        else:
+            self.graph.replay()
+        for slot in slots:
+            book.advance(slot, 1)
+        self.tokens_host.copy_(self.tokens, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return self.tokens_host.tolist()
+
+
+class Decoder:
+    """Keeps one ``DecodeBatch`` per batch size and remembers which slots ran last, so that a
+    batch that goes on unchanged feeds its tokens back without a trip through the host."""
+
+    def __init__(self, model, cache, use_graph: bool):
+        self.model, self.cache = model, cache
+        self.use_graph = use_graph and all(b.mixer.graph_safe for b in model.blocks)
+        self.batches: dict[tuple, DecodeBatch] = {}
+        self.last: tuple | None = None
+
+    def decode(self, slots: list[int], tokens: list[int], requests: list[int], step_index: int,
+               params: SamplingParams) -> list[int]:
+        cache = self.cache
+        widths = [max(1, -(-(g.ring_tokens or cache.max_context) // cache.page_size)) for g in cache.groups]
+        key = (len(slots), tuple(widths), params.temperature)
+        batch = self.batches.get(key)
+        if batch is None:
+            if len(self.batches) >= 16:
+                self.batches.pop(next(iter(self.batches)))
+            batch = self.batches[key] = DecodeBatch(self.model, cache, len(slots), widths, cache.max_context,
+                                                    params.temperature, self.use_graph)
+        uniforms = None
+        if params.temperature > 0:
+            uniforms = [uniform_for(params.seed, r, step_index) for r in requests]
+        same = self.last == (key, tuple(slots)) and batch.last_out == list(tokens)
+        out = batch.run(list(slots), None if same else list(tokens), uniforms)
+        batch.last_out = out
+        self.last = (key, tuple(slots))
+        return out

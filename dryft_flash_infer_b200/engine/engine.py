@@ -9,6 +9,7 @@ keyword arguments here.
 
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from pathlib import Path
 from typing import Iterator
@@ -21,6 +22,7 @@ from ..config import ModelConfig, architecture_named, config_from_dict, load_con
 from ..sampling import SamplingParams, select_tokens
 from ..weights import fill_random, load_weights
 from .context import StepEntry
+from .decode import Decoder
 from .generate import Request, generate_all, generate_batch
 from .model import DecoderModel
 from .stepper import Stepper
@@ -46,7 +48,9 @@ class EngineOptions:
     max_seqs: int | None = None
     max_context: int | None = None
     step_tokens: int = 512
-    cuda_graph: bool = True
+    #: capture the decode step in a CUDA graph; the default follows the reference's
+    #: DRYFT_GRAPH=on|off environment variable (engine/engine.py:79)
+    cuda_graph: bool = os.environ.get("DRYFT_GRAPH", "on") == "on"
     device: str = "cuda:0"
 
 
@@ -85,6 +89,7 @@ class Engine:
 
         self.cache: SequenceCache | None = None
         self.stepper: Stepper | None = None
+        self.decoder: Decoder | None = None
         self._positions_ready = 0
         if self.options.max_tokens is not None:
             max_tokens = _round_up(self.options.max_tokens, PAGE_SIZE)
@@ -97,7 +102,7 @@ class Engine:
         if max_context > self.model.spec.max_positions:
             raise ValueError(f"max_context {max_context} exceeds the model's max_position_embeddings "
                              f"{self.model.spec.max_positions}")
-        self.cache = self.stepper = None
+        self.cache = self.stepper = self.decoder = None
         torch.cuda.empty_cache()
         kv_needs, state_needs = self.model.cache_needs()
         self.cache = SequenceCache(kv_needs, state_needs, max_tokens=max_tokens, max_seqs=max_seqs,
@@ -107,6 +112,7 @@ class Engine:
             self.model.prepare(max_context)
             self._positions_ready = max_context
         self.stepper = Stepper(self.model, self.cache, self.options.step_tokens)
+        self.decoder = Decoder(self.model, self.cache, self.options.cuda_graph)
 
     def _ensure_room(self, lengths: list[int]) -> None:
         """Makes the cache fit a batch whose sequences reach ``lengths`` tokens."""
@@ -137,6 +143,13 @@ class Engine:
         if self.stepper is None:
             raise RuntimeError("the engine has no cache yet: build it with max_tokens=..., or call generate")
         return self.stepper.step(entries)
+
+    def decode(self, slots: list[int], tokens: list[int], requests: list[int], step_index: int,
+               params: SamplingParams) -> list[int]:
+        """One decode step for ``slots`` fed ``tokens``; returns the tokens chosen next.  The
+        step runs on fixed buffers (as a CUDA graph unless switched off) and samples on the
+        device, so no logits cross to the host."""
+        return self.decoder.decode(slots, tokens, requests, step_index, params)
 
     def select(self, logits, requests: list[int], step_index: int, params: SamplingParams) -> list[int]:
         return select_tokens(logits, params, requests, step_index).tolist()

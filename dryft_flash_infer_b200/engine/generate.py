@@ -8,6 +8,11 @@ device:
     open_slot() -> slot            close_slot(slot)
     step(entries) -> logits        (entries: list of StepEntry; one logits row per wanted place)
     select(logits, requests, step_index, params) -> list[int]
+    decode(slots, tokens, requests, step_index, params) -> list[int]     (optional)
+
+``decode`` is one step of one token per sequence with the choice of the next token
+folded in; a backend that has it is given the decode steps whole, so that it can keep
+them on the device.
 
 Behaviour follows the reference's ``generate`` (engine/engine.py:1121-1157): one list
 with one token per sequence for every output step, exactly ``max_new_tokens`` of them,
@@ -55,9 +60,14 @@ def generate_batch(backend, requests: list[Request], params: SamplingParams) -> 
         # all prompts in one step; only each prompt's last place is wanted
         entries = [StepEntry(slots[i], list(requests[i].prompt), [len(requests[i].prompt) - 1]) for i in live]
         step_index = 0
+        fused_decode = getattr(backend, "decode", None)
         while live:
-            logits = backend.step(entries)
-            chosen = backend.select(logits, [requests[i].request_id for i in live], step_index, params)
+            ids = [requests[i].request_id for i in live]
+            if step_index > 0 and fused_decode is not None:
+                chosen = fused_decode([slots[i] for i in live], [requests[i].output[-1] for i in live], ids,
+                                      step_index, params)
+            else:
+                chosen = backend.select(backend.step(entries), ids, step_index, params)
             row: list[int | None] = [None] * len(requests)
             still = []
             for i, token in zip(live, chosen):

@@ -53,7 +53,14 @@ def _stream():
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+#: kernels launched through this module since import (a step captured in a CUDA graph counts
+#: once at capture; replays are counted by the caller)
+LAUNCHES = 0
+
+
 def _check(rc: int, what: str, detail: str = "") -> None:
+    global LAUNCHES
+    LAUNCHES += 1
     if rc != 0:
         raise KernelError(f"{what}: {_ERRORS.get(rc, f'error {rc}')}{' (' + detail + ')' if detail else ''}")
 
@@ -226,24 +233,29 @@ def attention(q: torch.Tensor, cache, ctx, n_q: int, n_kv: int, head_dim: int, s
     return attention_generic(q, cache, ctx.row_seq, ctx.row_pos, n_q, n_kv, head_dim, scale, window)
 
 
-def argmax(logits: torch.Tensor) -> torch.Tensor:
+def argmax(logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
     """Index of the largest float32 logit per row (lowest index on ties), int32."""
     _need_cuda(logits)
     assert logits.dtype == torch.float32 and logits.dim() == 2 and logits.stride(1) == 1
-    out = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
+    if out is None:
+        out = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
+    assert out.dtype == torch.int32 and out.numel() == logits.shape[0] and out.is_contiguous()
     _check(_core().dfi_argmax(_ptr(logits), logits.shape[0], logits.stride(0), logits.shape[1], _ptr(out), _stream()),
            "argmax")
     return out
 
 
-def sample_temperature(logits: torch.Tensor, uniforms: torch.Tensor, temperature: float) -> torch.Tensor:
+def sample_temperature(logits: torch.Tensor, uniforms: torch.Tensor, temperature: float,
+                       out: torch.Tensor | None = None) -> torch.Tensor:
     """One draw per row from ``softmax(logits / temperature)`` by inverse CDF at ``uniforms [rows]``."""
     _need_cuda(logits, uniforms)
     assert logits.dtype == torch.float32 and logits.dim() == 2 and logits.stride(1) == 1
     assert uniforms.dtype == torch.float32 and uniforms.numel() == logits.shape[0]
     if not temperature > 0:
         raise KernelError("sample_temperature: temperature must be positive (use argmax for greedy)")
-    out = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
+    if out is None:
+        out = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
+    assert out.dtype == torch.int32 and out.numel() == logits.shape[0] and out.is_contiguous()
     _check(_core().dfi_sample_temperature(_ptr(logits), logits.shape[0], logits.stride(0), logits.shape[1],
                                           _ptr(uniforms), _f(temperature), _ptr(out), _stream()),
            "sample_temperature")

@@ -21,6 +21,7 @@ class Attention(Mixer):
     """
 
     kind = "attention"
+    graph_safe = True
 
     def __init__(self, hidden_size: int, n_heads: int, n_kv_heads: int, head_dim: int, qk_norm: bool = True,
                  qk_norm_eps: float = 1e-6, position: PartSpec | None = None, window: int = 0,

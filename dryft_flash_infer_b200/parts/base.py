@@ -96,6 +96,10 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    #: True if ``forward`` only launches work on the current stream from device-resident
+    #: numbers, so that a decode step through it can be captured in a CUDA graph
+    graph_safe = False
+
     def cache_need(self) -> KVNeed | None:
         return None
 
