@@ -159,6 +159,9 @@ def main() -> int:
     parser.add_argument("--layers", type=int, default=QWEN3_4B["num_hidden_layers"],
                         help="fewer layers than the configuration has (both numbers are reported)")
     parser.add_argument("--quick", action="store_true", help="skip the batch 1/64 points and the end-to-end run")
+    parser.add_argument("--profile", choices=["decode", "prefill"],
+                        help="run only a few plain (graph-less) decode steps or one prefill, for a profiler; prints no JSON")
+    parser.add_argument("--batch", type=int, default=BATCH, help="batch of the --profile decode steps")
     args = parser.parse_args()
     if args.gpus != 1:
         print(f"bench.py measures a single-GPU engine: --gpus {args.gpus} is not supported, run it with --gpus 1")
@@ -184,6 +187,18 @@ def main() -> int:
         group.k.normal_(0.0, 1.0)
         group.v.normal_(0.0, 1.0)
     g = torch.Generator().manual_seed(0)
+    if args.profile == "decode":
+        engine.decoder.use_graph = False
+        ms, launches = time_decode(engine, args.batch, CONTEXT, steps, warmup)
+        print(f"profile run: {steps} plain decode steps at batch {args.batch}, {ms:.3f} ms and {launches} launches per step")
+        return 0
+    if args.profile == "prefill":
+        slot = engine.open_slot()
+        prompt = torch.randint(0, cfg["vocab_size"], (PREFILL_TOKENS,), generator=g).tolist()
+        engine.step([StepEntry(slot, prompt, [PREFILL_TOKENS - 1])])
+        torch.cuda.synchronize()
+        print("profile run: one prefill of", PREFILL_TOKENS, "tokens")
+        return 0
 
     # ---- prefill: one prompt of 2,048 tokens, logits at its last place
     prompt = torch.randint(0, cfg["vocab_size"], (PREFILL_TOKENS,), generator=g).tolist()

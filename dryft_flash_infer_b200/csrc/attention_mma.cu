@@ -424,6 +424,17 @@ DFI_EXPORT long long dfi_attention_decode_scratch_floats(int n_seqs, int n_q, in
     return (long long)n_seqs * n_q * n_splits * (D + 2);
 }
 
+// CTAs of the decode kernel that one SM holds at a time, times the SMs: what one wave can run.
+DFI_EXPORT int dfi_attention_decode_wave() {
+    int device = 0, sms = 0, per_sm = 0;
+    if (cudaGetDevice(&device) != cudaSuccess) return 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return 0;
+    cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecodeSmem);
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_decode_kernel, kThreads, kDecodeSmem) != cudaSuccess)
+        return 0;
+    return sms * per_sm;
+}
+
 DFI_EXPORT int dfi_attention_prefill(const void* q, int q_stride, void* out, int out_stride, const void* k_cache,
                                      const void* v_cache, const int* block_table, int table_width,
                                      const int* cu_rows, const int* seq_start, int n_seqs, int max_q_len, int n_q,

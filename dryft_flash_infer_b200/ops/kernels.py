@@ -172,18 +172,31 @@ def attention_generic(q: torch.Tensor, cache, row_seq: torch.Tensor, row_pos: to
     return out
 
 
-_SM_TARGET_CTAS = 4 * 148   # a few CTAs for each of the 148 SMs
-
-
 def _attention_library(head_dim: int):
     return load_library(f"dfi_attention_d{head_dim}", ATTENTION_SOURCES, [f"-DDFI_HEAD_DIM={head_dim}"])
 
 
-def decode_splits(n_seqs: int, n_kv: int, max_kv_len: int) -> int:
-    """How many parts the key range of a decode step is cut into: enough CTAs to fill the
-    GPU, but at least two pages of keys per part."""
+_DECODE_WAVE: dict[int, int] = {}
+
+
+def decode_splits(n_seqs: int, n_kv: int, max_kv_len: int, head_dim: int = 128) -> int:
+    """How many parts the key range of a decode step is cut into.
+
+    A part is whole pages; the CTAs (sequences x key/value heads x parts) run in waves of
+    as many as the GPU holds at once, and a wave lasts as long as its longest part.  The
+    number of parts is the one with the least ``waves x pages per part``, the smaller on ties.
+    """
+    if head_dim not in _DECODE_WAVE:
+        _DECODE_WAVE[head_dim] = _attention_library(head_dim).dfi_attention_decode_wave() or 4 * 148
+    wave = _DECODE_WAVE[head_dim]
     tiles = max(1, -(-max_kv_len // 64))
-    return max(1, min(_SM_TARGET_CTAS // max(1, n_seqs * n_kv), tiles // 2))
+    groups = max(1, n_seqs * n_kv)
+    best, best_cost = 1, None
+    for parts in range(1, min(tiles, 64) + 1):
+        cost = -(-groups * parts // wave) * -(-tiles // parts) + 0.25 * (parts > 1)   # a merge is not free
+        if best_cost is None or cost < best_cost:
+            best, best_cost = parts, cost
+    return best
 
 
 def attention_prefill(q, cache, ctx, n_q: int, n_kv: int, head_dim: int, scale: float, window: int = 0):
@@ -205,7 +218,7 @@ def attention_decode(q, cache, ctx, n_q: int, n_kv: int, head_dim: int, scale: f
     _need_cuda(q, cache.k)
     assert q.dtype == torch.bfloat16 and q.stride(1) == 1 and q.shape == (ctx.n_seqs, n_q * head_dim)
     if n_splits is None:
-        n_splits = getattr(ctx, "decode_splits", None) or decode_splits(ctx.n_seqs, n_kv, ctx.max_kv_len)
+        n_splits = getattr(ctx, "decode_splits", None) or decode_splits(ctx.n_seqs, n_kv, ctx.max_kv_len, head_dim)
     lib = _attention_library(head_dim)
     out = torch.empty((q.shape[0], n_q * head_dim), dtype=q.dtype, device=q.device)
     scratch = None
@@ -263,34 +276,27 @@ def sample_temperature(logits: torch.Tensor, uniforms: torch.Tensor, temperature
 
 
 _GEMM_SCRATCH: dict = {}
-_GEMM_TARGET_CTAS = 8 * 148
 SKINNY_MAX_ROWS = 64
 
 
-def _gemm_scratch(device, partial_floats: int, counters: int):
-    """The split-K scratch of a device: partial sums (grown on demand) and zeroed counters."""
+def _gemm_scratch(device, n_ctas: int, counters: int):
+    """The stream-K scratch of a device: room for every CTA's partial sums, and zeroed counters."""
+    lib = _core()
+    lib.dfi_skinny_gemm_partial_floats.restype = ctypes.c_longlong
+    floats = lib.dfi_skinny_gemm_partial_floats(n_ctas)
     held = _GEMM_SCRATCH.get(device)
-    if held is None or held[0].numel() < partial_floats or held[1].numel() < counters:
-        partials = torch.empty(max(partial_floats, 1 << 20, held[0].numel() if held else 0), dtype=torch.float32,
-                               device=device)
+    if held is None or held[0].numel() < floats or held[1].numel() < counters:
+        partials = torch.empty(max(floats, held[0].numel() if held else 0), dtype=torch.float32, device=device)
         count = torch.zeros(max(counters, 8192, held[1].numel() if held else 0), dtype=torch.int32, device=device)
         _GEMM_SCRATCH[device] = held = (partials, count)
     return held
 
 
-def skinny_splits(m: int, n_blocks: int, k: int) -> int:
-    """Slices of K that run in parallel: enough CTAs to fill the GPU, slices of at least 256,
-    and partial sums that stay small beside the weights."""
-    m_pad = -(-m // 8) * 8
-    want = max(1, min(round(_GEMM_TARGET_CTAS / n_blocks), k // 256, max(1, k // (8 * m_pad))))
-    per = -(-(-(-k // want)) // 32) * 32
-    return -(-k // per)
-
-
 def skinny_linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None,
-                  swiglu: bool = False, n_splits: int | None = None) -> torch.Tensor:
+                  swiglu: bool = False, n_ctas: int | None = None) -> torch.Tensor:
     """``x @ weight.T`` (or, with ``swiglu``, ``silu(x @ gate.T) * (x @ up.T)`` for ``weight = [gate; up]``)
-    for at most 64 rows of bfloat16 ``x``: the decode step's matrix product, bound by reading ``weight`` once."""
+    for at most 64 rows of bfloat16 ``x``: the decode step's matrix product, bound by reading ``weight`` once.
+    ``n_ctas`` (default: one per SM) is how many persistent CTAs share the work."""
     _need_cuda(x, weight)
     m, k = x.shape
     assert x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and weight.shape[1] == k
@@ -300,13 +306,11 @@ def skinny_linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype 
     n = weight.shape[0] // 2 if swiglu else weight.shape[0]
     out_dtype = out_dtype or x.dtype
     lib = _core()
-    lib.dfi_skinny_gemm_partial_floats.restype = ctypes.c_longlong
-    n_blocks = lib.dfi_skinny_gemm_counters(n, int(swiglu))
-    if n_splits is None:
-        n_splits = skinny_splits(m, n_blocks, k)
-    partials, counters = _gemm_scratch(x.device, lib.dfi_skinny_gemm_partial_floats(m, n, int(swiglu), n_splits), n_blocks)
+    if not n_ctas:
+        n_ctas = lib.dfi_sm_count()
+    partials, counters = _gemm_scratch(x.device, n_ctas, lib.dfi_skinny_gemm_counters(n, int(swiglu)))
     out = torch.empty((m, n), dtype=out_dtype, device=x.device)
-    _check(lib.dfi_skinny_gemm(_ptr(x), _ptr(weight), _ptr(out), m, n, k, int(swiglu), n_splits, _ptr(partials),
+    _check(lib.dfi_skinny_gemm(_ptr(x), _ptr(weight), _ptr(out), m, n, k, int(swiglu), n_ctas, _ptr(partials),
                                _ptr(counters), _DTYPE_CODE[out_dtype], _stream()), "skinny_linear",
            f"{m} x {k} by {weight.shape[0]} x {k}")
     return out
