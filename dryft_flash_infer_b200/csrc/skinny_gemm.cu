@@ -320,3 +320,66 @@ DFI_EXPORT int dfi_skinny_gemm(const void* x, const void* w, void* out, int M, i
     DFI_CHECK_LAUNCH();
     return DFI_OK;
 }
+
+// ------------------------------------------------------------------ the allocation-free entry point
+// See skinny_gemm_static.h for who needs it and what it promises.
+#include "skinny_gemm_static.h"
+
+namespace dfi {
+
+constexpr int kStaticCtas = 160;                                            // at least one per SM of a B200
+constexpr int kStaticPartialFloats = kStaticCtas * 2 * kBlockRows * DFI_STATIC_MAX_ROWS;
+constexpr int kStaticCounters = (DFI_STATIC_MAX_COLS + kBlockRows / 2 - 1) / (kBlockRows / 2);
+constexpr int kMaxDevices = 64;
+
+struct StaticScratch {
+    float partials[kStaticPartialFloats];
+    int counters[kStaticCounters];
+};
+
+// In host code this name is only a handle for cudaGetSymbolAddress; it is not a device pointer.
+static __device__ __align__(256) StaticScratch g_static_scratch;
+
+static StaticScratch* g_static_ptr[kMaxDevices] = {};
+
+}  // namespace dfi
+
+extern "C" __attribute__((visibility("default"))) const char* dfi_error_string(int code) {
+    switch (code) {
+        case DFI_OK: return "ok";
+        case DFI_ERR_DTYPE: return "unsupported dtype code (0 float32, 1 bfloat16)";
+        case DFI_ERR_SHAPE: return "a size the kernel does not take";
+        case DFI_ERR_ALIGN: return "a pointer or stride is not aligned as required";
+        case DFI_ERR_LAUNCH: return "a CUDA call failed";
+        case DFI_ERR_LIMIT: return "a size beyond the stated maximum";
+        default: return "unknown error code";
+    }
+}
+
+extern "C" __attribute__((visibility("default")))
+int dfi_skinny_gemm_static(const void* x, const void* w, void* out, int M, int N, int K, int swiglu, int out_dtype,
+                           void* stream) {
+    if (M <= 0 || N <= 0) return DFI_OK;
+    if (M > DFI_STATIC_MAX_ROWS || N > DFI_STATIC_MAX_COLS) return DFI_ERR_LIMIT;
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess) return DFI_ERR_LAUNCH;
+    if (device < 0 || device >= kMaxDevices) return DFI_ERR_LIMIT;
+    if (g_static_ptr[device] == nullptr) {
+        // set-up, once per device, with that device current
+        StaticScratch* ptr = nullptr;
+        if (cudaGetSymbolAddress((void**)&ptr, g_static_scratch) != cudaSuccess || ptr == nullptr) {
+            cudaGetLastError();
+            return DFI_ERR_LAUNCH;
+        }
+        if (cudaMemsetAsync(ptr->counters, 0, sizeof(ptr->counters), (cudaStream_t)stream) != cudaSuccess) {
+            cudaGetLastError();
+            return DFI_ERR_LAUNCH;
+        }
+        g_static_ptr[device] = ptr;
+    }
+    StaticScratch* scratch = g_static_ptr[device];
+    int n_ctas = dfi_sm_count();
+    if (n_ctas <= 0) return DFI_ERR_LAUNCH;
+    if (n_ctas > kStaticCtas) n_ctas = kStaticCtas;
+    return dfi_skinny_gemm(x, w, out, M, N, K, swiglu, n_ctas, scratch->partials, scratch->counters, out_dtype, stream);
+}
