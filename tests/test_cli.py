@@ -1,0 +1,42 @@
+"""The command line: the part that needs no GPU, and generation through it on one."""
+
+import json
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+
+import plain_model
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def run(*args):
+    return subprocess.run([sys.executable, "-m", "dryft_flash_infer_b200", *args], cwd=ROOT, capture_output=True, text=True)
+
+
+def test_random_model_writes_a_loadable_folder(tmp_path):
+    from dryft_flash_infer_b200.config import load_config
+    from dryft_flash_infer_b200.weights import ModelFiles
+
+    (tmp_path / "c.json").write_text(json.dumps(plain_model.TINY_A))
+    done = run("random-model", "--config", str(tmp_path / "c.json"), "--seed", "3", "--out", str(tmp_path / "m"))
+    assert done.returncode == 0, done.stderr
+    assert load_config(tmp_path / "m").hidden_size == 64
+    assert "model.layers.1.mlp.down_proj.weight" in ModelFiles(tmp_path / "m").names()
+
+
+@pytest.mark.gpu
+def test_generate_prints_one_line_per_step(tmp_path):
+    (tmp_path / "c.json").write_text(json.dumps(plain_model.TINY_B))
+    assert run("random-model", "--config", str(tmp_path / "c.json"), "--out", str(tmp_path / "m")).returncode == 0
+    (tmp_path / "p.json").write_text(json.dumps([[1, 2, 3], [4, 5, 6, 7, 8]]))
+    done = run("generate", "--model", str(tmp_path / "m"), "--prompt-ids", str(tmp_path / "p.json"),
+               "--max-new-tokens", "5", "--temperature", "0.7", "--seed", "2")
+    assert done.returncode == 0, done.stderr
+    lines = [json.loads(l) for l in done.stdout.strip().splitlines()]
+    assert len(lines) == 6 and all(len(row) == 2 for row in lines[:5]) and lines[5]["steps"] == 5
+    again = run("generate", "--model", str(tmp_path / "m"), "--prompt-ids", str(tmp_path / "p.json"),
+                "--max-new-tokens", "5", "--temperature", "0.7", "--seed", "2", "--cuda-graph", "off")
+    assert [json.loads(l) for l in again.stdout.strip().splitlines()][:5] == lines[:5]
