@@ -316,6 +316,36 @@ def skinny_linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype 
     return out
 
 
+TC_NORMAL, TC_SWIGLU, TC_SWAP = 0, 1, 2
+
+
+def tc_linear(x: torch.Tensor, weight: torch.Tensor, mode: int = TC_NORMAL,
+              out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """``x @ weight.T`` on the tcgen05 tensor cores (TMA-fed, accumulator in tensor memory).
+
+    ``TC_NORMAL``: the rows of ``x`` take the 128-row side of the instruction (prefill).
+    ``TC_SWIGLU``: ``weight = [gate; up]``; returns ``silu(x @ gate.T) * (x @ up.T)``.
+    ``TC_SWAP``: the same product as normal with the weights on the 128-row side (up to 256 rows of ``x``).
+    """
+    _need_cuda(x, weight)
+    m, k = x.shape
+    assert x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and weight.shape[1] == k
+    assert x.is_contiguous() and weight.is_contiguous()
+    n = weight.shape[0] // 2 if mode == TC_SWIGLU else weight.shape[0]
+    if k % 8 or (mode != TC_SWAP and n % 8):
+        raise KernelError(f"tc_linear takes K and N in steps of 8, got K={k}, N={n}")
+    out_dtype = out_dtype or x.dtype
+    out = torch.empty((m, n), dtype=out_dtype, device=x.device)
+    _check(_core().dfi_gemm_tcgen05(_ptr(x), _ptr(weight), _ptr(out), m, n, k, mode, _DTYPE_CODE[out_dtype], _stream()),
+           "tc_linear", f"{m} x {k} by {weight.shape[0]} x {k}, mode {mode}")
+    return out
+
+
+def tc_error(reset: bool = True) -> int:
+    """0, or the code of the first bounded wait that ran out in a tcgen05 kernel (synchronises)."""
+    return _core().dfi_gemm_tcgen05_error(int(reset))
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
     """``x @ weight.T`` for ``weight [out, in]`` as stored in the model file.
 

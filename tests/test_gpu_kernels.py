@@ -329,3 +329,48 @@ def test_skinny_gemm_with_swiglu(m, inter, k):
         assert torch.allclose(got.cpu(), want, atol=3e-3, rtol=2e-3), (ctas, float((got.cpu() - want).abs().max()))
     got = kernels.linear_swiglu(x.cuda(), w.cuda())
     assert got.dtype == torch.bfloat16 and torch.allclose(got.float().cpu(), want, atol=3e-2, rtol=1e-2)
+
+
+@pytest.mark.parametrize("m, n, k", [(128, 128, 64), (300, 320, 200), (2048, 256, 2560), (1, 128, 128), (130, 6144, 96)])
+def test_tcgen05_gemm_normal(m, n, k):
+    from dryft_flash_infer_b200.ops import kernels
+
+    g = torch.Generator().manual_seed(m + n + k)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    w = (torch.randn(n, k, generator=g) * 0.05).to(torch.bfloat16)
+    want = x.float() @ w.float().T
+    got = kernels.tc_linear(x.cuda(), w.cuda(), kernels.TC_NORMAL, torch.float32)
+    assert kernels.tc_error() == 0
+    assert torch.allclose(got.cpu(), want, atol=2e-3, rtol=1e-3), float((got.cpu() - want).abs().max())
+    got16 = kernels.tc_linear(x.cuda(), w.cuda())
+    assert torch.allclose(got16.float().cpu(), want, atol=2e-2, rtol=1e-2)
+
+
+@pytest.mark.parametrize("m, inter, k", [(128, 128, 64), (300, 200, 96), (2048, 9728, 2560), (5, 72, 40)])
+def test_tcgen05_gemm_swiglu(m, inter, k):
+    from dryft_flash_infer_b200.ops import kernels
+
+    g = torch.Generator().manual_seed(m + inter + k)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    w = (torch.randn(2 * inter, k, generator=g) * 0.1).to(torch.bfloat16)
+    gu = x.float() @ w.float().T
+    want = gu[:, :inter] / (1 + torch.exp(-gu[:, :inter])) * gu[:, inter:]
+    got = kernels.tc_linear(x.cuda(), w.cuda(), kernels.TC_SWIGLU, torch.float32)
+    assert kernels.tc_error() == 0
+    assert torch.allclose(got.cpu(), want, atol=3e-3, rtol=2e-3), float((got.cpu() - want).abs().max())
+    got16 = kernels.tc_linear(x.cuda(), w.cuda(), kernels.TC_SWIGLU)
+    assert torch.allclose(got16.float().cpu(), want, atol=3e-2, rtol=1e-2)
+
+
+@pytest.mark.parametrize("m", [1, 8, 17, 33, 64, 100, 256])
+@pytest.mark.parametrize("n, k", [(128, 64), (320, 200), (2560, 4096), (100, 96)])
+def test_tcgen05_gemm_swapped(m, n, k):
+    from dryft_flash_infer_b200.ops import kernels
+
+    g = torch.Generator().manual_seed(m * n + k)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    w = (torch.randn(n, k, generator=g) * 0.05).to(torch.bfloat16)
+    want = x.float() @ w.float().T
+    got = kernels.tc_linear(x.cuda(), w.cuda(), kernels.TC_SWAP, torch.float32)
+    assert kernels.tc_error() == 0
+    assert torch.allclose(got.cpu(), want, atol=2e-3, rtol=1e-3), float((got.cpu() - want).abs().max())
