@@ -18,86 +18,9 @@
 //
 // Every wait on an mbarrier is bounded: a wait that runs out records a code in an error word that
 // the host can read (dfi_gemm_tcgen05_error) and the CTA winds down, frees its tensor memory and returns.
-#include <cuda.h>
-
-#include "common.cuh"
+#include "tcgen05.cuh"
 
 namespace dfi {
-
-constexpr int kTileM = 128;
-constexpr int kTileK = 64;                    // 64 bfloat16 = 128 bytes: one swizzle row
-constexpr int kUmmaK = 16;
-constexpr int kTcThreads = 192;
-constexpr int kSmemBudget = 200 * 1024;
-constexpr uint32_t kSpinLimit = 1u << 22;     // tries of mbarrier.try_wait before giving up
-
-enum { MODE_NORMAL = 0, MODE_SWIGLU = 1, MODE_SWAP = 2 };
-
-__device__ int g_tc_error = 0;
-
-__device__ __forceinline__ uint32_t s32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(s32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(s32(bar)), "r"(bytes) : "memory");
-}
-// Waits for the phase with the given parity to complete; false if the bound ran out.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int code) {
-    for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
-        uint32_t done;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}\n"
-            : "=r"(done) : "r"(s32(bar)), "r"(parity) : "memory");
-        if (done) return true;
-    }
-    atomicCAS(&g_tc_error, 0, code);
-    return false;
-}
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
-        ::"r"(s32(dst)), "l"(map), "r"(x), "r"(y), "r"(s32(bar)) : "memory");
-}
-__device__ __forceinline__ uint64_t umma_desc(const void* tile) {
-    // K-major, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart
-    return (uint64_t)((s32(tile) >> 4) & 0x3FFF) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
-}
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
-        ::"r"(tmem_d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(s32(bar)) : "memory");
-}
-__device__ __forceinline__ void tmem_load32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-}
-__device__ __forceinline__ void tmem_load16(uint32_t taddr, uint32_t (&r)[16]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-}
-__device__ __forceinline__ float silu_times(float gate, float up) { return gate / (1.0f + expf(-gate)) * up; }
 
 template <int BN> struct TcConfig {
     static constexpr int kBBytes = BN * kTileK * 2;
@@ -273,17 +196,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
 }
 
-// A [rows, K] bfloat16 matrix (row stride K) as a TMA map with boxes of box_rows x 64, 128-byte swizzle.
-static bool make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
-    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)K * 2};
-    cuuint32_t box[2] = {(cuuint32_t)kTileK, (cuuint32_t)box_rows};
-    cuuint32_t elem[2] = {1, 1};
-    return cuTensorMapEncodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-                                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 template <int BN, int MODE>
 static int launch_tc(const void* a, const void* b, void* out, int rows_a, int rows_b, int K, int ldo, int out_dtype,
                      cudaStream_t st) {
@@ -296,8 +208,8 @@ static int launch_tc(const void* a, const void* b, void* out, int rows_a, int ro
     }
     CUtensorMap map_a, map_b;
     const int b_rows_total = MODE == MODE_SWIGLU ? 2 * rows_b : rows_b;
-    if (!make_map(&map_a, a, rows_a, K, kTileM)) return DFI_ERR_LAUNCH;
-    if (!make_map(&map_b, b, b_rows_total, K, MODE == MODE_SWIGLU ? BN / 2 : BN)) return DFI_ERR_LAUNCH;
+    if (!make_tile_map(&map_a, a, rows_a, K, kTileM)) return DFI_ERR_LAUNCH;
+    if (!make_tile_map(&map_b, b, b_rows_total, K, MODE == MODE_SWIGLU ? BN / 2 : BN)) return DFI_ERR_LAUNCH;
     const int cols_per_tile = MODE == MODE_SWIGLU ? BN / 2 : BN;
     dim3 grid((rows_a + kTileM - 1) / kTileM, (rows_b + cols_per_tile - 1) / cols_per_tile);
     gemm_tcgen05_kernel<BN, MODE><<<grid, kTcThreads, Cfg::kSmemBytes, st>>>(map_a, map_b, out, rows_a, rows_b, K, ldo, out_dtype);

@@ -1,0 +1,336 @@
+// The decode step's matrix product on tcgen05: out[M, N] = x[M, K] . W[N, K]^T for a small batch
+// (M <= 64), bound by reading W once.  W's rows take the 128-row side of tcgen05.mma and the
+// batch the narrow side (N = 16, 32 or 64 of the instruction), so a batch of 8 pads to 16 columns
+// of tensor memory and nothing else.
+//
+// One persistent CTA per SM.  W is cut into units of 128 rows x 64 k; units are numbered row block
+// by row block and dealt to the CTAs in equal contiguous runs (stream-K), so that every SM reads
+// the same number of bytes even when W has few rows.  Inside a CTA: warp 0 feeds a ring of
+// shared-memory stages with TMA, warp 1 issues the MMAs into one of two TMEM accumulators, warps
+// 2-5 drain the other.  A CTA whose run covers a whole row block stores the result itself;
+// otherwise it leaves float32 partial sums in scratch memory and takes a ticket from the row
+// block's counter, and the CTA that draws the last ticket adds the parts in the order of their k
+// ranges (the result does not depend on who finished when), applies the epilogue and resets the
+// counter.  No CTA waits for another CTA; waits inside a CTA (on its own mbarriers) are bounded.
+//
+// SWIGLU variant: W = [gate; up] of 2N rows; a row block is 64 gate rows and the 64 up rows that
+// belong to them, and the epilogue writes silu(gate) * up (engine/kernels/reference.py:74-79;
+// the fusion follows the idea of engine/kernels/cuda_mlp.py:39-125).
+#include "tcgen05.cuh"
+
+namespace dfi {
+
+constexpr int kDecThreads = 192;
+constexpr int kDecSmemBudget = 190 * 1024;
+
+struct StreamShape {
+    int M, N, K;          // N: columns of the output
+    int k_chunks;         // units per row block
+    int row_blocks;
+    int units;
+    int n_ctas;
+};
+
+__device__ __forceinline__ int sk_run_begin(const StreamShape& s, int cta) {
+    return (int)((unsigned)s.units * (unsigned)cta / (unsigned)s.n_ctas);
+}
+__device__ __forceinline__ int sk_cta_of_unit(const StreamShape& s, int u) {
+    int c = (int)((unsigned)u * (unsigned)s.n_ctas / (unsigned)s.units);
+    while (c + 1 < s.n_ctas && sk_run_begin(s, c + 1) <= u) ++c;
+    while (c > 0 && sk_run_begin(s, c) > u) --c;
+    return c;
+}
+__device__ __forceinline__ void epilogue_barrier() { asm volatile("bar.sync 1, 128;\n" ::: "memory"); }
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(s32(bar)) : "memory");
+}
+
+template <int BN> struct DecConfig {
+    static constexpr int kABytes = kTileM * kTileK * 2;
+    static constexpr int kBBytes = BN * kTileK * 2;
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kStagingBytes = BN * kTileM * 4;            // float [BN][128] for the epilogue
+    static constexpr int kStagesRaw = (kDecSmemBudget - 1024 - kStagingBytes) / kStageBytes;
+    static constexpr int kStages = kStagesRaw > 10 ? 10 : kStagesRaw;
+    static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;      // two accumulators
+    static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024;
+    static constexpr int kSlotFloats = BN * kTileM;                  // one part of one row block
+};
+
+template <int BN, bool SWIGLU>
+__global__ void __launch_bounds__(kDecThreads, 1)
+gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                   void* __restrict__ out, StreamShape s, float* __restrict__ partials, int* __restrict__ counters,
+                   int out_dtype) {
+    using Cfg = DecConfig<BN>;
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ __align__(8) uint64_t full_bar[Cfg::kStages];
+    __shared__ __align__(8) uint64_t empty_bar[Cfg::kStages];
+    __shared__ __align__(8) uint64_t acc_full[2];
+    __shared__ __align__(8) uint64_t acc_empty[2];
+    __shared__ uint32_t tmem_base_s;
+    __shared__ int ticket_s;
+
+    unsigned char* ring = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    float* staging = reinterpret_cast<float*>(ring + (size_t)Cfg::kStages * Cfg::kStageBytes);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int cta = blockIdx.x;
+    const int u_begin = sk_run_begin(s, cta), u_end = sk_run_begin(s, cta + 1);
+    const int n_units = u_end - u_begin;
+    const int first_rb = u_begin / s.k_chunks, first_kc = u_begin % s.k_chunks;
+    constexpr int kCols = SWIGLU ? kTileM / 2 : kTileM;      // output columns per row block
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < Cfg::kStages; ++i) {
+            mbar_init(&full_bar[i], 1);
+            mbar_init(&empty_bar[i], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&acc_full[i], 1);
+            mbar_init(&acc_empty[i], 128);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(s32(&tmem_base_s)), "r"(Cfg::kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const uint32_t tmem_base = tmem_base_s;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int rb = first_rb, kc = first_kc;
+            for (int i = 0; i < n_units; ++i) {
+                const int st = i % Cfg::kStages;
+                const uint32_t round = i / Cfg::kStages;
+                if (round > 0 && !mbar_wait(&empty_bar[st], (round - 1) & 1, 1)) break;
+                unsigned char* a_tile = ring + (size_t)st * Cfg::kStageBytes;
+                mbar_expect_tx(&full_bar[st], Cfg::kStageBytes);
+                if (SWIGLU) {
+                    tma_load_2d(a_tile, &map_w, kc * kTileK, rb * 64, &full_bar[st]);
+                    tma_load_2d(a_tile + Cfg::kABytes / 2, &map_w, kc * kTileK, s.N + rb * 64, &full_bar[st]);
+                } else {
+                    tma_load_2d(a_tile, &map_w, kc * kTileK, rb * kTileM, &full_bar[st]);
+                }
+                tma_load_2d(a_tile + Cfg::kABytes, &map_x, kc * kTileK, 0, &full_bar[st]);
+                if (++kc == s.k_chunks) { kc = 0; ++rb; }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
+                                       ((uint32_t)(kTileM >> 4) << 24);
+            int kc = first_kc, segment = 0;
+            bool fresh = true;       // the next MMA starts a row block's sum
+            bool ok = true;
+            for (int i = 0; i < n_units && ok; ++i) {
+                const int buf = segment & 1;
+                if (fresh && segment >= 2) {
+                    // the drain of the accumulator's previous use must be over
+                    ok = mbar_wait(&acc_empty[buf], ((segment >> 1) - 1) & 1, 4);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                }
+                const int st = i % Cfg::kStages;
+                ok = mbar_wait(&full_bar[st], (i / Cfg::kStages) & 1, 2);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                const unsigned char* a_tile = ring + (size_t)st * Cfg::kStageBytes;
+                const uint64_t a_desc = umma_desc(a_tile), b_desc = umma_desc(a_tile + Cfg::kABytes);
+#pragma unroll
+                for (int k = 0; k < kTileK / kUmmaK; ++k)
+                    umma_bf16(tmem_base + buf * BN, a_desc + 2 * k, b_desc + 2 * k, idesc, (!fresh || k > 0) ? 1u : 0u);
+                umma_commit(&empty_bar[st]);
+                fresh = false;
+                if (++kc == s.k_chunks || i == n_units - 1) {
+                    umma_commit(&acc_full[buf]);     // this row block's share of the CTA is summed
+                    kc = 0;
+                    ++segment;
+                    fresh = true;
+                }
+            }
+        }
+    } else {
+        // warps 2..5: thread t of the 128 holds row `t` of the row block (TMEM lane t)
+        const int quarter = warp & 3;
+        const int t = quarter * 32 + lane;
+        int rb = first_rb, seg_first_kc = first_kc, done = 0, segment = 0;
+        bool ok = true;
+        while (done < n_units && ok) {
+            const int seg_units = min(s.k_chunks - seg_first_kc, n_units - done);
+            const bool complete = seg_units == s.k_chunks;
+            const int buf = segment & 1;
+            ok = mbar_wait(&acc_full[buf], (segment >> 1) & 1, 3);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN;
+            // staging[b][t] = D[t][b]: transposed so that what follows reads along the row block
+#pragma unroll
+            for (int c = 0; c < BN; c += 16) {
+                uint32_t d[16];
+                tmem_load16(taddr + c, d);
+#pragma unroll
+                for (int e = 0; e < 16; ++e) staging[(c + e) * kTileM + t] = __uint_as_float(d[e]);
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            mbar_arrive(&acc_empty[buf]);            // the issuer may reuse this accumulator
+            epilogue_barrier();
+
+            bool reduce = complete;
+            int c_first = cta, c_last = cta, first_slot = 0;
+            if (!complete) {
+                float* mine = partials + ((size_t)cta * 2 + (rb == first_rb ? 0 : 1)) * Cfg::kSlotFloats;
+                for (int b = 0; b < s.M; ++b) mine[b * kTileM + t] = staging[b * kTileM + t];
+                __threadfence();
+                epilogue_barrier();
+                const int rb_first_unit = rb * s.k_chunks;
+                c_first = sk_cta_of_unit(s, rb_first_unit);
+                c_last = sk_cta_of_unit(s, rb_first_unit + s.k_chunks - 1);
+                first_slot = sk_run_begin(s, c_first) >= rb_first_unit ? 0 : 1;
+                if (t == 0) ticket_s = atomicAdd(&counters[rb], 1);
+                epilogue_barrier();
+                reduce = ticket_s == c_last - c_first;      // the last of the row block's parts to arrive
+                if (reduce) __threadfence();
+            }
+            if (reduce) {
+                // 128 threads share the block's M x kCols outputs in groups of four columns; the parts'
+                // loads of a group do not depend on each other, so they travel together
+                constexpr int kGroups = kCols / 4;
+                const float* first_part = complete ? staging
+                                                   : partials + ((size_t)c_first * 2 + first_slot) * Cfg::kSlotFloats;
+                const float* next_part = partials + ((size_t)c_first * 2 + 2) * Cfg::kSlotFloats;
+                const int n_more = complete ? 0 : c_last - c_first;
+                for (int item = t; item < s.M * kGroups; item += 128) {
+                    const int b = item / kGroups, c4 = (item % kGroups) * 4;
+                    const int offset = b * kTileM + c4;
+                    float4 v = complete ? *reinterpret_cast<const float4*>(first_part + offset)
+                                        : __ldcg(reinterpret_cast<const float4*>(first_part + offset));
+                    float4 u = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (SWIGLU) u = complete ? *reinterpret_cast<const float4*>(first_part + offset + 64)
+                                             : __ldcg(reinterpret_cast<const float4*>(first_part + offset + 64));
+                    const float* p = next_part + offset;
+#pragma unroll 8
+                    for (int part = 0; part < n_more; ++part, p += 2 * Cfg::kSlotFloats) {
+                        const float4 w4 = __ldcg(reinterpret_cast<const float4*>(p));
+                        v.x += w4.x; v.y += w4.y; v.z += w4.z; v.w += w4.w;
+                        if (SWIGLU) {
+                            const float4 u4 = __ldcg(reinterpret_cast<const float4*>(p + 64));
+                            u.x += u4.x; u.y += u4.y; u.z += u4.z; u.w += u4.w;
+                        }
+                    }
+                    if (SWIGLU) {
+                        v.x = silu_times(v.x, u.x); v.y = silu_times(v.y, u.y);
+                        v.z = silu_times(v.z, u.z); v.w = silu_times(v.w, u.w);
+                    }
+                    const int col = rb * kCols + c4;
+                    const float vals[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        if (col + e < s.N) {
+                            if (out_dtype == DFI_DTYPE_F32) ((float*)out)[(size_t)b * s.N + col + e] = vals[e];
+                            else ((bf16*)out)[(size_t)b * s.N + col + e] = __float2bfloat16_rn(vals[e]);
+                        }
+                    }
+                }
+                if (!complete && t == 0) counters[rb] = 0;   // ready for the next call
+            }
+            epilogue_barrier();          // staging is free for the next row block
+            done += seg_units;
+            seg_first_kc = 0;
+            ++rb;
+            ++segment;
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(Cfg::kTmemCols) : "memory");
+    }
+}
+
+static int g_dec_sm_count = 0;
+
+static int dec_sm_count() {
+    if (g_dec_sm_count == 0) {
+        int device = 0;
+        if (cudaGetDevice(&device) != cudaSuccess) return 0;
+        if (cudaDeviceGetAttribute(&g_dec_sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) g_dec_sm_count = 0;
+    }
+    return g_dec_sm_count;
+}
+
+template <int BN, bool SWIGLU>
+static int launch_decode(const void* x, const void* w, void* out, StreamShape s, float* partials, int* counters,
+                         int out_dtype, cudaStream_t st) {
+    using Cfg = DecConfig<BN>;
+    static_assert(Cfg::kStages >= 2, "the ring needs at least two stages");
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(gemm_decode_kernel<BN, SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess)
+            return DFI_ERR_LAUNCH;
+        configured = true;
+    }
+    CUtensorMap map_w, map_x;
+    if (!make_tile_map(&map_w, w, SWIGLU ? 2 * s.N : s.N, s.K, SWIGLU ? 64 : kTileM)) return DFI_ERR_LAUNCH;
+    if (!make_tile_map(&map_x, x, s.M, s.K, BN)) return DFI_ERR_LAUNCH;
+    gemm_decode_kernel<BN, SWIGLU><<<s.n_ctas, kDecThreads, Cfg::kSmemBytes, st>>>(map_w, map_x, out, s, partials, counters, out_dtype);
+    return DFI_OK;
+}
+
+}  // namespace dfi
+
+using namespace dfi;
+
+DFI_EXPORT int dfi_gemm_decode_error(int reset) {
+    int value = 0;
+    if (cudaMemcpyFromSymbol(&value, g_tc_error, sizeof(int)) != cudaSuccess) return -1;
+    if (reset && value != 0) {
+        const int zero = 0;
+        cudaMemcpyToSymbol(g_tc_error, &zero, sizeof(int));
+    }
+    return value;
+}
+
+// Scratch: two parts of 128 x (padded batch) floats for each CTA; one counter per row block (zero
+// before the first call, left zero by every call).
+DFI_EXPORT long long dfi_gemm_decode_partial_floats(int n_ctas) { return (long long)n_ctas * 2 * kTileM * 64; }
+DFI_EXPORT int dfi_gemm_decode_counters(int N, int swiglu) {
+    const int cols = swiglu ? kTileM / 2 : kTileM;
+    return (N + cols - 1) / cols;
+}
+
+// out[M, N] (row stride N) = x[M, K] . w[N, K]^T, or with swiglu: silu(x . gate^T) * (x . up^T) for
+// w = [gate; up] of 2N rows.  M <= 64; K a multiple of 8.  n_ctas <= 0: one per SM.
+DFI_EXPORT int dfi_gemm_decode(const void* x, const void* w, void* out, int M, int N, int K, int swiglu, int n_ctas,
+                               float* partials, int* counters, int out_dtype, void* stream) {
+    if (M <= 0 || N <= 0) return DFI_OK;
+    if (M > 64 || K <= 0 || K % 8) return DFI_ERR_SHAPE;
+    if (out_dtype != DFI_DTYPE_F32 && out_dtype != DFI_DTYPE_BF16) return DFI_ERR_DTYPE;
+    if (!aligned16(x) || !aligned16(w)) return DFI_ERR_ALIGN;
+    if (counters == nullptr || partials == nullptr) return DFI_ERR_SHAPE;
+    StreamShape s;
+    s.M = M; s.N = N; s.K = K;
+    s.k_chunks = (K + kTileK - 1) / kTileK;
+    s.row_blocks = dfi_gemm_decode_counters(N, swiglu);
+    if ((long long)s.row_blocks * s.k_chunks > (1 << 22)) return DFI_ERR_LIMIT;
+    s.units = s.row_blocks * s.k_chunks;
+    if (n_ctas <= 0) n_ctas = dec_sm_count();
+    if (n_ctas <= 0) return DFI_ERR_LAUNCH;
+    if (n_ctas > 512) n_ctas = 512;
+    s.n_ctas = s.units < n_ctas ? s.units : n_ctas;
+    cudaStream_t st = (cudaStream_t)stream;
+    int rc;
+#define DFI_DEC(BNV)                                                                                       \
+    rc = swiglu ? launch_decode<BNV, true>(x, w, out, s, partials, counters, out_dtype, st)                 \
+                : launch_decode<BNV, false>(x, w, out, s, partials, counters, out_dtype, st)
+    if (M <= 16) DFI_DEC(16);
+    else if (M <= 32) DFI_DEC(32);
+    else DFI_DEC(64);
+#undef DFI_DEC
+    if (rc != DFI_OK) return rc;
+    DFI_CHECK_LAUNCH();
+    return DFI_OK;
+}

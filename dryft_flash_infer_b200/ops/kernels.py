@@ -343,13 +343,48 @@ def tc_linear(x: torch.Tensor, weight: torch.Tensor, mode: int = TC_NORMAL,
 
 def tc_error(reset: bool = True) -> int:
     """0, or the code of the first bounded wait that ran out in a tcgen05 kernel (synchronises)."""
-    return _core().dfi_gemm_tcgen05_error(int(reset))
+    lib = _core()
+    return lib.dfi_gemm_tcgen05_error(int(reset)) or lib.dfi_gemm_decode_error(int(reset))
+
+
+_DECODE_SCRATCH: dict = {}
+
+
+def decode_linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None,
+                  swiglu: bool = False, n_ctas: int | None = None) -> torch.Tensor:
+    """``x @ weight.T`` (with ``swiglu``: ``silu(x @ gate.T) * (x @ up.T)`` for ``weight = [gate; up]``)
+    for at most 64 rows of bfloat16 ``x``: the decode step's product as a persistent stream-K kernel on
+    tcgen05, with TMA loads and the accumulator in tensor memory.  ``n_ctas``: CTAs that share the
+    work (default one per SM)."""
+    _need_cuda(x, weight)
+    m, k = x.shape
+    assert x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and weight.shape[1] == k
+    assert x.is_contiguous() and weight.is_contiguous()
+    if m > SKINNY_MAX_ROWS or k % 8:
+        raise KernelError(f"decode_linear takes at most {SKINNY_MAX_ROWS} rows and K in steps of 8, got {m} x {k}")
+    n = weight.shape[0] // 2 if swiglu else weight.shape[0]
+    out_dtype = out_dtype or x.dtype
+    lib = _core()
+    if not n_ctas:
+        n_ctas = lib.dfi_sm_count()
+    lib.dfi_gemm_decode_partial_floats.restype = ctypes.c_longlong
+    floats, counters = lib.dfi_gemm_decode_partial_floats(n_ctas), lib.dfi_gemm_decode_counters(n, int(swiglu))
+    held = _DECODE_SCRATCH.get(x.device)
+    if held is None or held[0].numel() < floats or held[1].numel() < counters:
+        held = (torch.empty(max(floats, held[0].numel() if held else 0), dtype=torch.float32, device=x.device),
+                torch.zeros(max(counters, 8192, held[1].numel() if held else 0), dtype=torch.int32, device=x.device))
+        _DECODE_SCRATCH[x.device] = held
+    out = torch.empty((m, n), dtype=out_dtype, device=x.device)
+    _check(lib.dfi_gemm_decode(_ptr(x), _ptr(weight), _ptr(out), m, n, k, int(swiglu), n_ctas, _ptr(held[0]),
+                               _ptr(held[1]), _DTYPE_CODE[out_dtype], _stream()), "decode_linear",
+           f"{m} x {k} by {weight.shape[0]} x {k}")
+    return out
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
     """``x @ weight.T`` for ``weight [out, in]`` as stored in the model file.
 
-    bfloat16 with at most 64 rows (decoding) runs the hand-written skinny kernel; larger
+    bfloat16 with at most 64 rows (decoding) runs the hand-written stream-K tcgen05 kernel; larger
     products go to the library's GEMM, as the reference's prefill does
     (engine/engine.py:881-884).  float32 operands take the library's float32 product with
     no reduced-precision mode.  ``out_dtype=torch.float32`` keeps bfloat16 products
@@ -358,7 +393,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None 
     _need_cuda(x, weight)
     assert x.dim() == 2 and weight.dim() == 2 and x.shape[1] == weight.shape[1] and x.dtype == weight.dtype
     if x.dtype == torch.bfloat16 and x.shape[0] <= SKINNY_MAX_ROWS and x.shape[1] % 8 == 0 and x.is_contiguous():
-        return skinny_linear(x, weight, out_dtype)
+        return decode_linear(x, weight, out_dtype)
     if out_dtype is not None and out_dtype != x.dtype:
         return torch.mm(x, weight.t(), out_dtype=out_dtype)
     return torch.mm(x, weight.t())
@@ -368,5 +403,5 @@ def linear_swiglu(x: torch.Tensor, gate_up: torch.Tensor) -> torch.Tensor:
     """``silu(x @ gate.T) * (x @ up.T)`` for the fused matrix ``gate_up = [gate; up]``: one kernel
     when decoding in bfloat16, else the product followed by the SwiGLU kernel."""
     if x.dtype == torch.bfloat16 and x.shape[0] <= SKINNY_MAX_ROWS and x.shape[1] % 8 == 0 and x.is_contiguous():
-        return skinny_linear(x, gate_up, swiglu=True)
+        return decode_linear(x, gate_up, swiglu=True)
     return swiglu(linear(x, gate_up))

@@ -374,3 +374,38 @@ def test_tcgen05_gemm_swapped(m, n, k):
     got = kernels.tc_linear(x.cuda(), w.cuda(), kernels.TC_SWAP, torch.float32)
     assert kernels.tc_error() == 0
     assert torch.allclose(got.cpu(), want, atol=2e-3, rtol=1e-3), float((got.cpu() - want).abs().max())
+
+
+@pytest.mark.parametrize("m", [1, 3, 8, 17, 33, 64])
+@pytest.mark.parametrize("n, k", [(128, 64), (100, 200), (2560, 4096), (320, 2560), (37, 72)])
+def test_tcgen05_decode_gemm(m, n, k):
+    from dryft_flash_infer_b200.ops import kernels
+
+    g = torch.Generator().manual_seed(m * n + k)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    w = (torch.randn(n, k, generator=g) * 0.05).to(torch.bfloat16)
+    want = x.float() @ w.float().T
+    for ctas in (None, 1, 2, 3, 7, 500):             # however the units are dealt out, the sum is the same
+        got = kernels.decode_linear(x.cuda(), w.cuda(), torch.float32, n_ctas=ctas)
+        assert kernels.tc_error() == 0
+        assert torch.allclose(got.cpu(), want, atol=2e-3, rtol=1e-3), (ctas, float((got.cpu() - want).abs().max()))
+        again = kernels.decode_linear(x.cuda(), w.cuda(), torch.float32, n_ctas=ctas)
+        assert torch.equal(again, got)
+    got = kernels.decode_linear(x.cuda(), w.cuda())
+    assert got.dtype == torch.bfloat16 and torch.allclose(got.float().cpu(), want, atol=2e-2, rtol=1e-2)
+
+
+@pytest.mark.parametrize("m", [1, 8, 20, 64])
+@pytest.mark.parametrize("inter, k", [(200, 96), (128, 64), (9728, 2560), (40, 40)])
+def test_tcgen05_decode_gemm_with_swiglu(m, inter, k):
+    from dryft_flash_infer_b200.ops import kernels
+
+    g = torch.Generator().manual_seed(m + inter)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    w = (torch.randn(2 * inter, k, generator=g) * 0.1).to(torch.bfloat16)
+    gu = x.float() @ w.float().T
+    want = gu[:, :inter] / (1 + torch.exp(-gu[:, :inter])) * gu[:, inter:]
+    for ctas in (None, 1, 2, 5, 333):
+        got = kernels.decode_linear(x.cuda(), w.cuda(), torch.float32, swiglu=True, n_ctas=ctas)
+        assert kernels.tc_error() == 0
+        assert torch.allclose(got.cpu(), want, atol=3e-3, rtol=2e-3), (ctas, float((got.cpu() - want).abs().max()))
