@@ -19,6 +19,8 @@ __global__ void attention_generic_kernel(const T* __restrict__ q, int q_row_stri
                                          int table_width, const int* __restrict__ row_seq,
                                          const int* __restrict__ row_pos, int n_q, int n_kv, int D, int page_size,
                                          int ring_tokens, int window, float scale) {
+    pdl_launch_next();
+    pdl_wait();
     __shared__ float q_s[kGenericWarps][kMaxHeadDim];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int head = blockIdx.y * kGenericWarps + warp;
@@ -108,12 +110,12 @@ DFI_EXPORT int dfi_attention_generic(const void* q, int q_row_stride, void* out,
     dim3 grid(rows, (n_q + kGenericWarps - 1) / kGenericWarps);
     if (grid.y > 65535) return DFI_ERR_LIMIT;
     if (dtype == DFI_DTYPE_F32)
-        attention_generic_kernel<float><<<grid, kGenericWarps * 32, 0, st>>>(
+        launch(attention_generic_kernel<float>, grid, kGenericWarps * 32, 0, st, 
             (const float*)q, q_row_stride, (float*)out, out_row_stride, (const float*)k_cache,
             (const float*)v_cache, block_table, table_width, row_seq, row_pos, n_q, n_kv, head_dim, page_size,
             ring_tokens, window, scale);
     else if (dtype == DFI_DTYPE_BF16)
-        attention_generic_kernel<bf16><<<grid, kGenericWarps * 32, 0, st>>>(
+        launch(attention_generic_kernel<bf16>, grid, kGenericWarps * 32, 0, st, 
             (const bf16*)q, q_row_stride, (bf16*)out, out_row_stride, (const bf16*)k_cache,
             (const bf16*)v_cache, block_table, table_width, row_seq, row_pos, n_q, n_kv, head_dim, page_size,
             ring_tokens, window, scale);

@@ -161,6 +161,8 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
                          const int* __restrict__ block_table, int table_width, const int* __restrict__ cu_rows,
                          const int* __restrict__ seq_start, int n_q, int n_kv, int ring_tokens, int window,
                          float scale_log2) {
+    pdl_launch_next();
+    pdl_wait();
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* q_s = reinterpret_cast<bf16*>(smem_raw);   // [64][kStride]
     bf16* k_s = q_s + kPage * kStride;               // [2][64][kStride]
@@ -270,6 +272,8 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
                         const int* __restrict__ block_table, int table_width, const int* __restrict__ seq_start,
                         int n_q, int n_kv, int ring_tokens, int window, float scale_log2, int n_splits,
                         float* __restrict__ part_o, float* __restrict__ part_ml) {
+    pdl_launch_next();
+    pdl_wait();
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* q_s = reinterpret_cast<bf16*>(smem_raw);   // [16][kStride]
     bf16* k_s = q_s + 16 * kStride;                  // [2][64][kStride]
@@ -392,6 +396,8 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
 // grid (sequences * query heads); merges the splits by their log-sum-exp (attention.py:140-177).
 __global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                        bf16* __restrict__ out, int out_stride, int n_q, int n_splits) {
+    pdl_launch_next();
+    pdl_wait();
     const int seq = blockIdx.x / n_q, head = blockIdx.x % n_q;
     const size_t base = (size_t)blockIdx.x * n_splits;
     float mx = -INFINITY;
@@ -416,6 +422,14 @@ constexpr int kDecodeSmem = kDecodeTiles > kDecodeReduce ? kDecodeTiles : kDecod
 }  // namespace dfi
 
 using namespace dfi;
+
+// 1: kernels of this library are launched so that they may overlap the tail of the kernel before
+// them (programmatic dependent launch); 0: plain launches.  Returns the previous setting.
+DFI_EXPORT int dfi_attention_set_pdl(int enabled) {
+    const int before = pdl_enabled();
+    pdl_enabled() = enabled ? 1 : 0;
+    return before;
+}
 
 DFI_EXPORT int dfi_attention_head_dim() { return D; }
 
@@ -451,7 +465,7 @@ DFI_EXPORT int dfi_attention_prefill(const void* q, int q_stride, void* out, int
         configured = true;
     }
     dim3 grid((max_q_len + 63) / 64, n_q, n_seqs);
-    attention_prefill_kernel<<<grid, kThreads, kPrefillSmem, (cudaStream_t)stream>>>(
+    launch(attention_prefill_kernel, grid, kThreads, kPrefillSmem, (cudaStream_t)stream, 
         (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_cache, (const bf16*)v_cache, block_table,
         table_width, cu_rows, seq_start, n_q, n_kv, ring_tokens, window, scale * kLog2e);
     DFI_CHECK_LAUNCH();
@@ -479,12 +493,12 @@ DFI_EXPORT int dfi_attention_decode(const void* q, int q_stride, void* out, int 
     float* part_o = scratch;
     float* part_ml = scratch == nullptr ? nullptr : scratch + (size_t)n_seqs * n_q * n_splits * D;
     dim3 grid(n_seqs * n_kv, n_splits);
-    attention_decode_kernel<<<grid, kThreads, kDecodeSmem, (cudaStream_t)stream>>>(
+    launch(attention_decode_kernel, grid, kThreads, kDecodeSmem, (cudaStream_t)stream, 
         (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_cache, (const bf16*)v_cache, block_table,
         table_width, seq_start, n_q, n_kv, ring_tokens, window, scale * kLog2e, n_splits, part_o, part_ml);
     DFI_CHECK_LAUNCH();
     if (n_splits > 1) {
-        attention_merge_kernel<<<n_seqs * n_q, D < 32 ? 32 : D, 0, (cudaStream_t)stream>>>(
+        launch(attention_merge_kernel, n_seqs * n_q, D < 32 ? 32 : D, 0, (cudaStream_t)stream, 
             part_o, part_ml, (bf16*)out, out_stride, n_q, n_splits);
         DFI_CHECK_LAUNCH();
     }

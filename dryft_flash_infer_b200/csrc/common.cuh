@@ -93,6 +93,35 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
     return warp_sum(total);
 }
 
+// Programmatic dependent launch: a kernel launched through `launch` may begin while the kernel
+// before it on the stream is still running; it must call pdl_wait() before it reads anything an
+// earlier kernel wrote (or writes anything an earlier kernel reads), and may do work that depends
+// on no earlier kernel (set-up, loading weights) before that.  pdl_launch_next() lets the kernel
+// after this one begin.  Both are no-ops in a kernel that was launched the ordinary way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_next() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+
+inline int& pdl_enabled() {
+    static int enabled = 1;
+    return enabled;
+}
+
+template <typename... KernelArgs, typename... Args>
+static inline cudaError_t launch(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                 Args... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attr;
+    config.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...);
+}
+
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 // Place of position `p` in a sequence's storage: itself, or its place in the ring.

@@ -11,6 +11,8 @@ namespace dfi {
 template <typename T, bool VEC>
 __global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids, T* __restrict__ out,
                                  int hidden, int vocab) {
+    pdl_launch_next();
+    pdl_wait();
     const int row = blockIdx.x;
     int id = ids[row];
     id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
@@ -28,6 +30,8 @@ __global__ void embedding_kernel(const T* __restrict__ table, const int* __restr
 // ------------------------------------------------------------------ gather rows
 template <typename T, bool VEC>
 __global__ void gather_rows_kernel(const T* __restrict__ x, const int* __restrict__ rows, T* __restrict__ out, int dim) {
+    pdl_launch_next();
+    pdl_wait();
     const T* src = x + (size_t)rows[blockIdx.x] * dim;
     T* dst = out + (size_t)blockIdx.x * dim;
     if (VEC) {
@@ -45,6 +49,8 @@ __global__ void gather_rows_kernel(const T* __restrict__ x, const int* __restric
 template <typename T, bool VEC, bool ADD>
 __global__ void rmsnorm_kernel(T* __restrict__ residual, const T* __restrict__ delta,
                                const float* __restrict__ weight, T* __restrict__ out, int dim, float eps) {
+    pdl_launch_next();
+    pdl_wait();
     __shared__ float scratch[32];
     T* x = residual + (size_t)blockIdx.x * dim;
     const T* d = ADD ? delta + (size_t)blockIdx.x * dim : nullptr;
@@ -98,6 +104,8 @@ __global__ void rmsnorm_kernel(T* __restrict__ residual, const T* __restrict__ d
 // gate_up [rows, 2*inter] (gate first), out [rows, inter] = silu(gate) * up.
 template <typename T, bool VEC>
 __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter) {
+    pdl_launch_next();
+    pdl_wait();
     const T* g = gate_up + (size_t)blockIdx.y * 2 * inter;
     const T* u = g + inter;
     T* y = out + (size_t)blockIdx.y * inter;
@@ -137,6 +145,8 @@ __global__ void qk_norm_rope_write_kernel(T* __restrict__ qkv, int row_stride, i
                                           T* __restrict__ k_cache, T* __restrict__ v_cache,
                                           const int* __restrict__ block_table, int table_width, int page_size,
                                           int ring_tokens, int write_cache) {
+    pdl_launch_next();
+    pdl_wait();
     const int lane = threadIdx.x & 31;
     const int head = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int total_heads = n_q + 2 * n_kv;
@@ -206,16 +216,16 @@ static int launch_embedding(const void* table, const int* ids, void* out, int ro
                             cudaStream_t st) {
     const bool vec = hidden % Vec16<T>::n == 0 && aligned16(table) && aligned16(out);
     const int threads = 128;
-    if (vec) embedding_kernel<T, true><<<rows, threads, 0, st>>>((const T*)table, ids, (T*)out, hidden, vocab);
-    else embedding_kernel<T, false><<<rows, threads, 0, st>>>((const T*)table, ids, (T*)out, hidden, vocab);
+    if (vec) launch(embedding_kernel<T, true>, rows, threads, 0, st, (const T*)table, ids, (T*)out, hidden, vocab);
+    else launch(embedding_kernel<T, false>, rows, threads, 0, st, (const T*)table, ids, (T*)out, hidden, vocab);
     return DFI_OK;
 }
 
 template <typename T>
 static int launch_gather(const void* x, const int* rows_idx, void* out, int rows, int dim, cudaStream_t st) {
     const bool vec = dim % Vec16<T>::n == 0 && aligned16(x) && aligned16(out);
-    if (vec) gather_rows_kernel<T, true><<<rows, 128, 0, st>>>((const T*)x, rows_idx, (T*)out, dim);
-    else gather_rows_kernel<T, false><<<rows, 128, 0, st>>>((const T*)x, rows_idx, (T*)out, dim);
+    if (vec) launch(gather_rows_kernel<T, true>, rows, 128, 0, st, (const T*)x, rows_idx, (T*)out, dim);
+    else launch(gather_rows_kernel<T, false>, rows, 128, 0, st, (const T*)x, rows_idx, (T*)out, dim);
     return DFI_OK;
 }
 
@@ -228,11 +238,11 @@ static int launch_rmsnorm(void* residual, const void* delta, const float* weight
     const int per = vec ? Vec16<T>::n : 1;
     while (threads < 512 && threads * per < dim) threads <<= 1;
     if (delta != nullptr) {
-        if (vec) rmsnorm_kernel<T, true, true><<<rows, threads, 0, st>>>((T*)residual, (const T*)delta, weight, (T*)out, dim, eps);
-        else rmsnorm_kernel<T, false, true><<<rows, threads, 0, st>>>((T*)residual, (const T*)delta, weight, (T*)out, dim, eps);
+        if (vec) launch(rmsnorm_kernel<T, true, true>, rows, threads, 0, st, (T*)residual, (const T*)delta, weight, (T*)out, dim, eps);
+        else launch(rmsnorm_kernel<T, false, true>, rows, threads, 0, st, (T*)residual, (const T*)delta, weight, (T*)out, dim, eps);
     } else {
-        if (vec) rmsnorm_kernel<T, true, false><<<rows, threads, 0, st>>>((T*)residual, nullptr, weight, (T*)out, dim, eps);
-        else rmsnorm_kernel<T, false, false><<<rows, threads, 0, st>>>((T*)residual, nullptr, weight, (T*)out, dim, eps);
+        if (vec) launch(rmsnorm_kernel<T, true, false>, rows, threads, 0, st, (T*)residual, nullptr, weight, (T*)out, dim, eps);
+        else launch(rmsnorm_kernel<T, false, false>, rows, threads, 0, st, (T*)residual, nullptr, weight, (T*)out, dim, eps);
     }
     return DFI_OK;
 }
@@ -243,14 +253,22 @@ static int launch_swiglu(const void* gate_up, void* out, int rows, int inter, cu
     const int per = vec ? Vec16<T>::n : 1;
     const int threads = 256;
     dim3 grid((inter + threads * per - 1) / (threads * per), rows);
-    if (vec) swiglu_kernel<T, true><<<grid, threads, 0, st>>>((const T*)gate_up, (T*)out, inter);
-    else swiglu_kernel<T, false><<<grid, threads, 0, st>>>((const T*)gate_up, (T*)out, inter);
+    if (vec) launch(swiglu_kernel<T, true>, grid, threads, 0, st, (const T*)gate_up, (T*)out, inter);
+    else launch(swiglu_kernel<T, false>, grid, threads, 0, st, (const T*)gate_up, (T*)out, inter);
     return DFI_OK;
 }
 
 }  // namespace dfi
 
 using namespace dfi;
+
+// 1: kernels of this library are launched so that they may overlap the tail of the kernel before
+// them (programmatic dependent launch); 0: plain launches.  Returns the previous setting.
+DFI_EXPORT int dfi_set_pdl(int enabled) {
+    const int before = pdl_enabled();
+    pdl_enabled() = enabled ? 1 : 0;
+    return before;
+}
 
 DFI_EXPORT int dfi_embedding(const void* table, const int* ids, void* out, int rows, int hidden, int vocab,
                              int dtype, void* stream) {
@@ -315,11 +333,11 @@ DFI_EXPORT int dfi_qk_norm_rope_write(void* qkv, int rows, int row_stride, int n
     dim3 grid(rows, (heads + warps - 1) / warps);
     if (grid.y > 65535) return DFI_ERR_LIMIT;
     if (dtype == DFI_DTYPE_F32)
-        qk_norm_rope_write_kernel<float><<<grid, warps * 32, 0, st>>>(
+        launch(qk_norm_rope_write_kernel<float>, grid, warps * 32, 0, st, 
             (float*)qkv, row_stride, n_q, n_kv, head_dim, q_w, k_w, eps, cos_t, sin_t, row_pos, row_seq,
             (float*)k_cache, (float*)v_cache, block_table, table_width, page_size, ring_tokens, write_cache);
     else if (dtype == DFI_DTYPE_BF16)
-        qk_norm_rope_write_kernel<bf16><<<grid, warps * 32, 0, st>>>(
+        launch(qk_norm_rope_write_kernel<bf16>, grid, warps * 32, 0, st, 
             (bf16*)qkv, row_stride, n_q, n_kv, head_dim, q_w, k_w, eps, cos_t, sin_t, row_pos, row_seq,
             (bf16*)k_cache, (bf16*)v_cache, block_table, table_width, page_size, ring_tokens, write_cache);
     else return DFI_ERR_DTYPE;

@@ -38,6 +38,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     void* __restrict__ out, int rows_a, int rows_b, int K, int ldo, int out_dtype) {
     using Cfg = TcConfig<BN>;
+    pdl_launch_next();
     extern __shared__ unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[Cfg::kStages];
     __shared__ __align__(8) uint64_t empty_bar[Cfg::kStages];
@@ -67,6 +68,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     const uint32_t tmem_base = tmem_base_s;
+    pdl_wait();    // set-up is done; everything below reads what earlier kernels wrote
 
     if (warp == 0) {
         if (lane == 0) {
@@ -212,7 +214,7 @@ static int launch_tc(const void* a, const void* b, void* out, int rows_a, int ro
     if (!make_tile_map(&map_b, b, b_rows_total, K, MODE == MODE_SWIGLU ? BN / 2 : BN)) return DFI_ERR_LAUNCH;
     const int cols_per_tile = MODE == MODE_SWIGLU ? BN / 2 : BN;
     dim3 grid((rows_a + kTileM - 1) / kTileM, (rows_b + cols_per_tile - 1) / cols_per_tile);
-    gemm_tcgen05_kernel<BN, MODE><<<grid, kTcThreads, Cfg::kSmemBytes, st>>>(map_a, map_b, out, rows_a, rows_b, K, ldo, out_dtype);
+    launch(gemm_tcgen05_kernel<BN, MODE>, grid, kTcThreads, Cfg::kSmemBytes, st, map_a, map_b, out, rows_a, rows_b, K, ldo, out_dtype);
     return DFI_OK;
 }
 

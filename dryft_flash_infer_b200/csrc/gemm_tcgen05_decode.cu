@@ -63,6 +63,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                    void* __restrict__ out, StreamShape s, float* __restrict__ partials, int* __restrict__ counters,
                    int out_dtype) {
     using Cfg = DecConfig<BN>;
+    pdl_launch_next();
     extern __shared__ unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[Cfg::kStages];
     __shared__ __align__(8) uint64_t empty_bar[Cfg::kStages];
@@ -102,11 +103,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 
     if (warp == 0) {
         if (lane == 0) {
-            int rb = first_rb, kc = first_kc;
-            for (int i = 0; i < n_units; ++i) {
-                const int st = i % Cfg::kStages;
-                const uint32_t round = i / Cfg::kStages;
-                if (round > 0 && !mbar_wait(&empty_bar[st], (round - 1) & 1, 1)) break;
+            auto load_w = [&](int st, int rb, int kc) {
                 unsigned char* a_tile = ring + (size_t)st * Cfg::kStageBytes;
                 mbar_expect_tx(&full_bar[st], Cfg::kStageBytes);
                 if (SWIGLU) {
@@ -115,7 +112,30 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 } else {
                     tma_load_2d(a_tile, &map_w, kc * kTileK, rb * kTileM, &full_bar[st]);
                 }
-                tma_load_2d(a_tile + Cfg::kABytes, &map_x, kc * kTileK, 0, &full_bar[st]);
+            };
+            auto load_x = [&](int st, int kc) {
+                tma_load_2d(ring + (size_t)st * Cfg::kStageBytes + Cfg::kABytes, &map_x, kc * kTileK, 0, &full_bar[st]);
+            };
+            // The weights depend on no earlier kernel: the first round of the ring is filled with
+            // them before this kernel waits for the one that produces the activations.
+            const int first_round = min(n_units, Cfg::kStages);
+            int rb = first_rb, kc = first_kc;
+            for (int i = 0; i < first_round; ++i) {
+                load_w(i, rb, kc);
+                if (++kc == s.k_chunks) { kc = 0; ++rb; }
+            }
+            pdl_wait();
+            int kc_x = first_kc;
+            for (int i = 0; i < first_round; ++i) {
+                load_x(i, kc_x);
+                if (++kc_x == s.k_chunks) kc_x = 0;
+            }
+            for (int i = first_round; i < n_units; ++i) {
+                const int st = i % Cfg::kStages;
+                const uint32_t round = i / Cfg::kStages;
+                if (!mbar_wait(&empty_bar[st], (round - 1) & 1, 1)) break;
+                load_w(st, rb, kc);
+                load_x(st, kc);
                 if (++kc == s.k_chunks) { kc = 0; ++rb; }
             }
         }
@@ -276,7 +296,7 @@ static int launch_decode(const void* x, const void* w, void* out, StreamShape s,
     CUtensorMap map_w, map_x;
     if (!make_tile_map(&map_w, w, SWIGLU ? 2 * s.N : s.N, s.K, SWIGLU ? 64 : kTileM)) return DFI_ERR_LAUNCH;
     if (!make_tile_map(&map_x, x, s.M, s.K, BN)) return DFI_ERR_LAUNCH;
-    gemm_decode_kernel<BN, SWIGLU><<<s.n_ctas, kDecThreads, Cfg::kSmemBytes, st>>>(map_w, map_x, out, s, partials, counters, out_dtype);
+    launch(gemm_decode_kernel<BN, SWIGLU>, s.n_ctas, kDecThreads, Cfg::kSmemBytes, st, map_w, map_x, out, s, partials, counters, out_dtype);
     return DFI_OK;
 }
 

@@ -9,6 +9,8 @@ namespace dfi {
 constexpr int kSampleThreads = 1024;
 
 __global__ void argmax_kernel(const float* __restrict__ logits, int row_stride, int vocab, int* __restrict__ out) {
+    pdl_launch_next();
+    pdl_wait();
     __shared__ float best_v[32];
     __shared__ int best_i[32];
     const float* x = logits + (size_t)blockIdx.x * row_stride;
@@ -47,6 +49,8 @@ __global__ void argmax_kernel(const float* __restrict__ logits, int row_stride, 
 __global__ void sample_temperature_kernel(const float* __restrict__ logits, int row_stride, int vocab,
                                           const float* __restrict__ uniforms, float inv_temperature,
                                           int* __restrict__ out) {
+    pdl_launch_next();
+    pdl_wait();
     __shared__ float scratch[32];
     __shared__ float sums[kSampleThreads];
     __shared__ float warp_tot[32];
@@ -124,7 +128,7 @@ using namespace dfi;
 DFI_EXPORT int dfi_argmax(const float* logits, int rows, int row_stride, int vocab, int* out, void* stream) {
     if (rows <= 0) return DFI_OK;
     if (vocab <= 0) return DFI_ERR_SHAPE;
-    argmax_kernel<<<rows, 1024, 0, (cudaStream_t)stream>>>(logits, row_stride, vocab, out);
+    launch(argmax_kernel, rows, 1024, 0, (cudaStream_t)stream, logits, row_stride, vocab, out);
     DFI_CHECK_LAUNCH();
     return DFI_OK;
 }
@@ -134,7 +138,7 @@ DFI_EXPORT int dfi_sample_temperature(const float* logits, int rows, int row_str
                                       const float* uniforms, float temperature, int* out, void* stream) {
     if (rows <= 0) return DFI_OK;
     if (vocab <= 0 || !(temperature > 0.f)) return DFI_ERR_SHAPE;
-    sample_temperature_kernel<<<rows, kSampleThreads, 0, (cudaStream_t)stream>>>(
+    launch(sample_temperature_kernel, rows, kSampleThreads, 0, (cudaStream_t)stream, 
         logits, row_stride, vocab, uniforms, 1.0f / temperature, out);
     DFI_CHECK_LAUNCH();
     return DFI_OK;

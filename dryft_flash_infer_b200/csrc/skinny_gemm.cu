@@ -93,6 +93,8 @@ template <int NT, bool SWIGLU>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, void* __restrict__ out, GemmShape s,
                    float* __restrict__ partials, int* __restrict__ counters, int out_dtype) {
+    pdl_launch_next();
+    pdl_wait();
     extern __shared__ __align__(16) unsigned char smem_raw[];
     constexpr int kStages = Stages<NT>::n;
     constexpr int kXRows = NT * 8;
@@ -258,7 +260,7 @@ static int launch_skinny(const bf16* x, const bf16* w, void* out, const GemmShap
             return DFI_ERR_LAUNCH;
         configured = true;
     }
-    skinny_gemm_kernel<NT, SWIGLU><<<s.n_ctas, kGemmThreads, smem, st>>>(x, w, out, s, partials, counters, out_dtype);
+    launch(skinny_gemm_kernel<NT, SWIGLU>, s.n_ctas, kGemmThreads, smem, st, x, w, out, s, partials, counters, out_dtype);
     return DFI_OK;
 }
 

@@ -8,6 +8,7 @@ does not take, raise ``KernelError`` with the reason.
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 
@@ -29,8 +30,29 @@ class KernelError(RuntimeError):
 _DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
 
 
+#: Programmatic dependent launch of the kernels (a kernel's set-up and weight loads overlap the tail
+#: of the kernel before it).  The reference's switch keeps its name: DRYFT_PDL=off|on|early
+#: (engine/kernels/cuda_small.py:22); anything but "off" turns it on.
+PDL = os.environ.get("DRYFT_PDL", "early") != "off"
+_PDL_APPLIED: set = set()
+
+
+def _with_pdl(lib, setter: str):
+    if id(lib) not in _PDL_APPLIED:
+        getattr(lib, setter)(1 if PDL else 0)
+        _PDL_APPLIED.add(id(lib))
+    return lib
+
+
+def set_pdl(enabled: bool) -> None:
+    """Switches programmatic dependent launch on or off for every kernel launched from now on."""
+    global PDL
+    PDL = bool(enabled)
+    _PDL_APPLIED.clear()
+
+
 def _core():
-    return load_library("dfi_core", CORE_SOURCES)
+    return _with_pdl(load_library("dfi_core", CORE_SOURCES), "dfi_set_pdl")
 
 
 def _code(t: torch.Tensor) -> int:
@@ -173,7 +195,8 @@ def attention_generic(q: torch.Tensor, cache, row_seq: torch.Tensor, row_pos: to
 
 
 def _attention_library(head_dim: int):
-    return load_library(f"dfi_attention_d{head_dim}", ATTENTION_SOURCES, [f"-DDFI_HEAD_DIM={head_dim}"])
+    return _with_pdl(load_library(f"dfi_attention_d{head_dim}", ATTENTION_SOURCES, [f"-DDFI_HEAD_DIM={head_dim}"]),
+                     "dfi_attention_set_pdl")
 
 
 _DECODE_WAVE: dict[int, int] = {}
