@@ -29,13 +29,27 @@ struct StreamShape {
     int row_blocks;
     int units;
     int n_ctas;
+    int parts;            // > 0: every row block is cut into this many parts, one CTA each (n_ctas = row_blocks * parts)
 };
 
+// First unit of a CTA's run.  Two ways of dealing the units out: equal contiguous runs over the
+// whole matrix (stream-K), or, for a matrix with few row blocks, each row block cut into the same
+// number of parts, so that no CTA's run crosses from one row block into the next.
 __device__ __forceinline__ int sk_run_begin(const StreamShape& s, int cta) {
+    if (s.parts > 0) {
+        if (cta >= s.n_ctas) return s.units;
+        return (cta / s.parts) * s.k_chunks + s.k_chunks * (cta % s.parts) / s.parts;
+    }
     return (int)((unsigned)s.units * (unsigned)cta / (unsigned)s.n_ctas);
 }
 __device__ __forceinline__ int sk_cta_of_unit(const StreamShape& s, int u) {
-    int c = (int)((unsigned)u * (unsigned)s.n_ctas / (unsigned)s.units);
+    int c;
+    if (s.parts > 0) {
+        const int rb = u / s.k_chunks, kc = u % s.k_chunks;
+        c = rb * s.parts + min(s.parts - 1, kc * s.parts / s.k_chunks);
+    } else {
+        c = (int)((unsigned)u * (unsigned)s.n_ctas / (unsigned)s.units);
+    }
     while (c + 1 < s.n_ctas && sk_run_begin(s, c + 1) <= u) ++c;
     while (c > 0 && sk_run_begin(s, c) > u) --c;
     return c;
@@ -44,6 +58,18 @@ __device__ __forceinline__ void epilogue_barrier() { asm volatile("bar.sync 1, 1
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(s32(bar)) : "memory");
 }
+
+// -DDFI_TRACE: every CTA records the global timer at a few points of its life (a debugging build).
+#ifdef DFI_TRACE
+__device__ unsigned long long g_trace[512 * 8];
+__device__ __forceinline__ void trace(int slot) {
+    unsigned long long now;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+    g_trace[blockIdx.x * 8 + slot] = now;
+}
+#else
+__device__ __forceinline__ void trace(int) {}
+#endif
 
 template <int BN> struct DecConfig {
     static constexpr int kABytes = kTileM * kTileK * 2;
@@ -63,6 +89,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                    void* __restrict__ out, StreamShape s, float* __restrict__ partials, int* __restrict__ counters,
                    int out_dtype) {
     using Cfg = DecConfig<BN>;
+    if (threadIdx.x == 0) trace(0);
     pdl_launch_next();
     extern __shared__ unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[Cfg::kStages];
@@ -81,6 +108,22 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     const int first_rb = u_begin / s.k_chunks, first_kc = u_begin % s.k_chunks;
     constexpr int kCols = SWIGLU ? kTileM / 2 : kTileM;      // output columns per row block
 
+    auto load_w = [&](int st, int rb, int kc) {
+        unsigned char* a_tile = ring + (size_t)st * Cfg::kStageBytes;
+        mbar_expect_tx(&full_bar[st], Cfg::kStageBytes);
+        if (SWIGLU) {
+            tma_load_2d(a_tile, &map_w, kc * kTileK, rb * 64, &full_bar[st]);
+            tma_load_2d(a_tile + Cfg::kABytes / 2, &map_w, kc * kTileK, s.N + rb * 64, &full_bar[st]);
+        } else {
+            tma_load_2d(a_tile, &map_w, kc * kTileK, rb * kTileM, &full_bar[st]);
+        }
+    };
+    auto load_x = [&](int st, int kc) {
+        tma_load_2d(ring + (size_t)st * Cfg::kStageBytes + Cfg::kABytes, &map_x, kc * kTileK, 0, &full_bar[st]);
+    };
+    const int first_round = min(n_units, Cfg::kStages);
+    int prod_rb = first_rb, prod_kc = first_kc;      // the producer's place (thread 0 only)
+
     if (threadIdx.x == 0) {
         for (int i = 0; i < Cfg::kStages; ++i) {
             mbar_init(&full_bar[i], 1);
@@ -91,6 +134,13 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             mbar_init(&acc_empty[i], 128);
         }
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        // The weights depend on no earlier kernel and on no other thread of this CTA: the first
+        // round of the ring is on its way before the CTA has finished setting up.
+        for (int i = 0; i < first_round; ++i) {
+            load_w(i, prod_rb, prod_kc);
+            if (++prod_kc == s.k_chunks) { prod_kc = 0; ++prod_rb; }
+        }
+        trace(1);
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(s32(&tmem_base_s)), "r"(Cfg::kTmemCols) : "memory");
@@ -103,28 +153,8 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 
     if (warp == 0) {
         if (lane == 0) {
-            auto load_w = [&](int st, int rb, int kc) {
-                unsigned char* a_tile = ring + (size_t)st * Cfg::kStageBytes;
-                mbar_expect_tx(&full_bar[st], Cfg::kStageBytes);
-                if (SWIGLU) {
-                    tma_load_2d(a_tile, &map_w, kc * kTileK, rb * 64, &full_bar[st]);
-                    tma_load_2d(a_tile + Cfg::kABytes / 2, &map_w, kc * kTileK, s.N + rb * 64, &full_bar[st]);
-                } else {
-                    tma_load_2d(a_tile, &map_w, kc * kTileK, rb * kTileM, &full_bar[st]);
-                }
-            };
-            auto load_x = [&](int st, int kc) {
-                tma_load_2d(ring + (size_t)st * Cfg::kStageBytes + Cfg::kABytes, &map_x, kc * kTileK, 0, &full_bar[st]);
-            };
-            // The weights depend on no earlier kernel: the first round of the ring is filled with
-            // them before this kernel waits for the one that produces the activations.
-            const int first_round = min(n_units, Cfg::kStages);
-            int rb = first_rb, kc = first_kc;
-            for (int i = 0; i < first_round; ++i) {
-                load_w(i, rb, kc);
-                if (++kc == s.k_chunks) { kc = 0; ++rb; }
-            }
-            pdl_wait();
+            pdl_wait();          // from here on the activations are read
+            trace(2);
             int kc_x = first_kc;
             for (int i = 0; i < first_round; ++i) {
                 load_x(i, kc_x);
@@ -134,9 +164,9 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 const int st = i % Cfg::kStages;
                 const uint32_t round = i / Cfg::kStages;
                 if (!mbar_wait(&empty_bar[st], (round - 1) & 1, 1)) break;
-                load_w(st, rb, kc);
-                load_x(st, kc);
-                if (++kc == s.k_chunks) { kc = 0; ++rb; }
+                load_w(st, prod_rb, prod_kc);
+                load_x(st, prod_kc);
+                if (++prod_kc == s.k_chunks) { prod_kc = 0; ++prod_rb; }
             }
         }
     } else if (warp == 1) {
@@ -185,35 +215,43 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             const int buf = segment & 1;
             ok = mbar_wait(&acc_full[buf], (segment >> 1) & 1, 3);
             if (!ok) break;
+            if (t == 0 && done + seg_units >= n_units) trace(3);
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN;
-            // staging[b][t] = D[t][b]: transposed so that what follows reads along the row block
+            // D[t][b] goes, transposed, either to the staging buffer (this CTA summed the whole row
+            // block) or straight to this CTA's part in scratch memory: [b][t], so that what follows
+            // reads along the row block
+            float* dest = complete ? staging
+                                   : partials + ((size_t)cta * 2 + (rb == first_rb ? 0 : 1)) * Cfg::kSlotFloats;
 #pragma unroll
             for (int c = 0; c < BN; c += 16) {
                 uint32_t d[16];
                 tmem_load16(taddr + c, d);
 #pragma unroll
-                for (int e = 0; e < 16; ++e) staging[(c + e) * kTileM + t] = __uint_as_float(d[e]);
+                for (int e = 0; e < 16; ++e)
+                    if (c + e < s.M) dest[(c + e) * kTileM + t] = __uint_as_float(d[e]);
             }
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
             mbar_arrive(&acc_empty[buf]);            // the issuer may reuse this accumulator
-            epilogue_barrier();
+            epilogue_barrier();                      // the 128 threads' writes are ordered before what thread 0 does next
 
             bool reduce = complete;
             int c_first = cta, c_last = cta, first_slot = 0;
             if (!complete) {
-                float* mine = partials + ((size_t)cta * 2 + (rb == first_rb ? 0 : 1)) * Cfg::kSlotFloats;
-                for (int b = 0; b < s.M; ++b) mine[b * kTileM + t] = staging[b * kTileM + t];
-                __threadfence();
-                epilogue_barrier();
                 const int rb_first_unit = rb * s.k_chunks;
                 c_first = sk_cta_of_unit(s, rb_first_unit);
                 c_last = sk_cta_of_unit(s, rb_first_unit + s.k_chunks - 1);
                 first_slot = sk_run_begin(s, c_first) >= rb_first_unit ? 0 : 1;
-                if (t == 0) ticket_s = atomicAdd(&counters[rb], 1);
+                if (t == 0) {
+                    if (done + seg_units >= n_units) trace(4);
+                    __threadfence();                 // release: the part is visible before the ticket is taken
+                    const int ticket = atomicAdd(&counters[rb], 1);
+                    __threadfence();                 // acquire: the other parts are visible after it
+                    ticket_s = ticket;
+                    if (done + seg_units >= n_units) trace(5);
+                }
                 epilogue_barrier();
                 reduce = ticket_s == c_last - c_first;      // the last of the row block's parts to arrive
-                if (reduce) __threadfence();
             }
             if (reduce) {
                 // 128 threads share the block's M x kCols outputs in groups of four columns; the parts'
@@ -232,13 +270,20 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                     if (SWIGLU) u = complete ? *reinterpret_cast<const float4*>(first_part + offset + 64)
                                              : __ldcg(reinterpret_cast<const float4*>(first_part + offset + 64));
                     const float* p = next_part + offset;
-#pragma unroll 8
-                    for (int part = 0; part < n_more; ++part, p += 2 * Cfg::kSlotFloats) {
-                        const float4 w4 = __ldcg(reinterpret_cast<const float4*>(p));
-                        v.x += w4.x; v.y += w4.y; v.z += w4.z; v.w += w4.w;
-                        if (SWIGLU) {
-                            const float4 u4 = __ldcg(reinterpret_cast<const float4*>(p + 64));
-                            u.x += u4.x; u.y += u4.y; u.z += u4.z; u.w += u4.w;
+                    // the parts' loads are issued eight at a time and added in the order of their k ranges
+                    for (int part0 = 0; part0 < n_more; part0 += 8, p += 16 * Cfg::kSlotFloats) {
+                        float4 w4[8], u4[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const bool live = part0 + j < n_more;
+                            const float* q = p + (size_t)j * 2 * Cfg::kSlotFloats;
+                            w4[j] = live ? __ldcg(reinterpret_cast<const float4*>(q)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                            if (SWIGLU) u4[j] = live ? __ldcg(reinterpret_cast<const float4*>(q + 64)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        }
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            v.x += w4[j].x; v.y += w4[j].y; v.z += w4[j].z; v.w += w4[j].w;
+                            if (SWIGLU) { u.x += u4[j].x; u.y += u4[j].y; u.z += u4[j].z; u.w += u4[j].w; }
                         }
                     }
                     if (SWIGLU) {
@@ -257,6 +302,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 }
                 if (!complete && t == 0) counters[rb] = 0;   // ready for the next call
             }
+            if (t == 0 && done + seg_units >= n_units) trace(6);
             epilogue_barrier();          // staging is free for the next row block
             done += seg_units;
             seg_first_kc = 0;
@@ -304,6 +350,12 @@ static int launch_decode(const void* x, const void* w, void* out, StreamShape s,
 
 using namespace dfi;
 
+#ifdef DFI_TRACE
+DFI_EXPORT int dfi_gemm_decode_trace(unsigned long long* host_out) {
+    return cudaMemcpyFromSymbol(host_out, g_trace, sizeof(unsigned long long) * 512 * 8) == cudaSuccess ? 0 : 1;
+}
+#endif
+
 DFI_EXPORT int dfi_gemm_decode_error(int reset) {
     int value = 0;
     if (cudaMemcpyFromSymbol(&value, g_tc_error, sizeof(int)) != cudaSuccess) return -1;
@@ -340,7 +392,15 @@ DFI_EXPORT int dfi_gemm_decode(const void* x, const void* w, void* out, int M, i
     if (n_ctas <= 0) n_ctas = dec_sm_count();
     if (n_ctas <= 0) return DFI_ERR_LAUNCH;
     if (n_ctas > 512) n_ctas = 512;
+    s.parts = 0;
     s.n_ctas = s.units < n_ctas ? s.units : n_ctas;
+    if (s.row_blocks * 2 <= n_ctas) {
+        // few row blocks: the same number of parts for each, as many as fill the CTAs
+        int parts = n_ctas / s.row_blocks;
+        if (parts > s.k_chunks) parts = s.k_chunks;
+        s.parts = parts;
+        s.n_ctas = s.row_blocks * parts;
+    }
     cudaStream_t st = (cudaStream_t)stream;
     int rc;
 #define DFI_DEC(BNV)                                                                                       \

@@ -8,25 +8,38 @@ namespace dfi {
 
 constexpr int kSampleThreads = 1024;
 
+constexpr int kArgmaxParts = 64;       // CTAs that share one row
+constexpr int kArgmaxMaxRows = 4096;   // rows the arrival counters cover
+
+// Arrival counters of the rows (zero between calls) and the parts' candidates.
+__device__ int g_argmax_counters[kArgmaxMaxRows];
+__device__ float g_argmax_value[kArgmaxMaxRows * kArgmaxParts];
+__device__ int g_argmax_index[kArgmaxMaxRows * kArgmaxParts];
+
+__device__ __forceinline__ void keep_better(float& v, int& idx, float ov, int oi) {
+    if (ov > v || (ov == v && oi < idx)) { v = ov; idx = oi; }
+}
+
+// grid (parts, rows).  Each CTA finds the best of its share of the row; the CTA that arrives last
+// (a ticket per row, no waiting) reduces the parts' candidates in index order and writes the row's
+// result, so the choice does not depend on which CTA finished when.
 __global__ void argmax_kernel(const float* __restrict__ logits, int row_stride, int vocab, int* __restrict__ out) {
     pdl_launch_next();
     pdl_wait();
     __shared__ float best_v[32];
     __shared__ int best_i[32];
-    const float* x = logits + (size_t)blockIdx.x * row_stride;
+    __shared__ int ticket_s;
+    const int row = blockIdx.y, part = blockIdx.x, parts = gridDim.x;
+    const float* x = logits + (size_t)row * row_stride;
+    const int per = (vocab + parts - 1) / parts;
+    const int begin = min(vocab, part * per), end = min(vocab, begin + per);
     float v = -INFINITY;
     int idx = 0x7fffffff;
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-        const float c = x[i];
-        if (c > v || (c == v && i < idx)) { v = c; idx = i; }
-    }
+    for (int i = begin + threadIdx.x; i < end; i += blockDim.x) keep_better(v, idx, x[i], i);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        const float ov = __shfl_xor_sync(0xffffffffu, v, o);
-        const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
-        if (ov > v || (ov == v && oi < idx)) { v = ov; idx = oi; }
-    }
+    for (int o = 16; o > 0; o >>= 1)
+        keep_better(v, idx, __shfl_xor_sync(0xffffffffu, v, o), __shfl_xor_sync(0xffffffffu, idx, o));
     if (lane == 0) { best_v[warp] = v; best_i[warp] = idx; }
     __syncthreads();
     if (warp == 0) {
@@ -34,12 +47,28 @@ __global__ void argmax_kernel(const float* __restrict__ logits, int row_stride, 
         v = lane < n_warps ? best_v[lane] : -INFINITY;
         idx = lane < n_warps ? best_i[lane] : 0x7fffffff;
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, v, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
-            if (ov > v || (ov == v && oi < idx)) { v = ov; idx = oi; }
+        for (int o = 16; o > 0; o >>= 1)
+            keep_better(v, idx, __shfl_xor_sync(0xffffffffu, v, o), __shfl_xor_sync(0xffffffffu, idx, o));
+        if (lane == 0) {
+            g_argmax_value[row * kArgmaxParts + part] = v;
+            g_argmax_index[row * kArgmaxParts + part] = idx;
+            __threadfence();
+            ticket_s = atomicAdd(&g_argmax_counters[row], 1);
         }
-        if (lane == 0) out[blockIdx.x] = idx == 0x7fffffff ? 0 : idx;
+    }
+    __syncthreads();
+    if (ticket_s != parts - 1 || warp != 0) return;
+    __threadfence();
+    v = -INFINITY;
+    idx = 0x7fffffff;
+    for (int p = lane; p < parts; p += 32)
+        keep_better(v, idx, __ldcg(&g_argmax_value[row * kArgmaxParts + p]), __ldcg(&g_argmax_index[row * kArgmaxParts + p]));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+        keep_better(v, idx, __shfl_xor_sync(0xffffffffu, v, o), __shfl_xor_sync(0xffffffffu, idx, o));
+    if (lane == 0) {
+        out[row] = idx == 0x7fffffff ? 0 : idx;
+        g_argmax_counters[row] = 0;
     }
 }
 
@@ -128,7 +157,12 @@ using namespace dfi;
 DFI_EXPORT int dfi_argmax(const float* logits, int rows, int row_stride, int vocab, int* out, void* stream) {
     if (rows <= 0) return DFI_OK;
     if (vocab <= 0) return DFI_ERR_SHAPE;
-    launch(argmax_kernel, rows, 1024, 0, (cudaStream_t)stream, logits, row_stride, vocab, out);
+    for (int first = 0; first < rows; first += kArgmaxMaxRows) {
+        const int n = rows - first < kArgmaxMaxRows ? rows - first : kArgmaxMaxRows;
+        const int parts = vocab >= 8192 ? kArgmaxParts : 1;
+        launch(argmax_kernel, dim3(parts, n), 256, 0, (cudaStream_t)stream, logits + (size_t)first * row_stride, row_stride,
+               vocab, out + first);
+    }
     DFI_CHECK_LAUNCH();
     return DFI_OK;
 }
