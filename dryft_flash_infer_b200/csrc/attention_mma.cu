@@ -264,66 +264,179 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
 }
 
 // ------------------------------------------------------------------ decode
-// grid (sequences * kv heads, splits).  part_o [seq*n_q + head][split][D] float32 holds the
-// unnormalised accumulators, part_ml [..][split][2] their (maximum, sum); unused when splits == 1.
+// One query row per sequence.  The work is the list of (sequence, key/value head, page of keys)
+// triples, sequence after sequence; it is dealt to the CTAs in equal contiguous runs, so that a
+// batch of unequal contexts, or one that does not fill a whole number of waves, still keeps every
+// SM busy for the same time.  A run visits one (sequence, head) group after another.  A CTA that
+// sees all the pages of a group writes the group's output itself.  Otherwise it leaves its
+// unnormalised accumulator with (maximum, sum) in scratch memory and takes a ticket from the
+// group's counter; the CTA that draws the last ticket merges the parts by their log-sum-exp in
+// the order of their key ranges (engine/kernels/attention.py:140-177), writes the output and
+// resets the counter.  No CTA waits for another.
+//
+//   part_o  [cta][2][16][D] float32, part_ml [cta][2][16][2]: a CTA's first and last group
+//   counters [sequences * kv heads] int32, zero between calls
+struct DecodeRun {
+    int total;      // units of the whole step
+    int n_ctas;
+};
+__device__ __forceinline__ int dec_run_begin(const DecodeRun& r, int cta) {
+    return (int)((unsigned long long)r.total * (unsigned)cta / (unsigned)r.n_ctas);
+}
+__device__ __forceinline__ int dec_cta_of_unit(const DecodeRun& r, int u) {
+    int c = (int)((unsigned long long)u * (unsigned)r.n_ctas / (unsigned)r.total);
+    while (c + 1 < r.n_ctas && dec_run_begin(r, c + 1) <= u) ++c;
+    while (c > 0 && dec_run_begin(r, c) > u) --c;
+    return c;
+}
+
+#ifdef DFI_TRACE
+__device__ unsigned long long g_attn_trace[4096 * 8];
+__device__ __forceinline__ void atrace(int slot) {
+    if (threadIdx.x == 0) {
+        unsigned long long now;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+        g_attn_trace[blockIdx.x * 8 + slot] = now;
+    }
+}
+#else
+__device__ __forceinline__ void atrace(int) {}
+#endif
+
+constexpr int kKvStages = 3;            // pages of keys and values in the decode kernel's ring
+constexpr int kMaxParts = 16;           // CTAs that may share one (sequence, head) group
+constexpr int kMaxDecodeSeqs = 1024;    // sequences per launch (their page counts sit in shared memory)
+
 __global__ void __launch_bounds__(kThreads)
 attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, int out_stride,
                         const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                         const int* __restrict__ block_table, int table_width, const int* __restrict__ seq_start,
-                        int n_q, int n_kv, int ring_tokens, int window, float scale_log2, int n_splits,
-                        float* __restrict__ part_o, float* __restrict__ part_ml) {
+                        int n_seqs, int n_q, int n_kv, int ring_tokens, int window, float scale_log2,
+                        float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters) {
+    atrace(0);
     pdl_launch_next();
-    pdl_wait();
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* q_s = reinterpret_cast<bf16*>(smem_raw);   // [16][kStride]
-    bf16* k_s = q_s + 16 * kStride;                  // [2][64][kStride]
-    bf16* v_s = k_s + 2 * kPage * kStride;           // [2][64][kStride]
+    bf16* k_s = q_s + 16 * kStride;                  // [kKvStages][64][kStride]
+    bf16* v_s = k_s + kKvStages * kPage * kStride;   // [kKvStages][64][kStride]
+    __shared__ int cum_s[kMaxDecodeSeqs + 1];        // pages of the sequences before each one
+    __shared__ int warp_tot_s[4];
+    __shared__ int warp_max_s[4];
+    __shared__ int ticket_s;
 
-    const int seq = blockIdx.x / n_kv, kv_head = blockIdx.x % n_kv, split = blockIdx.y;
-    const int group = n_q / n_kv;
-    const int pos = seq_start[seq];                  // the new token's position: keys 0..pos are live
-    const int kv_len = pos + 1;
-    const int* table = block_table + (size_t)seq * table_width;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t4 = lane & 3;
+    const int group = n_q / n_kv;
 
-    const int first_key = window > 0 ? max(0, pos - window + 1) : 0;
-    const int t_first = first_key / kPage, t_last = pos / kPage;
-    const int per = (t_last - t_first + n_splits) / n_splits;
-    const int t_begin = t_first + split * per, t_end = min(t_last, t_begin + per - 1);
-
-    float o[D / 8][4];
+    // ---- how many pages each sequence brings: known before this step's kernels ran, so this part
+    // overlaps the kernel before (the positions were uploaded ahead of the step)
+    {
+        const int per = (n_seqs + kThreads - 1) / kThreads;
+        const int lo = min(n_seqs, (int)threadIdx.x * per), hi = min(n_seqs, lo + per);
+        int mine = 0, longest = 0;
+        for (int i = lo; i < hi; ++i) {
+            const int pos = seq_start[i];
+            const int first_key = window > 0 ? max(0, pos - window + 1) : 0;
+            const int tiles = pos / kPage - first_key / kPage + 1;
+            mine += tiles;
+            longest = max(longest, tiles);
+        }
+        longest = __reduce_max_sync(0xffffffffu, longest);
+        if (lane == 0) warp_max_s[warp] = longest;
+        int incl = mine;
 #pragma unroll
-    for (int n = 0; n < D / 8; ++n)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) o[n][e] = 0.f;
-    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+        for (int o = 1; o < 32; o <<= 1) {
+            const int up = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += up;
+        }
+        if (lane == 31) warp_tot_s[warp] = incl;
+        __syncthreads();
+        int before = incl - mine;
+        for (int w = 0; w < warp; ++w) before += warp_tot_s[w];
+        for (int i = lo; i < hi; ++i) {
+            cum_s[i] = before;
+            const int pos = seq_start[i];
+            const int first_key = window > 0 ? max(0, pos - window + 1) : 0;
+            before += pos / kPage - first_key / kPage + 1;
+        }
+        if (threadIdx.x == kThreads - 1) cum_s[n_seqs] = before;
+        __syncthreads();
+    }
+    DecodeRun run;
+    run.total = cum_s[n_seqs] * n_kv;
+    // A CTA takes at least four pages, and enough of them that no sequence is spread over more than
+    // kMaxParts CTAs (the merge holds all the parts of a group at once).
+    const int longest = max(max(warp_max_s[0], warp_max_s[1]), max(warp_max_s[2], warp_max_s[3]));
+    const int least = max(4, (longest + kMaxParts - 3) / (kMaxParts - 2));
+    run.n_ctas = max(1, min((int)gridDim.x, run.total / least));
+    const int cta = blockIdx.x;
+    atrace(1);
+    pdl_wait();        // from here on the queries and the new keys and values are read
+    if (cta >= run.n_ctas) return;
+    atrace(2);
+    const int u_begin = dec_run_begin(run, cta), u_end = dec_run_begin(run, cta + 1);
 
-    if (t_begin <= t_end) {
+    // the sequence that holds unit u_begin: the last one whose first unit is not past it
+    int seq;
+    {
+        int lo = 0, hi = n_seqs - 1;
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (cum_s[mid] * n_kv <= u_begin) lo = mid; else hi = mid - 1;
+        }
+        seq = lo;
+    }
+    int u = u_begin;
+    bool first_segment = true;
+    while (u < u_end) {
+        while (cum_s[seq + 1] * n_kv <= u) ++seq;
+        const int seq_tiles = cum_s[seq + 1] - cum_s[seq];
+        const int in_seq = u - cum_s[seq] * n_kv;
+        const int kv_head = in_seq / seq_tiles, t_a = in_seq % seq_tiles;
+        const int t_b = min(seq_tiles, t_a + (u_end - u));            // tiles [t_a, t_b) of this group
+        const bool whole = t_a == 0 && t_b == seq_tiles;
+        const int group_first_unit = cum_s[seq] * n_kv + kv_head * seq_tiles;
+
+        const int pos = seq_start[seq];
+        const int kv_len = pos + 1;
+        const int first_key = window > 0 ? max(0, pos - window + 1) : 0;
+        const int t_first = first_key / kPage;
+        const int* table = block_table + (size_t)seq * table_width;
+        const int t_begin = t_first + t_a, t_end = t_first + t_b - 1;
+
+        float o[D / 8][4];
+#pragma unroll
+        for (int n = 0; n < D / 8; ++n)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) o[n][e] = 0.f;
+        float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
         for (int i = threadIdx.x; i < 16 * kChunks; i += kThreads) {
             const int row = i / kChunks, c = i % kChunks;
             const bool valid = row < group;
             const bf16* src = q + (size_t)seq * q_stride + (size_t)(kv_head * group + (valid ? row : 0)) * D + c * 8;
             cp_async16(q_s + row * kStride + c * 8, src, valid);
         }
-        load_page(k_s, page_ptr(k_cache, table, t_begin, ring_tokens, n_kv, kv_head), t_begin * kPage, kv_len, false);
-        load_page(v_s, page_ptr(v_cache, table, t_begin, ring_tokens, n_kv, kv_head), t_begin * kPage, kv_len, true);
-        cp_async_commit();
+        // a ring of kKvStages pages of keys and values: kKvStages - 1 of them are on their way while one is used
+        auto load_tile = [&](int t) {
+            const int stage = (t - t_begin) % kKvStages;
+            load_page(k_s + stage * kPage * kStride, page_ptr(k_cache, table, t, ring_tokens, n_kv, kv_head), t * kPage, kv_len, false);
+            load_page(v_s + stage * kPage * kStride, page_ptr(v_cache, table, t, ring_tokens, n_kv, kv_head), t * kPage, kv_len, true);
+        };
+#pragma unroll
+        for (int i = 0; i < kKvStages - 1; ++i) {
+            if (t_begin + i <= t_end) load_tile(t_begin + i);
+            cp_async_commit();
+        }
         uint32_t qf[D / 16][4];
         for (int t = t_begin; t <= t_end; ++t) {
-            const int stage = (t - t_begin) & 1;
-            if (t < t_end) {
-                bf16* k_next = k_s + (stage ^ 1) * kPage * kStride;
-                bf16* v_next = v_s + (stage ^ 1) * kPage * kStride;
-                load_page(k_next, page_ptr(k_cache, table, t + 1, ring_tokens, n_kv, kv_head), (t + 1) * kPage, kv_len, false);
-                load_page(v_next, page_ptr(v_cache, table, t + 1, ring_tokens, n_kv, kv_head), (t + 1) * kPage, kv_len, true);
-                cp_async_commit();
-                cp_async_wait<1>();
-            } else {
-                cp_async_wait<0>();
-            }
-            __syncthreads();
+            const int stage = (t - t_begin) % kKvStages;
+            cp_async_wait<kKvStages - 2>();
+            __syncthreads();     // page t has landed for everyone, and everyone is done with the stage refilled next
+            if (t + kKvStages - 1 <= t_end) load_tile(t + kKvStages - 1);
+            cp_async_commit();
             if (t == t_begin) {
+                atrace(3);
                 const int mi = lane >> 3, r = lane & 7;
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk)
@@ -332,8 +445,8 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
             const bf16* k_t = k_s + stage * kPage * kStride;
             const bf16* v_t = v_s + stage * kPage * kStride;
             // each warp takes 16 of the tile's 64 keys
-            float s[2][4];
-            scores<2>(s, qf, k_t, warp * 16, lane);
+            float sc[2][4];
+            scores<2>(sc, qf, k_t, warp * 16, lane);
             const int key_base = t * kPage + warp * 16;
 #pragma unroll
             for (int j = 0; j < 2; ++j)
@@ -341,81 +454,111 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
                 for (int e = 0; e < 4; ++e) {
                     const int key = key_base + j * 8 + t4 * 2 + (e & 1);
                     const bool seen = key <= pos && key >= first_key;
-                    s[j][e] = seen ? s[j][e] * scale_log2 : -INFINITY;
+                    sc[j][e] = seen ? sc[j][e] * scale_log2 : -INFINITY;
                 }
-            softmax_update<2>(s, m, l, o);
-            weighted_values<2>(o, s, v_t, warp * 16, lane);
-            __syncthreads();
+            softmax_update<2>(sc, m, l, o);
+            weighted_values<2>(o, sc, v_t, warp * 16, lane);
         }
-    }
+        atrace(4);
+        cp_async_wait<0>();
+        __syncthreads();         // everyone is done with the pages: their memory is reused below
 
-    // merge the four warps' partial results: the tile buffers are free now
-    float* red_o = reinterpret_cast<float*>(k_s);        // [4][16][D]
-    float* red_ml = red_o + 4 * 16 * D;                  // [4][16][2]
+        // merge the four warps' results: the tile buffers are free now
+        float* red_o = reinterpret_cast<float*>(k_s);        // [4][16][D]
+        float* red_ml = red_o + 4 * 16 * D;                  // [4][16][2]
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        const int row = g + h * 8;
+        for (int h = 0; h < 2; ++h) {
+            const int row = g + h * 8;
 #pragma unroll
-        for (int n = 0; n < D / 8; ++n) {
-            red_o[(warp * 16 + row) * D + n * 8 + t4 * 2] = o[n][2 * h];
-            red_o[(warp * 16 + row) * D + n * 8 + t4 * 2 + 1] = o[n][2 * h + 1];
-        }
-        if (t4 == 0) {
-            red_ml[(warp * 16 + row) * 2] = m[h];
-            red_ml[(warp * 16 + row) * 2 + 1] = l[h];
-        }
-    }
-    __syncthreads();
-    for (int i = threadIdx.x; i < group * D; i += kThreads) {
-        const int row = i / D, d = i % D;
-        float mx = -INFINITY;
-#pragma unroll
-        for (int w = 0; w < 4; ++w) mx = fmaxf(mx, red_ml[(w * 16 + row) * 2]);
-        const float m_use = mx == -INFINITY ? 0.f : mx;
-        float acc = 0.f, sum = 0.f;
-#pragma unroll
-        for (int w = 0; w < 4; ++w) {
-            const float c = exp2f(red_ml[(w * 16 + row) * 2] - m_use);
-            acc += c * red_o[(w * 16 + row) * D + d];
-            sum += c * red_ml[(w * 16 + row) * 2 + 1];
-        }
-        const int head = kv_head * group + row;
-        if (n_splits == 1) {
-            out[(size_t)seq * out_stride + (size_t)head * D + d] = __float2bfloat16_rn(sum > 0.f ? acc / sum : 0.f);
-        } else {
-            const size_t slot = ((size_t)seq * n_q + head) * n_splits + split;
-            part_o[slot * D + d] = acc;
-            if (d == 0) {
-                part_ml[slot * 2] = mx;
-                part_ml[slot * 2 + 1] = sum;
+            for (int n = 0; n < D / 8; ++n) {
+                red_o[(warp * 16 + row) * D + n * 8 + t4 * 2] = o[n][2 * h];
+                red_o[(warp * 16 + row) * D + n * 8 + t4 * 2 + 1] = o[n][2 * h + 1];
+            }
+            if (t4 == 0) {
+                red_ml[(warp * 16 + row) * 2] = m[h];
+                red_ml[(warp * 16 + row) * 2 + 1] = l[h];
             }
         }
-    }
-}
-
-// grid (sequences * query heads); merges the splits by their log-sum-exp (attention.py:140-177).
-__global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                       bf16* __restrict__ out, int out_stride, int n_q, int n_splits) {
-    pdl_launch_next();
-    pdl_wait();
-    const int seq = blockIdx.x / n_q, head = blockIdx.x % n_q;
-    const size_t base = (size_t)blockIdx.x * n_splits;
-    float mx = -INFINITY;
-    for (int s = 0; s < n_splits; ++s) mx = fmaxf(mx, part_ml[(base + s) * 2]);
-    const float m_use = mx == -INFINITY ? 0.f : mx;
-    for (int d = threadIdx.x; d < D; d += blockDim.x) {
-        float acc = 0.f, sum = 0.f;
-        for (int s = 0; s < n_splits; ++s) {
-            const float c = exp2f(part_ml[(base + s) * 2] - m_use);
-            acc += c * part_o[(base + s) * D + d];
-            sum += c * part_ml[(base + s) * 2 + 1];
+        __syncthreads();
+        const int slot = cta * 2 + (first_segment ? 0 : 1);
+        for (int i = threadIdx.x; i < group * D; i += kThreads) {
+            const int row = i / D, d = i % D;
+            float mx = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) mx = fmaxf(mx, red_ml[(w * 16 + row) * 2]);
+            const float m_use = mx == -INFINITY ? 0.f : mx;
+            float acc = 0.f, sum = 0.f;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const float c = exp2f(red_ml[(w * 16 + row) * 2] - m_use);
+                acc += c * red_o[(w * 16 + row) * D + d];
+                sum += c * red_ml[(w * 16 + row) * 2 + 1];
+            }
+            if (whole) {
+                out[(size_t)seq * out_stride + (size_t)(kv_head * group + row) * D + d] =
+                    __float2bfloat16_rn(sum > 0.f ? acc / sum : 0.f);
+            } else {
+                part_o[((size_t)slot * 16 + row) * D + d] = acc;
+                if (d == 0) {
+                    part_ml[((size_t)slot * 16 + row) * 2] = mx;
+                    part_ml[((size_t)slot * 16 + row) * 2 + 1] = sum;
+                }
+            }
         }
-        out[(size_t)seq * out_stride + (size_t)head * D + d] = __float2bfloat16_rn(sum > 0.f ? acc / sum : 0.f);
+        if (!whole) {
+            __syncthreads();
+            const int c_first = dec_cta_of_unit(run, group_first_unit);
+            const int c_last = dec_cta_of_unit(run, group_first_unit + seq_tiles - 1);
+            atrace(5);
+            if (threadIdx.x == 0) {
+                __threadfence();                 // release: this part is visible before the ticket is taken
+                const int ticket = atomicAdd(&counters[seq * n_kv + kv_head], 1);
+                __threadfence();                 // acquire: the other parts are visible after it
+                ticket_s = ticket;
+            }
+            __syncthreads();
+            if (ticket_s == c_last - c_first) {
+                // a part lies in its CTA's first place if the group is the first of its run: true for
+                // every part after the first, whose runs begin inside the group
+                const int first_slot = dec_run_begin(run, c_first) >= group_first_unit ? 0 : 1;
+                const int n_parts = c_last - c_first + 1;       // at most kMaxParts by the choice of run length
+                for (int i = threadIdx.x; i < group * D; i += kThreads) {
+                    const int row = i / D, d = i % D;
+                    float pm[kMaxParts], pl[kMaxParts], po[kMaxParts];
+#pragma unroll
+                    for (int j = 0; j < kMaxParts; ++j) {
+                        const bool live = j < n_parts;
+                        const size_t sl = (size_t)(c_first + (live ? j : 0)) * 2 + (j == 0 ? first_slot : 0);
+                        pm[j] = live ? __ldcg(&part_ml[(sl * 16 + row) * 2]) : -INFINITY;
+                        pl[j] = live ? __ldcg(&part_ml[(sl * 16 + row) * 2 + 1]) : 0.f;
+                        po[j] = live ? __ldcg(&part_o[(sl * 16 + row) * D + d]) : 0.f;
+                    }
+                    float mx = -INFINITY;
+#pragma unroll
+                    for (int j = 0; j < kMaxParts; ++j) mx = fmaxf(mx, pm[j]);
+                    const float m_use = mx == -INFINITY ? 0.f : mx;
+                    float acc = 0.f, sum = 0.f;
+#pragma unroll
+                    for (int j = 0; j < kMaxParts; ++j) {
+                        const float w = exp2f(pm[j] - m_use);
+                        acc += w * po[j];
+                        sum += w * pl[j];
+                    }
+                    out[(size_t)seq * out_stride + (size_t)(kv_head * group + row) * D + d] =
+                        __float2bfloat16_rn(sum > 0.f ? acc / sum : 0.f);
+                }
+                if (threadIdx.x == 0) counters[seq * n_kv + kv_head] = 0;   // ready for the next call
+            }
+        }
+        atrace(6);
+        __syncthreads();     // the reduction buffers alias the tile buffers of the next group
+        u += t_b - t_a;
+        first_segment = false;
     }
 }
 
 constexpr int kPrefillSmem = (64 + 4 * kPage) * kStride * (int)sizeof(bf16);
-constexpr int kDecodeTiles = (16 + 4 * kPage) * kStride * (int)sizeof(bf16);
+constexpr int kDecodeTiles = (16 + 2 * kKvStages * kPage) * kStride * (int)sizeof(bf16);
 constexpr int kDecodeReduce = 16 * kStride * (int)sizeof(bf16) + (4 * 16 * D + 4 * 16 * 2) * (int)sizeof(float);
 constexpr int kDecodeSmem = kDecodeTiles > kDecodeReduce ? kDecodeTiles : kDecodeReduce;
 
@@ -431,12 +574,16 @@ DFI_EXPORT int dfi_attention_set_pdl(int enabled) {
     return before;
 }
 
+#ifdef DFI_TRACE
+DFI_EXPORT int dfi_attention_trace(unsigned long long* host_out) {
+    return cudaMemcpyFromSymbol(host_out, g_attn_trace, sizeof(unsigned long long) * 4096 * 8) == cudaSuccess ? 0 : 1;
+}
+#endif
+
 DFI_EXPORT int dfi_attention_head_dim() { return D; }
 
-// Scratch the decode kernel needs for `n_splits` > 1: floats for part_o, then for part_ml.
-DFI_EXPORT long long dfi_attention_decode_scratch_floats(int n_seqs, int n_q, int n_splits) {
-    return (long long)n_seqs * n_q * n_splits * (D + 2);
-}
+// Scratch of the decode kernel for a launch of `n_ctas` CTAs: floats for part_o, then for part_ml.
+DFI_EXPORT long long dfi_attention_decode_scratch_floats(int n_ctas) { return (long long)n_ctas * 2 * 16 * (D + 2); }
 
 // CTAs of the decode kernel that one SM holds at a time, times the SMs: what one wave can run.
 DFI_EXPORT int dfi_attention_decode_wave() {
@@ -472,17 +619,19 @@ DFI_EXPORT int dfi_attention_prefill(const void* q, int q_stride, void* out, int
     return DFI_OK;
 }
 
-// One query row per sequence (row i belongs to sequence i).  `scratch` holds at least
-// dfi_attention_decode_scratch_floats(...) floats when n_splits > 1.
+// One query row per sequence (row i belongs to sequence i).  `scratch` holds
+// dfi_attention_decode_scratch_floats(n_ctas) floats; `counters` holds n_seqs * n_kv ints, zero
+// before the first call and left zero by every call.  n_ctas <= 0: as many as run at once.
 DFI_EXPORT int dfi_attention_decode(const void* q, int q_stride, void* out, int out_stride, const void* k_cache,
                                     const void* v_cache, const int* block_table, int table_width,
                                     const int* seq_start, int n_seqs, int n_q, int n_kv, int page_size,
-                                    int ring_tokens, int window, float scale, int n_splits, float* scratch,
-                                    void* stream) {
+                                    int ring_tokens, int window, float scale, int n_ctas, float* scratch,
+                                    int* counters, void* stream) {
     if (n_seqs <= 0) return DFI_OK;
     if (page_size != kPage || n_q <= 0 || n_kv <= 0 || n_q % n_kv || n_q / n_kv > 16 || ring_tokens % kPage)
         return DFI_ERR_SHAPE;
-    if (n_splits < 1 || n_splits > 65535 || (n_splits > 1 && scratch == nullptr)) return DFI_ERR_SHAPE;
+    if (n_seqs > kMaxDecodeSeqs) return DFI_ERR_LIMIT;
+    if (scratch == nullptr || counters == nullptr) return DFI_ERR_SHAPE;
     if (q_stride % 8 || !aligned16(q) || !aligned16(k_cache) || !aligned16(v_cache)) return DFI_ERR_ALIGN;
     static bool configured = false;
     if (!configured) {
@@ -490,17 +639,14 @@ DFI_EXPORT int dfi_attention_decode(const void* q, int q_stride, void* out, int 
             return DFI_ERR_LAUNCH;
         configured = true;
     }
+    if (n_ctas <= 0) n_ctas = dfi_attention_decode_wave();
+    if (n_ctas <= 0) return DFI_ERR_LAUNCH;
+    if (n_ctas > 4096) n_ctas = 4096;
     float* part_o = scratch;
-    float* part_ml = scratch == nullptr ? nullptr : scratch + (size_t)n_seqs * n_q * n_splits * D;
-    dim3 grid(n_seqs * n_kv, n_splits);
-    launch(attention_decode_kernel, grid, kThreads, kDecodeSmem, (cudaStream_t)stream, 
-        (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_cache, (const bf16*)v_cache, block_table,
-        table_width, seq_start, n_q, n_kv, ring_tokens, window, scale * kLog2e, n_splits, part_o, part_ml);
+    float* part_ml = scratch + (size_t)n_ctas * 2 * 16 * D;
+    launch(attention_decode_kernel, n_ctas, kThreads, kDecodeSmem, (cudaStream_t)stream,
+           (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_cache, (const bf16*)v_cache, block_table,
+           table_width, seq_start, n_seqs, n_q, n_kv, ring_tokens, window, scale * kLog2e, part_o, part_ml, counters);
     DFI_CHECK_LAUNCH();
-    if (n_splits > 1) {
-        launch(attention_merge_kernel, n_seqs * n_q, D < 32 ? 32 : D, 0, (cudaStream_t)stream, 
-            part_o, part_ml, (bf16*)out, out_stride, n_q, n_splits);
-        DFI_CHECK_LAUNCH();
-    }
     return DFI_OK;
 }

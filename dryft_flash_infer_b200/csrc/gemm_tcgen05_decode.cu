@@ -21,7 +21,7 @@
 namespace dfi {
 
 constexpr int kDecThreads = 192;
-constexpr int kDecSmemBudget = 190 * 1024;
+constexpr int kDecSmemBudget = 110 * 1024;   // two CTAs fit an SM: the next kernel sets up and loads weights beside this one
 
 struct StreamShape {
     int M, N, K;          // N: columns of the output

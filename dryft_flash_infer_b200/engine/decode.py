@@ -43,11 +43,6 @@ class DecodeBatch:
         self.use_graph = use_graph
         self.q_lens = [1] * n
         self.max_kv_len = max_context
-        # the graph fixes the number of key-range parts: plan it for the largest group at full context
-        need = max((g.need for g in cache.groups), key=lambda k: k.n_kv_heads, default=None)
-        self.decode_splits = None
-        if need is not None and model.dtype == torch.bfloat16 and need.head_dim % 16 == 0 and need.head_dim <= 128:
-            self.decode_splits = kernels.decode_splits(n, need.n_kv_heads, max_context, need.head_dim)
         device = model.device
         sections = {"tokens": n, "row_seq": n, "row_pos": n, "seq_start": n, "seq_qlen": n, "seq_slot": n,
                     "cu_rows": n + 1, "wanted_rows": n, "uniforms": n}

@@ -199,27 +199,8 @@ def _attention_library(head_dim: int):
                      "dfi_attention_set_pdl")
 
 
-_DECODE_WAVE: dict[int, int] = {}
-
-
-def decode_splits(n_seqs: int, n_kv: int, max_kv_len: int, head_dim: int = 128) -> int:
-    """How many parts the key range of a decode step is cut into.
-
-    A part is whole pages; the CTAs (sequences x key/value heads x parts) run in waves of
-    as many as the GPU holds at once, and a wave lasts as long as its longest part.  The
-    number of parts is the one with the least ``waves x pages per part``, the smaller on ties.
-    """
-    if head_dim not in _DECODE_WAVE:
-        _DECODE_WAVE[head_dim] = _attention_library(head_dim).dfi_attention_decode_wave() or 4 * 148
-    wave = _DECODE_WAVE[head_dim]
-    tiles = max(1, -(-max_kv_len // 64))
-    groups = max(1, n_seqs * n_kv)
-    best, best_cost = 1, None
-    for parts in range(1, min(tiles, 64) + 1):
-        cost = -(-groups * parts // wave) * -(-tiles // parts) + 0.25 * (parts > 1)   # a merge is not free
-        if best_cost is None or cost < best_cost:
-            best, best_cost = parts, cost
-    return best
+DECODE_ATTENTION_MAX_SEQS = 1024
+_ATTENTION_SCRATCH: dict = {}
 
 
 def attention_prefill(q, cache, ctx, n_q: int, n_kv: int, head_dim: int, scale: float, window: int = 0):
@@ -236,23 +217,28 @@ def attention_prefill(q, cache, ctx, n_q: int, n_kv: int, head_dim: int, scale: 
 
 
 def attention_decode(q, cache, ctx, n_q: int, n_kv: int, head_dim: int, scale: float, window: int = 0,
-                     n_splits: int | None = None):
-    """Split-KV tensor-core attention (bfloat16) for steps with one query row per sequence."""
+                     n_ctas: int | None = None):
+    """Tensor-core attention (bfloat16) for steps with one query row per sequence: the pages of
+    all sequences are dealt to ``n_ctas`` CTAs (default: as many as run at once) in equal runs, and
+    the parts of a sequence that end up in different CTAs are merged by the last of them to finish."""
     _need_cuda(q, cache.k)
     assert q.dtype == torch.bfloat16 and q.stride(1) == 1 and q.shape == (ctx.n_seqs, n_q * head_dim)
-    if n_splits is None:
-        n_splits = getattr(ctx, "decode_splits", None) or decode_splits(ctx.n_seqs, n_kv, ctx.max_kv_len, head_dim)
     lib = _attention_library(head_dim)
+    if not n_ctas:
+        n_ctas = lib.dfi_attention_decode_wave()
+    n_ctas = min(n_ctas, 4096)
+    lib.dfi_attention_decode_scratch_floats.restype = ctypes.c_longlong
+    floats, n_counters = lib.dfi_attention_decode_scratch_floats(n_ctas), ctx.n_seqs * n_kv
+    held = _ATTENTION_SCRATCH.get(q.device)
+    if held is None or held[0].numel() < floats or held[1].numel() < n_counters:
+        held = (torch.empty(max(floats, held[0].numel() if held else 0), dtype=torch.float32, device=q.device),
+                torch.zeros(max(n_counters, 8192, held[1].numel() if held else 0), dtype=torch.int32, device=q.device))
+        _ATTENTION_SCRATCH[q.device] = held
     out = torch.empty((q.shape[0], n_q * head_dim), dtype=q.dtype, device=q.device)
-    scratch = None
-    if n_splits > 1:
-        lib.dfi_attention_decode_scratch_floats.restype = ctypes.c_longlong
-        scratch = torch.empty(lib.dfi_attention_decode_scratch_floats(ctx.n_seqs, n_q, n_splits),
-                              dtype=torch.float32, device=q.device)
     _check(lib.dfi_attention_decode(
         _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cache.k), _ptr(cache.v), _ptr(cache.block_table),
         cache.block_table.shape[1], _ptr(ctx.seq_start), ctx.n_seqs, n_q, n_kv, cache.page_size, cache.ring_tokens,
-        window, _f(scale), n_splits, _ptr(scratch), _stream()), "attention_decode",
+        window, _f(scale), n_ctas, _ptr(held[0]), _ptr(held[1]), _stream()), "attention_decode",
         f"head_dim {head_dim}, {n_q}/{n_kv} heads")
     return out
 
@@ -263,7 +249,7 @@ def attention(q: torch.Tensor, cache, ctx, n_q: int, n_kv: int, head_dim: int, s
     tensor-core kernels for bfloat16 and head sizes in steps of 16 up to 128, the plain
     kernel for float32 and for head sizes up to 256."""
     if q.dtype == torch.bfloat16 and head_dim % 16 == 0 and head_dim <= 128:
-        if ctx.all_decode and n_q // n_kv <= 16:
+        if ctx.all_decode and n_q // n_kv <= 16 and ctx.n_seqs <= DECODE_ATTENTION_MAX_SEQS:
             return attention_decode(q, cache, ctx, n_q, n_kv, head_dim, scale, window)
         return attention_prefill(q, cache, ctx, n_q, n_kv, head_dim, scale, window)
     return attention_generic(q, cache, ctx.row_seq, ctx.row_pos, n_q, n_kv, head_dim, scale, window)

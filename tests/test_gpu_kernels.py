@@ -263,17 +263,19 @@ def test_attention_tensor_core_prefill(n_q, n_kv, dim):
 
 
 @pytest.mark.parametrize("n_q, n_kv, dim", [(6, 3, 48), (4, 4, 16), (8, 2, 128), (32, 8, 128), (16, 1, 32), (3, 1, 64)])
-def test_attention_tensor_core_decode_with_splits(n_q, n_kv, dim):
+def test_attention_tensor_core_decode_dealt_to_any_number_of_ctas(n_q, n_kv, dim):
     from dryft_flash_infer_b200.ops import kernels
 
     dtype = torch.bfloat16
     lengths, new = [257, 64, 1, 1000, 65], [1, 1, 1, 1, 1]
     q, cache, row_seq, row_pos, scale, want = attention_case(dtype, n_q, n_kv, dim, lengths, new, seed=dim, sharp=5)
     ctx = step_like(lengths, new)
-    for splits in (None, 1, 2, 3, 16, 40):             # 40 parts of 16 pages: most are empty
-        got = kernels.attention_decode(q, cache, ctx, n_q, n_kv, dim, scale, n_splits=splits)
+    for ctas in (None, 1, 2, 3, 16, 40, 1000):         # however the pages are dealt out
+        got = kernels.attention_decode(q, cache, ctx, n_q, n_kv, dim, scale, n_ctas=ctas)
         assert torch.isfinite(got).all()
-        assert torch.allclose(got.float().cpu(), want, atol=tol(dtype, 2), rtol=tol(dtype)), splits
+        assert torch.allclose(got.float().cpu(), want, atol=tol(dtype, 2), rtol=tol(dtype)), ctas
+        again = kernels.attention_decode(q, cache, ctx, n_q, n_kv, dim, scale, n_ctas=ctas)
+        assert torch.equal(again, got)                 # the counters were left ready; the order of the merge is fixed
 
 
 def test_attention_tensor_core_window_edges():
@@ -290,10 +292,10 @@ def test_attention_tensor_core_window_edges():
         lengths, new = [500, 131, 40, 1], [1, 1, 1, 1]
         q, cache, row_seq, row_pos, scale, want = attention_case(dtype, 4, 2, 32, lengths, new, window=window,
                                                                  ring_tokens=ring, seed=window + 1)
-        for splits in (1, 3):
-            got = kernels.attention_decode(q, cache, step_like(lengths, new), 4, 2, 32, scale, window, n_splits=splits)
+        for ctas in (1, 3, 11, None):
+            got = kernels.attention_decode(q, cache, step_like(lengths, new), 4, 2, 32, scale, window, n_ctas=ctas)
             assert torch.isfinite(got).all()
-            assert torch.allclose(got.float().cpu(), want, atol=tol(dtype, 2), rtol=tol(dtype)), (window, splits)
+            assert torch.allclose(got.float().cpu(), want, atol=tol(dtype, 2), rtol=tol(dtype)), (window, ctas)
 
 
 @pytest.mark.parametrize("m", [1, 3, 8, 9, 17, 33, 64])
