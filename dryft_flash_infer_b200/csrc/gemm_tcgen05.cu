@@ -83,6 +83,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 if (MODE == MODE_SWIGLU) {
                     tma_load_2d(b_tile, &map_b, kc * kTileK, n0, &full_bar[s]);
                     tma_load_2d(b_tile + Cfg::kBBytes / 2, &map_b, kc * kTileK, rows_b + n0, &full_bar[s]);
+                } else if (MODE == MODE_NN) {
+                    // B is [K, N] with N contiguous: 64 x 64 boxes, one per 64 columns of the tile
+#pragma unroll
+                    for (int h = 0; h < BN / 64; ++h)
+                        tma_load_2d(b_tile + h * 8192, &map_b, n0 + h * 64, kc * kTileK, &full_bar[s]);
                 } else {
                     tma_load_2d(b_tile, &map_b, kc * kTileK, n0, &full_bar[s]);
                 }
@@ -92,7 +97,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         if (lane == 0) {
             // instruction descriptor: float32 accumulator, bfloat16 A and B, both K-major, N = BN, M = 128
             constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
-                                       ((uint32_t)(kTileM >> 4) << 24);
+                                       ((uint32_t)(kTileM >> 4) << 24) | (MODE == MODE_NN ? (1u << 16) : 0u);
             bool ok = true;
             for (int kc = 0; kc < k_chunks && ok; ++kc) {
                 const int s = kc % Cfg::kStages;
@@ -103,8 +108,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 const uint64_t a_desc = umma_desc(a_tile), b_desc = umma_desc(a_tile + Cfg::kABytes);
 #pragma unroll
                 for (int k = 0; k < kTileK / kUmmaK; ++k) {
-                    // 16 elements further along k = 32 bytes = 2 units of the descriptor's address field
-                    umma_bf16(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc, (kc > 0 || k > 0) ? 1u : 0u);
+                    // 16 elements further along k = 32 bytes = 2 units of the descriptor's address field;
+                    // in an MN-major tile 16 steps of k are 16 rows of 128 bytes
+                    const uint64_t b_k = MODE == MODE_NN ? umma_desc_mn(a_tile + Cfg::kABytes + k * 2048, 8192) : b_desc + 2 * k;
+                    umma_bf16(tmem_base, a_desc + 2 * k, b_k, idesc, (kc > 0 || k > 0) ? 1u : 0u);
                 }
                 umma_commit(&empty_bar[s]);        // the stage is free once these MMAs have read it
             }
@@ -211,7 +218,11 @@ static int launch_tc(const void* a, const void* b, void* out, int rows_a, int ro
     CUtensorMap map_a, map_b;
     const int b_rows_total = MODE == MODE_SWIGLU ? 2 * rows_b : rows_b;
     if (!make_tile_map(&map_a, a, rows_a, K, kTileM)) return DFI_ERR_LAUNCH;
-    if (!make_tile_map(&map_b, b, b_rows_total, K, MODE == MODE_SWIGLU ? BN / 2 : BN)) return DFI_ERR_LAUNCH;
+    if (MODE == MODE_NN) {
+        if (!make_tile_map(&map_b, b, K, rows_b, 64)) return DFI_ERR_LAUNCH;      // [K, N]: rows are k
+    } else if (!make_tile_map(&map_b, b, b_rows_total, K, MODE == MODE_SWIGLU ? BN / 2 : BN)) {
+        return DFI_ERR_LAUNCH;
+    }
     const int cols_per_tile = MODE == MODE_SWIGLU ? BN / 2 : BN;
     dim3 grid((rows_a + kTileM - 1) / kTileM, (rows_b + cols_per_tile - 1) / cols_per_tile);
     launch(gemm_tcgen05_kernel<BN, MODE>, grid, kTcThreads, Cfg::kSmemBytes, st, map_a, map_b, out, rows_a, rows_b, K, ldo, out_dtype);
@@ -237,6 +248,7 @@ DFI_EXPORT int dfi_gemm_tcgen05_error(int reset) {
 // mode 0: out[M, N] = x[M, K] . w[N, K]^T            (x rows on the 128-row side)
 // mode 1: out[M, N] = silu(x . gate^T) * (x . up^T), w = [gate; up] of 2N rows
 // mode 2: the same product as mode 0 computed with w on the 128-row side (M <= 256: small batches)
+// mode 3: out[M, N] = x[M, K] . w[K, N] with w stored [K, N] (N contiguous)
 // K a multiple of 8, x and w 16-byte aligned and contiguous; out row stride = N.
 DFI_EXPORT int dfi_gemm_tcgen05(const void* x, const void* w, void* out, int M, int N, int K, int mode, int out_dtype,
                                 void* stream) {
@@ -252,6 +264,9 @@ DFI_EXPORT int dfi_gemm_tcgen05(const void* x, const void* w, void* out, int M, 
     } else if (mode == MODE_SWIGLU) {
         if (N % 8) return DFI_ERR_SHAPE;
         rc = launch_tc<256, MODE_SWIGLU>(x, w, out, M, N, K, N, out_dtype, st);
+    } else if (mode == MODE_NN) {
+        if (N % 8) return DFI_ERR_SHAPE;
+        rc = launch_tc<128, MODE_NN>(x, w, out, M, N, K, N, out_dtype, st);
     } else if (mode == MODE_SWAP) {
         if (M <= 16) rc = launch_tc<16, MODE_SWAP>(w, x, out, N, M, K, N, out_dtype, st);
         else if (M <= 32) rc = launch_tc<32, MODE_SWAP>(w, x, out, N, M, K, N, out_dtype, st);

@@ -15,7 +15,7 @@ constexpr int kTcThreads = 192;
 constexpr int kSmemBudget = 200 * 1024;
 constexpr uint32_t kSpinLimit = 1u << 22;     // tries of mbarrier.try_wait before giving up
 
-enum { MODE_NORMAL = 0, MODE_SWIGLU = 1, MODE_SWAP = 2 };
+enum { MODE_NORMAL = 0, MODE_SWIGLU = 1, MODE_SWAP = 2, MODE_NN = 3 };
 
 // one error word per translation unit (each .cu that includes this header reads its own)
 static __device__ int g_tc_error = 0;
@@ -50,6 +50,12 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
 __device__ __forceinline__ uint64_t umma_desc(const void* tile) {
     // K-major, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart
     return (uint64_t)((s32(tile) >> 4) & 0x3FFF) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+// MN-major operand (rows of the tile run along k, each row holds 64 contiguous elements of the M or
+// N side, 128-byte swizzle): 8-row groups 1024 bytes apart, 64-element column blocks `block_bytes` apart.
+__device__ __forceinline__ uint64_t umma_desc_mn(const void* tile, uint32_t block_bytes) {
+    return (uint64_t)((s32(tile) >> 4) & 0x3FFF) | ((uint64_t)((block_bytes >> 4) & 0x3FFF) << 16) | (64ull << 32) |
+           (1ull << 46) | (2ull << 61);
 }
 __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
@@ -86,9 +92,10 @@ __device__ __forceinline__ float silu_times(float gate, float up) { return gate 
 
 
 // A [rows, K] bfloat16 matrix (row stride K) as a TMA map with boxes of box_rows x 64, 128-byte swizzle.
-static inline bool make_tile_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
+static inline bool make_tile_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows,
+                                 long long row_stride_elems = 0) {
     cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+    cuuint64_t strides[1] = {(cuuint64_t)(row_stride_elems > 0 ? row_stride_elems : K) * 2};
     cuuint32_t box[2] = {(cuuint32_t)kTileK, (cuuint32_t)box_rows};
     cuuint32_t elem[2] = {1, 1};
     return cuTensorMapEncodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,

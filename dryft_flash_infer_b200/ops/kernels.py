@@ -325,7 +325,7 @@ def skinny_linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype 
     return out
 
 
-TC_NORMAL, TC_SWIGLU, TC_SWAP = 0, 1, 2
+TC_NORMAL, TC_SWIGLU, TC_SWAP, TC_NN = 0, 1, 2, 3
 
 
 def tc_linear(x: torch.Tensor, weight: torch.Tensor, mode: int = TC_NORMAL,
@@ -338,9 +338,14 @@ def tc_linear(x: torch.Tensor, weight: torch.Tensor, mode: int = TC_NORMAL,
     """
     _need_cuda(x, weight)
     m, k = x.shape
-    assert x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and weight.shape[1] == k
+    assert x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
     assert x.is_contiguous() and weight.is_contiguous()
-    n = weight.shape[0] // 2 if mode == TC_SWIGLU else weight.shape[0]
+    if mode == TC_NN:                       # weight is [K, N]
+        assert weight.shape[0] == k
+        n = weight.shape[1]
+    else:
+        assert weight.shape[1] == k
+        n = weight.shape[0] // 2 if mode == TC_SWIGLU else weight.shape[0]
     if k % 8 or (mode != TC_SWAP and n % 8):
         raise KernelError(f"tc_linear takes K and N in steps of 8, got K={k}, N={n}")
     out_dtype = out_dtype or x.dtype

@@ -411,3 +411,17 @@ def test_tcgen05_decode_gemm_with_swiglu(m, inter, k):
         got = kernels.decode_linear(x.cuda(), w.cuda(), torch.float32, swiglu=True, n_ctas=ctas)
         assert kernels.tc_error() == 0
         assert torch.allclose(got.cpu(), want, atol=3e-3, rtol=2e-3), (ctas, float((got.cpu() - want).abs().max()))
+
+
+@pytest.mark.parametrize("m, n, k", [(128, 128, 64), (300, 320, 200), (256, 256, 1024)])
+def test_tcgen05_gemm_with_a_row_major_second_operand(m, n, k):
+    """out = x @ w for w stored [K, N]: the operand layout the value product of attention uses."""
+    from dryft_flash_infer_b200.ops import kernels
+
+    g = torch.Generator().manual_seed(m + n + k)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    w = (torch.randn(k, n, generator=g) * 0.05).to(torch.bfloat16)
+    want = x.float() @ w.float()
+    got = kernels.tc_linear(x.cuda(), w.cuda(), kernels.TC_NN, torch.float32)
+    assert kernels.tc_error() == 0
+    assert torch.allclose(got.cpu(), want, atol=2e-3, rtol=1e-3), float((got.cpu() - want).abs().max())
