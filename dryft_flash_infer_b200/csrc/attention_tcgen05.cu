@@ -1,0 +1,352 @@
+// Causal grouped-query flash attention for prompts on the fifth-generation tensor cores
+// (head sizes 64 and 128, bfloat16), reading keys and values from the paged cache.
+//
+// One CTA owns 128 query rows of one head of one sequence and walks the sequence's pages of 64
+// keys up to the diagonal (or through the window).  Per page:
+//     S = Q K^T      tcgen05.mma, M = 128, N = 64, operands in shared memory (TMA, 128-byte swizzle),
+//                    accumulator in tensor memory (two buffers, so the next S is computed while
+//                    this one is being turned into probabilities)
+//     P = exp2(S * scale - max)   by 128 threads, one query row each: a row's maximum and sum need
+//                    no exchange between threads; the online softmax is the reference's
+//                    (engine/kernels/attention.py:40-137) with float32 maximum, sum and output
+//     O_page = P V   tcgen05.mma with P (bfloat16, written to shared memory in the swizzled layout)
+//                    as the 128-row operand and V, as it lies in the cache ([key][d]), as an
+//                    MN-major second operand; the page's product is added into the thread's
+//                    float32 output row, which is rescaled when the maximum moves
+// Warp 0 feeds a ring of K/V pages with TMA, warp 1 issues the MMAs, warps 2-5 do the softmax and
+// the output.  Every wait on an mbarrier is bounded (see tcgen05.cuh).
+//
+// Rows of the last page that no token was written to may hold anything: their scores are
+// replaced (not added to) by -inf, and their value rows are zeroed in shared memory before use.
+#include "tcgen05.cuh"
+
+#ifndef DFI_HEAD_DIM
+#define DFI_HEAD_DIM 128
+#endif
+
+namespace dfi {
+
+#if DFI_HEAD_DIM == 64 || DFI_HEAD_DIM == 128
+#define DFI_FA_ENABLED 1
+constexpr int kFaD = DFI_HEAD_DIM;
+#else
+#define DFI_FA_ENABLED 0
+constexpr int kFaD = 128;
+#endif
+
+constexpr int kFaRows = 128;                          // query rows per CTA
+constexpr int kFaKeys = 64;                           // keys per page
+constexpr int kFaThreads = 192;
+constexpr int kFaBlocks = kFaD / 64;                  // 64-wide column blocks of a head
+constexpr int kFaQBytes = kFaRows * kFaD * 2;
+constexpr int kFaKBytes = kFaKeys * kFaD * 2;
+constexpr int kFaPBytes = kFaRows * kFaKeys * 2;
+constexpr int kFaStages = 3;
+constexpr int kFaSmem = kFaQBytes + kFaStages * 2 * kFaKBytes + 2 * kFaPBytes + 1024;
+constexpr int kFaTmemCols = 256;                      // S0 at 0, S1 at 64, O_page at 128
+constexpr float kFaLog2e = 1.4426950408889634f;
+
+__device__ __forceinline__ void fa_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(s32(bar)) : "memory");
+}
+__device__ __forceinline__ float fa_exp2(float x) {
+    float y;
+    asm volatile("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+
+#if DFI_FA_ENABLED
+__global__ void __launch_bounds__(kFaThreads, 1)
+attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                            const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out, int out_stride,
+                            const int* __restrict__ block_table, int table_width, const int* __restrict__ cu_rows,
+                            const int* __restrict__ seq_start, int n_q, int n_kv, int ring_tokens, int window,
+                            float scale_log2) {
+    pdl_launch_next();
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ __align__(8) uint64_t q_full, kv_full[kFaStages], kv_empty[kFaStages];
+    __shared__ __align__(8) uint64_t s_full[2], s_empty[2], p_full[2], pv_done[2], o_empty;
+    __shared__ uint32_t tmem_base_s;
+
+    unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    unsigned char* q_s = base;                                   // [blocks][128 rows][128 bytes]
+    unsigned char* kv_s = q_s + kFaQBytes;                       // [stages][K: blocks x 64 x 128 B | V: blocks x 64 x 128 B]
+    unsigned char* p_s = kv_s + kFaStages * 2 * kFaKBytes;       // [2][128 rows][128 bytes]
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int seq = blockIdx.z, head = blockIdx.y;
+    const int row0 = cu_rows[seq], q_len = cu_rows[seq + 1] - row0;
+    // the heaviest tiles (the last rows of a prompt) are started first
+    const int n_row_tiles = (q_len + kFaRows - 1) / kFaRows;
+    if ((int)blockIdx.x >= n_row_tiles) return;
+    const int r0 = (n_row_tiles - 1 - blockIdx.x) * kFaRows;
+    const int rows_here = min(kFaRows, q_len - r0);
+    const int start = seq_start[seq];
+    const int kv_len = start + q_len;
+    const int kv_head = head / (n_q / n_kv);
+    const int* table = block_table + (size_t)seq * table_width;
+    const int last_key = start + r0 + rows_here - 1;
+    const int first_key = window > 0 ? max(0, start + r0 - window + 1) : 0;
+    const int t_begin = first_key / kFaKeys, t_end = last_key / kFaKeys;
+    const int n_tiles = t_end - t_begin + 1;
+
+    if (threadIdx.x == 0) {
+        mbar_init(&q_full, 1);
+        for (int i = 0; i < kFaStages; ++i) {
+            mbar_init(&kv_full[i], 1);
+            mbar_init(&kv_empty[i], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&s_full[i], 1);
+            mbar_init(&s_empty[i], 128);
+            mbar_init(&p_full[i], 128);
+            mbar_init(&pv_done[i], 1);
+        }
+        mbar_init(&o_empty, 128);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(s32(&tmem_base_s)), "r"(kFaTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const uint32_t tmem_base = tmem_base_s;
+    pdl_wait();        // the queries and this step's keys and values come from the kernel before
+
+    if (warp == 0) {
+        if (lane == 0) {
+            mbar_expect_tx(&q_full, kFaQBytes);
+#pragma unroll
+            for (int b = 0; b < kFaBlocks; ++b)
+                tma_load_2d(q_s + b * (kFaRows * 128), &map_q, head * kFaD + b * 64, row0 + r0, &q_full);
+            for (int j = 0; j < n_tiles; ++j) {
+                const int st = j % kFaStages;
+                const uint32_t round = j / kFaStages;
+                if (round > 0 && !mbar_wait(&kv_empty[st], (round - 1) & 1, 11)) break;
+                const int tile = t_begin + j;
+                const int place = place_of(tile * kFaKeys, ring_tokens);
+                const int page = table[place / kFaKeys];
+                const int cache_row = (page * n_kv + kv_head) * kFaKeys;
+                unsigned char* k_tile = kv_s + (size_t)st * 2 * kFaKBytes;
+                unsigned char* v_tile = k_tile + kFaKBytes;
+                mbar_expect_tx(&kv_full[st], 2 * kFaKBytes);
+#pragma unroll
+                for (int b = 0; b < kFaBlocks; ++b) {
+                    tma_load_2d(k_tile + b * (kFaKeys * 128), &map_k, b * 64, cache_row, &kv_full[st]);
+                    tma_load_2d(v_tile + b * (kFaKeys * 128), &map_v, b * 64, cache_row, &kv_full[st]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // S = Q K^T: N = 64 keys.  O_page = P V: N = head size, second operand MN-major.
+        constexpr uint32_t idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kFaKeys >> 3) << 17) | ((uint32_t)(kFaRows >> 4) << 24);
+        constexpr uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(kFaD >> 3) << 17) | ((uint32_t)(kFaRows >> 4) << 24);
+        bool ok = mbar_wait(&q_full, 0, 12);
+        auto issue_pv = [&](int j) {
+            // the page's P is in shared memory, and the output of the page before has been taken
+            if (!mbar_wait(&p_full[j & 1], (j >> 1) & 1, 13)) return false;
+            if (j >= 1 && !mbar_wait(&o_empty, (j - 1) & 1, 14)) return false;
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            const int st = j % kFaStages;
+            unsigned char* v_tile = kv_s + (size_t)st * 2 * kFaKBytes + kFaKBytes;
+            // value rows of keys that were never written (only in a sequence's last page) are zeroed
+            const int dead_from = kv_len - (t_begin + j) * kFaKeys;
+            if (dead_from < kFaKeys) {
+                for (int i = lane; i < (kFaKeys - max(dead_from, 0)) * 8 * kFaBlocks; i += 32) {
+                    const int b = i / ((kFaKeys - max(dead_from, 0)) * 8), rest = i % ((kFaKeys - max(dead_from, 0)) * 8);
+                    const int row = max(dead_from, 0) + rest / 8, chunk = rest % 8;
+                    *reinterpret_cast<uint4*>(v_tile + b * (kFaKeys * 128) + row * 128 + chunk * 16) = make_uint4(0, 0, 0, 0);
+                }
+                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                __syncwarp();
+            }
+            if (lane == 0) {
+                const uint64_t p_desc = umma_desc(p_s + (j & 1) * kFaPBytes);
+#pragma unroll
+                for (int k = 0; k < kFaKeys / kUmmaK; ++k)
+                    umma_bf16(tmem_base + 128, p_desc + 2 * k, umma_desc_mn(v_tile + k * 2048, kFaKeys * 128), idesc_pv, k > 0 ? 1u : 0u);
+                umma_commit(&pv_done[j & 1]);
+                umma_commit(&kv_empty[st]);
+            }
+            __syncwarp();
+            return true;
+        };
+        for (int j = 0; j < n_tiles && ok; ++j) {
+            const int st = j % kFaStages;
+            ok = mbar_wait(&kv_full[st], (j / kFaStages) & 1, 15);
+            if (ok && j >= 2) ok = mbar_wait(&s_empty[j & 1], ((j >> 1) - 1) & 1, 16);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            if (lane == 0) {
+                const unsigned char* k_tile = kv_s + (size_t)st * 2 * kFaKBytes;
+#pragma unroll
+                for (int kk = 0; kk < kFaD / kUmmaK; ++kk) {
+                    const uint64_t a = umma_desc(q_s + (kk / 4) * (kFaRows * 128)) + 2 * (kk % 4);
+                    const uint64_t b = umma_desc(k_tile + (kk / 4) * (kFaKeys * 128)) + 2 * (kk % 4);
+                    umma_bf16(tmem_base + (j & 1) * 64, a, b, idesc_qk, kk > 0 ? 1u : 0u);
+                }
+                umma_commit(&s_full[j & 1]);
+            }
+            __syncwarp();
+            if (j >= 1) ok = issue_pv(j - 1);
+        }
+        if (ok) issue_pv(n_tiles - 1);
+    } else {
+        // ---- softmax and output: thread `t` owns query row r0 + t (tensor-memory lane t)
+        const int quarter = warp & 3;
+        const int t = quarter * 32 + lane;
+        const int pos = start + r0 + t;
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        float o[kFaD];
+#pragma unroll
+        for (int d = 0; d < kFaD; ++d) o[d] = 0.f;
+        float m = -INFINITY, l = 0.f;
+        bool ok = true;
+        auto take_page_output = [&](int j) {
+            if (!mbar_wait(&pv_done[j & 1], (j >> 1) & 1, 17)) return false;
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+#pragma unroll
+            for (int c = 0; c < kFaD; c += 32) {
+                uint32_t v[32];
+                tmem_load32(lane_addr + 128 + c, v);
+#pragma unroll
+                for (int e = 0; e < 32; ++e) o[c + e] += __uint_as_float(v[e]);
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            fa_arrive(&o_empty);
+            return true;
+        };
+        for (int j = 0; j < n_tiles && ok; ++j) {
+            ok = mbar_wait(&s_full[j & 1], (j >> 1) & 1, 18);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            uint32_t sv[64];
+            {
+                uint32_t half[32];
+                tmem_load32(lane_addr + (j & 1) * 64, half);
+#pragma unroll
+                for (int e = 0; e < 32; ++e) sv[e] = half[e];
+                tmem_load32(lane_addr + (j & 1) * 64 + 32, half);
+#pragma unroll
+                for (int e = 0; e < 32; ++e) sv[32 + e] = half[e];
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            fa_arrive(&s_empty[j & 1]);
+
+            const int key0 = (t_begin + j) * kFaKeys;
+            const bool partial = key0 + kFaKeys - 1 > pos || (window > 0 && key0 < pos - window + 1);
+            float mx = -INFINITY;
+#pragma unroll
+            for (int e = 0; e < 64; ++e) {
+                float x = __uint_as_float(sv[e]) * scale_log2;
+                if (partial) {
+                    const int key = key0 + e;
+                    const bool seen = key <= pos && (window <= 0 || key > pos - window);
+                    x = seen ? x : -INFINITY;
+                }
+                sv[e] = __float_as_uint(x);
+                mx = fmaxf(mx, x);
+            }
+            const float m_new = fmaxf(m, mx);
+            const float m_use = m_new == -INFINITY ? 0.f : m_new;
+            const float corr = fa_exp2(m - m_use);
+            // the page before is added in before the row is rescaled for this one
+            if (j >= 1) ok = take_page_output(j - 1);
+            if (!ok) break;
+            float sum = 0.f;
+            uint32_t packed[32];
+#pragma unroll
+            for (int e = 0; e < 64; e += 2) {
+                const float p0 = fa_exp2(__uint_as_float(sv[e]) - m_use);
+                const float p1 = fa_exp2(__uint_as_float(sv[e + 1]) - m_use);
+                sum += p0 + p1;
+                __nv_bfloat162 pair = __floats2bfloat162_rn(p0, p1);
+                packed[e >> 1] = *reinterpret_cast<uint32_t*>(&pair);
+            }
+            l = l * corr + sum;
+            m = m_new;
+#pragma unroll
+            for (int d = 0; d < kFaD; ++d) o[d] *= corr;
+            // row t of P: 128 bytes, its 16-byte pieces placed as the 128-byte swizzle places them
+            unsigned char* p_row = p_s + (j & 1) * kFaPBytes + t * 128;
+#pragma unroll
+            for (int c = 0; c < 8; ++c)
+                *reinterpret_cast<uint4*>(p_row + ((c ^ (t & 7)) << 4)) =
+                    make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+            fa_arrive(&p_full[j & 1]);
+        }
+        if (ok) ok = take_page_output(n_tiles - 1);
+        if (ok && t < rows_here) {
+            const float inv = l > 0.f ? 1.0f / l : 0.f;
+            bf16* dst = out + (size_t)(row0 + r0 + t) * out_stride + (size_t)head * kFaD;
+#pragma unroll
+            for (int d = 0; d < kFaD; d += 8) {
+                float v[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[e] = o[d + e] * inv;
+                store16(dst + d, v);
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(kFaTmemCols) : "memory");
+    }
+}
+#endif  // DFI_FA_ENABLED
+
+}  // namespace dfi
+
+using namespace dfi;
+
+DFI_EXPORT int dfi_attention_prefill_tc_error(int reset) {
+    int value = 0;
+    if (cudaMemcpyFromSymbol(&value, g_tc_error, sizeof(int)) != cudaSuccess) return -1;
+    if (reset && value != 0) {
+        const int zero = 0;
+        cudaMemcpyToSymbol(g_tc_error, &zero, sizeof(int));
+    }
+    return value;
+}
+
+// 1 if this build (head size) has the tcgen05 prefill kernel.
+DFI_EXPORT int dfi_attention_prefill_tc_available() { return DFI_FA_ENABLED; }
+
+// q [rows, q_stride] (the head's columns start at head * head_dim), out [rows, out_stride];
+// k_cache, v_cache [pages, n_kv, 64, head_dim]; cache_pages = number of pages in them.
+DFI_EXPORT int dfi_attention_prefill_tc(const void* q, int q_rows, int q_stride, void* out, int out_stride,
+                                        const void* k_cache, const void* v_cache, long long cache_pages,
+                                        const int* block_table, int table_width, const int* cu_rows,
+                                        const int* seq_start, int n_seqs, int max_q_len, int n_q, int n_kv,
+                                        int page_size, int ring_tokens, int window, float scale, void* stream) {
+#if DFI_FA_ENABLED
+    if (n_seqs <= 0 || max_q_len <= 0) return DFI_OK;
+    if (page_size != kFaKeys || n_q <= 0 || n_kv <= 0 || n_q % n_kv || ring_tokens % kFaKeys) return DFI_ERR_SHAPE;
+    if (q_stride % 8 || out_stride % 8 || !aligned16(q) || !aligned16(out) || !aligned16(k_cache) || !aligned16(v_cache))
+        return DFI_ERR_ALIGN;
+    if (n_q > 65535 || n_seqs > 65535) return DFI_ERR_LIMIT;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kFaSmem) != cudaSuccess)
+            return DFI_ERR_LAUNCH;
+        configured = true;
+    }
+    CUtensorMap map_q, map_k, map_v;
+    const long long cache_rows = cache_pages * n_kv * kFaKeys;
+    if (cache_rows > 0x7fffffffLL) return DFI_ERR_LIMIT;
+    if (!make_tile_map(&map_q, q, q_rows, n_q * kFaD, kFaRows, q_stride)) return DFI_ERR_LAUNCH;
+    if (!make_tile_map(&map_k, k_cache, (int)cache_rows, kFaD, kFaKeys)) return DFI_ERR_LAUNCH;
+    if (!make_tile_map(&map_v, v_cache, (int)cache_rows, kFaD, kFaKeys)) return DFI_ERR_LAUNCH;
+    dim3 grid((max_q_len + kFaRows - 1) / kFaRows, n_q, n_seqs);
+    launch(attention_prefill_tc_kernel, grid, kFaThreads, kFaSmem, (cudaStream_t)stream, map_q, map_k, map_v, (bf16*)out,
+           out_stride, block_table, table_width, cu_rows, seq_start, n_q, n_kv, ring_tokens, window, scale * kFaLog2e);
+    DFI_CHECK_LAUNCH();
+    return DFI_OK;
+#else
+    return DFI_ERR_SHAPE;
+#endif
+}

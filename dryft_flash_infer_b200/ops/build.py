@@ -32,9 +32,9 @@ COMMON_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcomp
 #: sources of the core library; further modules (built per head size) name their own
 CORE_SOURCES = ["elementwise.cu", "attention_generic.cu", "sampling.cu", "skinny_gemm.cu", "gemm_tcgen05.cu", "gemm_tcgen05_decode.cu"]
 #: the tensor-core attention, built once per head size (-DDFI_HEAD_DIM=...)
-ATTENTION_SOURCES = ["attention_mma.cu"]
+ATTENTION_SOURCES = ["attention_mma.cu", "attention_tcgen05.cu"]
 #: head sizes compiled ahead by ``all_libraries`` (others compile at first use)
-PREBUILT_HEAD_DIMS = (16, 32, 128)
+PREBUILT_HEAD_DIMS = (16, 32, 64, 128)
 
 
 class BuildError(RuntimeError):

@@ -216,6 +216,28 @@ def attention_prefill(q, cache, ctx, n_q: int, n_kv: int, head_dim: int, scale: 
     return out
 
 
+def attention_prefill_tc(q, cache, ctx, n_q: int, n_kv: int, head_dim: int, scale: float, window: int = 0):
+    """Flash attention for prompts on tcgen05 (head sizes 64 and 128): TMA-fed pages of keys and values,
+    scores and the page's output in tensor memory, one thread per query row for the softmax."""
+    _need_cuda(q, cache.k)
+    assert q.dtype == torch.bfloat16 and q.stride(1) == 1 and q.shape[1] == n_q * head_dim
+    lib = _attention_library(head_dim)
+    if not lib.dfi_attention_prefill_tc_available():
+        raise KernelError(f"attention_prefill_tc: head_dim {head_dim} has no tcgen05 kernel (64 and 128 have)")
+    out = torch.empty((q.shape[0], n_q * head_dim), dtype=q.dtype, device=q.device)
+    _check(lib.dfi_attention_prefill_tc(
+        _ptr(q), q.shape[0], q.stride(0), _ptr(out), out.stride(0), _ptr(cache.k), _ptr(cache.v),
+        ctypes.c_longlong(cache.k.shape[0]), _ptr(cache.block_table), cache.block_table.shape[1], _ptr(ctx.cu_rows),
+        _ptr(ctx.seq_start), ctx.n_seqs, ctx.max_q_len, n_q, n_kv, cache.page_size, cache.ring_tokens, window,
+        _f(scale), _stream()), "attention_prefill_tc", f"head_dim {head_dim}, {n_q}/{n_kv} heads")
+    return out
+
+
+def attention_tc_error(head_dim: int, reset: bool = True) -> int:
+    """0, or the code of the first bounded wait that ran out in the tcgen05 attention kernel (synchronises)."""
+    return _attention_library(head_dim).dfi_attention_prefill_tc_error(int(reset))
+
+
 def attention_decode(q, cache, ctx, n_q: int, n_kv: int, head_dim: int, scale: float, window: int = 0,
                      n_ctas: int | None = None):
     """Tensor-core attention (bfloat16) for steps with one query row per sequence: the pages of
@@ -246,11 +268,14 @@ def attention_decode(q, cache, ctx, n_q: int, n_kv: int, head_dim: int, scale: f
 def attention(q: torch.Tensor, cache, ctx, n_q: int, n_kv: int, head_dim: int, scale: float,
               window: int = 0) -> torch.Tensor:
     """Attention of a step's query rows over the cache, by the kernel that fits: the
-    tensor-core kernels for bfloat16 and head sizes in steps of 16 up to 128, the plain
-    kernel for float32 and for head sizes up to 256."""
+    tensor-core kernels for bfloat16 and head sizes in steps of 16 up to 128 (prompts with head
+    size 64 or 128 on tcgen05, the others and decoding on mma.sync), the plain kernel for float32
+    and for head sizes up to 256."""
     if q.dtype == torch.bfloat16 and head_dim % 16 == 0 and head_dim <= 128:
         if ctx.all_decode and n_q // n_kv <= 16 and ctx.n_seqs <= DECODE_ATTENTION_MAX_SEQS:
             return attention_decode(q, cache, ctx, n_q, n_kv, head_dim, scale, window)
+        if head_dim in (64, 128):
+            return attention_prefill_tc(q, cache, ctx, n_q, n_kv, head_dim, scale, window)
         return attention_prefill(q, cache, ctx, n_q, n_kv, head_dim, scale, window)
     return attention_generic(q, cache, ctx.row_seq, ctx.row_pos, n_q, n_kv, head_dim, scale, window)
 

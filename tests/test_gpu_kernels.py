@@ -425,3 +425,25 @@ def test_tcgen05_gemm_with_a_row_major_second_operand(m, n, k):
     got = kernels.tc_linear(x.cuda(), w.cuda(), kernels.TC_NN, torch.float32)
     assert kernels.tc_error() == 0
     assert torch.allclose(got.cpu(), want, atol=2e-3, rtol=1e-3), float((got.cpu() - want).abs().max())
+
+
+@pytest.mark.parametrize("n_q, n_kv, dim", [(8, 2, 128), (3, 1, 64), (4, 4, 128), (32, 8, 128)])
+def test_attention_tcgen05_prefill(n_q, n_kv, dim):
+    from dryft_flash_infer_b200.ops import kernels
+
+    dtype = torch.bfloat16
+    for lengths, new in (([70, 3, 130], [70, 3, 130]), ([70, 3, 200], [10, 3, 67]), ([257, 64, 1], [1, 1, 1]),
+                         ([300], [300]), ([700, 129], [257, 128])):
+        q, cache, row_seq, row_pos, scale, want = attention_case(dtype, n_q, n_kv, dim, lengths, new, seed=dim, sharp=5)
+        got = kernels.attention_prefill_tc(q, cache, step_like(lengths, new), n_q, n_kv, dim, scale)
+        assert kernels.attention_tc_error(dim) == 0
+        assert torch.isfinite(got).all(), (lengths, new)
+        assert torch.allclose(got.float().cpu(), want, atol=tol(dtype, 2), rtol=tol(dtype)), (lengths, new)
+    for window, ring in ((100, 192), (64, 128), (130, 320)):
+        lengths, new = [500, 131, 40], [3, 2, 40]
+        q, cache, row_seq, row_pos, scale, want = attention_case(dtype, n_q, n_kv, dim, lengths, new, window=window,
+                                                                 ring_tokens=ring, seed=window)
+        got = kernels.attention_prefill_tc(q, cache, step_like(lengths, new), n_q, n_kv, dim, scale, window)
+        assert kernels.attention_tc_error(dim) == 0
+        assert torch.isfinite(got).all()
+        assert torch.allclose(got.float().cpu(), want, atol=tol(dtype, 2), rtol=tol(dtype)), window
