@@ -237,38 +237,35 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 
             const int key0 = (t_begin + j) * kFaKeys;
             const bool partial = key0 + kFaKeys - 1 > pos || (window > 0 && key0 < pos - window + 1);
+            // the maximum is kept in the scores' own units; the scale enters in the exponent's multiply-add
             float mx = -INFINITY;
+            if (partial) {
 #pragma unroll
-            for (int e = 0; e < 64; ++e) {
-                float x = __uint_as_float(sv[e]) * scale_log2;
-                if (partial) {
+                for (int e = 0; e < 64; ++e) {
                     const int key = key0 + e;
                     const bool seen = key <= pos && (window <= 0 || key > pos - window);
-                    x = seen ? x : -INFINITY;
+                    const float x = seen ? __uint_as_float(sv[e]) : -INFINITY;
+                    sv[e] = __float_as_uint(x);
+                    mx = fmaxf(mx, x);
                 }
-                sv[e] = __float_as_uint(x);
-                mx = fmaxf(mx, x);
+            } else {
+#pragma unroll
+                for (int e = 0; e < 64; ++e) mx = fmaxf(mx, __uint_as_float(sv[e]));
             }
             const float m_new = fmaxf(m, mx);
             const float m_use = m_new == -INFINITY ? 0.f : m_new;
-            const float corr = fa_exp2(m - m_use);
-            // the page before is added in before the row is rescaled for this one
-            if (j >= 1) ok = take_page_output(j - 1);
-            if (!ok) break;
+            const float corr = fa_exp2((m - m_use) * scale_log2);
+            const float shift = -m_use * scale_log2;
             float sum = 0.f;
             uint32_t packed[32];
 #pragma unroll
             for (int e = 0; e < 64; e += 2) {
-                const float p0 = fa_exp2(__uint_as_float(sv[e]) - m_use);
-                const float p1 = fa_exp2(__uint_as_float(sv[e + 1]) - m_use);
+                const float p0 = fa_exp2(fmaf(__uint_as_float(sv[e]), scale_log2, shift));
+                const float p1 = fa_exp2(fmaf(__uint_as_float(sv[e + 1]), scale_log2, shift));
                 sum += p0 + p1;
                 __nv_bfloat162 pair = __floats2bfloat162_rn(p0, p1);
                 packed[e >> 1] = *reinterpret_cast<uint32_t*>(&pair);
             }
-            l = l * corr + sum;
-            m = m_new;
-#pragma unroll
-            for (int d = 0; d < kFaD; ++d) o[d] *= corr;
             // row t of P: 128 bytes, its 16-byte pieces placed as the 128-byte swizzle places them
             unsigned char* p_row = p_s + (j & 1) * kFaPBytes + t * 128;
 #pragma unroll
@@ -277,6 +274,16 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
             fa_arrive(&p_full[j & 1]);
+            // while the tensor core multiplies this page's P by V: add the page before into the row,
+            // then rescale the row for this page's maximum (skipped when no row of the warp moved)
+            if (j >= 1) ok = take_page_output(j - 1);
+            if (!ok) break;
+            l = l * corr + sum;
+            m = m_new;
+            if (__any_sync(0xffffffffu, corr != 1.0f)) {
+#pragma unroll
+                for (int d = 0; d < kFaD; ++d) o[d] *= corr;
+            }
         }
         if (ok) ok = take_page_output(n_tiles - 1);
         if (ok && t < rows_here) {
