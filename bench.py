@@ -159,7 +159,7 @@ def main() -> int:
     parser.add_argument("--layers", type=int, default=QWEN3_4B["num_hidden_layers"],
                         help="fewer layers than the configuration has (both numbers are reported)")
     parser.add_argument("--quick", action="store_true", help="skip the batch 1/64 points and the end-to-end run")
-    parser.add_argument("--profile", choices=["decode", "prefill"],
+    parser.add_argument("--profile", choices=["decode", "prefill", "timeline"],
                         help="run only a few plain (graph-less) decode steps or one prefill, for a profiler; prints no JSON")
     parser.add_argument("--batch", type=int, default=BATCH, help="batch of the --profile decode steps")
     args = parser.parse_args()
@@ -191,6 +191,33 @@ def main() -> int:
         engine.decoder.use_graph = False
         ms, launches = time_decode(engine, args.batch, CONTEXT, steps, warmup)
         print(f"profile run: {steps} plain decode steps at batch {args.batch}, {ms:.3f} ms and {launches} launches per step")
+        return 0
+    if args.profile == "timeline":
+        # kernel records of one graph replay: when each kernel of a layer ends after the one before it
+        from torch.profiler import ProfilerActivity, profile
+        from dryft_flash_infer_b200.sampling import SamplingParams
+
+        slots = fill_context(engine, args.batch, CONTEXT - 64)
+        tokens = [3] * args.batch
+        for i in range(5):
+            tokens = engine.decode(slots, tokens, list(range(args.batch)), 1 + i, SamplingParams())
+        torch.cuda.synchronize()
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            for i in range(3):
+                tokens = engine.decode(slots, tokens, list(range(args.batch)), 10 + i, SamplingParams())
+            torch.cuda.synchronize()
+        events = sorted((e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA),
+                        key=lambda e: e.time_range.end)
+        marks = [i for i, e in enumerate(events) if "argmax" in e.name]
+        step = events[marks[0] + 1: marks[1] + 1]
+        kernels_only = [e for e in step if "Memcpy" not in e.name]
+        per_layer = (len(kernels_only) - 4) // args.layers
+        first = 2 + per_layer * min(2, args.layers - 1)           # a layer in the middle of the model
+        before = kernels_only[first - 1].time_range.end
+        print(f"step span {step[-1].time_range.end - step[0].time_range.start:.1f} us, {len(kernels_only)} kernels")
+        for e in kernels_only[first: first + per_layer]:
+            print(f"  ends {e.time_range.end - before:6.1f} us after the kernel before   {e.name[:70]}")
+            before = e.time_range.end
         return 0
     if args.profile == "prefill":
         slot = engine.open_slot()
