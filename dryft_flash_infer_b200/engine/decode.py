@@ -56,6 +56,11 @@ class DecodeBatch:
         self.host_np = self.host.numpy()
         self.device_buffer = torch.zeros(total, dtype=torch.int32, device=device)
         self.tokens_host = torch.zeros(n, dtype=torch.int32).pin_memory()
+        # results come back through two pinned buffers in turn, so that the host can read one step's
+        # tokens while the next step is already running
+        self.result_host = [torch.zeros(n, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self.result_event = [torch.cuda.Event() for _ in range(2)]
+        self.launched = 0
 
         def dev(name, size):
             return self.device_buffer[self.offsets[name]: self.offsets[name] + size]
@@ -99,8 +104,9 @@ class DecodeBatch:
         first = self.first_refreshed
         self.device_buffer[first:].copy_(self.host[first:], non_blocking=True)
 
-    def run(self, slots: list[int], tokens: list[int] | None, uniforms=None) -> list[int]:
-        """One decode step for ``slots``.  ``tokens`` None means: the tokens the last step chose."""
+    def launch(self, slots: list[int], tokens: list[int] | None, uniforms=None) -> int:
+        """Starts one decode step for ``slots`` and returns a ticket for ``fetch``.  ``tokens`` None
+        means: the tokens the last step chose (they are still on the device)."""
         book = self.cache.book
         for slot in slots:
             book.reserve(slot, 1)
@@ -128,9 +134,23 @@ class DecodeBatch:
             self.graph.replay()
         for slot in slots:
             book.advance(slot, 1)
-        self.tokens_host.copy_(self.tokens, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-        return self.tokens_host.tolist()
+        ticket = self.launched
+        self.launched += 1
+        self.result_host[ticket & 1].copy_(self.tokens, non_blocking=True)
+        self.result_event[ticket & 1].record()
+        return ticket
+
+    def fetch(self, ticket: int) -> list[int]:
+        """The tokens chosen by the step that ``launch`` gave ``ticket`` for (at most one newer step
+        may have been launched since)."""
+        if ticket < self.launched - 2:
+            raise RuntimeError("the result of this decode step has been overwritten by later steps")
+        self.result_event[ticket & 1].synchronize()
+        return self.result_host[ticket & 1].tolist()
+
+    def run(self, slots: list[int], tokens: list[int] | None, uniforms=None) -> list[int]:
+        """One decode step for ``slots``, waited for."""
+        return self.fetch(self.launch(slots, tokens, uniforms))
 
 
 class Decoder:
@@ -143,22 +163,48 @@ class Decoder:
         self.batches: dict[tuple, DecodeBatch] = {}
         self.last: tuple | None = None
 
-    def decode(self, slots: list[int], tokens: list[int], requests: list[int], step_index: int,
-               params: SamplingParams) -> list[int]:
+    def _batch_for(self, n: int, params: SamplingParams) -> tuple[tuple, DecodeBatch]:
         cache = self.cache
         widths = [max(1, -(-(g.ring_tokens or cache.max_context) // cache.page_size)) for g in cache.groups]
-        key = (len(slots), tuple(widths), params.temperature)
+        key = (n, tuple(widths), params.temperature)
         batch = self.batches.get(key)
         if batch is None:
             if len(self.batches) >= 16:
                 self.batches.pop(next(iter(self.batches)))
-            batch = self.batches[key] = DecodeBatch(self.model, cache, len(slots), widths, cache.max_context,
+            batch = self.batches[key] = DecodeBatch(self.model, cache, n, widths, cache.max_context,
                                                     params.temperature, self.use_graph)
+        return key, batch
+
+    def decode_launch(self, slots: list[int], tokens: list[int] | None, requests: list[int], step_index: int,
+                      params: SamplingParams):
+        """Starts one decode step and returns a handle whose ``result()`` gives the chosen tokens.
+        ``tokens`` None: ``slots`` are the slots of the step launched last, fed what that step chose."""
+        key, batch = self._batch_for(len(slots), params)
+        if tokens is None and self.last != (key, tuple(slots)):
+            raise ValueError("tokens=None needs the same slots as the decode step launched last")
         uniforms = None
         if params.temperature > 0:
             uniforms = [uniform_for(params.seed, r, step_index) for r in requests]
-        same = self.last == (key, tuple(slots)) and batch.last_out == list(tokens)
-        out = batch.run(list(slots), None if same else list(tokens), uniforms)
-        batch.last_out = out
+        ticket = batch.launch(list(slots), None if tokens is None else list(tokens), uniforms)
         self.last = (key, tuple(slots))
+        return DecodeHandle(batch, ticket)
+
+    def decode(self, slots: list[int], tokens: list[int], requests: list[int], step_index: int,
+               params: SamplingParams) -> list[int]:
+        key, batch = self._batch_for(len(slots), params)
+        same = self.last == (key, tuple(slots)) and batch.last_out == list(tokens)
+        out = self.decode_launch(slots, None if same else tokens, requests, step_index, params).result()
+        batch.last_out = out
+        return out
+
+
+class DecodeHandle:
+    """A decode step that has been launched; ``result()`` waits for it and returns its tokens."""
+
+    def __init__(self, batch: DecodeBatch, ticket: int):
+        self.batch, self.ticket = batch, ticket
+
+    def result(self) -> list[int]:
+        out = self.batch.fetch(self.ticket)
+        self.batch.last_out = out
         return out

@@ -151,6 +151,12 @@ class Engine:
         device, so no logits cross to the host."""
         return self.decoder.decode(slots, tokens, requests, step_index, params)
 
+    def decode_launch(self, slots: list[int], tokens: list[int] | None, requests: list[int], step_index: int,
+                      params: SamplingParams):
+        """Like ``decode`` without the wait: returns a handle whose ``result()`` gives the tokens.  With
+        ``tokens`` None the step is fed what the step launched last chose, which never left the device."""
+        return self.decoder.decode_launch(slots, tokens, requests, step_index, params)
+
     def select(self, logits, requests: list[int], step_index: int, params: SamplingParams) -> list[int]:
         return select_tokens(logits, params, requests, step_index).tolist()
 

@@ -9,10 +9,14 @@ device:
     step(entries) -> logits        (entries: list of StepEntry; one logits row per wanted place)
     select(logits, requests, step_index, params) -> list[int]
     decode(slots, tokens, requests, step_index, params) -> list[int]     (optional)
+    decode_launch(slots, tokens or None, requests, step_index, params) -> handle with result()   (optional)
 
 ``decode`` is one step of one token per sequence with the choice of the next token
 folded in; a backend that has it is given the decode steps whole, so that it can keep
-them on the device.
+them on the device.  With ``decode_launch`` the loop starts the next step before it reads
+the tokens of the one before (as the reference's stream stays one step ahead of the host,
+engine/engine.py:1159-1185) whenever it knows without them who goes on: no stop tokens, and
+nobody reaches its length at this step.
 
 Behaviour follows the reference's ``generate`` (engine/engine.py:1121-1157): one list
 with one token per sequence for every output step, exactly ``max_new_tokens`` of them,
@@ -61,13 +65,29 @@ def generate_batch(backend, requests: list[Request], params: SamplingParams) -> 
         entries = [StepEntry(slots[i], list(requests[i].prompt), [len(requests[i].prompt) - 1]) for i in live]
         step_index = 0
         fused_decode = getattr(backend, "decode", None)
+        launch_decode = getattr(backend, "decode_launch", None)
+        if any(requests[i].stop_token_ids for i in live):
+            launch_decode = None                      # who goes on depends on the tokens themselves
+        in_flight = None                              # a launched step whose tokens have not been read
         while live:
             ids = [requests[i].request_id for i in live]
-            if step_index > 0 and fused_decode is not None:
+            ahead = None
+            if step_index == 0:
+                chosen = backend.select(backend.step(entries), ids, step_index, params)
+            elif launch_decode is not None:
+                if in_flight is None:
+                    in_flight = launch_decode([slots[i] for i in live], [requests[i].output[-1] for i in live], ids,
+                                              step_index, params)
+                # if nobody ends with the step in flight, the one after it can start before its tokens are read
+                if all(len(requests[i].output) + 1 < requests[i].max_new_tokens for i in live):
+                    ahead = launch_decode([slots[i] for i in live], None, ids, step_index + 1, params)
+                chosen = in_flight.result()
+            elif fused_decode is not None:
                 chosen = fused_decode([slots[i] for i in live], [requests[i].output[-1] for i in live], ids,
                                       step_index, params)
             else:
                 chosen = backend.select(backend.step(entries), ids, step_index, params)
+            in_flight = ahead
             row: list[int | None] = [None] * len(requests)
             still = []
             for i, token in zip(live, chosen):

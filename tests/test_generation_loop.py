@@ -142,3 +142,62 @@ def test_request_ids_reach_the_sampler_and_uniforms_do_not_depend_on_the_batch()
     assert 0.0 <= u < 1.0 and u == uniform_for(3, 41, 5)
     assert len({uniform_for(3, r, s) for r in range(20) for s in range(20)}) > 390
     assert abs(sum(uniform_for(1, r, 0) for r in range(4000)) / 4000 - 0.5) < 0.03
+
+
+class AsyncBackend(FakeBackend):
+    """A backend that can start a decode step without waiting for it; it logs what happens in order."""
+
+    def __init__(self):
+        super().__init__()
+        self.log = []
+        self.device_tokens = {}
+
+    def decode_launch(self, slots, tokens, requests, step_index, params):
+        backend = self
+        if tokens is None:                       # fed from the device: what the step launched last chose
+            tokens = [backend.device_tokens[s] for s in slots]
+            self.log.append(("launch-from-device", step_index))
+        else:
+            self.log.append(("launch-from-host", step_index))
+        chosen = []
+        for slot, token in zip(slots, tokens):
+            self.held[slot].append(token)
+            chosen.append(sum(self.held[slot]) % 50)
+            backend.device_tokens[slot] = chosen[-1]
+
+        class Handle:
+            def result(self_inner):
+                backend.log.append(("read", step_index))
+                return chosen
+
+        return Handle()
+
+
+def test_the_next_step_starts_before_the_last_one_is_read():
+    backend = AsyncBackend()
+    prompts = [[1, 2, 3], [4, 5]]
+    requests = [Request(p, 5, request_id=i) for i, p in enumerate(prompts)]
+    rows = list(generate_batch(backend, requests, SamplingParams()))
+    assert [[r[i] for r in rows] for i in range(2)] == [expected(p, 5) for p in prompts]
+    # step 1 is launched with host tokens, steps 2.. from the device, each before the step before it is read;
+    # the last step (4) is not followed by another launch
+    assert backend.log == [("launch-from-host", 1), ("launch-from-device", 2), ("read", 1), ("launch-from-device", 3),
+                           ("read", 2), ("launch-from-device", 4), ("read", 3), ("read", 4)]
+    assert backend.held == {}
+
+
+def test_lookahead_stops_where_a_sequence_ends_and_with_stop_tokens():
+    backend = AsyncBackend()
+    requests = [Request([1, 2, 3], 3, request_id=0), Request([4, 5], 5, request_id=1)]
+    rows = list(generate_batch(backend, requests, SamplingParams()))
+    assert requests[0].output == expected([1, 2, 3], 3) and requests[1].output == expected([4, 5], 5)
+    assert rows[3][0] is None and rows[4][0] is None
+    # step 2 ends request 0: nothing is launched ahead of it; step 3 starts from the host with the survivor
+    assert ("launch-from-host", 3) in backend.log and ("launch-from-device", 3) not in backend.log
+    assert backend.log.index(("read", 2)) < backend.log.index(("launch-from-host", 3))
+    # with stop tokens nothing is ever launched ahead
+    backend = AsyncBackend()
+    backend.decode = lambda slots, tokens, requests, step_index, params: \
+        backend.decode_launch(slots, tokens, requests, step_index, params).result()
+    list(generate_batch(backend, [Request([1, 2, 3], 4, stop_token_ids=(49,))], SamplingParams()))
+    assert all(kind != "launch-from-device" for kind, _ in backend.log)
