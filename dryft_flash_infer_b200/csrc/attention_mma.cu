@@ -279,12 +279,23 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
 struct DecodeRun {
     int total;      // units of the whole step
     int n_ctas;
+    int parts;      // > 0: every group has `tiles` pages and is cut into this many parts, one CTA each
+    int tiles;
 };
+// First unit of a CTA's run: equal contiguous runs over all units, or (when every sequence brings
+// the same number of pages) the same number of parts for every group, so that no run crosses from
+// one group into the next.
 __device__ __forceinline__ int dec_run_begin(const DecodeRun& r, int cta) {
+    if (r.parts > 0) {
+        if (cta >= r.n_ctas) return r.total;
+        return (cta / r.parts) * r.tiles + r.tiles * (cta % r.parts) / r.parts;
+    }
     return (int)((unsigned long long)r.total * (unsigned)cta / (unsigned)r.n_ctas);
 }
 __device__ __forceinline__ int dec_cta_of_unit(const DecodeRun& r, int u) {
-    int c = (int)((unsigned long long)u * (unsigned)r.n_ctas / (unsigned)r.total);
+    int c;
+    if (r.parts > 0) c = (u / r.tiles) * r.parts + min(r.parts - 1, (u % r.tiles) * r.parts / r.tiles);
+    else c = (int)((unsigned long long)u * (unsigned)r.n_ctas / (unsigned)r.total);
     while (c + 1 < r.n_ctas && dec_run_begin(r, c + 1) <= u) ++c;
     while (c > 0 && dec_run_begin(r, c) > u) --c;
     return c;
@@ -322,6 +333,7 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
     __shared__ int cum_s[kMaxDecodeSeqs + 1];        // pages of the sequences before each one
     __shared__ int warp_tot_s[4];
     __shared__ int warp_max_s[4];
+    __shared__ int warp_min_s[4];
     __shared__ int ticket_s;
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -333,16 +345,18 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
     {
         const int per = (n_seqs + kThreads - 1) / kThreads;
         const int lo = min(n_seqs, (int)threadIdx.x * per), hi = min(n_seqs, lo + per);
-        int mine = 0, longest = 0;
+        int mine = 0, longest = 0, shortest = 0x7fffffff;
         for (int i = lo; i < hi; ++i) {
             const int pos = seq_start[i];
             const int first_key = window > 0 ? max(0, pos - window + 1) : 0;
             const int tiles = pos / kPage - first_key / kPage + 1;
             mine += tiles;
             longest = max(longest, tiles);
+            shortest = min(shortest, tiles);
         }
         longest = __reduce_max_sync(0xffffffffu, longest);
-        if (lane == 0) warp_max_s[warp] = longest;
+        shortest = __reduce_min_sync(0xffffffffu, shortest);
+        if (lane == 0) { warp_max_s[warp] = longest; warp_min_s[warp] = shortest; }
         int incl = mine;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
@@ -367,8 +381,20 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
     // A CTA takes at least four pages, and enough of them that no sequence is spread over more than
     // kMaxParts CTAs (the merge holds all the parts of a group at once).
     const int longest = max(max(warp_max_s[0], warp_max_s[1]), max(warp_max_s[2], warp_max_s[3]));
+    const int shortest = min(min(warp_min_s[0], warp_min_s[1]), min(warp_min_s[2], warp_min_s[3]));
     const int least = max(4, (longest + kMaxParts - 3) / (kMaxParts - 2));
     run.n_ctas = max(1, min((int)gridDim.x, run.total / least));
+    run.parts = 0;
+    run.tiles = longest;
+    if (shortest == longest) {
+        // every group has the same number of pages: the same number of parts for each, none crossing over
+        const int per_cta = max(least, (run.total + (int)gridDim.x - 1) / (int)gridDim.x);
+        const int parts = max(1, longest / per_cta);
+        if (n_seqs * n_kv * parts <= (int)gridDim.x) {       // else: more groups than CTAs, runs must cross
+            run.parts = parts;
+            run.n_ctas = n_seqs * n_kv * parts;
+        }
+    }
     const int cta = blockIdx.x;
     atrace(1);
     pdl_wait();        // from here on the queries and the new keys and values are read

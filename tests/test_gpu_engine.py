@@ -260,3 +260,54 @@ def test_engine_errors_are_loud(folders):
     engine.close_slot(a)
     with pytest.raises(CacheError, match="freed twice"):
         engine.close_slot(a)
+
+
+QWEN3_4B_WIDTHS = {
+    "architectures": ["Qwen3ForCausalLM"], "num_hidden_layers": 2, "hidden_size": 2560, "num_attention_heads": 32,
+    "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 9728, "vocab_size": 151936,
+    "rope_theta": 5000000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": True, "hidden_act": "silu",
+    "max_position_embeddings": 40960,
+}
+
+
+def test_layer_sizes_of_the_benchmark_model_against_the_float32_path():
+    """Two layers at the widths of Qwen3-4B (the sizes the tcgen05 kernels are built for): the bfloat16
+    engine against the true float32 engine on the same random weights, cut three ways."""
+    from dryft_flash_infer_b200 import Engine, StepEntry
+
+    engines = {d: Engine(config=QWEN3_4B_WIDTHS, random_weights=True, seed=5, dtype=d, max_tokens=2048)
+               for d in ("float32", "bfloat16")}
+    # the float32 engine's weights are the bfloat16 engine's, widened: random weights are rounded first
+    for e32, e16 in zip(engines["float32"].model._buffers.values(), engines["bfloat16"].model._buffers.values()):
+        for name in e32:
+            e32[name].copy_(e16[name].float())
+    g = torch.Generator().manual_seed(9)
+    prompts = [torch.randint(0, 151936, (n,), generator=g).tolist() for n in (300, 64, 129, 7)]
+    out = {}
+    for dtype, engine in engines.items():
+        rows = []
+        slots = [engine.open_slot() for _ in prompts]
+        first = engine.step([StepEntry(s, p[:-3], [len(p) - 4, 0]) for s, p in zip(slots, prompts)])
+        rows.append(first)
+        for t in (3, 2, 1):
+            rows.append(engine.step([StepEntry(s, [p[len(p) - t]], [0]) for s, p in zip(slots, prompts)]))
+        for s in slots:
+            engine.close_slot(s)
+        # and the first prompt whole, alone
+        slot = engine.open_slot()
+        rows.append(engine.step([StepEntry(slot, prompts[0], [0, 150, 299])]))
+        engine.close_slot(slot)
+        out[dtype] = torch.cat(rows).float().cpu()
+        # the decode path on fixed buffers (graph) gives the same tokens as the step function's logits
+        tokens = [r[0] for r in engine.generate([prompts[1]], 3)]
+        slot = engine.open_slot()
+        lg = engine.step([StepEntry(slot, prompts[1], [len(prompts[1]) - 1])])
+        engine.close_slot(slot)
+        assert tokens[0] == int(lg[0].argmax())
+    from dryft_flash_infer_b200.ops import kernels
+    assert kernels.tc_error() == 0 and kernels.attention_tc_error(128) == 0
+    want, got = out["float32"], out["bfloat16"]
+    assert torch.isfinite(got).all()
+    # whole prompt alone and in the batch agree in float32 to rounding (row 0 of the batch = place 296 of prompt 0 ...)
+    err = float((got - want).abs().max())
+    assert err <= 0.03 * max(1.0, float(want.abs().max())), err
