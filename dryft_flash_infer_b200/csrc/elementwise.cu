@@ -137,6 +137,11 @@ __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out
 // cos may be null (no rotation).  cos/sin are [max_positions, D/2] float32.
 constexpr int kMaxPairsPerLane = 4;  // D <= 256
 
+__device__ __forceinline__ float2 load2(const float* p) { return *reinterpret_cast<const float2*>(p); }
+__device__ __forceinline__ float2 load2(const bf16* p) { return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p)); }
+__device__ __forceinline__ void store2(float* p, float2 v) { *reinterpret_cast<float2*>(p) = v; }
+__device__ __forceinline__ void store2(bf16* p, float2 v) { *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(v.x, v.y); }
+
 template <typename T>
 __global__ void qk_norm_rope_write_kernel(T* __restrict__ qkv, int row_stride, int n_q, int n_kv, int D,
                                           const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
@@ -168,15 +173,16 @@ __global__ void qk_norm_rope_write_kernel(T* __restrict__ qkv, int row_stride, i
         dst = cache + (((size_t)page * n_kv + kv_head) * page_size + place % page_size) * D;
     }
 
-    float lo[kMaxPairsPerLane], hi[kMaxPairsPerLane];
+    // a lane takes two neighbouring elements of each half at a time (head sizes are multiples of 4)
+    float2 lo[kMaxPairsPerLane / 2], hi[kMaxPairsPerLane / 2];
     float ssq = 0.f;
 #pragma unroll
-    for (int j = 0; j < kMaxPairsPerLane; ++j) {
-        const int i = lane + 32 * j;
+    for (int j = 0; j < kMaxPairsPerLane / 2; ++j) {
+        const int i = 2 * lane + 64 * j;
         if (i < half) {
-            lo[j] = to_float(src[i]);
-            hi[j] = to_float(src[i + half]);
-            ssq += lo[j] * lo[j] + hi[j] * hi[j];
+            lo[j] = load2(src + i);
+            hi[j] = load2(src + i + half);
+            ssq += lo[j].x * lo[j].x + lo[j].y * lo[j].y + hi[j].x * hi[j].x + hi[j].y * hi[j].y;
         }
     }
     const float* w = is_q ? q_w : (is_k ? k_w : nullptr);
@@ -184,11 +190,12 @@ __global__ void qk_norm_rope_write_kernel(T* __restrict__ qkv, int row_stride, i
         ssq = warp_sum(ssq);
         const float scale = 1.0f / sqrtf(ssq / (float)D + eps);
 #pragma unroll
-        for (int j = 0; j < kMaxPairsPerLane; ++j) {
-            const int i = lane + 32 * j;
+        for (int j = 0; j < kMaxPairsPerLane / 2; ++j) {
+            const int i = 2 * lane + 64 * j;
             if (i < half) {
-                lo[j] = lo[j] * scale * w[i];
-                hi[j] = hi[j] * scale * w[i + half];
+                const float2 wl = *reinterpret_cast<const float2*>(w + i), wh = *reinterpret_cast<const float2*>(w + i + half);
+                lo[j].x *= scale * wl.x; lo[j].y *= scale * wl.y;
+                hi[j].x *= scale * wh.x; hi[j].y *= scale * wh.y;
             }
         }
     }
@@ -196,17 +203,17 @@ __global__ void qk_norm_rope_write_kernel(T* __restrict__ qkv, int row_stride, i
     const float* c = rotate ? cos_t + (size_t)row_pos[row] * half : nullptr;
     const float* s = rotate ? sin_t + (size_t)row_pos[row] * half : nullptr;
 #pragma unroll
-    for (int j = 0; j < kMaxPairsPerLane; ++j) {
-        const int i = lane + 32 * j;
+    for (int j = 0; j < kMaxPairsPerLane / 2; ++j) {
+        const int i = 2 * lane + 64 * j;
         if (i < half) {
-            float a = lo[j], b = hi[j];
+            float2 a = lo[j], b = hi[j];
             if (rotate) {
-                const float cv = c[i], sv = s[i];
-                a = lo[j] * cv - hi[j] * sv;
-                b = hi[j] * cv + lo[j] * sv;
+                const float2 cv = *reinterpret_cast<const float2*>(c + i), sv = *reinterpret_cast<const float2*>(s + i);
+                a.x = lo[j].x * cv.x - hi[j].x * sv.x; a.y = lo[j].y * cv.y - hi[j].y * sv.y;
+                b.x = hi[j].x * cv.x + lo[j].x * sv.x; b.y = hi[j].y * cv.y + lo[j].y * sv.y;
             }
-            dst[i] = from_float<T>(a);
-            dst[i + half] = from_float<T>(b);
+            store2(dst + i, a);
+            store2(dst + i + half, b);
         }
     }
 }
@@ -325,7 +332,8 @@ DFI_EXPORT int dfi_qk_norm_rope_write(void* qkv, int rows, int row_stride, int n
                                       void* v_cache, const int* block_table, int table_width, int page_size,
                                       int ring_tokens, int write_cache, int dtype, void* stream) {
     if (rows <= 0) return DFI_OK;
-    if (head_dim <= 0 || head_dim % 2 || head_dim > 64 * kMaxPairsPerLane) return DFI_ERR_SHAPE;
+    if (head_dim <= 0 || head_dim % 4 || head_dim > 64 * kMaxPairsPerLane) return DFI_ERR_SHAPE;
+    if (row_stride % 2) return DFI_ERR_ALIGN;
     if (n_q < 0 || n_kv < 0 || page_size <= 0 || table_width <= 0) return DFI_ERR_SHAPE;
     cudaStream_t st = (cudaStream_t)stream;
     const int warps = 4;

@@ -159,8 +159,8 @@ def qk_norm_rope_write(qkv: torch.Tensor, n_q: int, n_kv: int, head_dim: int, q_
     assert row_pos.dtype == torch.int32 and row_seq.dtype == torch.int32
     assert cache.k.dtype == qkv.dtype and cache.k.is_contiguous() and cache.v.is_contiguous()
     assert cache.k.shape[1] == n_kv and cache.k.shape[3] == head_dim and cache.k.shape[2] == cache.page_size
-    if head_dim % 2 or head_dim > 256:
-        raise KernelError(f"qk_norm_rope_write: head_dim {head_dim} must be even and at most 256")
+    if head_dim % 4 or head_dim > 256:
+        raise KernelError(f"qk_norm_rope_write: head_dim {head_dim} must be a multiple of 4 and at most 256")
     for w in (q_weight, k_weight):
         assert w is None or (w.dtype == torch.float32 and w.numel() == head_dim)
     if cos is not None:
