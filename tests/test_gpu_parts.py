@@ -229,3 +229,60 @@ def test_a_toy_mixer_with_state_is_registered_built_and_stepped(dtype):
     slot = other.open_slot()
     changed = other.step([StepEntry(slot, seqs[0], list(range(len(seqs[0]))))])
     assert float((changed - whole[: len(seqs[0])]).abs().max()) > 10 * tol or dtype == "bfloat16"
+
+
+def test_rotary_tables_alone():
+    from dryft_flash_infer_b200.parts import PartSpec, build_part
+
+    rotary = build_part("position", PartSpec("rotary", {"head_dim": 48, "theta": 12345.0}), hidden_size=0)
+    rotary.prepare(300, "cuda")
+    angles = plain_model.rope_angles(torch.arange(300), 48, 12345.0)[:, :24]
+    assert rotary.cos.shape == (300, 24) and rotary.cos.dtype == torch.float32
+    assert torch.allclose(rotary.cos.cpu(), angles.cos(), atol=1e-6) and torch.allclose(rotary.sin.cpu(), angles.sin(), atol=1e-6)
+    with pytest.raises(ValueError, match="even"):
+        build_part("position", PartSpec("rotary", {"head_dim": 15, "theta": 1.0}), hidden_size=0)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_pre_norm_block_alone(dtype):
+    """The arrangement alone: two blocks chained by (residual, pending), against the unfused formulas."""
+    from dryft_flash_infer_b200.cache import SequenceCache
+    from dryft_flash_infer_b200.engine import StepContext, StepEntry
+    from dryft_flash_infer_b200.parts import PartSpec, build_part, part_factory
+
+    hidden, eps = 64, 1e-5
+
+    def make(seed):
+        mixer = build_part("mixer", PartSpec("attention", {"n_heads": 4, "n_kv_heads": 2, "head_dim": 16, "qk_norm": False}), hidden)
+        ffn = build_part("feed_forward", PartSpec("swiglu", {"intermediate_size": 96}), hidden)
+        n1 = build_part("norm", PartSpec("rms_norm", {"eps": eps}), hidden)
+        n2 = build_part("norm", PartSpec("rms_norm", {"eps": eps}), hidden)
+        w = {name: fill(part, dtype, seed + i, std=0.2) for i, (name, part) in
+             enumerate((("mixer", mixer), ("ffn", ffn), ("n1", n1), ("n2", n2)))}
+        return part_factory("block", "pre_norm")(mixer, ffn, n1, n2), w
+
+    blocks = [make(10), make(20)]
+    cache = SequenceCache({0: blocks[0][0].mixer.cache_need(), 1: blocks[1][0].mixer.cache_need()}, {}, max_tokens=256,
+                          max_seqs=1, max_context=256, step_tokens=64, dtype=dtype, device="cuda")
+    x = torch.randn(20, hidden).to(dtype)
+    slot = cache.open_slot()
+    entries = [StepEntry(slot, [0] * 20)]
+    cache.book.reserve(slot, 20)
+    ctx = StepContext(entries, cache, "cuda")
+    residual, pending = x.cuda().clone(), None
+    for i, (block, _) in enumerate(blocks):
+        residual, pending = block.forward(residual, pending, ctx, cache.layer_view(i, ctx.block_tables, True), None)
+    got = (residual.float() + pending.float()).cpu()
+
+    ref = x.float()
+    for block, w in blocks:
+        h = plain_model.rms_norm(ref, w["n1"]["weight"], eps)
+        q = (h @ w["mixer"]["qkv"][:64].T).view(20, 4, 16)
+        k = (h @ w["mixer"]["qkv"][64:96].T).view(20, 2, 16)
+        v = (h @ w["mixer"]["qkv"][96:].T).view(20, 2, 16)
+        ref = ref + plain_model.causal_attention(q, k, v).reshape(20, 64) @ w["mixer"]["o"].T
+        h = plain_model.rms_norm(ref, w["n2"]["weight"], eps)
+        names = {"g.gate_proj.weight": w["ffn"]["gate_up"][:96], "g.up_proj.weight": w["ffn"]["gate_up"][96:],
+                 "g.down_proj.weight": w["ffn"]["down"]}
+        ref = ref + plain_model.swiglu_mlp(h, names, "g.")
+    close(got, ref, dtype, scale=2.0)
