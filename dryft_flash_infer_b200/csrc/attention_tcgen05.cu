@@ -304,6 +304,286 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(kFaTmemCols) : "memory");
     }
 }
+
+// ------------------------------------------------------------------ two query tiles per CTA
+// For prompts longer than one tile: a CTA owns 256 query rows as two tiles of 128, each with a
+// softmax warp group of its own, and the tensor core alternates between them, so that the scores of
+// one tile are turned into probabilities while the other tile's products run.  The output rows stay
+// in tensor memory and are accumulated there by the MMA itself; a row is rescaled (by its softmax
+// thread, between two pages) only when its maximum has grown by more than 2^8 since the scale was
+// last fixed, which after the first pages of a row happens rarely.  A tcgen05.commit arrives only
+// when every MMA issued before it is complete, so "scores of page j+1 are ready" also tells the
+// softmax threads that the product of page j has finished reading P and writing the output.
+constexpr int kFa2Threads = 320;                                   // producer, issuer, 2 x 4 softmax warps
+constexpr int kFa2Smem = 2 * kFaQBytes + kFaStages * 2 * kFaKBytes + 2 * kFaPBytes + 1024;
+constexpr int kFa2TmemCols = 512;                                  // S of tile X at 64 X, output of tile X at 128 + 128 X
+constexpr float kFaRescaleStep = 8.0f;                             // in log2 units
+
+__global__ void __launch_bounds__(kFa2Threads, 1)
+attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                             const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out, int out_stride,
+                             const int* __restrict__ block_table, int table_width, const int* __restrict__ cu_rows,
+                             const int* __restrict__ seq_start, int n_q, int n_kv, int ring_tokens, int window,
+                             float scale_log2) {
+    pdl_launch_next();
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ __align__(8) uint64_t q_full, kv_full[kFaStages], kv_empty[kFaStages];
+    __shared__ __align__(8) uint64_t s_full[2], p_full[2], all_done;
+    __shared__ uint32_t tmem_base_s;
+
+    unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    unsigned char* q_s = base;                                   // [tile][blocks][128 rows][128 bytes]
+    unsigned char* kv_s = q_s + 2 * kFaQBytes;
+    unsigned char* p_s = kv_s + kFaStages * 2 * kFaKBytes;       // [tile][128 rows][128 bytes]
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int seq = blockIdx.z, head = blockIdx.y;
+    const int row0 = cu_rows[seq], q_len = cu_rows[seq + 1] - row0;
+    const int n_row_tiles = (q_len + 2 * kFaRows - 1) / (2 * kFaRows);
+    if ((int)blockIdx.x >= n_row_tiles) return;
+    const int r0 = (n_row_tiles - 1 - blockIdx.x) * 2 * kFaRows;          // the heaviest rows first
+    const int rows_here = min(2 * kFaRows, q_len - r0);
+    const bool has_b = rows_here > kFaRows;
+    const int start = seq_start[seq];
+    const int kv_len = start + q_len;
+    const int kv_head = head / (n_q / n_kv);
+    const int* table = block_table + (size_t)seq * table_width;
+    const int first_key = window > 0 ? max(0, start + r0 - window + 1) : 0;
+    const int t_begin = first_key / kFaKeys;
+    // pages each tile walks (both start at t_begin; a tile stops at its own diagonal)
+    const int n_a = (start + r0 + min(rows_here, kFaRows) - 1) / kFaKeys - t_begin + 1;
+    const int n_b = has_b ? (start + r0 + rows_here - 1) / kFaKeys - t_begin + 1 : 0;
+    const int n_tiles = max(n_a, n_b);
+
+    if (threadIdx.x == 0) {
+        mbar_init(&q_full, 1);
+        for (int i = 0; i < kFaStages; ++i) {
+            mbar_init(&kv_full[i], 1);
+            mbar_init(&kv_empty[i], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&s_full[i], 1);
+            mbar_init(&p_full[i], 128);
+        }
+        mbar_init(&all_done, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(s32(&tmem_base_s)), "r"(kFa2TmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const uint32_t tmem_base = tmem_base_s;
+    pdl_wait();
+
+    if (warp == 0) {
+        if (lane == 0) {
+            mbar_expect_tx(&q_full, (has_b ? 2 : 1) * kFaQBytes);
+            for (int x = 0; x < (has_b ? 2 : 1); ++x)
+#pragma unroll
+                for (int b = 0; b < kFaBlocks; ++b)
+                    tma_load_2d(q_s + x * kFaQBytes + b * (kFaRows * 128), &map_q, head * kFaD + b * 64,
+                                row0 + r0 + x * kFaRows, &q_full);
+            for (int j = 0; j < n_tiles; ++j) {
+                const int st = j % kFaStages;
+                const uint32_t round = j / kFaStages;
+                if (round > 0 && !mbar_wait(&kv_empty[st], (round - 1) & 1, 21)) break;
+                const int place = place_of((t_begin + j) * kFaKeys, ring_tokens);
+                const int page = table[place / kFaKeys];
+                const int cache_row = (page * n_kv + kv_head) * kFaKeys;
+                unsigned char* k_tile = kv_s + (size_t)st * 2 * kFaKBytes;
+                unsigned char* v_tile = k_tile + kFaKBytes;
+                mbar_expect_tx(&kv_full[st], 2 * kFaKBytes);
+#pragma unroll
+                for (int b = 0; b < kFaBlocks; ++b) {
+                    tma_load_2d(k_tile + b * (kFaKeys * 128), &map_k, b * 64, cache_row, &kv_full[st]);
+                    tma_load_2d(v_tile + b * (kFaKeys * 128), &map_v, b * 64, cache_row, &kv_full[st]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        constexpr uint32_t idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kFaKeys >> 3) << 17) | ((uint32_t)(kFaRows >> 4) << 24);
+        constexpr uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(kFaD >> 3) << 17) | ((uint32_t)(kFaRows >> 4) << 24);
+        bool ok = mbar_wait(&q_full, 0, 22);
+        auto n_of = [&](int x) { return x == 0 ? n_a : n_b; };
+        auto issue_qk = [&](int x, int j) {        // lane 0 only
+            const unsigned char* k_tile = kv_s + (size_t)(j % kFaStages) * 2 * kFaKBytes;
+#pragma unroll
+            for (int kk = 0; kk < kFaD / kUmmaK; ++kk) {
+                const uint64_t a = umma_desc(q_s + x * kFaQBytes + (kk / 4) * (kFaRows * 128)) + 2 * (kk % 4);
+                const uint64_t b = umma_desc(k_tile + (kk / 4) * (kFaKeys * 128)) + 2 * (kk % 4);
+                umma_bf16(tmem_base + x * 64, a, b, idesc_qk, kk > 0 ? 1u : 0u);
+            }
+            umma_commit(&s_full[x]);
+        };
+        // page 0: scores of both tiles
+        if (ok) ok = mbar_wait(&kv_full[0], 0, 23);
+        if (ok) {
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            if (lane == 0) {
+                issue_qk(0, 0);
+                if (has_b) issue_qk(1, 0);
+            }
+            __syncwarp();
+        }
+        for (int j = 0; j < n_tiles && ok; ++j) {
+            const int st = j % kFaStages;
+            unsigned char* v_tile = kv_s + (size_t)st * 2 * kFaKBytes + kFaKBytes;
+            // value rows of keys that were never written (only in the sequence's last page) are zeroed
+            const int dead_from = max(kv_len - (t_begin + j) * kFaKeys, 0);
+            if (dead_from < kFaKeys) {
+                const int n_dead = kFaKeys - dead_from;
+                for (int i = lane; i < n_dead * 8 * kFaBlocks; i += 32) {
+                    const int b = i / (n_dead * 8), rest = i % (n_dead * 8);
+                    *reinterpret_cast<uint4*>(v_tile + b * (kFaKeys * 128) + (dead_from + rest / 8) * 128 + (rest % 8) * 16) = make_uint4(0, 0, 0, 0);
+                }
+                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                __syncwarp();
+            }
+            if (j + 1 < n_tiles) {
+                ok = mbar_wait(&kv_full[(j + 1) % kFaStages], ((j + 1) / kFaStages) & 1, 24);
+                if (!ok) break;
+            }
+            for (int x = 0; x < 2 && ok; ++x) {
+                if (j >= n_of(x)) continue;
+                ok = mbar_wait(&p_full[x], j & 1, 25);        // P of page j is in shared memory, S has been read
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                if (lane == 0) {
+                    const uint64_t p_desc = umma_desc(p_s + x * kFaPBytes);
+#pragma unroll
+                    for (int k = 0; k < kFaKeys / kUmmaK; ++k)
+                        umma_bf16(tmem_base + 128 + x * 128, p_desc + 2 * k, umma_desc_mn(v_tile + k * 2048, kFaKeys * 128),
+                                  idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+                    if (j + 1 < n_of(x)) issue_qk(x, j + 1);  // its commit also covers the product just issued
+                }
+                __syncwarp();
+            }
+            if (lane == 0) umma_commit(&kv_empty[st]);         // the page's last user has been issued
+            __syncwarp();
+        }
+        if (lane == 0) umma_commit(&all_done);
+        __syncwarp();
+    } else {
+        // ---- softmax warp groups: warps 2-5 own tile 0, warps 6-9 tile 1; thread t of a group owns row t
+        const int x = (warp - 2) >> 2;
+        const int quarter = warp & 3;
+        const int t = quarter * 32 + lane;
+        const int n_mine = x == 0 ? n_a : n_b;
+        const int pos = start + r0 + x * kFaRows + t;
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        const uint32_t s_addr = lane_addr + x * 64, o_addr = lane_addr + 128 + x * 128;
+        float m_ref = -INFINITY, l = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n_mine && ok; ++j) {
+            ok = mbar_wait(&s_full[x], j & 1, 26);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            uint32_t sv[64];
+            {
+                uint32_t half[32];
+                tmem_load32(s_addr, half);
+#pragma unroll
+                for (int e = 0; e < 32; ++e) sv[e] = half[e];
+                tmem_load32(s_addr + 32, half);
+#pragma unroll
+                for (int e = 0; e < 32; ++e) sv[32 + e] = half[e];
+            }
+            const int key0 = (t_begin + j) * kFaKeys;
+            const bool partial = key0 + kFaKeys - 1 > pos || (window > 0 && key0 < pos - window + 1);
+            float mx = -INFINITY;
+            if (partial) {
+#pragma unroll
+                for (int e = 0; e < 64; ++e) {
+                    const int key = key0 + e;
+                    const bool seen = key <= pos && (window <= 0 || key > pos - window);
+                    const float v = seen ? __uint_as_float(sv[e]) : -INFINITY;
+                    sv[e] = __float_as_uint(v);
+                    mx = fmaxf(mx, v);
+                }
+            } else {
+#pragma unroll
+                for (int e = 0; e < 64; ++e) mx = fmaxf(mx, __uint_as_float(sv[e]));
+            }
+            // the scale of the row is moved only when its maximum has outgrown it by 2^8
+            float corr = 1.0f;
+            if (mx > m_ref && (m_ref == -INFINITY || (mx - m_ref) * scale_log2 > kFaRescaleStep)) {
+                corr = m_ref == -INFINITY ? 0.f : fa_exp2((m_ref - mx) * scale_log2);
+                m_ref = mx;
+            }
+            if (j > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
+                // the product of the page before is complete (s_full came after it): rescale this row's output
+#pragma unroll
+                for (int c = 0; c < kFaD; c += 32) {
+                    uint32_t v[32];
+                    tmem_load32(o_addr + c, v);
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) * corr);
+                    asm volatile(
+                        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+                        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+                        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};\n"
+                        ::"r"(o_addr + c), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+                          "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]),
+                          "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),
+                          "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+                        : "memory");
+                }
+                asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+            }
+            const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
+            const float shift = -m_use * scale_log2;
+            float sum = 0.f;
+            uint32_t packed[32];
+#pragma unroll
+            for (int e = 0; e < 64; e += 2) {
+                const float p0 = fa_exp2(fmaf(__uint_as_float(sv[e]), scale_log2, shift));
+                const float p1 = fa_exp2(fmaf(__uint_as_float(sv[e + 1]), scale_log2, shift));
+                sum += p0 + p1;
+                __nv_bfloat162 pair = __floats2bfloat162_rn(p0, p1);
+                packed[e >> 1] = *reinterpret_cast<uint32_t*>(&pair);
+            }
+            l = l * corr + sum;
+            unsigned char* p_row = p_s + x * kFaPBytes + t * 128;
+#pragma unroll
+            for (int c = 0; c < 8; ++c)
+                *reinterpret_cast<uint4*>(p_row + ((c ^ (t & 7)) << 4)) =
+                    make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            fa_arrive(&p_full[x]);
+        }
+        if (ok && n_mine > 0) ok = mbar_wait(&all_done, 0, 27);
+        if (ok && n_mine > 0) {
+            // every thread of the warp takes part in the loads; rows past the prompt's end store nothing
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            const bool mine = x * kFaRows + t < rows_here;
+            const float inv = l > 0.f ? 1.0f / l : 0.f;
+            bf16* dst = out + (size_t)(row0 + r0 + x * kFaRows + (mine ? t : 0)) * out_stride + (size_t)head * kFaD;
+#pragma unroll
+            for (int c = 0; c < kFaD; c += 32) {
+                uint32_t v[32];
+                tmem_load32(o_addr + c, v);
+                if (mine) {
+#pragma unroll
+                    for (int d = 0; d < 32; d += 8) {
+                        float f[8];
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(v[d + e]) * inv;
+                        store16(dst + c + d, f);
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(kFa2TmemCols) : "memory");
+    }
+}
 #endif  // DFI_FA_ENABLED
 
 }  // namespace dfi
@@ -348,6 +628,21 @@ DFI_EXPORT int dfi_attention_prefill_tc(const void* q, int q_rows, int q_stride,
     if (!make_tile_map(&map_q, q, q_rows, n_q * kFaD, kFaRows, q_stride)) return DFI_ERR_LAUNCH;
     if (!make_tile_map(&map_k, k_cache, (int)cache_rows, kFaD, kFaKeys)) return DFI_ERR_LAUNCH;
     if (!make_tile_map(&map_v, v_cache, (int)cache_rows, kFaD, kFaKeys)) return DFI_ERR_LAUNCH;
+    if (max_q_len > kFaRows) {
+        // long shares: two query tiles per CTA, each with softmax warps of its own
+        static bool configured2 = false;
+        if (!configured2) {
+            if (cudaFuncSetAttribute(attention_prefill_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kFa2Smem) != cudaSuccess)
+                return DFI_ERR_LAUNCH;
+            configured2 = true;
+        }
+        dim3 grid2((max_q_len + 2 * kFaRows - 1) / (2 * kFaRows), n_q, n_seqs);
+        launch(attention_prefill_tc2_kernel, grid2, kFa2Threads, kFa2Smem, (cudaStream_t)stream, map_q, map_k, map_v,
+               (bf16*)out, out_stride, block_table, table_width, cu_rows, seq_start, n_q, n_kv, ring_tokens, window,
+               scale * kFaLog2e);
+        DFI_CHECK_LAUNCH();
+        return DFI_OK;
+    }
     dim3 grid((max_q_len + kFaRows - 1) / kFaRows, n_q, n_seqs);
     launch(attention_prefill_tc_kernel, grid, kFaThreads, kFaSmem, (cudaStream_t)stream, map_q, map_k, map_v, (bf16*)out,
            out_stride, block_table, table_width, cu_rows, seq_start, n_q, n_kv, ring_tokens, window, scale * kFaLog2e);
