@@ -537,9 +537,9 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
             const int c_last = dec_cta_of_unit(run, group_first_unit + seq_tiles - 1);
             atrace(5);
             if (threadIdx.x == 0) {
-                __threadfence();                 // release: this part is visible before the ticket is taken
-                const int ticket = atomicAdd(&counters[seq * n_kv + kv_head], 1);
-                __threadfence();                 // acquire: the other parts are visible after it
+                // one acquire-release add at GPU scope: this CTA's part (ordered before it by the barrier
+                // above) is visible to whoever reads a later ticket, and the earlier parts are visible here
+                const int ticket = ticket_add(&counters[seq * n_kv + kv_head]);
                 ticket_s = ticket;
             }
             __syncthreads();

@@ -122,6 +122,13 @@ static inline cudaError_t launch(void (*kernel)(KernelArgs...), dim3 grid, dim3 
     return cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...);
 }
 
+// Takes a ticket from a counter in global memory with acquire-release ordering at GPU scope.
+__device__ __forceinline__ int ticket_add(int* counter) {
+    int ticket;
+    asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;\n" : "=r"(ticket) : "l"(counter) : "memory");
+    return ticket;
+}
+
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 // Place of position `p` in a sequence's storage: itself, or its place in the ring.

@@ -244,9 +244,9 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 first_slot = sk_run_begin(s, c_first) >= rb_first_unit ? 0 : 1;
                 if (t == 0) {
                     if (done + seg_units >= n_units) trace(4);
-                    __threadfence();                 // release: the part is visible before the ticket is taken
-                    const int ticket = atomicAdd(&counters[rb], 1);
-                    __threadfence();                 // acquire: the other parts are visible after it
+                    // one acquire-release add at GPU scope: this CTA's part (ordered before it by the barrier
+                    // above) is visible to whoever reads a later ticket, and the earlier parts are visible here
+                    const int ticket = ticket_add(&counters[rb]);
                     ticket_s = ticket;
                     if (done + seg_units >= n_units) trace(5);
                 }
