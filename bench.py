@@ -33,6 +33,10 @@ QWEN3_4B = {
     "vocab_size": 151936, "rope_theta": 5000000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": True,
     "max_position_embeddings": 40960, "hidden_act": "silu", "torch_dtype": "bfloat16",
 }
+# the other two shapes of BASELINE.json (configs[3] and configs[4]): end-to-end generation runs
+QWEN3_8B = dict(QWEN3_4B, hidden_size=4096, intermediate_size=12288, rope_theta=1000000.0, tie_word_embeddings=False)
+QWEN3_14B = dict(QWEN3_4B, num_hidden_layers=40, hidden_size=5120, num_attention_heads=40, intermediate_size=17408,
+                 rope_theta=1000000.0, tie_word_embeddings=False)
 CONTEXT = 4096
 BATCH = 8
 PREFILL_TOKENS = 2048
@@ -150,6 +154,48 @@ def time_decode(engine, n_seqs: int, context: int, steps: int, warmup: int, samp
     return ms, per_step
 
 
+def generation_run(shape: str) -> int:
+    """Generation through ``Engine.generate`` at the 8B shape (16 unequal prompts of 128..2,048 tokens, 256
+    greedy steps) or the 14B shape (32 prompts of 1,024 tokens, 128 steps): tokens per second, prefill included."""
+    import torch
+    from dryft_flash_infer_b200 import Engine
+
+    cfg, batch, new = (QWEN3_8B, 16, 256) if shape == "8b" else (QWEN3_14B, 32, 128)
+    g = torch.Generator().manual_seed(1)
+    if shape == "8b":
+        lengths = torch.randint(128, 2049, (batch,), generator=g).tolist()
+    else:
+        lengths = [1024] * batch
+    prompts = [torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist() for n in lengths]
+    engine = Engine(config=cfg, random_weights=True, seed=0, dtype="bfloat16")
+    list(engine.generate([p[:64] for p in prompts[:batch]], 4))            # warm-up: compiles nothing new, builds graphs
+    results = []
+    for _ in range(2):
+        torch.cuda.synchronize()
+        begin = time.perf_counter()
+        stream = engine.generate(prompts, new)
+        next(stream)
+        torch.cuda.synchronize()
+        first = time.perf_counter()
+        produced = 1 + sum(1 for _ in stream)
+        torch.cuda.synchronize()
+        end = time.perf_counter()
+        results.append((end - begin, first - begin, produced))
+    total, ttft, produced = min(results)
+    nums = model_numbers(cfg, cfg["num_hidden_layers"])
+    print(json.dumps({
+        "metric": f"generation tokens/s, prefill included (Qwen3-{shape.upper()} sizes, bf16, random weights)",
+        "value": round(batch * produced / total, 1), "unit": "tokens/s", "n_gpus": 1, "impl": "ours",
+        "ttft_ms": round(ttft * 1e3, 2), "tpot_ms": round((total - ttft) / max(1, produced - 1) * 1e3, 3),
+        "prefill_tokens_per_s": round(sum(lengths) / ttft, 1),
+        "config": {"model": f"Qwen3-{shape.upper()} sizes", "layers": cfg["num_hidden_layers"], "hidden": cfg["hidden_size"],
+                   "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+                   "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "global_batch": batch,
+                   "prompt_tokens": sum(lengths), "new_tokens": produced, "weight_gb": round(nums["weight_bytes"] / 1e9, 2)},
+        "data": "synthetic: random weights, random token ids"}))
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -162,6 +208,8 @@ def main() -> int:
     parser.add_argument("--profile", choices=["decode", "prefill", "timeline"],
                         help="run only a few plain (graph-less) decode steps or one prefill, for a profiler; prints no JSON")
     parser.add_argument("--batch", type=int, default=BATCH, help="batch of the --profile decode steps")
+    parser.add_argument("--shape", choices=["4b", "8b", "14b"], default="4b",
+                        help="8b / 14b: the end-to-end generation runs of the larger shapes instead of the headline run")
     args = parser.parse_args()
     if args.gpus != 1:
         print(f"bench.py measures a single-GPU engine: --gpus {args.gpus} is not supported, run it with --gpus 1")
@@ -173,6 +221,8 @@ def main() -> int:
         return 0
     warmup = max(3, args.warmup)
     steps = max(1, args.steps)
+    if args.shape != "4b":
+        return generation_run(args.shape)
 
     import torch
     from dryft_flash_infer_b200 import Engine, StepEntry
