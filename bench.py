@@ -26,14 +26,14 @@ from pathlib import Path
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
-# the sizes of the Qwen3-4B configuration named in BASELINE.json (configs[2])
+# the sizes of Qwen3-4B (36 layers, hidden 2560, 32/8 heads of 128, intermediate 9728, vocabulary 151936)
 QWEN3_4B = {
     "architectures": ["Qwen3ForCausalLM"], "num_hidden_layers": 36, "hidden_size": 2560,
     "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 9728,
     "vocab_size": 151936, "rope_theta": 5000000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": True,
     "max_position_embeddings": 40960, "hidden_act": "silu", "torch_dtype": "bfloat16",
 }
-# the other two shapes of BASELINE.json (configs[3] and configs[4]): end-to-end generation runs
+# the sizes of Qwen3-8B and Qwen3-14B, for the end-to-end generation runs of --shape
 QWEN3_8B = dict(QWEN3_4B, hidden_size=4096, intermediate_size=12288, rope_theta=1000000.0, tie_word_embeddings=False)
 QWEN3_14B = dict(QWEN3_4B, num_hidden_layers=40, hidden_size=5120, num_attention_heads=40, intermediate_size=17408,
                  rope_theta=1000000.0, tie_word_embeddings=False)
