@@ -311,3 +311,41 @@ def test_layer_sizes_of_the_benchmark_model_against_the_float32_path():
     # whole prompt alone and in the batch agree in float32 to rounding (row 0 of the batch = place 296 of prompt 0 ...)
     err = float((got - want).abs().max())
     assert err <= 0.03 * max(1.0, float(want.abs().max())), err
+
+
+TINY_C = {
+    "architectures": ["Qwen3ForCausalLM"], "num_hidden_layers": 1, "hidden_size": 80, "num_attention_heads": 5,
+    "num_key_value_heads": 5, "head_dim": 48, "intermediate_size": 72, "vocab_size": 100, "rope_theta": 500000.0,
+    "rms_norm_eps": 3e-6, "tie_word_embeddings": False, "hidden_act": "silu", "max_position_embeddings": 2048,
+}
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_third_shape_and_a_batch_wider_than_the_skinny_kernels(tmp_path, dtype):
+    """Head size 48 with as many key/value heads as query heads (another kernel path than 16/32/128), and a
+    batch of 70 sequences, which is past what the decode kernels for small batches take."""
+    from dryft_flash_infer_b200 import Engine, StepEntry
+
+    cfg = TINY_C
+    weights = plain_model.random_weights(cfg, seed=8, matrix_std=0.08, norm_std=0.1)
+    folder = write_model(tmp_path, cfg, weights)
+    ref_w = reference_weights(weights, dtype)
+    engine = Engine(folder, dtype=dtype, max_tokens=70 * 128)
+    prompts = prompts_for(cfg, [3 + (7 * i) % 40 for i in range(70)], seed=21)
+    want = [plain_model.forward(cfg, ref_w, p) for p in prompts]
+    slots = [engine.open_slot() for _ in prompts]
+    logits = engine.step([StepEntry(s, p[:-2], [len(p) - 3]) for s, p in zip(slots, prompts)])
+    for i, p in enumerate(prompts):
+        assert_close(logits[i], want[i][len(p) - 3], dtype, f"prefill {i}")
+    for t in (2, 1):
+        logits = engine.step([StepEntry(s, [p[len(p) - t]], [0]) for s, p in zip(slots, prompts)])
+        for i, p in enumerate(prompts):
+            assert_close(logits[i], want[i][len(p) - t], dtype, f"decode {i} -{t}")
+    for s in slots:
+        engine.close_slot(s)
+    # and through the generation loop (fixed buffers, CUDA graph) with all 70 at once
+    rows = list(engine.generate(prompts, 3))
+    assert len(rows) == 3 and all(len(r) == 70 for r in rows)
+    if dtype == "float32":
+        for i in (0, 33, 69):
+            assert [r[i] for r in rows] == plain_model.greedy_continue(cfg, ref_w, prompts[i], 3)
