@@ -100,6 +100,54 @@ __global__ void rmsnorm_kernel(T* __restrict__ residual, const T* __restrict__ d
     }
 }
 
+// The same for rows of up to kRowVectors 16-byte vectors per thread: the row stays in registers
+// between the sum of squares and the scaling, so it is read once.
+constexpr int kRowVectors = 4;
+
+template <typename T, bool ADD>
+__global__ void rmsnorm_registers_kernel(T* __restrict__ residual, const T* __restrict__ delta,
+                                         const float* __restrict__ weight, T* __restrict__ out, int dim, float eps) {
+    pdl_launch_next();
+    pdl_wait();
+    __shared__ float scratch[32];
+    constexpr int n = Vec16<T>::n;
+    T* x = residual + (size_t)blockIdx.x * dim;
+    const T* d = ADD ? delta + (size_t)blockIdx.x * dim : nullptr;
+    T* y = out + (size_t)blockIdx.x * dim;
+    float a[kRowVectors][n];
+    float ssq = 0.f;
+#pragma unroll
+    for (int v = 0; v < kRowVectors; ++v) {
+        const int i = (threadIdx.x + v * blockDim.x) * n;
+        if (i < dim) {
+            load16(x + i, a[v]);
+            if (ADD) {
+                float b[n];
+                load16(d + i, b);
+#pragma unroll
+                for (int j = 0; j < n; ++j) a[v][j] = to_float(from_float<T>(a[v][j] + b[j]));
+                store16(x + i, a[v]);
+            }
+#pragma unroll
+            for (int j = 0; j < n; ++j) ssq += a[v][j] * a[v][j];
+        }
+    }
+    ssq = block_sum(ssq, scratch);
+    const float scale = 1.0f / sqrtf(ssq / (float)dim + eps);
+#pragma unroll
+    for (int v = 0; v < kRowVectors; ++v) {
+        const int i = (threadIdx.x + v * blockDim.x) * n;
+        if (i < dim) {
+            float w[n];
+            load16(weight + i, w);
+            if constexpr (n == 8) load16(weight + i + 4, w + 4);
+#pragma unroll
+            for (int j = 0; j < n; ++j) a[v][j] = a[v][j] * scale * w[j];
+            store16(y + i, a[v]);
+        }
+    }
+}
+
 // ------------------------------------------------------------------ SwiGLU
 // gate_up [rows, 2*inter] (gate first), out [rows, inter] = silu(gate) * up.
 template <typename T, bool VEC>
@@ -241,6 +289,14 @@ static int launch_rmsnorm(void* residual, const void* delta, const float* weight
                           float eps, cudaStream_t st) {
     const bool vec = dim % Vec16<T>::n == 0 && aligned16(residual) && aligned16(out) &&
                      (delta == nullptr || aligned16(delta));
+    if (vec && aligned16(weight) && rows >= 64 && dim <= 256 * kRowVectors * Vec16<T>::n) {
+        // many rows (a prompt): each row is read once and kept in registers
+        int t = 64;
+        while (t < 256 && t * kRowVectors * Vec16<T>::n < dim) t <<= 1;
+        if (delta != nullptr) launch(rmsnorm_registers_kernel<T, true>, rows, t, 0, st, (T*)residual, (const T*)delta, weight, (T*)out, dim, eps);
+        else launch(rmsnorm_registers_kernel<T, false>, rows, t, 0, st, (T*)residual, (const T*)nullptr, weight, (T*)out, dim, eps);
+        return DFI_OK;
+    }
     int threads = 32;
     const int per = vec ? Vec16<T>::n : 1;
     while (threads < 512 && threads * per < dim) threads <<= 1;

@@ -23,7 +23,7 @@ def rounded(x, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("rows, dim", [(1, 8), (7, 100), (33, 2560), (5, 3001)])
+@pytest.mark.parametrize("rows, dim", [(1, 8), (7, 100), (33, 2560), (5, 3001), (70, 2560), (64, 40), (65, 8192), (66, 4100)])
 def test_rms_norm_and_add(dtype, rows, dim):
     from dryft_flash_infer_b200.ops import kernels
 
