@@ -266,6 +266,114 @@ __global__ void qk_norm_rope_write_kernel(T* __restrict__ qkv, int row_stride, i
     }
 }
 
+// The same with half a warp per head and four neighbouring elements of each half per lane, for
+// head sizes that are multiples of 8 up to 256: fewer, wider loads when there are many rows.
+struct Quad { float v[4]; };
+__device__ __forceinline__ Quad load4(const float* p) {
+    const float4 f = *reinterpret_cast<const float4*>(p);
+    return Quad{{f.x, f.y, f.z, f.w}};
+}
+__device__ __forceinline__ Quad load4(const bf16* p) {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+    return Quad{{a.x, a.y, b.x, b.y}};
+}
+__device__ __forceinline__ void store4(float* p, const Quad& q) {
+    *reinterpret_cast<float4*>(p) = make_float4(q.v[0], q.v[1], q.v[2], q.v[3]);
+}
+__device__ __forceinline__ void store4(bf16* p, const Quad& q) {
+    uint2 u;
+    *reinterpret_cast<__nv_bfloat162*>(&u.x) = __floats2bfloat162_rn(q.v[0], q.v[1]);
+    *reinterpret_cast<__nv_bfloat162*>(&u.y) = __floats2bfloat162_rn(q.v[2], q.v[3]);
+    *reinterpret_cast<uint2*>(p) = u;
+}
+
+constexpr int kWideSteps = 2;  // 16 lanes x 4 elements x 2 steps cover half a head of up to 128
+
+template <typename T>
+__global__ void qk_norm_rope_write_wide_kernel(T* __restrict__ qkv, int row_stride, int n_q, int n_kv, int D,
+                                               const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
+                                               const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                               const int* __restrict__ row_pos, const int* __restrict__ row_seq,
+                                               T* __restrict__ k_cache, T* __restrict__ v_cache,
+                                               const int* __restrict__ block_table, int table_width, int page_size,
+                                               int ring_tokens, int write_cache) {
+    pdl_launch_next();
+    pdl_wait();
+    const int lane = threadIdx.x & 15;
+    const int head = blockIdx.y * (blockDim.x >> 4) + (threadIdx.x >> 4);
+    const int row = blockIdx.x;
+    const bool is_q = head < n_q;
+    const bool is_k = !is_q && head < n_q + n_kv;
+    // a lane that has nothing to do still takes part in the sums of its warp
+    const bool active = head < n_q + 2 * n_kv && (is_q || write_cache);
+    const int half = D >> 1;
+    T* src = qkv + (size_t)row * row_stride + (size_t)(active ? head : 0) * D;
+    const int pos = row_pos[row];
+
+    T* dst = src;
+    if (active && !is_q) {
+        const int place = place_of(pos, ring_tokens);
+        const int page = block_table[(size_t)row_seq[row] * table_width + place / page_size];
+        const int kv_head = is_k ? head - n_q : head - n_q - n_kv;
+        T* cache = is_k ? k_cache : v_cache;
+        dst = cache + (((size_t)page * n_kv + kv_head) * page_size + place % page_size) * D;
+    }
+
+    Quad lo[kWideSteps], hi[kWideSteps];
+    float ssq = 0.f;
+#pragma unroll
+    for (int j = 0; j < kWideSteps; ++j) {
+        const int i = 4 * lane + 64 * j;
+        if (active && i < half) {
+            lo[j] = load4(src + i);
+            hi[j] = load4(src + i + half);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) ssq += lo[j].v[e] * lo[j].v[e] + hi[j].v[e] * hi[j].v[e];
+        }
+    }
+    const float* w = is_q ? q_w : (is_k ? k_w : nullptr);
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, o);
+    if (!active) return;
+    if (w != nullptr) {
+        const float scale = 1.0f / sqrtf(ssq / (float)D + eps);
+#pragma unroll
+        for (int j = 0; j < kWideSteps; ++j) {
+            const int i = 4 * lane + 64 * j;
+            if (i < half) {
+                const Quad wl = load4(w + i), wh = load4(w + i + half);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    lo[j].v[e] *= scale * wl.v[e];
+                    hi[j].v[e] *= scale * wh.v[e];
+                }
+            }
+        }
+    }
+    const bool rotate = (is_q || is_k) && cos_t != nullptr;
+    const float* c = rotate ? cos_t + (size_t)pos * half : nullptr;
+    const float* s = rotate ? sin_t + (size_t)pos * half : nullptr;
+#pragma unroll
+    for (int j = 0; j < kWideSteps; ++j) {
+        const int i = 4 * lane + 64 * j;
+        if (i < half) {
+            Quad a = lo[j], b = hi[j];
+            if (rotate) {
+                const Quad cv = load4(c + i), sv = load4(s + i);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    a.v[e] = lo[j].v[e] * cv.v[e] - hi[j].v[e] * sv.v[e];
+                    b.v[e] = hi[j].v[e] * cv.v[e] + lo[j].v[e] * sv.v[e];
+                }
+            }
+            store4(dst + i, a);
+            store4(dst + i + half, b);
+        }
+    }
+}
+
 template <typename T>
 static int launch_embedding(const void* table, const int* ids, void* out, int rows, int hidden, int vocab,
                             cudaStream_t st) {
@@ -394,6 +502,23 @@ DFI_EXPORT int dfi_qk_norm_rope_write(void* qkv, int rows, int row_stride, int n
     cudaStream_t st = (cudaStream_t)stream;
     const int warps = 4;
     const int heads = n_q + 2 * n_kv;
+    const bool wide = rows >= 64 && head_dim % 8 == 0 && head_dim <= 128 * kWideSteps && row_stride % 4 == 0 &&
+                      aligned16(qkv) && aligned16(k_cache) && aligned16(v_cache) && aligned16(q_w) && aligned16(k_w) &&
+                      aligned16(cos_t) && aligned16(sin_t);
+    if (wide) {
+        dim3 wide_grid(rows, (heads + 2 * warps - 1) / (2 * warps));
+        if (dtype == DFI_DTYPE_F32)
+            launch(qk_norm_rope_write_wide_kernel<float>, wide_grid, warps * 32, 0, st,
+                (float*)qkv, row_stride, n_q, n_kv, head_dim, q_w, k_w, eps, cos_t, sin_t, row_pos, row_seq,
+                (float*)k_cache, (float*)v_cache, block_table, table_width, page_size, ring_tokens, write_cache);
+        else if (dtype == DFI_DTYPE_BF16)
+            launch(qk_norm_rope_write_wide_kernel<bf16>, wide_grid, warps * 32, 0, st,
+                (bf16*)qkv, row_stride, n_q, n_kv, head_dim, q_w, k_w, eps, cos_t, sin_t, row_pos, row_seq,
+                (bf16*)k_cache, (bf16*)v_cache, block_table, table_width, page_size, ring_tokens, write_cache);
+        else return DFI_ERR_DTYPE;
+        DFI_CHECK_LAUNCH();
+        return DFI_OK;
+    }
     dim3 grid(rows, (heads + warps - 1) / warps);
     if (grid.y > 65535) return DFI_ERR_LIMIT;
     if (dtype == DFI_DTYPE_F32)
