@@ -305,6 +305,23 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     }
 }
 
+#ifdef DFI_TRACE
+// Timing of the two-tile kernel's phases, summed per CTA: [wait scores, load, arithmetic, store and
+// arrive, total, pages, issuer's wait for P, issuer's issue] in nanoseconds (first softmax thread of
+// tile 0 and the issuing thread).
+__device__ unsigned long long g_fa_trace[1024 * 8];
+__device__ __forceinline__ unsigned long long fa_now() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;\n" : "=l"(t));
+    return t;
+}
+#define FA_T(var) const unsigned long long var = fa_now()
+#define FA_ADD(slot, value) do { if (trace_cta < 1024) g_fa_trace[trace_cta * 8 + (slot)] += (value); } while (0)
+#else
+#define FA_T(var)
+#define FA_ADD(slot, value)
+#endif
+
 // ------------------------------------------------------------------ two query tiles per CTA
 // For prompts longer than one tile: a CTA owns 256 query rows as two tiles of 128, each with a
 // softmax warp group of its own, and the tensor core alternates between them, so that the scores of
@@ -337,11 +354,17 @@ attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __
     unsigned char* p_s = kv_s + kFaStages * 2 * kFaKBytes;       // [tile][128 rows][128 bytes]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int seq = blockIdx.z, head = blockIdx.y;
+    // CTAs start in the order of blockIdx.x, then y: the head is x and the rows are y, latest rows
+    // first, so that the CTAs with the most keys to walk all start in the first wave
+    const int seq = blockIdx.z, head = blockIdx.x;
+#ifdef DFI_TRACE
+    const int trace_cta = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+#endif
     const int row0 = cu_rows[seq], q_len = cu_rows[seq + 1] - row0;
     const int n_row_tiles = (q_len + 2 * kFaRows - 1) / (2 * kFaRows);
-    if ((int)blockIdx.x >= n_row_tiles) return;
-    const int r0 = (n_row_tiles - 1 - blockIdx.x) * 2 * kFaRows;          // the heaviest rows first
+    const int behind = (int)gridDim.y - 1 - (int)blockIdx.y;              // row tiles after this one
+    if (behind >= n_row_tiles) return;
+    const int r0 = behind * 2 * kFaRows;
     const int rows_here = min(2 * kFaRows, q_len - r0);
     const bool has_b = rows_here > kFaRows;
     const int start = seq_start[seq];
@@ -448,9 +471,12 @@ attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __
             }
             for (int x = 0; x < 2 && ok; ++x) {
                 if (j >= n_of(x)) continue;
+                FA_T(ti0);
                 ok = mbar_wait(&p_full[x], j & 1, 25);        // P of page j is in shared memory, S has been read
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                FA_T(ti1);
+                if (lane == 0) FA_ADD(6, ti1 - ti0);
                 if (lane == 0) {
                     const uint64_t p_desc = umma_desc(p_s + x * kFaPBytes);
 #pragma unroll
@@ -458,6 +484,8 @@ attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __
                         umma_bf16(tmem_base + 128 + x * 128, p_desc + 2 * k, umma_desc_mn(v_tile + k * 2048, kFaKeys * 128),
                                   idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
                     if (j + 1 < n_of(x)) issue_qk(x, j + 1);  // its commit also covers the product just issued
+                    FA_T(ti2);
+                    FA_ADD(7, ti2 - ti1);
                 }
                 __syncwarp();
             }
@@ -477,10 +505,16 @@ attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __
         const uint32_t s_addr = lane_addr + x * 64, o_addr = lane_addr + 128 + x * 128;
         float m_ref = -INFINITY, l = 0.f;
         bool ok = true;
+#ifdef DFI_TRACE
+        const bool tracer = x == 0 && t == 0;
+        const unsigned long long t_begin_all = fa_now();
+#endif
         for (int j = 0; j < n_mine && ok; ++j) {
+            FA_T(ts0);
             ok = mbar_wait(&s_full[x], j & 1, 26);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            FA_T(ts1);
             uint32_t sv[64];
             {
                 uint32_t half[32];
@@ -491,6 +525,7 @@ attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __
 #pragma unroll
                 for (int e = 0; e < 32; ++e) sv[32 + e] = half[e];
             }
+            FA_T(ts2);
             const int key0 = (t_begin + j) * kFaKeys;
             const bool partial = key0 + kFaKeys - 1 > pos || (window > 0 && key0 < pos - window + 1);
             float mx = -INFINITY;
@@ -551,10 +586,20 @@ attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __
             for (int c = 0; c < 8; ++c)
                 *reinterpret_cast<uint4*>(p_row + ((c ^ (t & 7)) << 4)) =
                     make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+            FA_T(ts3);
             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
             fa_arrive(&p_full[x]);
+#ifdef DFI_TRACE
+            if (tracer) {
+                const unsigned long long ts4 = fa_now();
+                FA_ADD(0, ts1 - ts0); FA_ADD(1, ts2 - ts1); FA_ADD(2, ts3 - ts2); FA_ADD(3, ts4 - ts3); FA_ADD(5, 1);
+            }
+#endif
         }
+#ifdef DFI_TRACE
+        if (tracer) FA_ADD(4, fa_now() - t_begin_all);
+#endif
         if (ok && n_mine > 0) ok = mbar_wait(&all_done, 0, 27);
         if (ok && n_mine > 0) {
             // every thread of the warp takes part in the loads; rows past the prompt's end store nothing
@@ -600,6 +645,18 @@ DFI_EXPORT int dfi_attention_prefill_tc_error(int reset) {
     return value;
 }
 
+#ifdef DFI_TRACE
+DFI_EXPORT int dfi_attention_prefill_trace(unsigned long long* host) {
+    if (cudaMemcpyFromSymbol(host, g_fa_trace, sizeof(unsigned long long) * 1024 * 8) != cudaSuccess) return -1;
+    cudaMemset(nullptr, 0, 0);
+    return 0;
+}
+DFI_EXPORT int dfi_attention_prefill_trace_reset() {
+    static unsigned long long zeros[1024 * 8];
+    return cudaMemcpyToSymbol(g_fa_trace, zeros, sizeof(zeros)) == cudaSuccess ? 0 : -1;
+}
+#endif
+
 // 1 if this build (head size) has the tcgen05 prefill kernel.
 DFI_EXPORT int dfi_attention_prefill_tc_available() { return DFI_FA_ENABLED; }
 
@@ -615,7 +672,7 @@ DFI_EXPORT int dfi_attention_prefill_tc(const void* q, int q_rows, int q_stride,
     if (page_size != kFaKeys || n_q <= 0 || n_kv <= 0 || n_q % n_kv || ring_tokens % kFaKeys) return DFI_ERR_SHAPE;
     if (q_stride % 8 || out_stride % 8 || !aligned16(q) || !aligned16(out) || !aligned16(k_cache) || !aligned16(v_cache))
         return DFI_ERR_ALIGN;
-    if (n_q > 65535 || n_seqs > 65535) return DFI_ERR_LIMIT;
+    if (n_q > 65535 || n_seqs > 65535 || max_q_len / (2 * kFaRows) >= 65535) return DFI_ERR_LIMIT;
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kFaSmem) != cudaSuccess)
@@ -636,7 +693,7 @@ DFI_EXPORT int dfi_attention_prefill_tc(const void* q, int q_rows, int q_stride,
                 return DFI_ERR_LAUNCH;
             configured2 = true;
         }
-        dim3 grid2((max_q_len + 2 * kFaRows - 1) / (2 * kFaRows), n_q, n_seqs);
+        dim3 grid2(n_q, (max_q_len + 2 * kFaRows - 1) / (2 * kFaRows), n_seqs);
         launch(attention_prefill_tc2_kernel, grid2, kFa2Threads, kFa2Smem, (cudaStream_t)stream, map_q, map_k, map_v,
                (bf16*)out, out_stride, block_table, table_width, cu_rows, seq_start, n_q, n_kv, ring_tokens, window,
                scale * kFaLog2e);
