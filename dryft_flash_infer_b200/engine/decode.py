@@ -159,7 +159,7 @@ class Decoder:
 
     def __init__(self, model, cache, use_graph: bool):
         self.model, self.cache = model, cache
-        self.use_graph = use_graph and all(b.mixer.graph_safe for b in model.blocks)
+        self.use_graph = use_graph and model.graph_safe
         self.batches: dict[tuple, DecodeBatch] = {}
         self.last: tuple | None = None
 

@@ -74,6 +74,11 @@ class DecoderModel:
         parts.append(self.final_norm)
         return parts
 
+    @property
+    def graph_safe(self) -> bool:
+        """True if every part says that a decode step through it can be captured in a CUDA graph."""
+        return all(part.graph_safe for part in self._parts())
+
     def allocate(self, dtype: torch.dtype, device) -> None:
         """Creates every part's device buffers (uninitialised)."""
         self.dtype, self.device = dtype, device

@@ -21,7 +21,6 @@ class Attention(Mixer):
     """
 
     kind = "attention"
-    graph_safe = True
 
     def __init__(self, hidden_size: int, n_heads: int, n_kv_heads: int, head_dim: int, qk_norm: bool = True,
                  qk_norm_eps: float = 1e-6, position: PartSpec | None = None, window: int = 0,
@@ -35,6 +34,10 @@ class Attention(Mixer):
         self.scale = float(scale) if scale is not None else head_dim ** -0.5
         self.position = build_part("position", position, hidden_size) if position is not None else None
         self.qkv = self.o = self.q_norm = self.k_norm = None
+
+    @property
+    def graph_safe(self) -> bool:
+        return self.position is None or self.position.graph_safe
 
     def tensors(self):
         q_rows, kv_rows = self.n_heads * self.head_dim, self.n_kv_heads * self.head_dim

@@ -61,6 +61,10 @@ class StateNeed:
 
 class Part:
     kind = ""
+    #: True if the part's ``forward`` only launches work on the current stream from device-resident
+    #: numbers (no host read-back, no shape that depends on values), so that a decode step through
+    #: it can be captured in a CUDA graph.  A model decodes through a graph only if all its parts say so.
+    graph_safe = False
 
     def tensors(self) -> dict[str, TensorDecl]:
         return {}
@@ -96,10 +100,6 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
-    #: True if ``forward`` only launches work on the current stream from device-resident
-    #: numbers, so that a decode step through it can be captured in a CUDA graph
-    graph_safe = False
-
     def cache_need(self) -> KVNeed | None:
         return None
 
@@ -134,6 +134,10 @@ class Block:
     def parts(self) -> dict[str, Part]:
         return {"mixer": self.mixer, "feed_forward": self.feed_forward,
                 "mixer_norm": self.mixer_norm, "ffn_norm": self.ffn_norm}
+
+    @property
+    def graph_safe(self) -> bool:
+        return all(part.graph_safe for part in self.parts().values())
 
     def forward(self, residual, pending, ctx, cache, state):
         raise NotImplementedError

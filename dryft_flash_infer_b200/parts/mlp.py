@@ -12,6 +12,7 @@ class SwiGLU(FeedForward):
     engine/kernels/reference.py:74-79)."""
 
     kind = "swiglu"
+    graph_safe = True
 
     def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "silu"):
         if activation != "silu":

@@ -15,6 +15,7 @@ class RMSNorm(Norm):
     """
 
     kind = "rms_norm"
+    graph_safe = True
 
     def __init__(self, hidden_size: int, eps: float, dim: int | None = None):
         self.dim = dim if dim is not None else hidden_size

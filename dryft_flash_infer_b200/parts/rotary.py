@@ -17,6 +17,7 @@ class RotaryEmbedding(PositionEncoding):
     """
 
     kind = "rotary"
+    graph_safe = True
 
     def __init__(self, hidden_size: int, head_dim: int, theta: float):
         if head_dim % 2:

@@ -286,3 +286,181 @@ def test_pre_norm_block_alone(dtype):
                  "g.down_proj.weight": w["ffn"]["down"]}
         ref = ref + plain_model.swiglu_mlp(h, names, "g.")
     close(got, ref, dtype, scale=2.0)
+
+
+# --------------------------------------------------------------------------- toy position encoding and routed feed-forward
+
+
+def register_toy_routed():
+    """A second toy architecture, again through the public registries only: attention with a position
+    encoding of another law (only the first pairs of a head rotate, positions are stretched) and a
+    feed-forward that routes each token to one of several small SwiGLU experts."""
+    from dryft_flash_infer_b200.config import ModelConfig, register_architecture
+    from dryft_flash_infer_b200.ops import kernels
+    from dryft_flash_infer_b200.parts import (FeedForward, LayerSpec, ModelSpec, PartSpec, PositionEncoding,
+                                              TensorDecl, register_part, straight_schedule)
+
+    class PartialRotary(PositionEncoding):
+        kind = "toy_partial_rotary"
+        graph_safe = True
+
+        def __init__(self, hidden_size: int, head_dim: int, theta: float, rotary_pairs: int, stretch: float):
+            self.head_dim, self.theta, self.rotary_pairs, self.stretch = head_dim, theta, rotary_pairs, stretch
+            self.cos = self.sin = None
+
+        def prepare(self, max_positions, device):
+            angles = toy_angles(torch.arange(max_positions), self.head_dim, self.theta, self.rotary_pairs, self.stretch)
+            half = angles[:, : self.head_dim // 2]
+            self.cos, self.sin = half.cos().contiguous().to(device), half.sin().contiguous().to(device)
+
+    class Top1Experts(FeedForward):
+        kind = "toy_top1_experts"            # not graph safe: the rows of an expert are gathered on the host's say
+
+        def __init__(self, hidden_size: int, intermediate_size: int, n_experts: int, router_scale: float):
+            self.hidden_size, self.inter, self.n_experts, self.router_scale = hidden_size, intermediate_size, n_experts, router_scale
+
+        def tensors(self):
+            out = {"router": TensorDecl((self.n_experts, self.hidden_size), "router", precision="float32")}
+            for e in range(self.n_experts):
+                out[f"experts.{e}.gate"] = TensorDecl((self.inter, self.hidden_size), f"gate_up{e}", 0)
+                out[f"experts.{e}.up"] = TensorDecl((self.inter, self.hidden_size), f"gate_up{e}", self.inter)
+                out[f"experts.{e}.down"] = TensorDecl((self.hidden_size, self.inter), f"down{e}")
+            return out
+
+        def forward(self, x, ctx):
+            logits = (x.float() @ self.router.t()) * self.router_scale           # router in float32
+            probs = torch.softmax(logits, -1)
+            chosen = probs.argmax(-1)
+            out = torch.zeros_like(x)
+            for e in range(self.n_experts):
+                rows = (chosen == e).nonzero().flatten()
+                if rows.numel():
+                    inner = kernels.linear_swiglu(x[rows].contiguous(), getattr(self, f"gate_up{e}"))
+                    y = kernels.linear(inner, getattr(self, f"down{e}"))
+                    out[rows] = (y.float() * probs[rows, e, None]).to(x.dtype)
+            return out
+
+    register_part("position", PartialRotary.kind, PartialRotary)
+    register_part("feed_forward", Top1Experts.kind, Top1Experts)
+
+    @dataclass(frozen=True)
+    class RoutedConfig(ModelConfig):
+        vocab_size: int
+        hidden_size: int
+        intermediate_size: int
+        num_hidden_layers: int
+        n_experts: int
+        router_scale: float
+        head_dim: int
+        rotary_pairs: int
+        stretch: float
+        theta: float
+        attention_scale: float
+        architecture: ClassVar[str] = "ToyRoutedForCausalLM"
+
+        @classmethod
+        def from_dict(cls, raw):
+            return cls(*(raw[f] for f in ("vocab_size", "hidden_size", "intermediate_size", "num_hidden_layers",
+                                          "n_experts", "router_scale", "head_dim", "rotary_pairs", "stretch", "theta",
+                                          "attention_scale")))
+
+    def build(c):
+        norm = PartSpec("rms_norm", {"eps": 1e-5})
+        position = PartSpec("toy_partial_rotary", {"head_dim": c.head_dim, "theta": c.theta,
+                                                   "rotary_pairs": c.rotary_pairs, "stretch": c.stretch})
+        layers = []
+        for i in range(c.num_hidden_layers):
+            names = {"mixer_norm.weight": f"l{i}.n1", "ffn_norm.weight": f"l{i}.n2", "feed_forward.router": f"l{i}.router",
+                     "mixer.q_proj": f"l{i}.q", "mixer.k_proj": f"l{i}.k", "mixer.v_proj": f"l{i}.v", "mixer.o_proj": f"l{i}.o"}
+            for e in range(c.n_experts):
+                for t in ("gate", "up", "down"):
+                    names[f"feed_forward.experts.{e}.{t}"] = f"l{i}.e{e}.{t}"
+            layers.append(LayerSpec(
+                "pre_norm",
+                PartSpec("attention", {"n_heads": 2, "n_kv_heads": 1, "head_dim": c.head_dim, "qk_norm": False, "position": position,
+                                       "scale": c.attention_scale}),
+                PartSpec("toy_top1_experts", {"intermediate_size": c.intermediate_size, "n_experts": c.n_experts,
+                                              "router_scale": c.router_scale}),
+                norm, norm, names))
+        return ModelSpec(c.architecture, c.vocab_size, c.hidden_size, 4096, tuple(layers),
+                         straight_schedule(c.num_hidden_layers), norm, "emb", {"weight": "final"}, None)
+
+    register_architecture(RoutedConfig.architecture, RoutedConfig, build)
+    return RoutedConfig
+
+
+def toy_angles(positions, head_dim, theta, rotary_pairs, stretch):
+    """[T, head_dim] angles of the toy law: pair i < rotary_pairs turns by (p / stretch) * theta^(-i / rotary_pairs)."""
+    half = head_dim // 2
+    steps = torch.arange(half).float()
+    inv = torch.where(steps < rotary_pairs, theta ** (-steps / rotary_pairs), torch.zeros(half))
+    angles = (positions.float() / stretch)[:, None] * inv[None, :]
+    return torch.cat([angles, angles], -1)
+
+
+def plain_routed_forward(raw, w, tokens):
+    """The toy architecture's formulas on the CPU in float32; also returns the smallest gap between the
+    two best router logits, which says how safe the comparison is from a flipped choice."""
+    hidden, dim, n_experts = raw["hidden_size"], raw["head_dim"], raw["n_experts"]
+    x = w["emb"][torch.as_tensor(tokens)]
+    t = x.shape[0]
+    angles = toy_angles(torch.arange(t), dim, raw["theta"], raw["rotary_pairs"], raw["stretch"])
+    gap = float("inf")
+    for i in range(raw["num_hidden_layers"]):
+        h = plain_model.rms_norm(x, w[f"l{i}.n1"], 1e-5)
+        q = plain_model.apply_rope((h @ w[f"l{i}.q"].T).view(t, 2, dim), angles)
+        k = plain_model.apply_rope((h @ w[f"l{i}.k"].T).view(t, 1, dim), angles)
+        v = (h @ w[f"l{i}.v"].T).view(t, 1, dim)
+        x = x + plain_model.causal_attention(q, k, v, scale=raw["attention_scale"]).reshape(t, -1) @ w[f"l{i}.o"].T
+        h = plain_model.rms_norm(x, w[f"l{i}.n2"], 1e-5)
+        logits = (h @ w[f"l{i}.router"].T) * raw["router_scale"]
+        probs = torch.softmax(logits, -1)
+        best = logits.topk(2, -1).values
+        gap = min(gap, float((best[:, 0] - best[:, 1]).min()))
+        delta = torch.zeros_like(x)
+        for r in range(t):
+            e = int(probs[r].argmax())
+            names = {"g.gate_proj.weight": w[f"l{i}.e{e}.gate"], "g.up_proj.weight": w[f"l{i}.e{e}.up"],
+                     "g.down_proj.weight": w[f"l{i}.e{e}.down"]}
+            delta[r] = plain_model.swiglu_mlp(h[r: r + 1], names, "g.")[0] * probs[r, e]
+        x = x + delta
+    return plain_model.rms_norm(x, w["final"], 1e-5) @ w["emb"].T, gap
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_toy_position_encoding_and_a_routed_feed_forward(dtype, tmp_path):
+    from dryft_flash_infer_b200 import Engine, StepEntry
+    from dryft_flash_infer_b200.config import config_from_dict
+    from dryft_flash_infer_b200.weights import ModelFiles, write_random_model
+
+    register_toy_routed()
+    raw = {"architectures": ["ToyRoutedForCausalLM"], "vocab_size": 61, "hidden_size": 40, "intermediate_size": 24,
+           "num_hidden_layers": 2, "n_experts": 3, "router_scale": 60.0, "head_dim": 32, "rotary_pairs": 5,
+           "stretch": 2.5, "theta": 300.0, "attention_scale": 40.0}      # a scale at which the rotation decides the scores
+    folder = write_random_model(config_from_dict(raw), 17, tmp_path / "routed", torch.bfloat16)
+    files = ModelFiles(folder)
+    w = {name: files.tensor(name).float() for name in files.names()}
+    seqs = [[3, 1, 4, 1, 5, 9, 2, 6, 5, 3, 5, 8], [9, 7, 9, 3, 2]]
+    plain = [plain_routed_forward(raw, w, s) for s in seqs]
+    assert min(gap for _, gap in plain) > 0.2, "router choices too close to call: pick another seed"
+    want = torch.cat([logits for logits, _ in plain])
+
+    engine = Engine(str(folder), dtype=dtype, max_tokens=512)
+    assert not engine.decoder.use_graph                       # the routed feed-forward is not graph safe
+    slots = [engine.open_slot() for _ in seqs]
+    whole = engine.step([StepEntry(s, q, list(range(len(q)))) for s, q in zip(slots, seqs)]).float().cpu()
+    for s in slots:
+        engine.close_slot(s)
+    slots = [engine.open_slot() for _ in seqs]
+    rows = {0: [], 1: []}
+    for t in range(max(map(len, seqs))):
+        live = [i for i, q in enumerate(seqs) if t < len(q)]
+        out = engine.step([StepEntry(slots[i], [seqs[i][t]], [0]) for i in live])
+        for row, i in enumerate(live):
+            rows[i].append(out[row].float().cpu())
+    stepped = torch.cat([torch.stack(rows[0]), torch.stack(rows[1])])
+    tol = 2e-4 if dtype == "float32" else 0.03 * float(want.abs().max())
+    assert float((whole - want).abs().max()) <= tol and float((stepped - want).abs().max()) <= tol
+    # the toy law is what ran: the plain formulas with every pair rotating give other logits
+    other, _ = plain_routed_forward({**raw, "rotary_pairs": 16, "stretch": 1.0}, w, seqs[0])
+    assert float((other - want[: len(seqs[0])]).abs().max()) > 20 * tol or dtype == "bfloat16"
