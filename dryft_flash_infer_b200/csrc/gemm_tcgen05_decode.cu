@@ -13,6 +13,15 @@
 // ranges (the result does not depend on who finished when), applies the epilogue and resets the
 // counter.  No CTA waits for another CTA; waits inside a CTA (on its own mbarriers) are bounded.
 //
+// Two optional fusions with the RMS norm around the product, both in the adding CTA's epilogue:
+// * scaled input: x holds rows w (.) r that still lack their 1/rms factor; the sums of squares of r
+//   come as partial sums per row, and since the factor is one number per row it is applied to the
+//   float32 result instead (before SwiGLU, to gate and up alike);
+// * add-norm output: the product y is a residual delta; the epilogue forms r = residual + y in
+//   place (y rounded to bfloat16 first, as an unfused step would store it), writes w (.) r as the
+//   next product's scaled input and this row block's sum of r^2 per row.
+// With both, the add + norm kernel between two products disappears.
+//
 // SWIGLU variant: W = [gate; up] of 2N rows; a row block is 64 gate rows and the 64 up rows that
 // belong to them, and the epilogue writes silu(gate) * up (engine/kernels/reference.py:74-79;
 // the fusion follows the idea of engine/kernels/cuda_mlp.py:39-125).
@@ -30,6 +39,17 @@ struct StreamShape {
     int units;
     int n_ctas;
     int parts;            // > 0: every row block is cut into this many parts, one CTA each (n_ctas = row_blocks * parts)
+};
+
+constexpr int kSsqStride = 64;   // floats per part in a sum-of-squares array: one per row of the batch
+
+struct RowFusion {
+    const float* in_ssq;      // scaled input: [in_parts][kSsqStride] partial sums of squares, or null
+    int in_parts;
+    float in_inv_dim, in_eps;
+    bf16* residual;           // add-norm output: [M, N] updated in place, or null
+    const float* norm_weight; // [N]
+    float* out_ssq;           // [row_blocks][kSsqStride]
 };
 
 // First unit of a CTA's run.  Two ways of dealing the units out: equal contiguous runs over the
@@ -87,7 +107,7 @@ template <int BN, bool SWIGLU>
 __global__ void __launch_bounds__(kDecThreads, 1)
 gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                    void* __restrict__ out, StreamShape s, float* __restrict__ partials, int* __restrict__ counters,
-                   int out_dtype) {
+                   int out_dtype, RowFusion fusion) {
     using Cfg = DecConfig<BN>;
     if (threadIdx.x == 0) trace(0);
     pdl_launch_next();
@@ -98,6 +118,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     __shared__ __align__(8) uint64_t acc_empty[2];
     __shared__ uint32_t tmem_base_s;
     __shared__ int ticket_s;
+    __shared__ float row_scale[BN];
 
     unsigned char* ring = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     float* staging = reinterpret_cast<float*>(ring + (size_t)Cfg::kStages * Cfg::kStageBytes);
@@ -209,6 +230,18 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         const int t = quarter * 32 + lane;
         int rb = first_rb, seg_first_kc = first_kc, done = 0, segment = 0;
         bool ok = true;
+        if (fusion.in_ssq != nullptr || fusion.residual != nullptr) {
+            pdl_wait();          // these threads read what the kernel before wrote
+            if (fusion.in_ssq != nullptr) {
+                if (t < BN) {
+                    float ssq = 0.f;
+                    if (t < s.M)
+                        for (int p = 0; p < fusion.in_parts; ++p) ssq += fusion.in_ssq[p * kSsqStride + t];
+                    row_scale[t] = 1.0f / sqrtf(ssq * fusion.in_inv_dim + fusion.in_eps);
+                }
+                epilogue_barrier();
+            }
+        }
         while (done < n_units && ok) {
             const int seg_units = min(s.k_chunks - seg_first_kc, n_units - done);
             const bool complete = seg_units == s.k_chunks;
@@ -264,6 +297,16 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 for (int item = t; item < s.M * kGroups; item += 128) {
                     const int b = item / kGroups, c4 = (item % kGroups) * 4;
                     const int offset = b * kTileM + c4;
+                    // add-norm output: the residual and the norm's weight travel with the parts (N is a
+                    // multiple of 4 there, so a group of four columns is inside the matrix or outside it)
+                    const bool add_norm = !SWIGLU && fusion.residual != nullptr;
+                    const bool inside = rb * kCols + c4 < s.N;
+                    uint2 res_raw = make_uint2(0u, 0u);
+                    float4 norm_w = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (add_norm && inside) {
+                        res_raw = *reinterpret_cast<const uint2*>(fusion.residual + (size_t)b * s.N + rb * kCols + c4);
+                        norm_w = *reinterpret_cast<const float4*>(fusion.norm_weight + rb * kCols + c4);
+                    }
                     float4 v = complete ? *reinterpret_cast<const float4*>(first_part + offset)
                                         : __ldcg(reinterpret_cast<const float4*>(first_part + offset));
                     float4 u = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -286,12 +329,46 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                             if (SWIGLU) { u.x += u4[j].x; u.y += u4[j].y; u.z += u4[j].z; u.w += u4[j].w; }
                         }
                     }
+                    if (fusion.in_ssq != nullptr) {
+                        const float rs = row_scale[b];
+                        v.x *= rs; v.y *= rs; v.z *= rs; v.w *= rs;
+                        if (SWIGLU) { u.x *= rs; u.y *= rs; u.z *= rs; u.w *= rs; }
+                    }
                     if (SWIGLU) {
                         v.x = silu_times(v.x, u.x); v.y = silu_times(v.y, u.y);
                         v.z = silu_times(v.z, u.z); v.w = silu_times(v.w, u.w);
                     }
                     const int col = rb * kCols + c4;
                     const float vals[4] = {v.x, v.y, v.z, v.w};
+                    if (add_norm) {
+                        // kGroups is 32 here: a warp holds one row's 128 columns of this row block
+                        float ssq = 0.f;
+                        if (inside) {
+                            const float2 r01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&res_raw.x));
+                            const float2 r23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&res_raw.y));
+                            const float old_r[4] = {r01.x, r01.y, r23.x, r23.y};
+                            const float w4[4] = {norm_w.x, norm_w.y, norm_w.z, norm_w.w};
+                            float r[4], xs[4];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const float delta = __bfloat162float(__float2bfloat16_rn(vals[e]));
+                                r[e] = __bfloat162float(__float2bfloat16_rn(old_r[e] + delta));
+                                xs[e] = r[e] * w4[e];
+                                ssq += r[e] * r[e];
+                            }
+                            uint2 r_out, x_out;
+                            *reinterpret_cast<__nv_bfloat162*>(&r_out.x) = __floats2bfloat162_rn(r[0], r[1]);
+                            *reinterpret_cast<__nv_bfloat162*>(&r_out.y) = __floats2bfloat162_rn(r[2], r[3]);
+                            *reinterpret_cast<__nv_bfloat162*>(&x_out.x) = __floats2bfloat162_rn(xs[0], xs[1]);
+                            *reinterpret_cast<__nv_bfloat162*>(&x_out.y) = __floats2bfloat162_rn(xs[2], xs[3]);
+                            const size_t at = (size_t)b * s.N + col;
+                            *reinterpret_cast<uint2*>(fusion.residual + at) = r_out;
+                            *reinterpret_cast<uint2*>((bf16*)out + at) = x_out;
+                        }
+                        ssq = warp_sum(ssq);
+                        if (lane == 0) fusion.out_ssq[rb * kSsqStride + b] = ssq;
+                        continue;
+                    }
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
                         if (col + e < s.N) {
@@ -330,7 +407,7 @@ static int dec_sm_count() {
 
 template <int BN, bool SWIGLU>
 static int launch_decode(const void* x, const void* w, void* out, StreamShape s, float* partials, int* counters,
-                         int out_dtype, cudaStream_t st) {
+                         int out_dtype, const RowFusion& fusion, cudaStream_t st) {
     using Cfg = DecConfig<BN>;
     static_assert(Cfg::kStages >= 2, "the ring needs at least two stages");
     static bool configured = false;
@@ -342,7 +419,7 @@ static int launch_decode(const void* x, const void* w, void* out, StreamShape s,
     CUtensorMap map_w, map_x;
     if (!make_tile_map(&map_w, w, SWIGLU ? 2 * s.N : s.N, s.K, SWIGLU ? 64 : kTileM)) return DFI_ERR_LAUNCH;
     if (!make_tile_map(&map_x, x, s.M, s.K, BN)) return DFI_ERR_LAUNCH;
-    launch(gemm_decode_kernel<BN, SWIGLU>, s.n_ctas, kDecThreads, Cfg::kSmemBytes, st, map_w, map_x, out, s, partials, counters, out_dtype);
+    launch(gemm_decode_kernel<BN, SWIGLU>, s.n_ctas, kDecThreads, Cfg::kSmemBytes, st, map_w, map_x, out, s, partials, counters, out_dtype, fusion);
     return DFI_OK;
 }
 
@@ -376,8 +453,8 @@ DFI_EXPORT int dfi_gemm_decode_counters(int N, int swiglu) {
 
 // out[M, N] (row stride N) = x[M, K] . w[N, K]^T, or with swiglu: silu(x . gate^T) * (x . up^T) for
 // w = [gate; up] of 2N rows.  M <= 64; K a multiple of 8.  n_ctas <= 0: one per SM.
-DFI_EXPORT int dfi_gemm_decode(const void* x, const void* w, void* out, int M, int N, int K, int swiglu, int n_ctas,
-                               float* partials, int* counters, int out_dtype, void* stream) {
+static int gemm_decode(const void* x, const void* w, void* out, int M, int N, int K, int swiglu, int n_ctas,
+                       float* partials, int* counters, int out_dtype, const RowFusion& fusion, void* stream) {
     if (M <= 0 || N <= 0) return DFI_OK;
     if (M > 64 || K <= 0 || K % 8) return DFI_ERR_SHAPE;
     if (out_dtype != DFI_DTYPE_F32 && out_dtype != DFI_DTYPE_BF16) return DFI_ERR_DTYPE;
@@ -404,8 +481,8 @@ DFI_EXPORT int dfi_gemm_decode(const void* x, const void* w, void* out, int M, i
     cudaStream_t st = (cudaStream_t)stream;
     int rc;
 #define DFI_DEC(BNV)                                                                                       \
-    rc = swiglu ? launch_decode<BNV, true>(x, w, out, s, partials, counters, out_dtype, st)                 \
-                : launch_decode<BNV, false>(x, w, out, s, partials, counters, out_dtype, st)
+    rc = swiglu ? launch_decode<BNV, true>(x, w, out, s, partials, counters, out_dtype, fusion, st)         \
+                : launch_decode<BNV, false>(x, w, out, s, partials, counters, out_dtype, fusion, st)
     if (M <= 16) DFI_DEC(16);
     else if (M <= 32) DFI_DEC(32);
     else DFI_DEC(64);
@@ -413,4 +490,40 @@ DFI_EXPORT int dfi_gemm_decode(const void* x, const void* w, void* out, int M, i
     if (rc != DFI_OK) return rc;
     DFI_CHECK_LAUNCH();
     return DFI_OK;
+}
+
+DFI_EXPORT int dfi_gemm_decode(const void* x, const void* w, void* out, int M, int N, int K, int swiglu, int n_ctas,
+                               float* partials, int* counters, int out_dtype, void* stream) {
+    RowFusion none = {};
+    return gemm_decode(x, w, out, M, N, K, swiglu, n_ctas, partials, counters, out_dtype, none, stream);
+}
+
+// Floats per part of a sum-of-squares array, and the number of parts a product with N output
+// columns writes (one per row block).
+DFI_EXPORT int dfi_gemm_decode_ssq_stride() { return kSsqStride; }
+
+// The same product with the RMS norm around it fused in (see the top of this file).
+// in_ssq != null: x's rows lack the factor 1/sqrt(sum(in_ssq parts) / in_dim + in_eps), applied to the result.
+// residual != null (not with swiglu; out is bfloat16): residual[M, N] += bf16(product) in place,
+// out = residual * norm_weight, out_ssq[row block][row] = this block's sum of squares of the new residual.
+DFI_EXPORT int dfi_gemm_decode_fused(const void* x, const void* w, void* out, int M, int N, int K, int swiglu,
+                                     int n_ctas, float* partials, int* counters, int out_dtype, const float* in_ssq,
+                                     int in_parts, int in_dim, float in_eps, void* residual, const float* norm_weight,
+                                     float* out_ssq, void* stream) {
+    RowFusion fusion = {};
+    if (in_ssq != nullptr) {
+        if (in_parts <= 0 || in_dim <= 0) return DFI_ERR_SHAPE;
+        fusion.in_ssq = in_ssq;
+        fusion.in_parts = in_parts;
+        fusion.in_inv_dim = 1.0f / (float)in_dim;
+        fusion.in_eps = in_eps;
+    }
+    if (residual != nullptr) {
+        if (swiglu || out_dtype != DFI_DTYPE_BF16 || norm_weight == nullptr || out_ssq == nullptr || N % 4) return DFI_ERR_SHAPE;
+        if (!aligned16(residual) || !aligned16(norm_weight) || !aligned16(out)) return DFI_ERR_ALIGN;
+        fusion.residual = (bf16*)residual;
+        fusion.norm_weight = norm_weight;
+        fusion.out_ssq = out_ssq;
+    }
+    return gemm_decode(x, w, out, M, N, K, swiglu, n_ctas, partials, counters, out_dtype, fusion, stream);
 }

@@ -139,14 +139,26 @@ class DecoderModel:
         """Runs ``ctx``'s rows through the model; logits float32 ``[wanted rows, vocab]``."""
         residual = kernels.embedding(self.embedding, ctx.tokens)
         pending = None
-        for position, entry in enumerate(self.spec.schedule):
+        schedule = self.spec.schedule
+        for position, entry in enumerate(schedule):
             block = self.blocks[entry.layer]
             view = cache.layer_view(entry.cache, ctx.block_tables, entry.writes_cache) \
                 if block.mixer.cache_need() is not None else None
             state = cache.state.get(position)
-            residual, pending = block.forward(residual, pending, ctx, view, state)
+            if block.fuses_next_norm:
+                # the norm that reads this block's result, if its reader takes rows that lack their factor
+                if position + 1 < len(schedule):
+                    follower = self.blocks[schedule[position + 1].layer]
+                    next_norm = follower.mixer_norm if follower.takes_scaled_pending else None
+                else:
+                    next_norm = self.final_norm if ctx.wants_every_row and ctx.n_wanted > 0 else None
+                residual, pending = block.forward(residual, pending, ctx, view, state, next_norm=next_norm)
+            else:
+                residual, pending = block.forward(residual, pending, ctx, view, state)
         if ctx.n_wanted == 0:
             return None
+        if isinstance(pending, kernels.ScaledRows):
+            return kernels.linear(pending, self.head, out_dtype=torch.float32)
         if not ctx.wants_every_row:
             residual = kernels.gather_rows(residual, ctx.wanted_rows)
             pending = kernels.gather_rows(pending, ctx.wanted_rows) if pending is not None else None

@@ -389,12 +389,45 @@ def tc_error(reset: bool = True) -> int:
 _DECODE_SCRATCH: dict = {}
 
 
-def decode_linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None,
-                  swiglu: bool = False, n_ctas: int | None = None) -> torch.Tensor:
+class ScaledRows:
+    """Rows ``w (.) r`` of an RMS norm that still lack their factor ``1 / rms(r)``: the product that
+    reads them applies it to its result.  ``ssq [parts, stride]`` holds partial sums of squares of
+    ``r`` per row; ``dim`` and ``eps`` are the norm's."""
+
+    __slots__ = ("rows", "ssq", "dim", "eps")
+
+    def __init__(self, rows: torch.Tensor, ssq: torch.Tensor, dim: int, eps: float):
+        self.rows, self.ssq, self.dim, self.eps = rows, ssq, dim, eps
+
+    @property
+    def shape(self):
+        return self.rows.shape
+
+    @property
+    def dtype(self):
+        return self.rows.dtype
+
+
+def add_norm_fusable(rows: torch.Tensor) -> bool:
+    """True if a product over ``rows`` runs the decode kernel, whose epilogue can add a residual and
+    prepare the next norm (``decode_linear(..., add_norm=...)``)."""
+    return (rows.is_cuda and rows.dtype == torch.bfloat16 and rows.dim() == 2 and rows.shape[0] <= SKINNY_MAX_ROWS
+            and rows.shape[1] % 8 == 0 and rows.is_contiguous())
+
+
+def decode_linear(x, weight: torch.Tensor, out_dtype: torch.dtype | None = None,
+                  swiglu: bool = False, n_ctas: int | None = None, add_norm=None):
     """``x @ weight.T`` (with ``swiglu``: ``silu(x @ gate.T) * (x @ up.T)`` for ``weight = [gate; up]``)
     for at most 64 rows of bfloat16 ``x``: the decode step's product as a persistent stream-K kernel on
     tcgen05, with TMA loads and the accumulator in tensor memory.  ``n_ctas``: CTAs that share the
-    work (default one per SM)."""
+    work (default one per SM).
+
+    ``x`` may be ``ScaledRows``: their factor is applied to the result.  ``add_norm = (residual,
+    norm_weight, eps)``: the product is a residual delta; ``residual`` is updated in place and the call
+    returns the ``ScaledRows`` of ``rms_norm(residual) * norm_weight`` for the next product."""
+    scaled = x if isinstance(x, ScaledRows) else None
+    if scaled is not None:
+        x = scaled.rows
     _need_cuda(x, weight)
     m, k = x.shape
     assert x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and weight.shape[1] == k
@@ -414,21 +447,45 @@ def decode_linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype 
                 torch.zeros(max(counters, 8192, held[1].numel() if held else 0), dtype=torch.int32, device=x.device))
         _DECODE_SCRATCH[x.device] = held
     out = torch.empty((m, n), dtype=out_dtype, device=x.device)
-    _check(lib.dfi_gemm_decode(_ptr(x), _ptr(weight), _ptr(out), m, n, k, int(swiglu), n_ctas, _ptr(held[0]),
-                               _ptr(held[1]), _DTYPE_CODE[out_dtype], _stream()), "decode_linear",
-           f"{m} x {k} by {weight.shape[0]} x {k}")
+    what = f"{m} x {k} by {weight.shape[0]} x {k}"
+    if scaled is None and add_norm is None:
+        _check(lib.dfi_gemm_decode(_ptr(x), _ptr(weight), _ptr(out), m, n, k, int(swiglu), n_ctas, _ptr(held[0]),
+                                   _ptr(held[1]), _DTYPE_CODE[out_dtype], _stream()), "decode_linear", what)
+        return out
+    in_ssq, in_parts, in_dim, in_eps = None, 0, 0, 0.0
+    if scaled is not None:
+        assert scaled.ssq.dtype == torch.float32 and scaled.ssq.shape[1] == lib.dfi_gemm_decode_ssq_stride()
+        in_ssq, in_parts, in_dim, in_eps = _ptr(scaled.ssq), scaled.ssq.shape[0], scaled.dim, scaled.eps
+    residual = norm_weight = out_ssq = ssq = None
+    if add_norm is not None:
+        res, norm_w, eps = add_norm
+        if swiglu or out_dtype != torch.bfloat16:
+            raise KernelError("decode_linear adds a residual to a plain bfloat16 product only")
+        assert res.shape == (m, n) and res.dtype == torch.bfloat16 and res.is_contiguous()
+        assert norm_w.shape == (n,) and norm_w.dtype == torch.float32
+        ssq = torch.empty((counters, lib.dfi_gemm_decode_ssq_stride()), dtype=torch.float32, device=x.device)
+        residual, norm_weight, out_ssq = _ptr(res), _ptr(norm_w), _ptr(ssq)
+    _check(lib.dfi_gemm_decode_fused(_ptr(x), _ptr(weight), _ptr(out), m, n, k, int(swiglu), n_ctas, _ptr(held[0]),
+                                     _ptr(held[1]), _DTYPE_CODE[out_dtype], in_ssq, in_parts, in_dim,
+                                     ctypes.c_float(in_eps), residual, norm_weight, out_ssq, _stream()),
+           "decode_linear", what)
+    if add_norm is not None:
+        return ScaledRows(out, ssq, n, float(add_norm[2]))
     return out
 
 
-def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+def linear(x, weight: torch.Tensor, out_dtype: torch.dtype | None = None, add_norm=None):
     """``x @ weight.T`` for ``weight [out, in]`` as stored in the model file.
 
     bfloat16 with at most 64 rows (decoding) runs the hand-written stream-K tcgen05 kernel; larger
     products go to the library's GEMM, as the reference's prefill does
     (engine/engine.py:881-884).  float32 operands take the library's float32 product with
     no reduced-precision mode.  ``out_dtype=torch.float32`` keeps bfloat16 products
-    unrounded (used for logits).
+    unrounded (used for logits).  ``ScaledRows`` in and ``add_norm`` are those of ``decode_linear``.
     """
+    if isinstance(x, ScaledRows) or add_norm is not None:
+        # only made and asked for where the decode kernel runs (add_norm_fusable)
+        return decode_linear(x, weight, out_dtype, add_norm=add_norm)
     _need_cuda(x, weight)
     assert x.dim() == 2 and weight.dim() == 2 and x.shape[1] == weight.shape[1] and x.dtype == weight.dtype
     if x.dtype == torch.bfloat16 and x.shape[0] <= SKINNY_MAX_ROWS and x.shape[1] % 8 == 0 and x.is_contiguous():
@@ -438,9 +495,11 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None 
     return torch.mm(x, weight.t())
 
 
-def linear_swiglu(x: torch.Tensor, gate_up: torch.Tensor) -> torch.Tensor:
+def linear_swiglu(x, gate_up: torch.Tensor) -> torch.Tensor:
     """``silu(x @ gate.T) * (x @ up.T)`` for the fused matrix ``gate_up = [gate; up]``: one kernel
     when decoding in bfloat16, else the product followed by the SwiGLU kernel."""
+    if isinstance(x, ScaledRows):
+        return decode_linear(x, gate_up, swiglu=True)
     if x.dtype == torch.bfloat16 and x.shape[0] <= SKINNY_MAX_ROWS and x.shape[1] % 8 == 0 and x.is_contiguous():
         return decode_linear(x, gate_up, swiglu=True)
     return swiglu(linear(x, gate_up))

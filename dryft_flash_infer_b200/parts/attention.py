@@ -21,6 +21,8 @@ class Attention(Mixer):
     """
 
     kind = "attention"
+    accepts_scaled_rows = True
+    fuses_add_norm = True
 
     def __init__(self, hidden_size: int, n_heads: int, n_kv_heads: int, head_dim: int, qk_norm: bool = True,
                  qk_norm_eps: float = 1e-6, position: PartSpec | None = None, window: int = 0,
@@ -59,7 +61,7 @@ class Attention(Mixer):
         if self.position is not None:
             self.position.prepare(max_positions, device)
 
-    def forward(self, x, ctx, cache, state):
+    def forward(self, x, ctx, cache, state, add_norm=None):
         qkv = kernels.linear(x, self.qkv)
         cos = self.position.cos if self.position is not None else None
         sin = self.position.sin if self.position is not None else None
@@ -67,7 +69,7 @@ class Attention(Mixer):
                                        self.qk_norm_eps, cos, sin, ctx.row_pos, ctx.row_seq, cache)
         attended = kernels.attention(q, cache, ctx, self.n_heads, self.n_kv_heads, self.head_dim, self.scale,
                                      self.window)
-        return kernels.linear(attended, self.o)
+        return kernels.linear(attended, self.o, add_norm=add_norm)
 
 
 register_part("mixer", Attention.kind, Attention)

@@ -65,6 +65,12 @@ class Part:
     #: numbers (no host read-back, no shape that depends on values), so that a decode step through
     #: it can be captured in a CUDA graph.  A model decodes through a graph only if all its parts say so.
     graph_safe = False
+    #: True if ``forward`` takes its rows as ``kernels.ScaledRows`` too (normalised rows that still
+    #: lack their 1/rms factor, which the part's first product applies)
+    accepts_scaled_rows = False
+    #: True if ``forward`` takes ``add_norm=(residual, weight, eps)``: its last product then adds its
+    #: result to ``residual`` in place and returns the ``ScaledRows`` of the norm that follows
+    fuses_add_norm = False
 
     def tensors(self) -> dict[str, TensorDecl]:
         return {}
@@ -92,6 +98,11 @@ class Norm(Part):
     def add_forward(self, residual, delta):
         residual.add_(delta)
         return self.forward(residual)
+
+    def scale_fusion(self):
+        """``(weight, eps)`` if the norm is ``x / rms(x) * weight`` over the whole row, so that a product
+        before it can prepare it and the product after it can finish it; else None."""
+        return None
 
 
 class PositionEncoding(Part):
@@ -126,6 +137,9 @@ class Block:
     """
 
     kind = ""
+    #: True if ``forward`` takes ``next_norm`` (the norm that will read this block's result) and may
+    #: then return ``pending`` as ``kernels.ScaledRows`` of that norm, the sum already in ``residual``
+    fuses_next_norm = False
 
     def __init__(self, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm, ffn_norm: Norm):
         self.mixer, self.feed_forward = mixer, feed_forward
@@ -138,6 +152,11 @@ class Block:
     @property
     def graph_safe(self) -> bool:
         return all(part.graph_safe for part in self.parts().values())
+
+    @property
+    def takes_scaled_pending(self) -> bool:
+        """True if ``pending`` may arrive as ``ScaledRows`` of this block's first norm."""
+        return False
 
     def forward(self, residual, pending, ctx, cache, state):
         raise NotImplementedError

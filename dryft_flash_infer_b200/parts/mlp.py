@@ -12,6 +12,8 @@ class SwiGLU(FeedForward):
     engine/kernels/reference.py:74-79)."""
 
     kind = "swiglu"
+    accepts_scaled_rows = True
+    fuses_add_norm = True
     graph_safe = True
 
     def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "silu"):
@@ -28,9 +30,9 @@ class SwiGLU(FeedForward):
             "down_proj": TensorDecl((hidden, inter), "down"),
         }
 
-    def forward(self, x, ctx):
+    def forward(self, x, ctx, add_norm=None):
         inner = kernels.linear_swiglu(x, self.gate_up)
-        return kernels.linear(inner, self.down)
+        return kernels.linear(inner, self.down, add_norm=add_norm)
 
 
 register_part("feed_forward", SwiGLU.kind, SwiGLU)

@@ -31,5 +31,8 @@ class RMSNorm(Norm):
     def add_forward(self, residual, delta):
         return kernels.add_rms_norm(residual, delta, self.weight, self.eps)
 
+    def scale_fusion(self):
+        return self.weight, self.eps
+
 
 register_part("norm", RMSNorm.kind, RMSNorm)

@@ -414,6 +414,45 @@ def test_tcgen05_decode_gemm_with_swiglu(m, inter, k):
         assert torch.allclose(got.cpu(), want, atol=3e-3, rtol=2e-3), (ctas, float((got.cpu() - want).abs().max()))
 
 
+@pytest.mark.parametrize("m", [1, 8, 33, 64])
+@pytest.mark.parametrize("hidden, k, n2", [(200, 96, 72), (128, 64, 256), (2560, 4096, 640), (40, 40, 40)])
+def test_tcgen05_decode_gemm_with_the_norm_fused_around_it(m, hidden, k, n2):
+    """A product that adds its result to the residual and prepares the norm, then products that finish
+    that norm (plain and with SwiGLU), against add -> rms_norm -> product done one after the other."""
+    from dryft_flash_infer_b200.ops import kernels
+
+    g = torch.Generator().manual_seed(m + hidden + k)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    w = (torch.randn(hidden, k, generator=g) * 0.1).to(torch.bfloat16)
+    residual = (torch.randn(m, hidden, generator=g) * 3).to(torch.bfloat16)
+    norm_w = 1 + 0.3 * torch.randn(hidden, generator=g)
+    w2 = (torch.randn(n2, hidden, generator=g) * 0.1).to(torch.bfloat16)
+    gate_up = (torch.randn(2 * n2, hidden, generator=g) * 0.1).to(torch.bfloat16)
+    eps = 1e-5
+    for ctas in (None, 1, 3, 500):
+        res = residual.clone().cuda()
+        scaled = kernels.decode_linear(x.cuda(), w.cuda(), n_ctas=ctas, add_norm=(res, norm_w.cuda(), eps))
+        assert kernels.tc_error() == 0 and isinstance(scaled, kernels.ScaledRows)
+        delta = (x.float() @ w.float().T).to(torch.bfloat16).float()
+        want_res = (residual.float() + delta).to(torch.bfloat16).float()
+        got_res = res.float().cpu()
+        # the delta may round the other way where the float32 sums differ in their last bits
+        assert torch.allclose(got_res, want_res, atol=0.04, rtol=1e-2)
+        assert torch.equal(scaled.rows.float().cpu(), (got_res * norm_w).to(torch.bfloat16).float())
+        ssq = scaled.ssq.cpu()[:, :m].sum(0)
+        assert torch.allclose(ssq, (got_res ** 2).sum(-1), rtol=1e-5)
+        normed = plain_model.rms_norm(got_res, norm_w, eps)
+        y = kernels.decode_linear(scaled, w2.cuda(), torch.float32, n_ctas=ctas)
+        want = normed @ w2.float().T
+        assert torch.allclose(y.cpu(), want, atol=0.02 * float(want.abs().max()), rtol=1e-2), float((y.cpu() - want).abs().max())
+        z = kernels.linear_swiglu(scaled, gate_up.cuda())
+        gu = normed @ gate_up.float().T
+        want = gu[:, :n2] / (1 + torch.exp(-gu[:, :n2])) * gu[:, n2:]
+        assert torch.allclose(z.float().cpu(), want, atol=0.03 * float(want.abs().max()), rtol=2e-2)
+    with pytest.raises(kernels.KernelError, match="plain bfloat16"):
+        kernels.decode_linear(x.cuda(), w.cuda(), torch.float32, add_norm=(residual.cuda(), norm_w.cuda(), eps))
+
+
 @pytest.mark.parametrize("m, n, k", [(128, 128, 64), (300, 320, 200), (256, 256, 1024)])
 def test_tcgen05_gemm_with_a_row_major_second_operand(m, n, k):
     """out = x @ w for w stored [K, N]: the operand layout the value product of attention uses."""
