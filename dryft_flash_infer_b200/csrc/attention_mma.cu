@@ -396,11 +396,8 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
         }
     }
     const int cta = blockIdx.x;
-    atrace(1);
-    pdl_wait();        // from here on the queries and the new keys and values are read
-    if (cta >= run.n_ctas) return;
-    atrace(2);
-    const int u_begin = dec_run_begin(run, cta), u_end = dec_run_begin(run, cta + 1);
+    const bool idle = cta >= run.n_ctas;
+    const int u_begin = idle ? 0 : dec_run_begin(run, cta), u_end = idle ? 0 : dec_run_begin(run, cta + 1);
 
     // the sequence that holds unit u_begin: the last one whose first unit is not past it
     int seq;
@@ -412,6 +409,33 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
         }
         seq = lo;
     }
+    // Pages that lie wholly before this step's token were written by earlier steps: the first of them
+    // are asked for now, while the kernel before (which writes the new token's keys and values and
+    // the queries) may still be running.
+    unsigned preloaded = 0;
+    if (!idle) {
+        const int seq_tiles = cum_s[seq + 1] - cum_s[seq];
+        const int in_seq = u_begin - cum_s[seq] * n_kv;
+        const int kv_head = in_seq / seq_tiles, t_a = in_seq % seq_tiles;
+        const int t_b = min(seq_tiles, t_a + (u_end - u_begin));
+        const int pos = seq_start[seq];
+        const int first_key = window > 0 ? max(0, pos - window + 1) : 0;
+        const int t_begin = first_key / kPage + t_a, t_end = first_key / kPage + t_b - 1;
+        const int* table = block_table + (size_t)seq * table_width;
+#pragma unroll
+        for (int i = 0; i < kKvStages - 1; ++i) {
+            const int t = t_begin + i;
+            if (t <= t_end && t < pos / kPage) {
+                load_page(k_s + i * kPage * kStride, page_ptr(k_cache, table, t, ring_tokens, n_kv, kv_head), t * kPage, pos + 1, false);
+                load_page(v_s + i * kPage * kStride, page_ptr(v_cache, table, t, ring_tokens, n_kv, kv_head), t * kPage, pos + 1, true);
+                preloaded |= 1u << i;
+            }
+        }
+    }
+    atrace(1);
+    pdl_wait();        // from here on the queries and the new keys and values are read
+    if (idle) return;
+    atrace(2);
     int u = u_begin;
     bool first_segment = true;
     while (u < u_end) {
@@ -451,7 +475,7 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
         };
 #pragma unroll
         for (int i = 0; i < kKvStages - 1; ++i) {
-            if (t_begin + i <= t_end) load_tile(t_begin + i);
+            if (t_begin + i <= t_end && !(first_segment && ((preloaded >> i) & 1u))) load_tile(t_begin + i);
             cp_async_commit();
         }
         uint32_t qf[D / 16][4];
