@@ -13,6 +13,13 @@
 // ranges (the result does not depend on who finished when), applies the epilogue and resets the
 // counter.  No CTA waits for another CTA; waits inside a CTA (on its own mbarriers) are bounded.
 //
+// CLUSTER variant, for a matrix with few row blocks cut into 2 to 8 parts each: the CTAs of a row
+// block form a thread-block cluster and add their parts through distributed shared memory instead
+// of scratch memory and tickets.  Every CTA owns the columns c of the row block with (c / 4) mod
+// parts equal to its rank; each CTA stores its sums for a column straight into the owner's shared
+// memory, all CTAs meet once at the cluster barrier, and every owner adds the parts in the order of
+// their k ranges and applies the epilogue to its columns.
+//
 // Two optional fusions with the RMS norm around the product, both in the adding CTA's epilogue:
 // * scaled input: x holds rows w (.) r that still lack their 1/rms factor; the sums of squares of r
 //   come as partial sums per row, and since the factor is one number per row it is applied to the
@@ -25,6 +32,8 @@
 // SWIGLU variant: W = [gate; up] of 2N rows; a row block is 64 gate rows and the 64 up rows that
 // belong to them, and the epilogue writes silu(gate) * up (engine/kernels/reference.py:74-79;
 // the fusion follows the idea of engine/kernels/cuda_mlp.py:39-125).
+#include <stdlib.h>
+
 #include "tcgen05.cuh"
 
 namespace dfi {
@@ -79,6 +88,28 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(s32(bar)) : "memory");
 }
 
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+    return r;
+}
+// Address of this CTA's shared-memory location `addr` in the CTA of rank `rank` of the cluster.
+__device__ __forceinline__ uint32_t cluster_map(uint32_t addr, uint32_t rank) {
+    uint32_t out;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(out) : "r"(addr), "r"(rank));
+    return out;
+}
+__device__ __forceinline__ void cluster_store(uint32_t addr, float v) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;\n" ::"r"(addr), "f"(v) : "memory");
+}
+// Every thread of every CTA of the cluster arrives (release) and waits (acquire).
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.aligned;\n" ::: "memory");
+    asm volatile("barrier.cluster.wait.aligned;\n" ::: "memory");
+}
+// Columns of a row block come in groups of four; group g belongs to rank g mod parts.
+__device__ __forceinline__ int owned_groups(int rank, int parts, int groups) { return (groups - rank + parts - 1) / parts; }
+
 // -DDFI_TRACE: every CTA records the global timer at a few points of its life (a debugging build).
 #ifdef DFI_TRACE
 __device__ unsigned long long g_trace[512 * 8];
@@ -95,7 +126,8 @@ template <int BN> struct DecConfig {
     static constexpr int kABytes = kTileM * kTileK * 2;
     static constexpr int kBBytes = BN * kTileK * 2;
     static constexpr int kStageBytes = kABytes + kBBytes;
-    static constexpr int kStagingBytes = BN * kTileM * 4;            // float [BN][128] for the epilogue
+    static constexpr int kStagingBytes = BN * 144 * 4;               // float [BN][128] for the epilogue; in a cluster
+                                                                     // [parts][BN][owned columns], at most 144 BN floats
     static constexpr int kStagesRaw = (kDecSmemBudget - 1024 - kStagingBytes) / kStageBytes;
     static constexpr int kStages = kStagesRaw > 10 ? 10 : kStagesRaw;
     static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;      // two accumulators
@@ -103,7 +135,82 @@ template <int BN> struct DecConfig {
     static constexpr int kSlotFloats = BN * kTileM;                  // one part of one row block
 };
 
-template <int BN, bool SWIGLU>
+// What the epilogue of one group of four columns needs from memory besides the sums: asked for
+// early, so that it travels together with the parts.
+struct FinishInput {
+    uint2 residual;
+    float4 norm_weight;
+    bool inside;
+};
+template <bool SWIGLU>
+__device__ __forceinline__ FinishInput finish_begin(const RowFusion& fusion, const StreamShape& s, int col, int b) {
+    FinishInput in;
+    in.residual = make_uint2(0u, 0u);
+    in.norm_weight = make_float4(0.f, 0.f, 0.f, 0.f);
+    in.inside = col < s.N;       // N is a multiple of 4 with an add-norm output: a group is inside the matrix or outside it
+    if (!SWIGLU && fusion.residual != nullptr && in.inside) {
+        in.residual = *reinterpret_cast<const uint2*>(fusion.residual + (size_t)b * s.N + col);
+        in.norm_weight = *reinterpret_cast<const float4*>(fusion.norm_weight + col);
+    }
+    return in;
+}
+// Sums v (and u, the "up" half with SwiGLU) of row b, columns col..col+3, become outputs: the input
+// rows' 1/rms factor, SwiGLU, then either the add-norm output or a plain store.  With an add-norm
+// output every lane of the warp must call this (inactive lanes contribute nothing); `seg` lanes
+// hold the columns of one row and share its sum of squares, written as part `ssq_part`.
+template <bool SWIGLU>
+__device__ __forceinline__ void finish_group(const RowFusion& fusion, const StreamShape& s, void* out, int out_dtype,
+                                             const float* row_scale, const FinishInput& in, int col, int b, float4 v,
+                                             float4 u, bool active, int seg, int ssq_part, int lane) {
+    if (fusion.in_ssq != nullptr && active) {
+        const float rs = row_scale[b];
+        v.x *= rs; v.y *= rs; v.z *= rs; v.w *= rs;
+        if (SWIGLU) { u.x *= rs; u.y *= rs; u.z *= rs; u.w *= rs; }
+    }
+    if (SWIGLU) {
+        v.x = silu_times(v.x, u.x); v.y = silu_times(v.y, u.y);
+        v.z = silu_times(v.z, u.z); v.w = silu_times(v.w, u.w);
+    }
+    const float vals[4] = {v.x, v.y, v.z, v.w};
+    if (!SWIGLU && fusion.residual != nullptr) {
+        float ssq = 0.f;
+        if (active && in.inside) {
+            const float2 r01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&in.residual.x));
+            const float2 r23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&in.residual.y));
+            const float old_r[4] = {r01.x, r01.y, r23.x, r23.y};
+            const float w4[4] = {in.norm_weight.x, in.norm_weight.y, in.norm_weight.z, in.norm_weight.w};
+            float r[4], xs[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float delta = __bfloat162float(__float2bfloat16_rn(vals[e]));
+                r[e] = __bfloat162float(__float2bfloat16_rn(old_r[e] + delta));
+                xs[e] = r[e] * w4[e];
+                ssq += r[e] * r[e];
+            }
+            uint2 r_out, x_out;
+            *reinterpret_cast<__nv_bfloat162*>(&r_out.x) = __floats2bfloat162_rn(r[0], r[1]);
+            *reinterpret_cast<__nv_bfloat162*>(&r_out.y) = __floats2bfloat162_rn(r[2], r[3]);
+            *reinterpret_cast<__nv_bfloat162*>(&x_out.x) = __floats2bfloat162_rn(xs[0], xs[1]);
+            *reinterpret_cast<__nv_bfloat162*>(&x_out.y) = __floats2bfloat162_rn(xs[2], xs[3]);
+            const size_t at = (size_t)b * s.N + col;
+            *reinterpret_cast<uint2*>(fusion.residual + at) = r_out;
+            *reinterpret_cast<uint2*>((bf16*)out + at) = x_out;
+        }
+        for (int o = seg >> 1; o > 0; o >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, o);
+        if (active && (lane & (seg - 1)) == 0) fusion.out_ssq[ssq_part * kSsqStride + b] = ssq;
+        return;
+    }
+    if (!active) return;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        if (col + e < s.N) {
+            if (out_dtype == DFI_DTYPE_F32) ((float*)out)[(size_t)b * s.N + col + e] = vals[e];
+            else ((bf16*)out)[(size_t)b * s.N + col + e] = __float2bfloat16_rn(vals[e]);
+        }
+    }
+}
+
+template <int BN, bool SWIGLU, bool CLUSTER>
 __global__ void __launch_bounds__(kDecThreads, 1)
 gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                    void* __restrict__ out, StreamShape s, float* __restrict__ partials, int* __restrict__ counters,
@@ -242,7 +349,31 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 epilogue_barrier();
             }
         }
-        while (done < n_units && ok) {
+        if (CLUSTER) {
+            // the run is one part of row block first_rb: every sum goes to the CTA that owns its column
+            ok = mbar_wait(&acc_full[0], 0, 3);
+            if (ok) {
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+                const int parts = s.parts;
+                const int stride = ((kTileM / 4 + parts - 1) / parts) * 4;       // floats per (sender, row) in an owner
+                const int group_of_t = t >> 2;
+                const uint32_t owner = (uint32_t)(group_of_t % parts);
+                const int local = (group_of_t / parts) * 4 + (t & 3);
+                const uint32_t base = cluster_map(s32(staging), owner) +
+                                      (uint32_t)(((int)cluster_rank() * BN * stride + local) * 4);
+#pragma unroll
+                for (int c = 0; c < BN; c += 16) {
+                    uint32_t d[16];
+                    tmem_load16(taddr + c, d);
+#pragma unroll
+                    for (int e = 0; e < 16; ++e)
+                        if (c + e < s.M) cluster_store(base + (uint32_t)((c + e) * stride * 4), __uint_as_float(d[e]));
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            }
+        }
+        while (!CLUSTER && done < n_units && ok) {
             const int seg_units = min(s.k_chunks - seg_first_kc, n_units - done);
             const bool complete = seg_units == s.k_chunks;
             const int buf = segment & 1;
@@ -297,16 +428,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 for (int item = t; item < s.M * kGroups; item += 128) {
                     const int b = item / kGroups, c4 = (item % kGroups) * 4;
                     const int offset = b * kTileM + c4;
-                    // add-norm output: the residual and the norm's weight travel with the parts (N is a
-                    // multiple of 4 there, so a group of four columns is inside the matrix or outside it)
-                    const bool add_norm = !SWIGLU && fusion.residual != nullptr;
-                    const bool inside = rb * kCols + c4 < s.N;
-                    uint2 res_raw = make_uint2(0u, 0u);
-                    float4 norm_w = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (add_norm && inside) {
-                        res_raw = *reinterpret_cast<const uint2*>(fusion.residual + (size_t)b * s.N + rb * kCols + c4);
-                        norm_w = *reinterpret_cast<const float4*>(fusion.norm_weight + rb * kCols + c4);
-                    }
+                    const FinishInput in = finish_begin<SWIGLU>(fusion, s, rb * kCols + c4, b);
                     float4 v = complete ? *reinterpret_cast<const float4*>(first_part + offset)
                                         : __ldcg(reinterpret_cast<const float4*>(first_part + offset));
                     float4 u = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -329,53 +451,8 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                             if (SWIGLU) { u.x += u4[j].x; u.y += u4[j].y; u.z += u4[j].z; u.w += u4[j].w; }
                         }
                     }
-                    if (fusion.in_ssq != nullptr) {
-                        const float rs = row_scale[b];
-                        v.x *= rs; v.y *= rs; v.z *= rs; v.w *= rs;
-                        if (SWIGLU) { u.x *= rs; u.y *= rs; u.z *= rs; u.w *= rs; }
-                    }
-                    if (SWIGLU) {
-                        v.x = silu_times(v.x, u.x); v.y = silu_times(v.y, u.y);
-                        v.z = silu_times(v.z, u.z); v.w = silu_times(v.w, u.w);
-                    }
-                    const int col = rb * kCols + c4;
-                    const float vals[4] = {v.x, v.y, v.z, v.w};
-                    if (add_norm) {
-                        // kGroups is 32 here: a warp holds one row's 128 columns of this row block
-                        float ssq = 0.f;
-                        if (inside) {
-                            const float2 r01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&res_raw.x));
-                            const float2 r23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&res_raw.y));
-                            const float old_r[4] = {r01.x, r01.y, r23.x, r23.y};
-                            const float w4[4] = {norm_w.x, norm_w.y, norm_w.z, norm_w.w};
-                            float r[4], xs[4];
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-                                const float delta = __bfloat162float(__float2bfloat16_rn(vals[e]));
-                                r[e] = __bfloat162float(__float2bfloat16_rn(old_r[e] + delta));
-                                xs[e] = r[e] * w4[e];
-                                ssq += r[e] * r[e];
-                            }
-                            uint2 r_out, x_out;
-                            *reinterpret_cast<__nv_bfloat162*>(&r_out.x) = __floats2bfloat162_rn(r[0], r[1]);
-                            *reinterpret_cast<__nv_bfloat162*>(&r_out.y) = __floats2bfloat162_rn(r[2], r[3]);
-                            *reinterpret_cast<__nv_bfloat162*>(&x_out.x) = __floats2bfloat162_rn(xs[0], xs[1]);
-                            *reinterpret_cast<__nv_bfloat162*>(&x_out.y) = __floats2bfloat162_rn(xs[2], xs[3]);
-                            const size_t at = (size_t)b * s.N + col;
-                            *reinterpret_cast<uint2*>(fusion.residual + at) = r_out;
-                            *reinterpret_cast<uint2*>((bf16*)out + at) = x_out;
-                        }
-                        ssq = warp_sum(ssq);
-                        if (lane == 0) fusion.out_ssq[rb * kSsqStride + b] = ssq;
-                        continue;
-                    }
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        if (col + e < s.N) {
-                            if (out_dtype == DFI_DTYPE_F32) ((float*)out)[(size_t)b * s.N + col + e] = vals[e];
-                            else ((bf16*)out)[(size_t)b * s.N + col + e] = __float2bfloat16_rn(vals[e]);
-                        }
-                    }
+                    // a warp holds one row's columns of this row block: 32 lanes share a sum of squares
+                    finish_group<SWIGLU>(fusion, s, out, out_dtype, row_scale, in, rb * kCols + c4, b, v, u, true, 32, rb, lane);
                 }
                 if (!complete && t == 0) counters[rb] = 0;   // ready for the next call
             }
@@ -387,11 +464,53 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             ++segment;
         }
     }
+    if (CLUSTER) {
+        // every thread of every CTA of the cluster comes here, whatever happened to it before
+        __syncwarp();
+        cluster_sync_all();
+        if (warp >= 2) {
+            const int t = (warp & 3) * 32 + lane;
+            const int parts = s.parts, rank = (int)cluster_rank();
+            const int stride = ((kTileM / 4 + parts - 1) / parts) * 4;
+            const int n_owned = owned_groups(rank, parts, kTileM / 4);
+            int pad = 4;                                        // lanes per row: a power of two that holds the owned groups
+            while (pad * parts < kTileM / 4) pad <<= 1;
+            const int total = s.M * pad;
+            for (int item = t; item < ((total + 31) & ~31); item += 128) {
+                const int b = item / pad, j = item % pad;
+                const bool active = item < total && j < n_owned;
+                const int col = first_rb * kTileM + (rank + parts * j) * 4;
+                FinishInput in = {};
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (active) {
+                    in = finish_begin<false>(fusion, s, col, b);
+                    float4 w4[8];
+#pragma unroll
+                    for (int p = 0; p < 8; ++p)
+                        w4[p] = p < parts ? *reinterpret_cast<const float4*>(staging + (p * BN + b) * stride + j * 4)
+                                          : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                    for (int p = 0; p < 8; ++p) { v.x += w4[p].x; v.y += w4[p].y; v.z += w4[p].z; v.w += w4[p].w; }
+                }
+                finish_group<false>(fusion, s, out, out_dtype, row_scale, in, col, b, v, make_float4(0.f, 0.f, 0.f, 0.f),
+                                    active, pad, first_rb * parts + rank, lane);
+            }
+        }
+    }
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(Cfg::kTmemCols) : "memory");
     }
+}
+
+static int cluster_enabled() {
+    static int enabled = -1;
+    if (enabled < 0) {
+        const char* text = getenv("DRYFT_GEMM_CLUSTER");        // "off": parts meet through scratch memory and tickets
+        enabled = (text != nullptr && (text[0] == 'o' || text[0] == 'O') && (text[1] == 'f' || text[1] == 'F')) ? 0 : 1;
+    }
+    return enabled;
 }
 
 static int g_dec_sm_count = 0;
@@ -405,22 +524,67 @@ static int dec_sm_count() {
     return g_dec_sm_count;
 }
 
-template <int BN, bool SWIGLU>
+template <int BN, bool SWIGLU, bool CLUSTER>
 static int launch_decode(const void* x, const void* w, void* out, StreamShape s, float* partials, int* counters,
                          int out_dtype, const RowFusion& fusion, cudaStream_t st) {
     using Cfg = DecConfig<BN>;
     static_assert(Cfg::kStages >= 2, "the ring needs at least two stages");
     static bool configured = false;
     if (!configured) {
-        if (cudaFuncSetAttribute(gemm_decode_kernel<BN, SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess)
+        if (cudaFuncSetAttribute(gemm_decode_kernel<BN, SWIGLU, CLUSTER>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess)
             return DFI_ERR_LAUNCH;
         configured = true;
     }
     CUtensorMap map_w, map_x;
     if (!make_tile_map(&map_w, w, SWIGLU ? 2 * s.N : s.N, s.K, SWIGLU ? 64 : kTileM)) return DFI_ERR_LAUNCH;
     if (!make_tile_map(&map_x, x, s.M, s.K, BN)) return DFI_ERR_LAUNCH;
-    launch(gemm_decode_kernel<BN, SWIGLU>, s.n_ctas, kDecThreads, Cfg::kSmemBytes, st, map_w, map_x, out, s, partials, counters, out_dtype, fusion);
+    if (CLUSTER) {
+        // the parts of a row block are neighbours in the grid: they form a cluster
+        cudaLaunchConfig_t config = {};
+        config.gridDim = dim3(s.n_ctas);
+        config.blockDim = dim3(kDecThreads);
+        config.dynamicSmemBytes = Cfg::kSmemBytes;
+        config.stream = st;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = s.parts;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        config.attrs = attr;
+        config.numAttrs = pdl_enabled() ? 2 : 1;
+        if (cudaLaunchKernelEx(&config, gemm_decode_kernel<BN, SWIGLU, CLUSTER>, map_w, map_x, out, s, partials, counters,
+                               out_dtype, fusion) != cudaSuccess)
+            return DFI_ERR_LAUNCH;
+        return DFI_OK;
+    }
+    launch(gemm_decode_kernel<BN, SWIGLU, CLUSTER>, s.n_ctas, kDecThreads, Cfg::kSmemBytes, st, map_w, map_x, out, s, partials, counters, out_dtype, fusion);
     return DFI_OK;
+}
+
+// The split of the work over CTAs: stream-K, or for few row blocks the same number of parts each.
+static bool plan_decode(StreamShape& s, int M, int N, int K, int swiglu, int n_ctas) {
+    s.M = M; s.N = N; s.K = K;
+    s.k_chunks = (K + kTileK - 1) / kTileK;
+    const int cols = swiglu ? kTileM / 2 : kTileM;
+    s.row_blocks = (N + cols - 1) / cols;
+    if ((long long)s.row_blocks * s.k_chunks > (1 << 22)) return false;
+    s.units = s.row_blocks * s.k_chunks;
+    s.parts = 0;
+    s.n_ctas = s.units < n_ctas ? s.units : n_ctas;
+    if (s.row_blocks * 2 <= n_ctas) {
+        // few row blocks: the same number of parts for each, as many as fill the CTAs
+        int parts = n_ctas / s.row_blocks;
+        if (parts > s.k_chunks) parts = s.k_chunks;
+        s.parts = parts;
+        s.n_ctas = s.row_blocks * parts;
+    }
+    return true;
+}
+// The parts of a row block meet in a cluster when there are 2 to 8 of them (and no SwiGLU epilogue).
+static bool plan_uses_cluster(const StreamShape& s, int swiglu) {
+    return !swiglu && s.parts >= 2 && s.parts <= 8 && cluster_enabled();
 }
 
 }  // namespace dfi
@@ -461,28 +625,17 @@ static int gemm_decode(const void* x, const void* w, void* out, int M, int N, in
     if (!aligned16(x) || !aligned16(w)) return DFI_ERR_ALIGN;
     if (counters == nullptr || partials == nullptr) return DFI_ERR_SHAPE;
     StreamShape s;
-    s.M = M; s.N = N; s.K = K;
-    s.k_chunks = (K + kTileK - 1) / kTileK;
-    s.row_blocks = dfi_gemm_decode_counters(N, swiglu);
-    if ((long long)s.row_blocks * s.k_chunks > (1 << 22)) return DFI_ERR_LIMIT;
-    s.units = s.row_blocks * s.k_chunks;
     if (n_ctas <= 0) n_ctas = dec_sm_count();
     if (n_ctas <= 0) return DFI_ERR_LAUNCH;
     if (n_ctas > 512) n_ctas = 512;
-    s.parts = 0;
-    s.n_ctas = s.units < n_ctas ? s.units : n_ctas;
-    if (s.row_blocks * 2 <= n_ctas) {
-        // few row blocks: the same number of parts for each, as many as fill the CTAs
-        int parts = n_ctas / s.row_blocks;
-        if (parts > s.k_chunks) parts = s.k_chunks;
-        s.parts = parts;
-        s.n_ctas = s.row_blocks * parts;
-    }
+    if (!plan_decode(s, M, N, K, swiglu, n_ctas)) return DFI_ERR_LIMIT;
+    const bool cluster = plan_uses_cluster(s, swiglu);
     cudaStream_t st = (cudaStream_t)stream;
     int rc;
 #define DFI_DEC(BNV)                                                                                       \
-    rc = swiglu ? launch_decode<BNV, true>(x, w, out, s, partials, counters, out_dtype, fusion, st)         \
-                : launch_decode<BNV, false>(x, w, out, s, partials, counters, out_dtype, fusion, st)
+    rc = swiglu ? launch_decode<BNV, true, false>(x, w, out, s, partials, counters, out_dtype, fusion, st)  \
+         : cluster ? launch_decode<BNV, false, true>(x, w, out, s, partials, counters, out_dtype, fusion, st) \
+                   : launch_decode<BNV, false, false>(x, w, out, s, partials, counters, out_dtype, fusion, st)
     if (M <= 16) DFI_DEC(16);
     else if (M <= 32) DFI_DEC(32);
     else DFI_DEC(64);
@@ -501,6 +654,14 @@ DFI_EXPORT int dfi_gemm_decode(const void* x, const void* w, void* out, int M, i
 // Floats per part of a sum-of-squares array, and the number of parts a product with N output
 // columns writes (one per row block).
 DFI_EXPORT int dfi_gemm_decode_ssq_stride() { return kSsqStride; }
+// Parts of the sum-of-squares array that a product with an add-norm output writes for this shape.
+DFI_EXPORT int dfi_gemm_decode_ssq_parts(int M, int N, int K, int n_ctas) {
+    StreamShape s;
+    if (n_ctas <= 0) n_ctas = dec_sm_count();
+    if (n_ctas > 512) n_ctas = 512;
+    if (n_ctas <= 0 || !plan_decode(s, M, N, K, 0, n_ctas)) return 0;
+    return plan_uses_cluster(s, 0) ? s.row_blocks * s.parts : s.row_blocks;
+}
 
 // The same product with the RMS norm around it fused in (see the top of this file).
 // in_ssq != null: x's rows lack the factor 1/sqrt(sum(in_ssq parts) / in_dim + in_eps), applied to the result.

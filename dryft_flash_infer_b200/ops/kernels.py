@@ -463,7 +463,8 @@ def decode_linear(x, weight: torch.Tensor, out_dtype: torch.dtype | None = None,
             raise KernelError("decode_linear adds a residual to a plain bfloat16 product only")
         assert res.shape == (m, n) and res.dtype == torch.bfloat16 and res.is_contiguous()
         assert norm_w.shape == (n,) and norm_w.dtype == torch.float32
-        ssq = torch.empty((counters, lib.dfi_gemm_decode_ssq_stride()), dtype=torch.float32, device=x.device)
+        ssq = torch.empty((lib.dfi_gemm_decode_ssq_parts(m, n, k, n_ctas), lib.dfi_gemm_decode_ssq_stride()),
+                          dtype=torch.float32, device=x.device)
         residual, norm_weight, out_ssq = _ptr(res), _ptr(norm_w), _ptr(ssq)
     _check(lib.dfi_gemm_decode_fused(_ptr(x), _ptr(weight), _ptr(out), m, n, k, int(swiglu), n_ctas, _ptr(held[0]),
                                      _ptr(held[1]), _DTYPE_CODE[out_dtype], in_ssq, in_parts, in_dim,
