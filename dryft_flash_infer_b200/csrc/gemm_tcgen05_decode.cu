@@ -579,6 +579,10 @@ static bool plan_decode(StreamShape& s, int M, int N, int K, int swiglu, int n_c
         if (parts > s.k_chunks) parts = s.k_chunks;
         s.parts = parts;
         s.n_ctas = s.row_blocks * parts;
+    } else if (s.row_blocks > n_ctas && s.row_blocks <= 2 * n_ctas) {
+        // up to two row blocks per SM: one CTA per row block (two CTAs fit an SM), and no sum is split
+        s.parts = 1;
+        s.n_ctas = s.row_blocks;
     }
     return true;
 }
