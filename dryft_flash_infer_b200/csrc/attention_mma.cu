@@ -531,28 +531,30 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
         }
         __syncthreads();
         const int slot = cta * 2 + (first_segment ? 0 : 1);
-        for (int i = threadIdx.x; i < group * D; i += kThreads) {
-            const int row = i / D, d = i % D;
+        // a thread takes four neighbouring output elements of a row at a time
+        for (int i = threadIdx.x; i < group * (D / 4); i += kThreads) {
+            const int row = i / (D / 4), d = (i % (D / 4)) * 4;
             float mx = -INFINITY;
 #pragma unroll
             for (int w = 0; w < 4; ++w) mx = fmaxf(mx, red_ml[(w * 16 + row) * 2]);
             const float m_use = mx == -INFINITY ? 0.f : mx;
-            float acc = 0.f, sum = 0.f;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            float sum = 0.f;
 #pragma unroll
             for (int w = 0; w < 4; ++w) {
                 const float c = exp2f(red_ml[(w * 16 + row) * 2] - m_use);
-                acc += c * red_o[(w * 16 + row) * D + d];
+                const float4 part = *reinterpret_cast<const float4*>(red_o + (w * 16 + row) * D + d);
+                acc.x += c * part.x; acc.y += c * part.y; acc.z += c * part.z; acc.w += c * part.w;
                 sum += c * red_ml[(w * 16 + row) * 2 + 1];
             }
             if (whole) {
-                out[(size_t)seq * out_stride + (size_t)(kv_head * group + row) * D + d] =
-                    __float2bfloat16_rn(sum > 0.f ? acc / sum : 0.f);
+                const float inv = sum > 0.f ? 1.0f / sum : 0.f;
+                bf16* dst = out + (size_t)seq * out_stride + (size_t)(kv_head * group + row) * D + d;
+                *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
+                *reinterpret_cast<__nv_bfloat162*>(dst + 2) = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
             } else {
-                part_o[((size_t)slot * 16 + row) * D + d] = acc;
-                if (d == 0) {
-                    part_ml[((size_t)slot * 16 + row) * 2] = mx;
-                    part_ml[((size_t)slot * 16 + row) * 2 + 1] = sum;
-                }
+                *reinterpret_cast<float4*>(part_o + ((size_t)slot * 16 + row) * D + d) = acc;
+                if (d == 0) *reinterpret_cast<float2*>(part_ml + ((size_t)slot * 16 + row) * 2) = make_float2(mx, sum);
             }
         }
         if (!whole) {
@@ -572,30 +574,36 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
                 // every part after the first, whose runs begin inside the group
                 const int first_slot = dec_run_begin(run, c_first) >= group_first_unit ? 0 : 1;
                 const int n_parts = c_last - c_first + 1;       // at most kMaxParts by the choice of run length
-                for (int i = threadIdx.x; i < group * D; i += kThreads) {
-                    const int row = i / D, d = i % D;
-                    float pm[kMaxParts], pl[kMaxParts], po[kMaxParts];
+                // four neighbouring elements of a row per thread; all parts' loads are issued before any is used
+                for (int i = threadIdx.x; i < group * (D / 4); i += kThreads) {
+                    const int row = i / (D / 4), d = (i % (D / 4)) * 4;
+                    float2 pml[kMaxParts];
+                    float4 po[kMaxParts];
 #pragma unroll
                     for (int j = 0; j < kMaxParts; ++j) {
                         const bool live = j < n_parts;
                         const size_t sl = (size_t)(c_first + (live ? j : 0)) * 2 + (j == 0 ? first_slot : 0);
-                        pm[j] = live ? __ldcg(&part_ml[(sl * 16 + row) * 2]) : -INFINITY;
-                        pl[j] = live ? __ldcg(&part_ml[(sl * 16 + row) * 2 + 1]) : 0.f;
-                        po[j] = live ? __ldcg(&part_o[(sl * 16 + row) * D + d]) : 0.f;
+                        pml[j] = live ? __ldcg(reinterpret_cast<const float2*>(part_ml + (sl * 16 + row) * 2))
+                                      : make_float2(-INFINITY, 0.f);
+                        po[j] = live ? __ldcg(reinterpret_cast<const float4*>(part_o + (sl * 16 + row) * D + d))
+                                     : make_float4(0.f, 0.f, 0.f, 0.f);
                     }
                     float mx = -INFINITY;
 #pragma unroll
-                    for (int j = 0; j < kMaxParts; ++j) mx = fmaxf(mx, pm[j]);
+                    for (int j = 0; j < kMaxParts; ++j) mx = fmaxf(mx, pml[j].x);
                     const float m_use = mx == -INFINITY ? 0.f : mx;
-                    float acc = 0.f, sum = 0.f;
+                    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                    float sum = 0.f;
 #pragma unroll
                     for (int j = 0; j < kMaxParts; ++j) {
-                        const float w = exp2f(pm[j] - m_use);
-                        acc += w * po[j];
-                        sum += w * pl[j];
+                        const float w = exp2f(pml[j].x - m_use);
+                        acc.x += w * po[j].x; acc.y += w * po[j].y; acc.z += w * po[j].z; acc.w += w * po[j].w;
+                        sum += w * pml[j].y;
                     }
-                    out[(size_t)seq * out_stride + (size_t)(kv_head * group + row) * D + d] =
-                        __float2bfloat16_rn(sum > 0.f ? acc / sum : 0.f);
+                    const float inv = sum > 0.f ? 1.0f / sum : 0.f;
+                    bf16* dst = out + (size_t)seq * out_stride + (size_t)(kv_head * group + row) * D + d;
+                    *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
+                    *reinterpret_cast<__nv_bfloat162*>(dst + 2) = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
                 }
                 if (threadIdx.x == 0) counters[seq * n_kv + kv_head] = 0;   // ready for the next call
             }
@@ -683,6 +691,7 @@ DFI_EXPORT int dfi_attention_decode(const void* q, int q_stride, void* out, int 
     if (n_seqs > kMaxDecodeSeqs) return DFI_ERR_LIMIT;
     if (scratch == nullptr || counters == nullptr) return DFI_ERR_SHAPE;
     if (q_stride % 8 || !aligned16(q) || !aligned16(k_cache) || !aligned16(v_cache)) return DFI_ERR_ALIGN;
+    if (out_stride % 2 || (reinterpret_cast<uintptr_t>(out) & 3)) return DFI_ERR_ALIGN;      // outputs are stored in pairs
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecodeSmem) != cudaSuccess)
