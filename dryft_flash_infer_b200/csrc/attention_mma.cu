@@ -314,6 +314,80 @@ __device__ __forceinline__ void atrace(int slot) {
 __device__ __forceinline__ void atrace(int) {}
 #endif
 
+// The step's own token, prepared inside the decode kernel instead of by a kernel before it: the
+// per-head RMS norm and the rotation of q and k (engine/kernels/reference.py:31-46) and the write of
+// the new key and value into the cache.  qkv == null: q is ready and the cache holds the token.
+struct DecodePrep {
+    const bf16* qkv;          // [sequences, qkv_stride]: q heads, then k heads, then v heads of the step's tokens
+    int qkv_stride;
+    const float* q_weight;    // [D] or null (no per-head norm)
+    const float* k_weight;
+    float eps;
+    const float* cos_table;   // [positions, D/2] or null (no rotation)
+    const float* sin_table;
+    bf16* k_cache;            // where the new key and value go when write_cache is set
+    bf16* v_cache;
+    int write_cache;
+};
+constexpr bool kPrepHeadDim = (D & (D - 1)) == 0;    // the rotation's partner is a lane away by a power of two
+
+// One head vector of D elements, four per lane.  head_load issues every load that the preparation
+// needs (so that they travel together); head_finish does the norm (if weight), the rotation (if
+// tables) and stores the result as bfloat16 to `dst` (shared or global memory) and, if dst2 is not
+// null, there as well.  src == null: zeros.
+struct HeadInput {
+    uint2 raw;
+    float4 weight, cosine, sine;
+};
+__device__ __forceinline__ HeadInput head_load(const bf16* src, const float* weight, const float* cos_t,
+                                               const float* sin_t, int pos, int lane) {
+    constexpr int kLanes = D / 4;
+    HeadInput in;
+    in.raw = make_uint2(0u, 0u);
+    in.weight = in.cosine = in.sine = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (lane < kLanes) {
+        if (src != nullptr) in.raw = *reinterpret_cast<const uint2*>(src + 4 * lane);
+        if (weight != nullptr) in.weight = *reinterpret_cast<const float4*>(weight + 4 * lane);
+        if (cos_t != nullptr) {
+            const int at = (4 * lane) % (D / 2);
+            in.cosine = *reinterpret_cast<const float4*>(cos_t + (size_t)pos * (D / 2) + at);
+            in.sine = *reinterpret_cast<const float4*>(sin_t + (size_t)pos * (D / 2) + at);
+        }
+    }
+    return in;
+}
+__device__ __forceinline__ void head_finish(const HeadInput& in, bool norm, float eps, bool rotate, bf16* dst, bf16* dst2,
+                                            int lane) {
+    constexpr int kLanes = D / 4;
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&in.raw.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&in.raw.y));
+    float v[4] = {a.x, a.y, b.x, b.y};
+    if (norm) {
+        float ssq = v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, o);
+        const float scale = 1.0f / sqrtf(ssq / (float)D + eps);
+        v[0] *= scale * in.weight.x; v[1] *= scale * in.weight.y; v[2] *= scale * in.weight.z; v[3] *= scale * in.weight.w;
+    }
+    if (rotate) {
+        float partner[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) partner[e] = __shfl_xor_sync(0xffffffffu, v[e], (kLanes / 2) & 31);
+        const bool low = lane < kLanes / 2;
+        const float cs[4] = {in.cosine.x, in.cosine.y, in.cosine.z, in.cosine.w};
+        const float ss[4] = {in.sine.x, in.sine.y, in.sine.z, in.sine.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v[e] = low ? v[e] * cs[e] - partner[e] * ss[e] : v[e] * cs[e] + partner[e] * ss[e];
+    }
+    if (lane < kLanes) {
+        uint2 packed;
+        *reinterpret_cast<__nv_bfloat162*>(&packed.x) = __floats2bfloat162_rn(v[0], v[1]);
+        *reinterpret_cast<__nv_bfloat162*>(&packed.y) = __floats2bfloat162_rn(v[2], v[3]);
+        *reinterpret_cast<uint2*>(dst + 4 * lane) = packed;
+        if (dst2 != nullptr) *reinterpret_cast<uint2*>(dst2 + 4 * lane) = packed;
+    }
+}
+
 constexpr int kKvStages = 3;            // pages of keys and values in the decode kernel's ring
 constexpr int kMaxParts = 16;           // CTAs that may share one (sequence, head) group
 constexpr int kMaxDecodeSeqs = 1024;    // sequences per launch (their page counts sit in shared memory)
@@ -323,7 +397,8 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
                         const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                         const int* __restrict__ block_table, int table_width, const int* __restrict__ seq_start,
                         int n_seqs, int n_q, int n_kv, int ring_tokens, int window, float scale_log2,
-                        float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters) {
+                        float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters,
+                        DecodePrep prep) {
     atrace(0);
     pdl_launch_next();
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -460,12 +535,34 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
 #pragma unroll
             for (int e = 0; e < 4; ++e) o[n][e] = 0.f;
         float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+        HeadInput token_in = {};
 
-        for (int i = threadIdx.x; i < 16 * kChunks; i += kThreads) {
-            const int row = i / kChunks, c = i % kChunks;
-            const bool valid = row < group;
-            const bf16* src = q + (size_t)seq * q_stride + (size_t)(kv_head * group + (valid ? row : 0)) * D + c * 8;
-            cp_async16(q_s + row * kStride + c * 8, src, valid);
+        if (kPrepHeadDim && prep.qkv != nullptr) {
+            // the group's query heads come raw from the projection: a warp prepares rows warp, warp + 4, ...
+            HeadInput rows_in[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int row = warp + 4 * i;
+                rows_in[i] = head_load(row < group ? prep.qkv + (size_t)seq * prep.qkv_stride + (size_t)(kv_head * group + row) * D : nullptr,
+                                       prep.q_weight, prep.cos_table, prep.sin_table, pos, lane);
+            }
+            // the step's own key and value, if this share of the group holds their page
+            if (prep.write_cache && warp < 2 && t_end == pos / kPage) {
+                const bf16* raw = prep.qkv + (size_t)seq * prep.qkv_stride + (size_t)(warp == 0 ? n_q + kv_head : n_q + n_kv + kv_head) * D;
+                token_in = warp == 0 ? head_load(raw, prep.k_weight, prep.cos_table, prep.sin_table, pos, lane)
+                                     : head_load(raw, nullptr, nullptr, nullptr, pos, lane);
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                head_finish(rows_in[i], prep.q_weight != nullptr, prep.eps, prep.cos_table != nullptr,
+                            q_s + (warp + 4 * i) * kStride, nullptr, lane);
+        } else {
+            for (int i = threadIdx.x; i < 16 * kChunks; i += kThreads) {
+                const int row = i / kChunks, c = i % kChunks;
+                const bool valid = row < group;
+                const bf16* src = q + (size_t)seq * q_stride + (size_t)(kv_head * group + (valid ? row : 0)) * D + c * 8;
+                cp_async16(q_s + row * kStride + c * 8, src, valid);
+            }
         }
         // a ring of kKvStages pages of keys and values: kKvStages - 1 of them are on their way while one is used
         auto load_tile = [&](int t) {
@@ -485,6 +582,18 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
             __syncthreads();     // page t has landed for everyone, and everyone is done with the stage refilled next
             if (t + kKvStages - 1 <= t_end) load_tile(t + kKvStages - 1);
             cp_async_commit();
+            if (kPrepHeadDim && prep.qkv != nullptr && prep.write_cache && t == pos / kPage) {
+                // this page holds the step's own token: its key (normalised, rotated) and value go into
+                // the page in shared memory and into the cache
+                if (warp < 2) {
+                    const int row = pos % kPage;
+                    bf16* tile = (warp == 0 ? k_s : v_s) + stage * kPage * kStride + row * kStride;
+                    bf16* cached = const_cast<bf16*>(page_ptr(warp == 0 ? prep.k_cache : prep.v_cache, table, t, ring_tokens, n_kv, kv_head)) + (size_t)row * D;
+                    if (warp == 0) head_finish(token_in, prep.k_weight != nullptr, prep.eps, prep.cos_table != nullptr, tile, cached, lane);
+                    else head_finish(token_in, false, 0.f, false, tile, cached, lane);
+                }
+                __syncthreads();
+            }
             if (t == t_begin) {
                 atrace(3);
                 const int mi = lane >> 3, r = lane & 7;
@@ -680,17 +789,18 @@ DFI_EXPORT int dfi_attention_prefill(const void* q, int q_stride, void* out, int
 // One query row per sequence (row i belongs to sequence i).  `scratch` holds
 // dfi_attention_decode_scratch_floats(n_ctas) floats; `counters` holds n_seqs * n_kv ints, zero
 // before the first call and left zero by every call.  n_ctas <= 0: as many as run at once.
-DFI_EXPORT int dfi_attention_decode(const void* q, int q_stride, void* out, int out_stride, const void* k_cache,
-                                    const void* v_cache, const int* block_table, int table_width,
-                                    const int* seq_start, int n_seqs, int n_q, int n_kv, int page_size,
-                                    int ring_tokens, int window, float scale, int n_ctas, float* scratch,
-                                    int* counters, void* stream) {
+static int attention_decode(const void* q, int q_stride, void* out, int out_stride, const void* k_cache,
+                            const void* v_cache, const int* block_table, int table_width,
+                            const int* seq_start, int n_seqs, int n_q, int n_kv, int page_size,
+                            int ring_tokens, int window, float scale, int n_ctas, float* scratch,
+                            int* counters, const DecodePrep& prep, void* stream) {
     if (n_seqs <= 0) return DFI_OK;
     if (page_size != kPage || n_q <= 0 || n_kv <= 0 || n_q % n_kv || n_q / n_kv > 16 || ring_tokens % kPage)
         return DFI_ERR_SHAPE;
     if (n_seqs > kMaxDecodeSeqs) return DFI_ERR_LIMIT;
     if (scratch == nullptr || counters == nullptr) return DFI_ERR_SHAPE;
-    if (q_stride % 8 || !aligned16(q) || !aligned16(k_cache) || !aligned16(v_cache)) return DFI_ERR_ALIGN;
+    if (prep.qkv == nullptr && (q_stride % 8 || !aligned16(q))) return DFI_ERR_ALIGN;
+    if (!aligned16(k_cache) || !aligned16(v_cache)) return DFI_ERR_ALIGN;
     if (out_stride % 2 || (reinterpret_cast<uintptr_t>(out) & 3)) return DFI_ERR_ALIGN;      // outputs are stored in pairs
     static bool configured = false;
     if (!configured) {
@@ -705,7 +815,50 @@ DFI_EXPORT int dfi_attention_decode(const void* q, int q_stride, void* out, int 
     float* part_ml = scratch + (size_t)n_ctas * 2 * 16 * D;
     launch(attention_decode_kernel, n_ctas, kThreads, kDecodeSmem, (cudaStream_t)stream,
            (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_cache, (const bf16*)v_cache, block_table,
-           table_width, seq_start, n_seqs, n_q, n_kv, ring_tokens, window, scale * kLog2e, part_o, part_ml, counters);
+           table_width, seq_start, n_seqs, n_q, n_kv, ring_tokens, window, scale * kLog2e, part_o, part_ml, counters, prep);
     DFI_CHECK_LAUNCH();
     return DFI_OK;
+}
+
+DFI_EXPORT int dfi_attention_decode(const void* q, int q_stride, void* out, int out_stride, const void* k_cache,
+                                    const void* v_cache, const int* block_table, int table_width,
+                                    const int* seq_start, int n_seqs, int n_q, int n_kv, int page_size,
+                                    int ring_tokens, int window, float scale, int n_ctas, float* scratch,
+                                    int* counters, void* stream) {
+    DecodePrep none = {};
+    return attention_decode(q, q_stride, out, out_stride, k_cache, v_cache, block_table, table_width, seq_start, n_seqs,
+                            n_q, n_kv, page_size, ring_tokens, window, scale, n_ctas, scratch, counters, none, stream);
+}
+
+// 1 if this build (head size) has the variant that prepares the step's token itself.
+DFI_EXPORT int dfi_attention_decode_prepares() { return kPrepHeadDim ? 1 : 0; }
+
+// The same with the step's token prepared inside the kernel: qkv [n_seqs, qkv_stride] holds the raw
+// projection (q heads, k heads, v heads) of each sequence's new token at position seq_start[i].  q and k
+// heads are RMS-normalised with q_weight / k_weight (null: not) and rotated by the tables (null: not);
+// with write_cache the new key and value are stored into the cache, else the cache holds them already.
+DFI_EXPORT int dfi_attention_decode_prepared(const void* qkv, int qkv_stride, const float* q_weight,
+                                             const float* k_weight, float eps, const float* cos_table,
+                                             const float* sin_table, int write_cache, void* out, int out_stride,
+                                             void* k_cache, void* v_cache, const int* block_table, int table_width,
+                                             const int* seq_start, int n_seqs, int n_q, int n_kv, int page_size,
+                                             int ring_tokens, int window, float scale, int n_ctas, float* scratch,
+                                             int* counters, void* stream) {
+    if (!kPrepHeadDim) return DFI_ERR_SHAPE;
+    if (qkv == nullptr || qkv_stride % 4 || (reinterpret_cast<uintptr_t>(qkv) & 7)) return DFI_ERR_ALIGN;
+    if (!aligned16(q_weight) || !aligned16(k_weight) || !aligned16(cos_table) || !aligned16(sin_table)) return DFI_ERR_ALIGN;
+    if ((cos_table == nullptr) != (sin_table == nullptr)) return DFI_ERR_SHAPE;
+    DecodePrep prep;
+    prep.qkv = (const bf16*)qkv;
+    prep.qkv_stride = qkv_stride;
+    prep.q_weight = q_weight;
+    prep.k_weight = k_weight;
+    prep.eps = eps;
+    prep.cos_table = cos_table;
+    prep.sin_table = sin_table;
+    prep.k_cache = (bf16*)k_cache;
+    prep.v_cache = (bf16*)v_cache;
+    prep.write_cache = write_cache;
+    return attention_decode(nullptr, 0, out, out_stride, k_cache, v_cache, block_table, table_width, seq_start, n_seqs,
+                            n_q, n_kv, page_size, ring_tokens, window, scale, n_ctas, scratch, counters, prep, stream);
 }

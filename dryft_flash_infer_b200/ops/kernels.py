@@ -238,13 +238,42 @@ def attention_tc_error(head_dim: int, reset: bool = True) -> int:
     return _attention_library(head_dim).dfi_attention_prefill_tc_error(int(reset))
 
 
+class TokenPrep:
+    """What ``attention_decode`` needs to prepare the step's tokens itself: the raw projection ``qkv
+    [sequences, (n_q + 2 n_kv) * head_dim]``, the per-head norm weights (or None), its eps, and the
+    rotation tables (or None)."""
+
+    __slots__ = ("qkv", "q_weight", "k_weight", "eps", "cos", "sin")
+
+    def __init__(self, qkv, q_weight, k_weight, eps, cos, sin):
+        self.qkv, self.q_weight, self.k_weight, self.eps, self.cos, self.sin = qkv, q_weight, k_weight, eps, cos, sin
+
+
+def decode_prepares_tokens(qkv: torch.Tensor, ctx, n_q: int, n_kv: int, head_dim: int) -> bool:
+    """True if ``attention_decode`` can take this step's raw projection (``prep=``) instead of queries
+    prepared by ``qk_norm_rope_write``: a bfloat16 step of one token per sequence with a head size that
+    is a power of two."""
+    return (qkv.is_cuda and qkv.dtype == torch.bfloat16 and ctx.all_decode and head_dim in (16, 32, 64, 128)
+            and n_q // n_kv <= 16 and ctx.n_seqs <= DECODE_ATTENTION_MAX_SEQS and qkv.stride(1) == 1
+            and qkv.stride(0) % 4 == 0 and bool(_attention_library(head_dim).dfi_attention_decode_prepares()))
+
+
 def attention_decode(q, cache, ctx, n_q: int, n_kv: int, head_dim: int, scale: float, window: int = 0,
-                     n_ctas: int | None = None):
+                     n_ctas: int | None = None, prep: TokenPrep | None = None):
     """Tensor-core attention (bfloat16) for steps with one query row per sequence: the pages of
     all sequences are dealt to ``n_ctas`` CTAs (default: as many as run at once) in equal runs, and
-    the parts of a sequence that end up in different CTAs are merged by the last of them to finish."""
-    _need_cuda(q, cache.k)
-    assert q.dtype == torch.bfloat16 and q.stride(1) == 1 and q.shape == (ctx.n_seqs, n_q * head_dim)
+    the parts of a sequence that end up in different CTAs are merged by the last of them to finish.
+
+    With ``prep`` (and ``q`` None) the kernel also does what ``qk_norm_rope_write`` does for the step's
+    tokens: per-head norm and rotation of q and k, and (if ``cache.writes``) the new key and value
+    into the cache."""
+    if prep is not None:
+        q = prep.qkv
+        _need_cuda(q, cache.k)
+        assert q.dtype == torch.bfloat16 and q.shape == (ctx.n_seqs, (n_q + 2 * n_kv) * head_dim)
+    else:
+        _need_cuda(q, cache.k)
+        assert q.dtype == torch.bfloat16 and q.stride(1) == 1 and q.shape == (ctx.n_seqs, n_q * head_dim)
     lib = _attention_library(head_dim)
     if not n_ctas:
         n_ctas = lib.dfi_attention_decode_wave()
@@ -257,6 +286,14 @@ def attention_decode(q, cache, ctx, n_q: int, n_kv: int, head_dim: int, scale: f
                 torch.zeros(max(n_counters, 8192, held[1].numel() if held else 0), dtype=torch.int32, device=q.device))
         _ATTENTION_SCRATCH[q.device] = held
     out = torch.empty((q.shape[0], n_q * head_dim), dtype=q.dtype, device=q.device)
+    if prep is not None:
+        _check(lib.dfi_attention_decode_prepared(
+            _ptr(q), q.stride(0), _ptr(prep.q_weight), _ptr(prep.k_weight), _f(prep.eps), _ptr(prep.cos), _ptr(prep.sin),
+            int(cache.writes), _ptr(out), out.stride(0), _ptr(cache.k), _ptr(cache.v), _ptr(cache.block_table),
+            cache.block_table.shape[1], _ptr(ctx.seq_start), ctx.n_seqs, n_q, n_kv, cache.page_size, cache.ring_tokens,
+            window, _f(scale), n_ctas, _ptr(held[0]), _ptr(held[1]), _stream()), "attention_decode",
+            f"head_dim {head_dim}, {n_q}/{n_kv} heads, tokens prepared inside")
+        return out
     _check(lib.dfi_attention_decode(
         _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cache.k), _ptr(cache.v), _ptr(cache.block_table),
         cache.block_table.shape[1], _ptr(ctx.seq_start), ctx.n_seqs, n_q, n_kv, cache.page_size, cache.ring_tokens,

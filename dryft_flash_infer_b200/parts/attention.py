@@ -65,6 +65,12 @@ class Attention(Mixer):
         qkv = kernels.linear(x, self.qkv)
         cos = self.position.cos if self.position is not None else None
         sin = self.position.sin if self.position is not None else None
+        if kernels.decode_prepares_tokens(qkv, ctx, self.n_heads, self.n_kv_heads, self.head_dim):
+            # decoding: the attention kernel normalises, rotates and stores the new token itself
+            prep = kernels.TokenPrep(qkv, self.q_norm, self.k_norm, self.qk_norm_eps, cos, sin)
+            attended = kernels.attention_decode(None, cache, ctx, self.n_heads, self.n_kv_heads, self.head_dim,
+                                                self.scale, self.window, prep=prep)
+            return kernels.linear(attended, self.o, add_norm=add_norm)
         q = kernels.qk_norm_rope_write(qkv, self.n_heads, self.n_kv_heads, self.head_dim, self.q_norm, self.k_norm,
                                        self.qk_norm_eps, cos, sin, ctx.row_pos, ctx.row_seq, cache)
         attended = kernels.attention(q, cache, ctx, self.n_heads, self.n_kv_heads, self.head_dim, self.scale,

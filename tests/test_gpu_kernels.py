@@ -279,6 +279,55 @@ def test_attention_tensor_core_decode_dealt_to_any_number_of_ctas(n_q, n_kv, dim
         assert torch.equal(again, got)                 # the counters were left ready; the order of the merge is fixed
 
 
+@pytest.mark.parametrize("n_q, n_kv, dim", [(4, 4, 16), (16, 1, 32), (3, 1, 64), (32, 8, 128)])
+@pytest.mark.parametrize("qk_norm, rotary, window, ring", [(True, True, 0, 0), (False, False, 0, 0), (True, True, 100, 192)])
+def test_attention_decode_that_prepares_the_tokens_itself(n_q, n_kv, dim, qk_norm, rotary, window, ring):
+    """The decode kernel given the raw projection (norm, rotation and cache write inside) against
+    qk_norm_rope_write followed by the same kernel: outputs, and the rows written into the cache."""
+    from dryft_flash_infer_b200.ops import kernels
+    from dryft_flash_infer_b200.parts.rotary import RotaryEmbedding
+
+    dtype = torch.bfloat16
+    # the new token is the last of its page (64, 128), the first of one (65, 257, 1), or in the middle
+    lengths = [257, 64, 1, 1000, 65, 128, 300]
+    new = [1] * len(lengths)
+    _, cache, row_seq, row_pos, scale, _ = attention_case(dtype, n_q, n_kv, dim, lengths, new, window=window,
+                                                          ring_tokens=ring, seed=dim + window)
+    table = cache.block_table.cpu()
+    for s_, l in enumerate(lengths):                    # nothing is known yet about the new token's place
+        place = (l - 1) % ring if ring else l - 1
+        cache.k[int(table[s_, place // 64]), :, place % 64] = float("nan")
+        cache.v[int(table[s_, place // 64]), :, place % 64] = float("nan")
+    g = torch.Generator().manual_seed(dim)
+    qkv = torch.randn(len(lengths), (n_q + 2 * n_kv) * dim, generator=g).to(dtype).cuda()
+    qw = (1 + 0.3 * torch.randn(dim, generator=g)).cuda() if qk_norm else None
+    kw = (1 + 0.3 * torch.randn(dim, generator=g)).cuda() if qk_norm else None
+    eps = 1e-5
+    rot = RotaryEmbedding(0, dim, 4321.0)
+    rot.prepare(1024, "cuda")
+    cos, sin = (rot.cos, rot.sin) if rotary else (None, None)
+    ctx = step_like(lengths, new)
+
+    two = LayerCache(cache.k.clone(), cache.v.clone(), cache.block_table, 64, ring, True)
+    q = kernels.qk_norm_rope_write(qkv.clone(), n_q, n_kv, dim, qw, kw, eps, cos, sin, row_pos, row_seq, two)
+    want = kernels.attention_decode(q, two, ctx, n_q, n_kv, dim, scale, window)
+    assert torch.isfinite(want).all()
+    for ctas in (None, 1, 3, 40):
+        one = LayerCache(cache.k.clone(), cache.v.clone(), cache.block_table, 64, ring, True)
+        prep = kernels.TokenPrep(qkv, qw, kw, eps, cos, sin)
+        assert kernels.decode_prepares_tokens(qkv, ctx, n_q, n_kv, dim)
+        got = kernels.attention_decode(None, one, ctx, n_q, n_kv, dim, scale, window, n_ctas=ctas, prep=prep)
+        assert torch.allclose(got.float(), want.float(), atol=tol(dtype, 2), rtol=tol(dtype)), ctas
+        assert torch.allclose(one.k.float(), two.k.float(), atol=tol(dtype), rtol=tol(dtype), equal_nan=True)
+        assert torch.equal(one.v.float().nan_to_num(7.0), two.v.float().nan_to_num(7.0))
+    # a layer that only reads the cache (another one wrote the token): queries prepared, cache untouched
+    read_only = LayerCache(two.k.clone(), two.v.clone(), cache.block_table, 64, ring, False)
+    got = kernels.attention_decode(None, read_only, ctx, n_q, n_kv, dim, scale, window,
+                                   prep=kernels.TokenPrep(qkv, qw, kw, eps, cos, sin))
+    assert torch.allclose(got.float(), want.float(), atol=tol(dtype, 2), rtol=tol(dtype))
+    assert torch.equal(read_only.k.float().nan_to_num(7.0), two.k.float().nan_to_num(7.0))
+
+
 def test_attention_tensor_core_window_edges():
     from dryft_flash_infer_b200.ops import kernels
 
