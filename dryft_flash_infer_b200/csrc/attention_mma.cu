@@ -17,6 +17,8 @@
 // Places of the cache that no token was written to may hold anything (NaN included):
 // scores of masked keys are replaced, not added to, and value rows past the sequence's
 // end are zero-filled on load, so such places never reach a result.
+#include <stdlib.h>
+
 #include "common.cuh"
 
 #ifndef DFI_HEAD_DIM
@@ -301,6 +303,21 @@ __device__ __forceinline__ int dec_cta_of_unit(const DecodeRun& r, int u) {
     return c;
 }
 
+// Thread-block cluster helpers for the decode kernel's merge.
+constexpr int kDecodeCluster = 4;       // CTAs per cluster when the launch uses clusters
+__device__ __forceinline__ uint32_t dec_cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t dec_cluster_map(const void* own, uint32_t rank) {
+    uint32_t out;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(out) : "r"((uint32_t)__cvta_generic_to_shared(own)), "r"(rank));
+    return out;
+}
+__device__ __forceinline__ void dec_cluster_arrive() { asm volatile("barrier.cluster.arrive.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void dec_cluster_wait() { asm volatile("barrier.cluster.wait.aligned;\n" ::: "memory"); }
+
 #ifdef DFI_TRACE
 __device__ unsigned long long g_attn_trace[4096 * 8];
 __device__ __forceinline__ void atrace(int slot) {
@@ -398,7 +415,7 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
                         const int* __restrict__ block_table, int table_width, const int* __restrict__ seq_start,
                         int n_seqs, int n_q, int n_kv, int ring_tokens, int window, float scale_log2,
                         float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters,
-                        DecodePrep prep) {
+                        DecodePrep prep, int cluster_size) {
     atrace(0);
     pdl_launch_next();
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -470,6 +487,13 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
             run.n_ctas = n_seqs * n_kv * parts;
         }
     }
+    // When the launch groups CTAs into clusters and every group of this step is cut into exactly that
+    // many parts, the CTAs of a cluster hold the parts of one group and merge them through distributed
+    // shared memory: each owns a share of the head's columns and receives the others' sums for them in
+    // the space of its query tile (free once the queries are in registers; a first cluster barrier
+    // says so), and a second barrier tells it that all parts have arrived.  All CTAs of a cluster
+    // take the same decision, since they compute it from the same numbers.
+    const bool clustered = cluster_size > 1 && run.parts == cluster_size && group <= 8 && (D / cluster_size) % 4 == 0;
     const int cta = blockIdx.x;
     const bool idle = cta >= run.n_ctas;
     const int u_begin = idle ? 0 : dec_run_begin(run, cta), u_end = idle ? 0 : dec_run_begin(run, cta + 1);
@@ -536,6 +560,7 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
             for (int e = 0; e < 4; ++e) o[n][e] = 0.f;
         float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
         HeadInput token_in = {};
+        bool freed = false;          // in a cluster: this CTA has told the others that its query tile's space is free
 
         if (kPrepHeadDim && prep.qkv != nullptr) {
             // the group's query heads come raw from the projection: a warp prepares rows warp, warp + 4, ...
@@ -580,6 +605,10 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
             const int stage = (t - t_begin) % kKvStages;
             cp_async_wait<kKvStages - 2>();
             __syncthreads();     // page t has landed for everyone, and everyone is done with the stage refilled next
+            if (clustered && t == t_begin + 1) {
+                dec_cluster_arrive();      // every warp has its queries in registers: the query tile's space is free
+                freed = true;
+            }
             if (t + kKvStages - 1 <= t_end) load_tile(t + kKvStages - 1);
             cp_async_commit();
             if (kPrepHeadDim && prep.qkv != nullptr && prep.write_cache && t == pos / kPage) {
@@ -621,6 +650,7 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
         atrace(4);
         cp_async_wait<0>();
         __syncthreads();         // everyone is done with the pages: their memory is reused below
+        if (clustered && !freed) dec_cluster_arrive();
 
         // merge the four warps' results: the tile buffers are free now
         float* red_o = reinterpret_cast<float*>(k_s);        // [4][16][D]
@@ -639,6 +669,7 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
             }
         }
         __syncthreads();
+        if (clustered) dec_cluster_wait();       // every CTA of the cluster has freed its query tile's space
         const int slot = cta * 2 + (first_segment ? 0 : 1);
         // a thread takes four neighbouring output elements of a row at a time
         for (int i = threadIdx.x; i < group * (D / 4); i += kThreads) {
@@ -656,7 +687,20 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
                 acc.x += c * part.x; acc.y += c * part.y; acc.z += c * part.z; acc.w += c * part.w;
                 sum += c * red_ml[(w * 16 + row) * 2 + 1];
             }
-            if (whole) {
+            if (clustered) {
+                // to the owner of these columns: [sender][row][column in the owner's share], then [sender][row][m, l]
+                constexpr int kRows = 8;
+                const int share = D / cluster_size;
+                const uint32_t owner = (uint32_t)(d / share);
+                const uint32_t base = dec_cluster_map(q_s, owner);
+                const int me = (int)dec_cluster_rank();
+                const uint32_t o_at = base + (uint32_t)(((me * kRows + row) * share + d % share) * 4);
+                asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};\n" ::"r"(o_at), "f"(acc.x), "f"(acc.y), "f"(acc.z), "f"(acc.w) : "memory");
+                if (d % share == 0) {
+                    const uint32_t ml_at = base + (uint32_t)((cluster_size * kRows * share + (me * kRows + row) * 2) * 4);
+                    asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};\n" ::"r"(ml_at), "f"(mx), "f"(sum) : "memory");
+                }
+            } else if (whole) {
                 const float inv = sum > 0.f ? 1.0f / sum : 0.f;
                 bf16* dst = out + (size_t)seq * out_stride + (size_t)(kv_head * group + row) * D + d;
                 *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
@@ -666,7 +710,34 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
                 if (d == 0) *reinterpret_cast<float2*>(part_ml + ((size_t)slot * 16 + row) * 2) = make_float2(mx, sum);
             }
         }
-        if (!whole) {
+        if (clustered) {
+            // all parts have arrived; this CTA finishes its share of the columns
+            dec_cluster_arrive();
+            dec_cluster_wait();
+            constexpr int kRows = 8;
+            const int share = D / cluster_size;
+            const float* recv_o = reinterpret_cast<const float*>(q_s);
+            const float* recv_ml = recv_o + cluster_size * kRows * share;
+            const int me = (int)dec_cluster_rank();
+            for (int i = threadIdx.x; i < group * (share / 4); i += kThreads) {
+                const int row = i / (share / 4), dl = (i % (share / 4)) * 4;
+                float mx = -INFINITY;
+                for (int j = 0; j < cluster_size; ++j) mx = fmaxf(mx, recv_ml[(j * kRows + row) * 2]);
+                const float m_use = mx == -INFINITY ? 0.f : mx;
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                float sum = 0.f;
+                for (int j = 0; j < cluster_size; ++j) {          // in the order of the parts' pages
+                    const float w = exp2f(recv_ml[(j * kRows + row) * 2] - m_use);
+                    const float4 part = *reinterpret_cast<const float4*>(recv_o + (j * kRows + row) * share + dl);
+                    acc.x += w * part.x; acc.y += w * part.y; acc.z += w * part.z; acc.w += w * part.w;
+                    sum += w * recv_ml[(j * kRows + row) * 2 + 1];
+                }
+                const float inv = sum > 0.f ? 1.0f / sum : 0.f;
+                bf16* dst = out + (size_t)seq * out_stride + (size_t)(kv_head * group + row) * D + me * share + dl;
+                *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
+                *reinterpret_cast<__nv_bfloat162*>(dst + 2) = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
+            }
+        } else if (!whole) {
             __syncthreads();
             const int c_first = dec_cta_of_unit(run, group_first_unit);
             const int c_last = dec_cta_of_unit(run, group_first_unit + seq_tiles - 1);
@@ -753,14 +824,46 @@ DFI_EXPORT int dfi_attention_head_dim() { return D; }
 DFI_EXPORT long long dfi_attention_decode_scratch_floats(int n_ctas) { return (long long)n_ctas * 2 * 16 * (D + 2); }
 
 // CTAs of the decode kernel that one SM holds at a time, times the SMs: what one wave can run.
+static int decode_clusters_enabled() {
+    static int enabled = -1;
+    if (enabled < 0) {
+        const char* text = getenv("DRYFT_ATTENTION_CLUSTER");      // "off": parts always meet through scratch memory
+        enabled = (text != nullptr && (text[0] == 'o' || text[0] == 'O') && (text[1] == 'f' || text[1] == 'F')) ? 0 : 1;
+    }
+    return enabled;
+}
+
 DFI_EXPORT int dfi_attention_decode_wave() {
+    static int wave = -1;
+    if (wave >= 0) return wave;
     int device = 0, sms = 0, per_sm = 0;
     if (cudaGetDevice(&device) != cudaSuccess) return 0;
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return 0;
     cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecodeSmem);
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_decode_kernel, kThreads, kDecodeSmem) != cudaSuccess)
         return 0;
-    return sms * per_sm;
+    int ctas = sms * per_sm;
+    if (decode_clusters_enabled()) {
+        // launched as clusters, only whole clusters that fit their part of the device run at once
+        cudaLaunchConfig_t config = {};
+        config.gridDim = dim3((ctas / kDecodeCluster) * kDecodeCluster);
+        config.blockDim = dim3(kThreads);
+        config.dynamicSmemBytes = kDecodeSmem;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = kDecodeCluster;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        config.attrs = attr;
+        config.numAttrs = 1;
+        int clusters = 0;
+        if (cudaOccupancyMaxActiveClusters(&clusters, attention_decode_kernel, &config) == cudaSuccess && clusters > 0)
+            ctas = min(ctas / kDecodeCluster, clusters) * kDecodeCluster;
+        else
+            cudaGetLastError();
+    }
+    wave = ctas;
+    return wave;
 }
 
 DFI_EXPORT int dfi_attention_prefill(const void* q, int q_stride, void* out, int out_stride, const void* k_cache,
@@ -813,9 +916,36 @@ static int attention_decode(const void* q, int q_stride, void* out, int out_stri
     if (n_ctas > 4096) n_ctas = 4096;
     float* part_o = scratch;
     float* part_ml = scratch + (size_t)n_ctas * 2 * 16 * D;
-    launch(attention_decode_kernel, n_ctas, kThreads, kDecodeSmem, (cudaStream_t)stream,
-           (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_cache, (const bf16*)v_cache, block_table,
-           table_width, seq_start, n_seqs, n_q, n_kv, ring_tokens, window, scale * kLog2e, part_o, part_ml, counters, prep);
+    // clusters only where the kernel can use them: every group cut into kDecodeCluster parts needs that many CTAs
+    const int cluster = (decode_clusters_enabled() && n_ctas % kDecodeCluster == 0 &&
+                         (long long)n_seqs * n_kv * kDecodeCluster <= n_ctas) ? kDecodeCluster : 1;
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(n_ctas);
+    config.blockDim = dim3(kThreads);
+    config.dynamicSmemBytes = kDecodeSmem;
+    config.stream = (cudaStream_t)stream;
+    cudaLaunchAttribute attr[2];
+    int n_attr = 0;
+    if (cluster > 1) {
+        attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+        attr[n_attr].val.clusterDim.x = cluster;
+        attr[n_attr].val.clusterDim.y = 1;
+        attr[n_attr].val.clusterDim.z = 1;
+        ++n_attr;
+    }
+    if (pdl_enabled()) {
+        attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+        ++n_attr;
+    }
+    config.attrs = attr;
+    config.numAttrs = n_attr;
+    if (cudaLaunchKernelEx(&config, attention_decode_kernel, (const bf16*)q, q_stride, (bf16*)out, out_stride,
+                           (const bf16*)k_cache, (const bf16*)v_cache, block_table, table_width, seq_start, n_seqs, n_q,
+                           n_kv, ring_tokens, window, scale * kLog2e, part_o, part_ml, counters, prep, cluster) != cudaSuccess) {
+        cudaGetLastError();
+        return DFI_ERR_LAUNCH;
+    }
     DFI_CHECK_LAUNCH();
     return DFI_OK;
 }

@@ -328,6 +328,25 @@ def test_attention_decode_that_prepares_the_tokens_itself(n_q, n_kv, dim, qk_nor
     assert torch.equal(read_only.k.float().nan_to_num(7.0), two.k.float().nan_to_num(7.0))
 
 
+@pytest.mark.parametrize("n_q, n_kv, dim", [(4, 4, 16), (8, 2, 128), (16, 2, 64), (32, 2, 32)])
+def test_attention_decode_with_equal_lengths_merges_in_clusters(n_q, n_kv, dim):
+    """Sequences of one length: every group is cut into the same number of parts; with 16 CTAs that is
+    four parts, which meet in a cluster (groups of up to 8 query heads) or through scratch memory (16)."""
+    from dryft_flash_infer_b200.ops import kernels
+
+    dtype = torch.bfloat16
+    n_seqs = 4 // n_kv if n_kv <= 4 else 1
+    lengths, new = [1270] * n_seqs, [1] * n_seqs                # 20 pages each
+    q, cache, row_seq, row_pos, scale, want = attention_case(dtype, n_q, n_kv, dim, lengths, new, seed=dim, sharp=700)
+    ctx = step_like(lengths, new)
+    for ctas in (16, 12, None):
+        got = kernels.attention_decode(q, cache, ctx, n_q, n_kv, dim, scale, n_ctas=ctas)
+        assert torch.isfinite(got).all()
+        assert torch.allclose(got.float().cpu(), want, atol=tol(dtype, 2), rtol=tol(dtype)), ctas
+        again = kernels.attention_decode(q, cache, ctx, n_q, n_kv, dim, scale, n_ctas=ctas)
+        assert torch.equal(again, got)
+
+
 def test_attention_tensor_core_window_edges():
     from dryft_flash_infer_b200.ops import kernels
 
