@@ -35,6 +35,8 @@ CORE_SOURCES = ["elementwise.cu", "attention_generic.cu", "sampling.cu", "skinny
 ATTENTION_SOURCES = ["attention_mma.cu", "attention_tcgen05.cu"]
 #: head sizes compiled ahead by ``all_libraries`` (others compile at first use)
 PREBUILT_HEAD_DIMS = (16, 32, 64, 128)
+#: host-only code (no CUDA calls, not linked against the driver): the safetensors reader
+IO_SOURCES = ["safetensors_reader.cpp"]
 
 
 class BuildError(RuntimeError):
@@ -74,9 +76,13 @@ def _headers() -> list[Path]:
     return sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h"))
 
 
+def _host_only(sources: list[str]) -> bool:
+    return all(s.endswith(".cpp") for s in sources)
+
+
 def _digest(sources: list[str], defines: list[str]) -> str:
     h = hashlib.sha256()
-    for path in [CSRC / s for s in sources] + _headers():
+    for path in [CSRC / s for s in sources] + ([] if _host_only(sources) else _headers()):
         if not path.is_file():
             raise BuildError(f"kernel source missing: {path}")
         h.update(path.name.encode())
@@ -98,7 +104,8 @@ def compile_library(name: str, sources: list[str], defines: list[str] | None = N
     nvcc = find_nvcc()
     work = Path(tempfile.mkdtemp(prefix=f"{name}_", dir=target.parent))
     started = time.time()
-    _say(f"compiling {len(sources)} CUDA source files for sm_100a ({name}); this happens once")
+    what = "C++ source files" if _host_only(sources) else "CUDA source files for sm_100a"
+    _say(f"compiling {len(sources)} {what} ({name}); this happens once")
     done = threading.Event()
 
     def ticker():
@@ -120,7 +127,9 @@ def compile_library(name: str, sources: list[str], defines: list[str] | None = N
         with ThreadPoolExecutor(max_workers=min(len(sources), os.cpu_count() or 1)) as pool:
             objects = list(pool.map(one, sources))
         partial = work / "out.so"
-        cmd = [nvcc, *ARCH_FLAGS, "-shared", "-o", str(partial), *map(str, objects), "-lcuda"]
+        cmd = [nvcc, *ARCH_FLAGS, "-shared", "-o", str(partial), *map(str, objects)]
+        if not _host_only(sources):
+            cmd.append("-lcuda")
         proc = subprocess.run(cmd, capture_output=True, text=True)
         if proc.returncode != 0:
             raise BuildError(f"linking {name} failed:\n{proc.stdout}\n{proc.stderr}")
@@ -134,7 +143,7 @@ def compile_library(name: str, sources: list[str], defines: list[str] | None = N
 
 def all_libraries() -> list[tuple[str, list[str], list[str]]]:
     """Every library the package can load: ``(name, sources, defines)``."""
-    out = [("dfi_core", CORE_SOURCES, [])]
+    out = [("dfi_io", IO_SOURCES, []), ("dfi_core", CORE_SOURCES, [])]
     for dim in PREBUILT_HEAD_DIMS:
         out.append((f"dfi_attention_d{dim}", ATTENTION_SOURCES, [f"-DDFI_HEAD_DIM={dim}"]))
     return out

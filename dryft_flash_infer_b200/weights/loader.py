@@ -54,6 +54,32 @@ def check_tensors(folder, files: ModelFiles, expected, ignorable=()) -> None:
         raise WeightError(folder, missing, unexpected, wrong_shape, wrong_dtype)
 
 
+_STAGED_FROM = 4 << 20       # tensors of this many bytes or more go through pinned staging memory
+_STAGE_BYTES = 64 << 20
+
+
+class _Staging:
+    """Two pinned buffers used in turn; a buffer is reused only after its copy to the device is done."""
+
+    def __init__(self, device):
+        self.device = device
+        self.buffers = [torch.empty(_STAGE_BYTES, dtype=torch.uint8).pin_memory() for _ in range(2)]
+        self.events = [None, None]
+        self.turn = 0
+
+    def next(self, dtype: torch.dtype, count: int) -> torch.Tensor:
+        event = self.events[self.turn]
+        if event is not None:
+            event.synchronize()
+        return self.buffers[self.turn].view(dtype)[:count]
+
+    def sent(self) -> None:
+        event = torch.cuda.Event()
+        event.record(torch.cuda.current_stream(self.device))
+        self.events[self.turn] = event
+        self.turn ^= 1
+
+
 def load_weights(model, folder: str | Path) -> None:
     """Copies every expected tensor from ``folder`` into ``model``'s allocated buffers."""
     files = ModelFiles(folder)
@@ -61,8 +87,26 @@ def load_weights(model, folder: str | Path) -> None:
     # a tied model's file may still carry a copy of the head: it is the embedding, so it is skipped
     ignorable = ("lm_head.weight",) if model.spec.head_name is None else ()
     check_tensors(folder, files, expected, ignorable)
+    staging = None
     for e in expected:
-        model.destination(e).copy_(files.tensor(e.name))
+        dest = model.destination(e)
+        dtype, shape = files.info(e.name)
+        n = dest.numel()
+        if dest.is_cuda and dest.is_contiguous() and n * torch.empty((), dtype=dtype).element_size() >= _STAGED_FROM:
+            # large tensors: the native reader fills pinned memory with several threads, piece by piece,
+            # while the piece before is on its way to the device
+            staging = staging or _Staging(dest.device)
+            flat = dest.view(-1)
+            per = _STAGE_BYTES // torch.empty((), dtype=dtype).element_size()
+            for at in range(0, n, per):
+                host = staging.next(dtype, min(per, n - at))
+                files.read_into(e.name, host, at)
+                flat[at: at + host.numel()].copy_(host, non_blocking=True)
+                staging.sent()
+        else:
+            dest.copy_(files.tensor(e.name))
+    if staging is not None:
+        torch.cuda.synchronize(staging.device)
     model.bind()
 
 

@@ -4,13 +4,14 @@ Format: 8 bytes little-endian header length N, N bytes of JSON mapping each name
 ``{"dtype", "shape", "data_offsets": [begin, end]}`` (offsets relative to the end of the
 header; ``__metadata__`` is free text), then the raw little-endian data.  A model folder
 holds ``model.safetensors`` or shards listed in ``model.safetensors.index.json``.
-Tensors are read through a memory map, so only what is copied to the device is touched.
+The file is opened, checked and mapped by a native reader (``csrc/safetensors_reader.cpp``);
+tensors are views of the map, so only what is copied to the device is touched.
 """
 
 from __future__ import annotations
 
+import ctypes
 import json
-import mmap
 import struct
 import warnings
 from pathlib import Path
@@ -38,39 +39,69 @@ def _numel(shape) -> int:
     return n
 
 
+def _reader():
+    """The native reader (``csrc/safetensors_reader.cpp``), compiled at first use."""
+    from ..ops import build
+
+    lib = build.load_library("dfi_io", build.IO_SOURCES)
+    if not getattr(lib, "_dfi_typed", False):
+        lib.dfi_st_open.argtypes = [ctypes.c_char_p, ctypes.POINTER(ctypes.c_void_p), ctypes.c_char_p, ctypes.c_int]
+        lib.dfi_st_close.argtypes = [ctypes.c_void_p]
+        lib.dfi_st_close.restype = None
+        lib.dfi_st_count.argtypes = [ctypes.c_void_p]
+        lib.dfi_st_entry.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.POINTER(ctypes.c_char_p),
+                                     ctypes.POINTER(ctypes.c_char_p), ctypes.POINTER(ctypes.c_int),
+                                     ctypes.POINTER(ctypes.c_longlong), ctypes.c_int,
+                                     ctypes.POINTER(ctypes.c_longlong), ctypes.POINTER(ctypes.c_longlong)]
+        lib.dfi_st_metadata.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_longlong)]
+        lib.dfi_st_metadata.restype = ctypes.c_void_p
+        lib.dfi_st_data.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_longlong)]
+        lib.dfi_st_data.restype = ctypes.c_void_p
+        lib.dfi_st_read.argtypes = [ctypes.c_void_p, ctypes.c_longlong, ctypes.c_longlong, ctypes.c_void_p, ctypes.c_int]
+        lib._dfi_typed = True
+    return lib
+
+
 class SafetensorsFile:
-    """One ``.safetensors`` file: its header, and tensors as CPU views of the memory map."""
+    """One ``.safetensors`` file, opened, checked and mapped by the native reader: its header, and
+    tensors as CPU views of the memory map (``tensor``) or as copies made by several threads
+    (``read_into``)."""
+
+    MAX_DIMS = 16
+    COPY_THREADS = 8
 
     def __init__(self, path: str | Path):
         self.path = Path(path)
-        size = self.path.stat().st_size
-        with open(self.path, "rb") as fh:
-            head = fh.read(8)
-            if len(head) < 8:
-                raise SafetensorsError(f"{self.path}: truncated (no header length)")
-            (n,) = struct.unpack("<Q", head)
-            if n > size - 8:
-                raise SafetensorsError(f"{self.path}: truncated (header of {n} bytes, file of {size})")
-            try:
-                header = json.loads(fh.read(n))
-            except (json.JSONDecodeError, UnicodeDecodeError) as exc:
-                raise SafetensorsError(f"{self.path}: header is not valid JSON ({exc})") from exc
-        self.data_start = 8 + n
-        self.metadata = header.pop("__metadata__", {})
+        self._lib = _reader()
+        handle = ctypes.c_void_p()
+        err = ctypes.create_string_buffer(1024)
+        if self._lib.dfi_st_open(str(self.path).encode(), ctypes.byref(handle), err, len(err)) != 0:
+            raise SafetensorsError(err.value.decode(errors="replace"))
+        self._handle = handle
+        length = ctypes.c_longlong()
+        text = self._lib.dfi_st_metadata(self._handle, ctypes.byref(length))
+        self.metadata = json.loads(ctypes.string_at(text, length.value)) if text else {}
+        size = ctypes.c_longlong()
+        self._data = self._lib.dfi_st_data(self._handle, ctypes.byref(size))
+        self._data_size = size.value
         self.entries: dict[str, tuple[torch.dtype, tuple[int, ...], int, int]] = {}
-        for name, info in header.items():
-            if info["dtype"] not in _DTYPES:
-                raise SafetensorsError(f"{self.path}: tensor '{name}' has unsupported dtype {info['dtype']}")
-            dtype = _DTYPES[info["dtype"]]
-            shape = tuple(int(s) for s in info["shape"])
-            begin, end = info["data_offsets"]
-            want = _numel(shape) * torch.empty((), dtype=dtype).element_size()
-            if end - begin != want:
-                raise SafetensorsError(f"{self.path}: tensor '{name}' spans {end - begin} bytes, shape needs {want}")
-            if self.data_start + end > size:
-                raise SafetensorsError(f"{self.path}: truncated (tensor '{name}' ends past the file)")
-            self.entries[name] = (dtype, shape, begin, end)
-        self._map = None
+        name, dtype = ctypes.c_char_p(), ctypes.c_char_p()
+        n_dims, begin, end = ctypes.c_int(), ctypes.c_longlong(), ctypes.c_longlong()
+        shape = (ctypes.c_longlong * self.MAX_DIMS)()
+        for i in range(self._lib.dfi_st_count(self._handle)):
+            if self._lib.dfi_st_entry(self._handle, i, ctypes.byref(name), ctypes.byref(dtype), ctypes.byref(n_dims),
+                                      shape, self.MAX_DIMS, ctypes.byref(begin), ctypes.byref(end)) != 0:
+                raise SafetensorsError(f"{self.path}: a tensor has more than {self.MAX_DIMS} dimensions")
+            label = dtype.value.decode()
+            if label not in _DTYPES:
+                raise SafetensorsError(f"{self.path}: tensor '{name.value.decode()}' has unsupported dtype {label}")
+            self.entries[name.value.decode()] = (_DTYPES[label], tuple(shape[d] for d in range(n_dims.value)),
+                                                 begin.value, end.value)
+
+    def __del__(self):
+        handle, self._handle = getattr(self, "_handle", None), None
+        if handle:
+            self._lib.dfi_st_close(handle)
 
     def names(self) -> list[str]:
         return list(self.entries)
@@ -80,16 +111,28 @@ class SafetensorsFile:
         return dtype, shape
 
     def tensor(self, name: str) -> torch.Tensor:
+        """A CPU view of the tensor in the read-only map (valid while this object lives)."""
         dtype, shape, begin, end = self.entries[name]
         if begin == end:
             return torch.empty(shape, dtype=dtype)
-        if self._map is None:
-            with open(self.path, "rb") as fh:
-                self._map = mmap.mmap(fh.fileno(), 0, access=mmap.ACCESS_READ)
+        window = (ctypes.c_char * (end - begin)).from_address(self._data + begin)
         with warnings.catch_warnings():
             warnings.simplefilter("ignore")  # the map is read-only; the view is only ever copied from
-            flat = torch.frombuffer(self._map, dtype=dtype, count=_numel(shape), offset=self.data_start + begin)
+            flat = torch.frombuffer(window, dtype=dtype, count=_numel(shape))
+        flat._dfi_keep = self            # the map must outlive the view
         return flat.view(shape)
+
+    def read_into(self, name: str, out: torch.Tensor, first_element: int = 0) -> torch.Tensor:
+        """Copies ``out.numel()`` elements of the tensor, from ``first_element`` on, into ``out`` (CPU,
+        contiguous, the tensor's dtype) with several threads."""
+        dtype, shape, begin, end = self.entries[name]
+        assert out.device.type == "cpu" and out.is_contiguous() and out.dtype == dtype
+        width = out.element_size()
+        assert 0 <= first_element and first_element + out.numel() <= _numel(shape)
+        if self._lib.dfi_st_read(self._handle, begin + first_element * width, out.numel() * width, out.data_ptr(),
+                                 self.COPY_THREADS) != 0:
+            raise SafetensorsError(f"{self.path}: tensor '{name}' could not be read")
+        return out
 
 
 class ModelFiles:
@@ -127,6 +170,9 @@ class ModelFiles:
 
     def tensor(self, name: str) -> torch.Tensor:
         return self.where[name].tensor(name)
+
+    def read_into(self, name: str, out: torch.Tensor, first_element: int = 0) -> torch.Tensor:
+        return self.where[name].read_into(name, out, first_element)
 
 
 def write_safetensors(path: str | Path, tensors: Iterable[tuple[str, torch.Tensor]], plan=None,

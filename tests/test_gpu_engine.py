@@ -349,3 +349,25 @@ def test_a_third_shape_and_a_batch_wider_than_the_skinny_kernels(tmp_path, dtype
     if dtype == "float32":
         for i in (0, 33, 69):
             assert [r[i] for r in rows] == plain_model.greedy_continue(cfg, ref_w, prompts[i], 3)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_large_tensors_load_through_pinned_pieces(tmp_path, dtype, monkeypatch):
+    """Tensors of 4 MB or more are read by the native reader's threads into pinned memory piece by
+    piece; with small pieces a tensor takes several, and every element still lands in its place."""
+    from dryft_flash_infer_b200 import Engine
+    from dryft_flash_infer_b200.config import config_from_dict
+    from dryft_flash_infer_b200.weights import ModelFiles, loader, write_random_model
+
+    raw = dict(plain_model.TINY_A, vocab_size=40000, intermediate_size=16384)      # embedding 5 MB, gate/up/down 2 MB each
+    folder = write_random_model(config_from_dict(raw), 3, tmp_path / "wide", torch.bfloat16)
+    monkeypatch.setattr(loader, "_STAGE_BYTES", 1 << 20)
+    monkeypatch.setattr(loader, "_STAGED_FROM", 1 << 20)
+    engine = Engine(str(folder), dtype=dtype, max_tokens=256)
+    files = ModelFiles(folder)
+    want = files.tensor("model.embed_tokens.weight").to(engine.model.embedding.dtype)
+    assert torch.equal(engine.model.embedding.cpu(), want)
+    ffn = engine.model.blocks[1].feed_forward
+    gate_up = torch.cat([files.tensor("model.layers.1.mlp.gate_proj.weight"), files.tensor("model.layers.1.mlp.up_proj.weight")])
+    assert torch.equal(ffn.gate_up.cpu(), gate_up.to(ffn.gate_up.dtype))
+    assert torch.equal(ffn.down.cpu(), files.tensor("model.layers.1.mlp.down_proj.weight").to(ffn.down.dtype))

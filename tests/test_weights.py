@@ -148,3 +148,31 @@ def test_random_weights_mode_writes_a_model_folder(tmp_path):
     assert abs(float(big.std()) - 0.02) < 1e-3 and abs(float(big.mean())) < 1e-3
     norm = random_tensor("n", (4000,), "norm", 1)
     assert abs(float(norm.mean()) - 1.0) < 1e-3 and abs(float(norm.std()) - 0.01) < 1e-3
+
+
+def _raw_file(path, header: bytes, data: bytes = b""):
+    path.write_bytes(struct.pack("<Q", len(header)) + header + data)
+    return path
+
+
+def test_native_reader_parses_and_checks_the_header(tmp_path):
+    # names with escapes, an unknown key, metadata, and a tensor read piece by piece
+    values = torch.arange(12, dtype=torch.float32)
+    header = (b'{"__metadata__": {"note": "a \\"quoted\\" word", "n": "1"}, '
+              b'"w\\u00e9ight \\"x\\"\\n": {"dtype": "F32", "extra": [1, {"a": null}], "shape": [3, 4], "data_offsets": [0, 48]}}')
+    f = SafetensorsFile(_raw_file(tmp_path / "ok.safetensors", header, values.numpy().tobytes()))
+    name = 'wéight "x"\n'
+    assert f.names() == [name] and f.metadata == {"note": 'a "quoted" word', "n": "1"}
+    assert torch.equal(f.tensor(name), values.view(3, 4))
+    piece = torch.empty(5)
+    assert torch.equal(f.read_into(name, piece, first_element=6), values[6:11])
+    for bad, message in (
+        (b'{"a": {"dtype": "F32", "shape": [2], "data_offsets": [0, 4]}}', "spans 4 bytes, shape needs 8"),
+        (b'{"a": {"dtype": "F33", "shape": [1], "data_offsets": [0, 4]}}', "unsupported dtype F33"),
+        (b'{"a": {"dtype": "F32", "shape": [1], "data_offsets": [0, 4]}', "not valid JSON"),
+        (b'{"a": {"dtype": "F32", "shape": [1]}}', "lacks dtype, shape or data_offsets"),
+        (b'{"a": {"dtype": "F32", "shape": [-1], "data_offsets": [0, 4]}}', "not a size"),
+        (b'{"a": {"dtype": "F32", "shape": [1], "data_offsets": [4, 8]}}', "truncated"),
+    ):
+        with pytest.raises(SafetensorsError, match=message):
+            SafetensorsFile(_raw_file(tmp_path / "bad.safetensors", bad, b"\0" * 4))
