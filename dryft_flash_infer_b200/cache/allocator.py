@@ -9,6 +9,8 @@ out again to later sequences.
 
 from __future__ import annotations
 
+import heapq
+
 
 class CacheError(RuntimeError):
     """The cache cannot do what was asked: out of slots or pages, or a misuse such as
@@ -21,7 +23,7 @@ class FreeList:
     def __init__(self, count: int, first: int = 0, what: str = "id"):
         self.what = what
         self._all = range(first, first + count)
-        self._free = list(reversed(self._all))
+        self._free = list(self._all)          # a heap: the lowest free id is taken next
         self._held: set[int] = set()
 
     @property
@@ -35,7 +37,7 @@ class FreeList:
     def take(self) -> int:
         if not self._free:
             raise CacheError(f"out of {self.what}s: all {len(self._all)} are held")
-        item = self._free.pop()
+        item = heapq.heappop(self._free)
         self._held.add(item)
         return item
 
@@ -44,9 +46,8 @@ class FreeList:
             state = "is already free" if item in self._all else "was never handed out"
             raise CacheError(f"{self.what} {item} {state}")
         self._held.remove(item)
-        self._free.append(item)
         # lowest id first keeps reuse predictable (and exercised: a freed id is the next one taken)
-        self._free.sort(reverse=True)
+        heapq.heappush(self._free, item)
 
     def check(self) -> None:
         """No id lost and none held twice."""
