@@ -574,7 +574,8 @@ static bool plan_decode(StreamShape& s, int M, int N, int K, int swiglu, int n_c
     s.parts = 0;
     s.n_ctas = s.units < n_ctas ? s.units : n_ctas;
     if (s.row_blocks * 2 <= n_ctas) {
-        // few row blocks: the same number of parts for each, as many as fill the CTAs
+        // few row blocks: the same number of parts for each, as many as fill the CTAs (more CTAs than
+        // SMs were measured: faster alone, slower in the step, where the neighbouring kernels need the room)
         int parts = n_ctas / s.row_blocks;
         if (parts > s.k_chunks) parts = s.k_chunks;
         s.parts = parts;
@@ -611,9 +612,10 @@ DFI_EXPORT int dfi_gemm_decode_error(int reset) {
     return value;
 }
 
-// Scratch: two parts of 128 x (padded batch) floats for each CTA; one counter per row block (zero
+// Scratch: two parts of 128 x (padded batch) floats for each CTA, and the launch may use up to twice the
+// CTAs it was asked for; one counter per row block (zero
 // before the first call, left zero by every call).
-DFI_EXPORT long long dfi_gemm_decode_partial_floats(int n_ctas) { return (long long)n_ctas * 2 * kTileM * 64; }
+DFI_EXPORT long long dfi_gemm_decode_partial_floats(int n_ctas) { return (long long)n_ctas * 2 * 2 * kTileM * 64; }
 DFI_EXPORT int dfi_gemm_decode_counters(int N, int swiglu) {
     const int cols = swiglu ? kTileM / 2 : kTileM;
     return (N + cols - 1) / cols;
@@ -633,6 +635,7 @@ static int gemm_decode(const void* x, const void* w, void* out, int M, int N, in
     if (n_ctas <= 0) return DFI_ERR_LAUNCH;
     if (n_ctas > 512) n_ctas = 512;
     if (!plan_decode(s, M, N, K, swiglu, n_ctas)) return DFI_ERR_LIMIT;
+    if (s.n_ctas > 2 * n_ctas) return DFI_ERR_LIMIT;      // the scratch memory is sized for twice the CTAs asked for
     const bool cluster = plan_uses_cluster(s, swiglu);
     cudaStream_t st = (cudaStream_t)stream;
     int rc;
