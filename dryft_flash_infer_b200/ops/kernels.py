@@ -426,6 +426,32 @@ def tc_error(reset: bool = True) -> int:
 _DECODE_SCRATCH: dict = {}
 
 
+def pair_linear(x: torch.Tensor, weight: torch.Tensor, swiglu: bool = False) -> torch.Tensor:
+    """``x @ weight.T`` (with ``swiglu``: ``silu(x @ gate.T) * (x @ up.T)`` for ``weight = [gate; up]``) in
+    bfloat16 for many rows: the persistent tcgen05 kernel that runs each 256 x 256 tile on a pair of SMs
+    (``csrc/gemm_tcgen05_pair.cu``)."""
+    _need_cuda(x, weight)
+    m, k = x.shape
+    assert x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and weight.shape[1] == k
+    assert x.is_contiguous() and weight.is_contiguous()
+    if k % 8:
+        raise KernelError(f"pair_linear takes K in steps of 8, got {k}")
+    n = weight.shape[0] // 2 if swiglu else weight.shape[0]
+    out = torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
+    _check(_core().dfi_gemm_pair(_ptr(x), _ptr(weight), _ptr(out), m, n, k, n, int(swiglu), _stream()), "pair_linear",
+           f"{m} x {k} by {weight.shape[0]} x {k}")
+    return out
+
+
+def pair_error(reset: bool = True) -> int:
+    """The error word of the pair kernel: 0, or the code of the wait that ran out."""
+    return _core().dfi_gemm_pair_error(int(reset))
+
+
+#: rows from which the pair kernel (256-row tiles) is used for the SwiGLU product
+PAIR_MIN_ROWS = 256
+
+
 class ScaledRows:
     """Rows ``w (.) r`` of an RMS norm that still lack their factor ``1 / rms(r)``: the product that
     reads them applies it to its result.  ``ssq [parts, stride]`` holds partial sums of squares of
@@ -535,9 +561,13 @@ def linear(x, weight: torch.Tensor, out_dtype: torch.dtype | None = None, add_no
 
 def linear_swiglu(x, gate_up: torch.Tensor) -> torch.Tensor:
     """``silu(x @ gate.T) * (x @ up.T)`` for the fused matrix ``gate_up = [gate; up]``: one kernel
-    when decoding in bfloat16, else the product followed by the SwiGLU kernel."""
+    for bfloat16 (the decode kernel for few rows, the pair kernel for many), else the product followed by
+    the SwiGLU kernel."""
     if isinstance(x, ScaledRows):
         return decode_linear(x, gate_up, swiglu=True)
-    if x.dtype == torch.bfloat16 and x.shape[0] <= SKINNY_MAX_ROWS and x.shape[1] % 8 == 0 and x.is_contiguous():
-        return decode_linear(x, gate_up, swiglu=True)
+    if x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and x.is_contiguous():
+        if x.shape[0] <= SKINNY_MAX_ROWS:
+            return decode_linear(x, gate_up, swiglu=True)
+        if x.shape[0] >= PAIR_MIN_ROWS and gate_up.is_contiguous():
+            return pair_linear(x, gate_up, swiglu=True)          # prompts: the activation on the accumulator
     return swiglu(linear(x, gate_up))

@@ -417,6 +417,37 @@ def test_tcgen05_gemm_normal(m, n, k):
     assert torch.allclose(got16.float().cpu(), want, atol=2e-2, rtol=1e-2)
 
 
+@pytest.mark.parametrize("m, n, k", [(256, 256, 64), (300, 320, 200), (2048, 2560, 4096), (1, 8, 8), (700, 6144, 96),
+                                     (5000, 520, 264)])
+def test_tcgen05_pair_gemm(m, n, k):
+    """The persistent kernel that runs a 256 x 256 tile on a pair of SMs: one tile, ragged edges, more
+    tiles than clusters (each cluster walks several, through both accumulators)."""
+    from dryft_flash_infer_b200.ops import kernels
+
+    g = torch.Generator().manual_seed(m + n + k)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    w = (torch.randn(n, k, generator=g) * 0.05).to(torch.bfloat16)
+    want = x.float() @ w.float().T
+    got = kernels.pair_linear(x.cuda(), w.cuda())
+    assert kernels.pair_error() == 0
+    assert got.dtype == torch.bfloat16 and torch.allclose(got.float().cpu(), want, atol=2e-2, rtol=1e-2)
+    assert torch.equal(kernels.pair_linear(x.cuda(), w.cuda()), got)
+
+
+@pytest.mark.parametrize("m, inter, k", [(256, 128, 64), (300, 200, 96), (2048, 9728, 2560), (5, 72, 40), (1000, 1000, 520)])
+def test_tcgen05_pair_gemm_swiglu(m, inter, k):
+    from dryft_flash_infer_b200.ops import kernels
+
+    g = torch.Generator().manual_seed(m + inter + k)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    w = (torch.randn(2 * inter, k, generator=g) * 0.1).to(torch.bfloat16)
+    gu = x.float() @ w.float().T
+    want = gu[:, :inter] / (1 + torch.exp(-gu[:, :inter])) * gu[:, inter:]
+    got = kernels.pair_linear(x.cuda(), w.cuda(), swiglu=True)
+    assert kernels.pair_error() == 0
+    assert torch.allclose(got.float().cpu(), want, atol=0.02 * float(want.abs().max()), rtol=2e-2)
+
+
 @pytest.mark.parametrize("m, inter, k", [(128, 128, 64), (300, 200, 96), (2048, 9728, 2560), (5, 72, 40)])
 def test_tcgen05_gemm_swiglu(m, inter, k):
     from dryft_flash_infer_b200.ops import kernels
