@@ -448,8 +448,8 @@ def pair_error(reset: bool = True) -> int:
     return _core().dfi_gemm_pair_error(int(reset))
 
 
-#: rows from which the pair kernel (256-row tiles) is used for the SwiGLU product
-PAIR_MIN_ROWS = 256
+#: rows from which the pair kernel is used for the SwiGLU product (below, the library product + SwiGLU kernel is as fast or faster)
+PAIR_MIN_ROWS = 1024
 
 
 class ScaledRows:
