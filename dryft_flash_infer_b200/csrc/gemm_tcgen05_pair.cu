@@ -75,6 +75,20 @@ struct PairShape {
     int ldo;                  // row stride of out in elements
 };
 
+// Tiles are numbered so that the clusters, which take consecutive numbers, work on a compact block of
+// the output at any time: bands of kBandTiles row tiles, inside a band column by column.  The rows of
+// x of a band (8 x 256 rows) and the rows of w of the columns in flight then stay in L2, whatever the
+// number of rows; numbering row tiles first over the whole matrix streams x from memory once per
+// column tile as soon as x outgrows L2.
+constexpr int kBandTiles = 8;
+__device__ __forceinline__ void tile_place(const PairShape& s, int t, int& tile_m, int& tile_n) {
+    const int per_band = kBandTiles * s.tiles_n;
+    const int band = t / per_band, in_band = t % per_band;
+    const int rows_here = min(kBandTiles, s.tiles_m - band * kBandTiles);
+    tile_m = band * kBandTiles + in_band % rows_here;
+    tile_n = in_band / rows_here;
+}
+
 template <bool SWIGLU>
 __global__ void __launch_bounds__(kPairThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
@@ -122,8 +136,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             uint32_t i = 0;          // stages filled so far, over all tiles
             bool ok = true;
             for (int t = cluster; t < n_tiles && ok; t += n_clusters) {
-                const int m0 = (t % s.tiles_m) * 2 * kTileM + (int)rank * kTileM;
-                const int tile_n = t / s.tiles_m;
+                int tile_m, tile_n;
+                tile_place(s, t, tile_m, tile_n);
+                const int m0 = tile_m * 2 * kTileM + (int)rank * kTileM;
                 // rows of w for this CTA's half of the tile
                 const int w_row = SWIGLU ? (rank == 0 ? 0 : s.N) + tile_n * kOutCols : tile_n * kPairN + (int)rank * kTileM;
                 for (int kc = 0; kc < k_chunks; ++kc, ++i) {
@@ -183,8 +198,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             ok = mbar_wait(&acc_full[buf], (j >> 1) & 1, 3);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-            const int row = (t % s.tiles_m) * 2 * kTileM + (int)rank * kTileM + row_in_cta;
-            const int col0 = (t / s.tiles_m) * kOutCols;
+            int tile_m, tile_n;
+            tile_place(s, t, tile_m, tile_n);
+            const int row = tile_m * 2 * kTileM + (int)rank * kTileM + row_in_cta;
+            const int col0 = tile_n * kOutCols;
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * kPairN;
             bf16* dst = out + (size_t)row * s.ldo + col0;
             const bool vector = (s.ldo % 8 == 0) && (reinterpret_cast<uintptr_t>(out) & 15) == 0 && col0 % 8 == 0;
