@@ -5,7 +5,8 @@
 
 Prints one JSON line.  ``value`` is decoded tokens per second at batch 8 with every
 sequence at the benchmark context length (the last timed step ends there), timed on the
-device over K decode steps after W warm-up steps.  ``e2e`` is the same through
+device over K decode steps after W warm-up steps (each step launched before the tokens of the
+step before it are read, as generation does).  ``e2e`` is the same through
 ``Engine.generate`` with host token lists in and out.  ``prefill`` is one prompt of 2,048
 tokens; ``points`` are decode at batch 1 and 64; ``roofline`` compares the bytes a decode
 step has to read (every weight once, the live requests' cache) with the HBM peak.
@@ -136,15 +137,22 @@ def time_decode(engine, n_seqs: int, context: int, steps: int, warmup: int, samp
     params = SamplingParams()
     slots = fill_context(engine, n_seqs, context - steps - warmup - 1)
     tokens = [(17 * i + 3) % engine.config.vocab_size for i in range(n_seqs)]
-    for i in range(warmup):
-        tokens = engine.decode(slots, tokens, list(range(n_seqs)), 1 + i, params)
-    torch.cuda.synchronize()
+    # as in generation, a step is launched before the tokens of the step before it are read: it is fed on
+    # the device, and the host's turn-around hides behind the running step
+    ids = list(range(n_seqs))
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     launches_before = kernels.LAUNCHES
-    start.record()
-    for i in range(steps):
-        tokens = engine.decode(slots, tokens, list(range(n_seqs)), 1 + warmup + i, params)
+    handle = None
+    for i in range(warmup + steps):
+        if i == warmup:
+            launches_before = kernels.LAUNCHES
+            start.record()
+        launched = engine.decode_launch(slots, tokens if i == 0 else None, ids, 1 + i, params)
+        if handle is not None:
+            handle.result()
+        handle = launched
     end.record()
+    handle.result()
     torch.cuda.synchronize()
     ms = start.elapsed_time(end) / steps
     batch = next(iter(b for b in engine.decoder.batches.values() if b.n == n_seqs))
