@@ -352,6 +352,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         if (CLUSTER) {
             // the run is one part of row block first_rb: every sum goes to the CTA that owns its column
             ok = mbar_wait(&acc_full[0], 0, 3);
+            if (t == 0) trace(3);
             if (ok) {
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                 const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
@@ -467,7 +468,9 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     if (CLUSTER) {
         // every thread of every CTA of the cluster comes here, whatever happened to it before
         __syncwarp();
+        if (threadIdx.x == 64) trace(4);
         cluster_sync_all();
+        if (threadIdx.x == 64) trace(5);
         if (warp >= 2) {
             const int t = (warp & 3) * 32 + lane;
             const int parts = s.parts, rank = (int)cluster_rank();
@@ -496,6 +499,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                                     active, pad, first_rb * parts + rank, lane);
             }
         }
+        if (threadIdx.x == 64) trace(6);
     }
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     __syncthreads();
