@@ -482,9 +482,9 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
         // every group has the same number of pages: the same number of parts for each, none crossing over
         const int per_cta = max(least, (run.total + (int)gridDim.x - 1) / (int)gridDim.x);
         const int parts = max(1, longest / per_cta);
-        // (not if the groups' parts would leave many CTAs without work, nor if there are more of them
-        // than CTAs: then equal runs that cross from group to group keep every CTA busy)
-        if (n_seqs * n_kv * parts <= (int)gridDim.x && n_seqs * n_kv * parts * 100 >= (int)gridDim.x * 80) {
+        // (not if there are more parts than CTAs, nor if they would keep fewer than 80 % of the CTAs busy
+        // that equal runs crossing from group to group would: then those runs are used)
+        if (n_seqs * n_kv * parts <= (int)gridDim.x && n_seqs * n_kv * parts * 100 >= run.n_ctas * 80) {
             run.parts = parts;
             run.n_ctas = n_seqs * n_kv * parts;
         }
