@@ -40,3 +40,21 @@ def test_generate_prints_one_line_per_step(tmp_path):
     again = run("generate", "--model", str(tmp_path / "m"), "--prompt-ids", str(tmp_path / "p.json"),
                 "--max-new-tokens", "5", "--temperature", "0.7", "--seed", "2", "--cuda-graph", "off")
     assert [json.loads(l) for l in again.stdout.strip().splitlines()][:5] == lines[:5]
+
+
+def bench(*args):
+    return subprocess.run([sys.executable, str(ROOT / "bench.py"), *args], cwd=ROOT, capture_output=True, text=True)
+
+
+def test_bench_measures_one_gpu_only_and_says_so():
+    done = bench("--gpus", "2", "--steps", "2", "--warmup", "1")
+    assert done.returncode == 2
+    lines = done.stdout.strip().splitlines()
+    assert len(lines) == 1 and "--gpus 2" in lines[0]
+
+
+def test_bench_reference_arm_is_unavailable_and_exits_zero():
+    done = bench("--impl", "reference", "--gpus", "1", "--steps", "2", "--warmup", "1")
+    assert done.returncode == 0
+    line = json.loads(done.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and "unavailable" in line and "\n" not in line["unavailable"]
