@@ -5,8 +5,15 @@
 //                           of one): flash attention with causal mask, grouped-query heads,
 //                           optional window.  One CTA per (64 query rows, query head).
 //   dfi_attention_decode    one query row per sequence: the G query heads of a key/value
-//                           head are the rows of one MMA tile, the key range is cut into
-//                           splits that run in parallel, and a second kernel merges them.
+//                           head are the rows of one MMA tile.  One kernel: the pages of all
+//                           (sequence, head) groups are dealt to the CTAs (equal parts per
+//                           group when all sequences are as long, else equal contiguous runs),
+//                           and the parts of a group are merged by the last CTA to arrive
+//                           or, four parts in a thread-block cluster, through distributed
+//                           shared memory.  No CTA waits for another outside a cluster barrier.
+//   dfi_attention_decode_prepared   the same, and the kernel also does the per-head RMS norm and
+//                           rotation of the step's q and k and writes the new key and value
+//                           into the cache (what a kernel before attention would do).
 //
 // Both follow the online softmax of the reference's split kernel
 // (engine/kernels/attention.py:40-137; merge :140-177): float32 scores, maximum, sum and
