@@ -55,6 +55,15 @@ __device__ __forceinline__ float fa_exp2(float x) {
     return y;
 }
 
+// The product with the first operand in tensor memory (rows = lanes, 16 k = 8 columns of bfloat16 pairs).
+__device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
+
 #if DFI_FA_ENABLED
 __global__ void __launch_bounds__(kFaThreads, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -332,8 +341,9 @@ __device__ __forceinline__ unsigned long long fa_now() {
 // when every MMA issued before it is complete, so "scores of page j+1 are ready" also tells the
 // softmax threads that the product of page j has finished reading P and writing the output.
 constexpr int kFa2Threads = 320;                                   // producer, issuer, 2 x 4 softmax warps
-constexpr int kFa2Smem = 2 * kFaQBytes + kFaStages * 2 * kFaKBytes + 2 * kFaPBytes + 1024;
-constexpr int kFa2TmemCols = 512;                                  // S of tile X at 64 X, output of tile X at 128 + 128 X
+constexpr int kFa2Stages = 4;                                      // pages of keys and values in flight
+constexpr int kFa2Smem = 2 * kFaQBytes + kFa2Stages * 2 * kFaKBytes + 1024;
+constexpr int kFa2TmemCols = 512;      // S of tile X at 64 X, output of tile X at 128 + 128 X, P of tile X at 384 + 32 X
 constexpr float kFaRescaleStep = 8.0f;                             // in log2 units
 
 __global__ void __launch_bounds__(kFa2Threads, 1)
@@ -344,14 +354,13 @@ attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __
                              float scale_log2) {
     pdl_launch_next();
     extern __shared__ unsigned char smem_raw[];
-    __shared__ __align__(8) uint64_t q_full, kv_full[kFaStages], kv_empty[kFaStages];
+    __shared__ __align__(8) uint64_t q_full, kv_full[kFa2Stages], kv_empty[kFa2Stages];
     __shared__ __align__(8) uint64_t s_full[2], p_full[2], all_done;
     __shared__ uint32_t tmem_base_s;
 
     unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     unsigned char* q_s = base;                                   // [tile][blocks][128 rows][128 bytes]
     unsigned char* kv_s = q_s + 2 * kFaQBytes;
-    unsigned char* p_s = kv_s + kFaStages * 2 * kFaKBytes;       // [tile][128 rows][128 bytes]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // CTAs start in the order of blockIdx.x, then y: the head is x and the rows are y, latest rows
@@ -380,7 +389,7 @@ attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __
 
     if (threadIdx.x == 0) {
         mbar_init(&q_full, 1);
-        for (int i = 0; i < kFaStages; ++i) {
+        for (int i = 0; i < kFa2Stages; ++i) {
             mbar_init(&kv_full[i], 1);
             mbar_init(&kv_empty[i], 1);
         }
@@ -410,8 +419,8 @@ attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __
                     tma_load_2d(q_s + x * kFaQBytes + b * (kFaRows * 128), &map_q, head * kFaD + b * 64,
                                 row0 + r0 + x * kFaRows, &q_full);
             for (int j = 0; j < n_tiles; ++j) {
-                const int st = j % kFaStages;
-                const uint32_t round = j / kFaStages;
+                const int st = j % kFa2Stages;
+                const uint32_t round = j / kFa2Stages;
                 if (round > 0 && !mbar_wait(&kv_empty[st], (round - 1) & 1, 21)) break;
                 const int place = place_of((t_begin + j) * kFaKeys, ring_tokens);
                 const int page = table[place / kFaKeys];
@@ -432,7 +441,7 @@ attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __
         bool ok = mbar_wait(&q_full, 0, 22);
         auto n_of = [&](int x) { return x == 0 ? n_a : n_b; };
         auto issue_qk = [&](int x, int j) {        // lane 0 only
-            const unsigned char* k_tile = kv_s + (size_t)(j % kFaStages) * 2 * kFaKBytes;
+            const unsigned char* k_tile = kv_s + (size_t)(j % kFa2Stages) * 2 * kFaKBytes;
 #pragma unroll
             for (int kk = 0; kk < kFaD / kUmmaK; ++kk) {
                 const uint64_t a = umma_desc(q_s + x * kFaQBytes + (kk / 4) * (kFaRows * 128)) + 2 * (kk % 4);
@@ -452,7 +461,7 @@ attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __
             __syncwarp();
         }
         for (int j = 0; j < n_tiles && ok; ++j) {
-            const int st = j % kFaStages;
+            const int st = j % kFa2Stages;
             unsigned char* v_tile = kv_s + (size_t)st * 2 * kFaKBytes + kFaKBytes;
             // value rows of keys that were never written (only in the sequence's last page) are zeroed
             const int dead_from = max(kv_len - (t_begin + j) * kFaKeys, 0);
@@ -466,7 +475,7 @@ attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __
                 __syncwarp();
             }
             if (j + 1 < n_tiles) {
-                ok = mbar_wait(&kv_full[(j + 1) % kFaStages], ((j + 1) / kFaStages) & 1, 24);
+                ok = mbar_wait(&kv_full[(j + 1) % kFa2Stages], ((j + 1) / kFa2Stages) & 1, 24);
                 if (!ok) break;
             }
             for (int x = 0; x < 2 && ok; ++x) {
@@ -478,11 +487,11 @@ attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __
                 FA_T(ti1);
                 if (lane == 0) FA_ADD(6, ti1 - ti0);
                 if (lane == 0) {
-                    const uint64_t p_desc = umma_desc(p_s + x * kFaPBytes);
+                    // P comes from tensor memory: 16 keys of a row are 8 columns of packed bfloat16 pairs
 #pragma unroll
                     for (int k = 0; k < kFaKeys / kUmmaK; ++k)
-                        umma_bf16(tmem_base + 128 + x * 128, p_desc + 2 * k, umma_desc_mn(v_tile + k * 2048, kFaKeys * 128),
-                                  idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+                        umma_bf16_ts(tmem_base + 128 + x * 128, tmem_base + 384 + x * 32 + 8 * k,
+                                     umma_desc_mn(v_tile + k * 2048, kFaKeys * 128), idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
                     if (j + 1 < n_of(x)) issue_qk(x, j + 1);  // its commit also covers the product just issued
                     FA_T(ti2);
                     FA_ADD(7, ti2 - ti1);
@@ -581,13 +590,20 @@ attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __
                 packed[e >> 1] = *reinterpret_cast<uint32_t*>(&pair);
             }
             l = l * corr + sum;
-            unsigned char* p_row = p_s + x * kFaPBytes + t * 128;
-#pragma unroll
-            for (int c = 0; c < 8; ++c)
-                *reinterpret_cast<uint4*>(p_row + ((c ^ (t & 7)) << 4)) =
-                    make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+            // the probabilities go to tensor memory as the first operand of the product with V
+            asm volatile(
+                "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+                "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+                "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};\n"
+                ::"r"(lane_addr + 384 + x * 32), "r"(packed[0]), "r"(packed[1]), "r"(packed[2]), "r"(packed[3]), "r"(packed[4]),
+                  "r"(packed[5]), "r"(packed[6]), "r"(packed[7]), "r"(packed[8]), "r"(packed[9]), "r"(packed[10]), "r"(packed[11]),
+                  "r"(packed[12]), "r"(packed[13]), "r"(packed[14]), "r"(packed[15]), "r"(packed[16]), "r"(packed[17]),
+                  "r"(packed[18]), "r"(packed[19]), "r"(packed[20]), "r"(packed[21]), "r"(packed[22]), "r"(packed[23]),
+                  "r"(packed[24]), "r"(packed[25]), "r"(packed[26]), "r"(packed[27]), "r"(packed[28]), "r"(packed[29]),
+                  "r"(packed[30]), "r"(packed[31])
+                : "memory");
+            asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
             FA_T(ts3);
-            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
             fa_arrive(&p_full[x]);
 #ifdef DFI_TRACE
