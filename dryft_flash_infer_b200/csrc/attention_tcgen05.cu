@@ -337,7 +337,9 @@ __device__ __forceinline__ unsigned long long fa_now() {
 // one tile are turned into probabilities while the other tile's products run.  The output rows stay
 // in tensor memory and are accumulated there by the MMA itself; a row is rescaled (by its softmax
 // thread, between two pages) only when its maximum has grown by more than 2^8 since the scale was
-// last fixed, which after the first pages of a row happens rarely.  A tcgen05.commit arrives only
+// last fixed, which after the first pages of a row happens rarely.  The probabilities never touch
+// shared memory: a thread writes its row's bfloat16 pairs into tensor memory (tcgen05.st), and the
+// product with V takes them from there as its first operand.  A tcgen05.commit arrives only
 // when every MMA issued before it is complete, so "scores of page j+1 are ready" also tells the
 // softmax threads that the product of page j has finished reading P and writing the output.
 constexpr int kFa2Threads = 320;                                   // producer, issuer, 2 x 4 softmax warps
