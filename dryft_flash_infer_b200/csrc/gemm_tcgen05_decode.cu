@@ -580,10 +580,11 @@ static bool plan_decode(StreamShape& s, int M, int N, int K, int swiglu, int n_c
     if (s.row_blocks * 2 <= n_ctas) {
         // few row blocks: the same number of parts for each, as many as fill the CTAs
         int parts = n_ctas / s.row_blocks;
-        // one part more if that overshoots the SMs by at most 16 % (a few SMs then hold two CTAs): 40 row
+        // one part more if fewer than 90 % of the SMs would be busy and that overshoots them by at most 16 %
+        // (a few SMs then hold two CTAs): 40 row
         // blocks on 148 SMs run better as 4 x 40 than as 3 x 40 with 28 SMs idle (measured on the 8B and
         // 14B shapes; larger overshoots were measured slower)
-        if (parts < 8 && (parts + 1) * s.row_blocks * 100 <= n_ctas * 116) ++parts;
+        if (parts < 8 && parts * s.row_blocks * 100 < n_ctas * 90 && (parts + 1) * s.row_blocks * 100 <= n_ctas * 116) ++parts;
         if (parts > s.k_chunks) parts = s.k_chunks;
         s.parts = parts;
         s.n_ctas = s.row_blocks * parts;
