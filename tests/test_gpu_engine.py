@@ -371,3 +371,47 @@ def test_large_tensors_load_through_pinned_pieces(tmp_path, dtype, monkeypatch):
     gate_up = torch.cat([files.tensor("model.layers.1.mlp.gate_proj.weight"), files.tensor("model.layers.1.mlp.up_proj.weight")])
     assert torch.equal(ffn.gate_up.cpu(), gate_up.to(ffn.gate_up.dtype))
     assert torch.equal(ffn.down.cpu(), files.tensor("model.layers.1.mlp.down_proj.weight").to(ffn.down.dtype))
+
+
+TINY_D = {
+    "architectures": ["Qwen3ForCausalLM"], "num_hidden_layers": 2, "hidden_size": 136, "num_attention_heads": 6,
+    "num_key_value_heads": 2, "head_dim": 64, "intermediate_size": 264, "vocab_size": 211, "rope_theta": 20000.0,
+    "rms_norm_eps": 2e-5, "tie_word_embeddings": True, "hidden_act": "silu", "max_position_embeddings": 2048,
+}
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_head_size_64_with_prompts_of_several_hundred_tokens(tmp_path, dtype):
+    """Head size 64, three query heads per key/value head, prompts of 150 to 700 tokens in one step (in
+    bfloat16: the tcgen05 attention with two query tiles per CTA, over page borders and ragged ends), then
+    tokens one by one for all, and a second prompt chunk on top of a first."""
+    from dryft_flash_infer_b200 import Engine, StepEntry
+
+    cfg = TINY_D
+    weights = plain_model.random_weights(cfg, seed=12, matrix_std=0.05, norm_std=0.1)
+    folder = write_model(tmp_path, cfg, weights)
+    ref_w = reference_weights(weights, dtype)
+    engine = Engine(folder, dtype=dtype, max_tokens=4096)
+    prompts = prompts_for(cfg, [700, 150, 257, 385], seed=5)
+    want = [plain_model.forward(cfg, ref_w, p) for p in prompts]
+    slots = [engine.open_slot() for _ in prompts]
+    places = [[0, len(p) // 2, len(p) - 5] for p in prompts]
+    logits = engine.step([StepEntry(s, p[:-4], w) for s, p, w in zip(slots, prompts, places)])
+    at = 0
+    for i, w in enumerate(places):
+        for place in w:
+            assert_close(logits[at], want[i][place], dtype, f"prompt {i} place {place}")
+            at += 1
+    for t in (4, 3):
+        logits = engine.step([StepEntry(s, [p[len(p) - t]], [0]) for s, p in zip(slots, prompts)])
+        for i, p in enumerate(prompts):
+            assert_close(logits[i], want[i][len(p) - t], dtype, f"decode {i} -{t}")
+    for s in slots:
+        engine.close_slot(s)
+    # a prompt in two shares: the second attends over the first's keys through the cache
+    slot = engine.open_slot()
+    p = prompts[0]
+    engine.step([StepEntry(slot, p[:300], [])])
+    logits = engine.step([StepEntry(slot, p[300:], [0, len(p) - 301])])
+    assert_close(logits[0], want[0][300], dtype, "second share, first place")
+    assert_close(logits[1], want[0][len(p) - 1], dtype, "second share, last place")
