@@ -413,7 +413,8 @@ __device__ __forceinline__ void head_finish(const HeadInput& in, bool norm, floa
 }
 
 constexpr int kKvStages = 3;            // pages of keys and values in the decode kernel's ring
-constexpr int kMaxParts = 16;           // CTAs that may share one (sequence, head) group
+constexpr int kMaxParts = 16;           // parts of a group that the merge holds at once (it takes more in rounds)
+constexpr int kMaxGroupParts = 64;      // CTAs that may share one (sequence, head) group
 constexpr int kMaxDecodeSeqs = 1024;    // sequences per launch (their page counts sit in shared memory)
 
 __global__ void __launch_bounds__(kThreads)
@@ -478,10 +479,10 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
     DecodeRun run;
     run.total = cum_s[n_seqs] * n_kv;
     // A CTA takes at least four pages, and enough of them that no sequence is spread over more than
-    // kMaxParts CTAs (the merge holds all the parts of a group at once).
+    // kMaxGroupParts CTAs.
     const int longest = max(max(warp_max_s[0], warp_max_s[1]), max(warp_max_s[2], warp_max_s[3]));
     const int shortest = min(min(warp_min_s[0], warp_min_s[1]), min(warp_min_s[2], warp_min_s[3]));
-    const int least = max(4, (longest + kMaxParts - 3) / (kMaxParts - 2));
+    const int least = max(4, (longest + kMaxGroupParts - 3) / (kMaxGroupParts - 2));
     run.n_ctas = max(1, min((int)gridDim.x, run.total / least));
     run.parts = 0;
     run.tiles = longest;
@@ -762,32 +763,41 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
                 // a part lies in its CTA's first place if the group is the first of its run: true for
                 // every part after the first, whose runs begin inside the group
                 const int first_slot = dec_run_begin(run, c_first) >= group_first_unit ? 0 : 1;
-                const int n_parts = c_last - c_first + 1;       // at most kMaxParts by the choice of run length
-                // four neighbouring elements of a row per thread; all parts' loads are issued before any is used
+                const int n_parts = c_last - c_first + 1;       // at most kMaxGroupParts by the choice of run length
+                // four neighbouring elements of a row per thread; the parts come in rounds of kMaxParts, the loads
+                // of a round issued before any is used, and are added in the order of their pages
                 for (int i = threadIdx.x; i < group * (D / 4); i += kThreads) {
                     const int row = i / (D / 4), d = (i % (D / 4)) * 4;
-                    float2 pml[kMaxParts];
-                    float4 po[kMaxParts];
-#pragma unroll
-                    for (int j = 0; j < kMaxParts; ++j) {
-                        const bool live = j < n_parts;
-                        const size_t sl = (size_t)(c_first + (live ? j : 0)) * 2 + (j == 0 ? first_slot : 0);
-                        pml[j] = live ? __ldcg(reinterpret_cast<const float2*>(part_ml + (sl * 16 + row) * 2))
-                                      : make_float2(-INFINITY, 0.f);
-                        po[j] = live ? __ldcg(reinterpret_cast<const float4*>(part_o + (sl * 16 + row) * D + d))
-                                     : make_float4(0.f, 0.f, 0.f, 0.f);
-                    }
-                    float mx = -INFINITY;
-#pragma unroll
-                    for (int j = 0; j < kMaxParts; ++j) mx = fmaxf(mx, pml[j].x);
-                    const float m_use = mx == -INFINITY ? 0.f : mx;
+                    float run_m = -INFINITY, sum = 0.f;
                     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-                    float sum = 0.f;
+                    for (int base = 0; base < n_parts; base += kMaxParts) {
+                        float2 pml[kMaxParts];
+                        float4 po[kMaxParts];
 #pragma unroll
-                    for (int j = 0; j < kMaxParts; ++j) {
-                        const float w = exp2f(pml[j].x - m_use);
-                        acc.x += w * po[j].x; acc.y += w * po[j].y; acc.z += w * po[j].z; acc.w += w * po[j].w;
-                        sum += w * pml[j].y;
+                        for (int j = 0; j < kMaxParts; ++j) {
+                            const bool live = base + j < n_parts;
+                            const size_t sl = (size_t)(c_first + (live ? base + j : 0)) * 2 + (base + j == 0 ? first_slot : 0);
+                            pml[j] = live ? __ldcg(reinterpret_cast<const float2*>(part_ml + (sl * 16 + row) * 2))
+                                          : make_float2(-INFINITY, 0.f);
+                            po[j] = live ? __ldcg(reinterpret_cast<const float4*>(part_o + (sl * 16 + row) * D + d))
+                                         : make_float4(0.f, 0.f, 0.f, 0.f);
+                        }
+                        float mx = run_m;
+#pragma unroll
+                        for (int j = 0; j < kMaxParts; ++j) mx = fmaxf(mx, pml[j].x);
+                        const float m_use = mx == -INFINITY ? 0.f : mx;
+                        if (base > 0) {
+                            const float keep = exp2f(run_m - m_use);       // what was added so far, on the new scale
+                            acc.x *= keep; acc.y *= keep; acc.z *= keep; acc.w *= keep;
+                            sum *= keep;
+                        }
+#pragma unroll
+                        for (int j = 0; j < kMaxParts; ++j) {
+                            const float w = exp2f(pml[j].x - m_use);
+                            acc.x += w * po[j].x; acc.y += w * po[j].y; acc.z += w * po[j].z; acc.w += w * po[j].w;
+                            sum += w * pml[j].y;
+                        }
+                        run_m = mx;
                     }
                     const float inv = sum > 0.f ? 1.0f / sum : 0.f;
                     bf16* dst = out + (size_t)seq * out_stride + (size_t)(kv_head * group + row) * D + d;
