@@ -137,6 +137,10 @@ class DecoderModel:
     # ------------------------------------------------------------------ forward
     def forward(self, ctx, cache) -> torch.Tensor | None:
         """Runs ``ctx``'s rows through the model; logits float32 ``[wanted rows, vocab]``."""
+        with kernels.on_current_stream():
+            return self._forward(ctx, cache)
+
+    def _forward(self, ctx, cache) -> torch.Tensor | None:
         residual = kernels.embedding(self.embedding, ctx.tokens)
         pending = None
         schedule = self.spec.schedule

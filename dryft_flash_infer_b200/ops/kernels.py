@@ -71,8 +71,30 @@ def _ptr(t: torch.Tensor | None):
     return ctypes.c_void_p(0 if t is None else t.data_ptr())
 
 
+_HELD_STREAM: ctypes.c_void_p | None = None
+
+
 def _stream():
+    if _HELD_STREAM is not None:
+        return _HELD_STREAM
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+class on_current_stream:
+    """Within this block the kernels are launched on the stream that is current at its entry, looked up
+    once instead of at every launch (the look-up costs as much as a launch).  The caller does not
+    switch streams inside the block."""
+
+    def __enter__(self):
+        global _HELD_STREAM
+        self.before = _HELD_STREAM
+        _HELD_STREAM = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        return self
+
+    def __exit__(self, *exc):
+        global _HELD_STREAM
+        _HELD_STREAM = self.before
+        return False
 
 
 #: kernels launched through this module since import (a step captured in a CUDA graph counts
