@@ -17,8 +17,9 @@
 // block form a thread-block cluster and add their parts through distributed shared memory instead
 // of scratch memory and tickets.  Every CTA owns the columns c of the row block with (c / 4) mod
 // parts equal to its rank; each CTA stores its sums for a column straight into the owner's shared
-// memory, all CTAs meet once at the cluster barrier, and every owner adds the parts in the order of
-// their k ranges and applies the epilogue to its columns.
+// memory (for a batch above 16 rows four columns at a time, after turning them in its own shared
+// memory), all CTAs meet once at the cluster barrier, and every owner adds the parts in the order
+// of their k ranges and applies the epilogue to its columns.
 //
 // Two optional fusions with the RMS norm around the product, both in the adding CTA's epilogue:
 // * scaled input: x holds rows w (.) r that still lack their 1/rms factor; the sums of squares of r
@@ -48,6 +49,7 @@ struct StreamShape {
     int units;
     int n_ctas;
     int parts;            // > 0: every row block is cut into this many parts, one CTA each (n_ctas = row_blocks * parts)
+    int wide_out;         // plain outputs may be stored four at a time (N a multiple of 4, out on a 16-byte boundary)
 };
 
 constexpr int kSsqStride = 64;   // floats per part in a sum-of-squares array: one per row of the batch
@@ -102,6 +104,10 @@ __device__ __forceinline__ uint32_t cluster_map(uint32_t addr, uint32_t rank) {
 __device__ __forceinline__ void cluster_store(uint32_t addr, float v) {
     asm volatile("st.shared::cluster.f32 [%0], %1;\n" ::"r"(addr), "f"(v) : "memory");
 }
+__device__ __forceinline__ void cluster_store4(uint32_t addr, float4 v) {
+    asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};\n" ::"r"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
+                 : "memory");
+}
 // Every thread of every CTA of the cluster arrives (release) and waits (acquire).
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.aligned;\n" ::: "memory");
@@ -133,6 +139,7 @@ template <int BN> struct DecConfig {
     static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;      // two accumulators
     static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024;
     static constexpr int kSlotFloats = BN * kTileM;                  // one part of one row block
+    static_assert(kStagesRaw < 2 || kStages * kStageBytes >= BN * kTileM * 4, "the ring also holds a CTA's sums, turned, at the end");
 };
 
 // What the epilogue of one group of four columns needs from memory besides the sums: asked for
@@ -201,6 +208,18 @@ __device__ __forceinline__ void finish_group(const RowFusion& fusion, const Stre
         return;
     }
     if (!active) return;
+    if (s.wide_out && col + 3 < s.N) {
+        // four outputs as one store: N is a multiple of four and the output starts on a 16-byte boundary
+        if (out_dtype == DFI_DTYPE_F32) {
+            *reinterpret_cast<float4*>((float*)out + (size_t)b * s.N + col) = make_float4(vals[0], vals[1], vals[2], vals[3]);
+        } else {
+            uint2 packed;
+            *reinterpret_cast<__nv_bfloat162*>(&packed.x) = __floats2bfloat162_rn(vals[0], vals[1]);
+            *reinterpret_cast<__nv_bfloat162*>(&packed.y) = __floats2bfloat162_rn(vals[2], vals[3]);
+            *reinterpret_cast<uint2*>((bf16*)out + (size_t)b * s.N + col) = packed;
+        }
+        return;
+    }
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
         if (col + e < s.N) {
@@ -350,28 +369,48 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             }
         }
         if (CLUSTER) {
-            // the run is one part of row block first_rb: every sum goes to the CTA that owns its column
+            // The run is one part of row block first_rb: every sum goes to the CTA that owns its column.
+            // A thread holds one row of the block, a group is four neighbouring rows.  With few rows in
+            // the batch every sum travels on its own; with many, the sums are turned in this CTA's shared
+            // memory first (the ring is free: every MMA that read it is complete), so that a group
+            // travels as one 16-byte store.
+            constexpr bool kTurn = BN > 16;
+            float* turn = reinterpret_cast<float*>(ring);
+            const int parts = s.parts;
+            const int stride = ((kTileM / 4 + parts - 1) / parts) * 4;       // floats per (sender, row) in an owner
+            const uint32_t mine = (uint32_t)((int)cluster_rank() * BN * stride * 4);
             ok = mbar_wait(&acc_full[0], 0, 3);
             if (t == 0) trace(3);
             if (ok) {
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                 const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-                const int parts = s.parts;
-                const int stride = ((kTileM / 4 + parts - 1) / parts) * 4;       // floats per (sender, row) in an owner
                 const int group_of_t = t >> 2;
-                const uint32_t owner = (uint32_t)(group_of_t % parts);
-                const int local = (group_of_t / parts) * 4 + (t & 3);
-                const uint32_t base = cluster_map(s32(staging), owner) +
-                                      (uint32_t)(((int)cluster_rank() * BN * stride + local) * 4);
+                const uint32_t direct = cluster_map(s32(staging), (uint32_t)(group_of_t % parts)) + mine +
+                                        (uint32_t)(((group_of_t / parts) * 4 + (t & 3)) * 4);
 #pragma unroll
                 for (int c = 0; c < BN; c += 16) {
                     uint32_t d[16];
                     tmem_load16(taddr + c, d);
 #pragma unroll
-                    for (int e = 0; e < 16; ++e)
-                        if (c + e < s.M) cluster_store(base + (uint32_t)((c + e) * stride * 4), __uint_as_float(d[e]));
+                    for (int e = 0; e < 16; ++e) {
+                        if (c + e < s.M) {
+                            if (kTurn) turn[(c + e) * kTileM + t] = __uint_as_float(d[e]);
+                            else cluster_store(direct + (uint32_t)((c + e) * stride * 4), __uint_as_float(d[e]));
+                        }
+                    }
                 }
                 asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            }
+            if (kTurn) {
+                epilogue_barrier();
+                if (ok) {
+                    const int group = t & 31;                                    // the same in every pass: 128 = 4 x 32
+                    const uint32_t base = cluster_map(s32(staging), (uint32_t)(group % parts)) + mine +
+                                          (uint32_t)((group / parts) * 16);
+                    for (int b = t >> 5; b < s.M; b += 4)
+                        cluster_store4(base + (uint32_t)(b * stride * 4),
+                                       *reinterpret_cast<const float4*>(turn + b * kTileM + group * 4));
+                }
             }
         }
         while (!CLUSTER && done < n_units && ok) {
@@ -476,27 +515,47 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             const int parts = s.parts, rank = (int)cluster_rank();
             const int stride = ((kTileM / 4 + parts - 1) / parts) * 4;
             const int n_owned = owned_groups(rank, parts, kTileM / 4);
-            int pad = 4;                                        // lanes per row: a power of two that holds the owned groups
-            while (pad * parts < kTileM / 4) pad <<= 1;
-            const int total = s.M * pad;
-            for (int item = t; item < ((total + 31) & ~31); item += 128) {
-                const int b = item / pad, j = item % pad;
-                const bool active = item < total && j < n_owned;
-                const int col = first_rb * kTileM + (rank + parts * j) * 4;
-                FinishInput in = {};
-                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (active) {
-                    in = finish_begin<false>(fusion, s, col, b);
-                    float4 w4[8];
+            int pad_log2 = 2;                                   // lanes per row: a power of two that holds the owned groups
+            while ((parts << pad_log2) < kTileM / 4) ++pad_log2;
+            const int pad = 1 << pad_log2;
+            const int total = s.M << pad_log2;
+            const int rounded = (total + 31) & ~31;        // whole warps: the lanes of a row share its sum of squares
+            const int ssq_part = first_rb * parts + rank;
+            const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+            // two items per pass: the second one's loads from memory travel with the first one's
+            for (int first = t; first < rounded; first += 256) {
+                const bool two = first + 128 < rounded;     // the same for a whole warp
+                FinishInput in[2] = {};
+                float4 v[2] = {zero4, zero4};
+                int col[2], row[2];
+                bool active[2];
 #pragma unroll
-                    for (int p = 0; p < 8; ++p)
-                        w4[p] = p < parts ? *reinterpret_cast<const float4*>(staging + (p * BN + b) * stride + j * 4)
-                                          : make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-                    for (int p = 0; p < 8; ++p) { v.x += w4[p].x; v.y += w4[p].y; v.z += w4[p].z; v.w += w4[p].w; }
+                for (int u = 0; u < 2; ++u) {
+                    const int item = first + u * 128;
+                    const int j = item & (pad - 1);
+                    row[u] = item >> pad_log2;
+                    active[u] = (u == 0 || two) && item < total && j < n_owned;
+                    col[u] = first_rb * kTileM + (rank + parts * j) * 4;
+                    if (active[u]) in[u] = finish_begin<false>(fusion, s, col[u], row[u]);
                 }
-                finish_group<false>(fusion, s, out, out_dtype, row_scale, in, col, b, v, make_float4(0.f, 0.f, 0.f, 0.f),
-                                    active, pad, first_rb * parts + rank, lane);
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    if (active[u]) {
+                        const float* from = staging + row[u] * stride + ((first + u * 128) & (pad - 1)) * 4;
+#pragma unroll
+                        for (int p = 0; p < 8; ++p) {
+                            if (p < parts) {
+                                const float4 w4 = *reinterpret_cast<const float4*>(from + p * BN * stride);
+                                v[u].x += w4.x; v[u].y += w4.y; v[u].z += w4.z; v[u].w += w4.w;
+                            }
+                        }
+                    }
+                }
+                finish_group<false>(fusion, s, out, out_dtype, row_scale, in[0], col[0], row[0], v[0], zero4, active[0], pad,
+                                    ssq_part, lane);
+                if (two)
+                    finish_group<false>(fusion, s, out, out_dtype, row_scale, in[1], col[1], row[1], v[1], zero4, active[1], pad,
+                                        ssq_part, lane);
             }
         }
         if (threadIdx.x == 64) trace(6);
@@ -648,6 +707,7 @@ static int gemm_decode(const void* x, const void* w, void* out, int M, int N, in
     if (n_ctas > 512) n_ctas = 512;
     if (!plan_decode(s, M, N, K, swiglu, n_ctas)) return DFI_ERR_LIMIT;
     if (s.n_ctas > 2 * n_ctas) return DFI_ERR_LIMIT;      // the scratch memory is sized for twice the CTAs asked for
+    s.wide_out = (N % 4 == 0 && aligned16(out)) ? 1 : 0;
     const bool cluster = plan_uses_cluster(s, swiglu);
     cudaStream_t st = (cudaStream_t)stream;
     int rc;
