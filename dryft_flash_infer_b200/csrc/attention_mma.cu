@@ -37,6 +37,7 @@ namespace dfi {
 constexpr int D = DFI_HEAD_DIM;
 static_assert(D % 16 == 0 && D >= 16 && D <= 128, "head size must be a multiple of 16 up to 128");
 constexpr int kStride = D + 8;      // padded row: 16-byte chunks at an odd stride are conflict-free for ldmatrix
+constexpr int kRedStride = D + 8;   // floats per row of the merge buffers: eight rows stored at once fall into different banks
 constexpr int kPage = 64;           // keys per tile = tokens per cache page
 constexpr int kChunks = D / 8;      // 16-byte chunks per row
 constexpr int kThreads = 128;
@@ -503,7 +504,8 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
     // the space of its query tile (free once the queries are in registers; a first cluster barrier
     // says so), and a second barrier tells it that all parts have arrived.  All CTAs of a cluster
     // take the same decision, since they compute it from the same numbers.
-    const bool clustered = cluster_size > 1 && run.parts == cluster_size && group <= 8 && (D / cluster_size) % 4 == 0;
+    // (the cluster's size is a constant of this file, so that the shares of the columns below are divided by a constant)
+    const bool clustered = cluster_size == kDecodeCluster && run.parts == kDecodeCluster && group <= 8 && (D / kDecodeCluster) % 4 == 0;
     const int cta = blockIdx.x;
     const bool idle = cta >= run.n_ctas;
     const int u_begin = idle ? 0 : dec_run_begin(run, cta), u_end = idle ? 0 : dec_run_begin(run, cta + 1);
@@ -610,6 +612,21 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
             if (t_begin + i <= t_end && !(first_segment && ((preloaded >> i) & 1u))) load_tile(t_begin + i);
             cp_async_commit();
         }
+        // which CTAs hold the group's parts, and whether the first of them holds it in its second place:
+        // divisions whose latency is better spent here, while the queries and the first pages are on
+        // their way, than after the last page
+        int c_first = cta, c_last = cta, first_slot = 0;
+        if (!whole && !clustered) {
+            if (run.parts > 0) {
+                // every group is cut into the same number of parts and no run crosses into another group
+                c_first = (seq * n_kv + kv_head) * run.parts;
+                c_last = c_first + run.parts - 1;
+            } else {
+                c_first = dec_cta_of_unit(run, group_first_unit);
+                c_last = dec_cta_of_unit(run, group_first_unit + seq_tiles - 1);
+                first_slot = dec_run_begin(run, c_first) >= group_first_unit ? 0 : 1;
+            }
+        }
         uint32_t qf[D / 16][4];
         for (int t = t_begin; t <= t_end; ++t) {
             const int stage = (t - t_begin) % kKvStages;
@@ -662,20 +679,20 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
         __syncthreads();         // everyone is done with the pages: their memory is reused below
         if (clustered && !freed) dec_cluster_arrive();
 
-        // merge the four warps' results: the tile buffers are free now
-        float* red_o = reinterpret_cast<float*>(k_s);        // [4][16][D]
-        float* red_ml = red_o + 4 * 16 * D;                  // [4][16][2]
+        // merge the four warps' results: the tile buffers are free now.  Rows are kRedStride floats apart, so
+        // that the eight rows a warp stores at once fall into different banks; rows past the group are the
+        // padding of the 16-row MMA tile and are left out.
+        float* red_o = reinterpret_cast<float*>(k_s);        // [4][16][kRedStride]
+        float* red_ml = red_o + 4 * 16 * kRedStride;         // [4][16][2]
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             const int row = g + h * 8;
+            if (row < group) {
 #pragma unroll
-            for (int n = 0; n < D / 8; ++n) {
-                red_o[(warp * 16 + row) * D + n * 8 + t4 * 2] = o[n][2 * h];
-                red_o[(warp * 16 + row) * D + n * 8 + t4 * 2 + 1] = o[n][2 * h + 1];
-            }
-            if (t4 == 0) {
-                red_ml[(warp * 16 + row) * 2] = m[h];
-                red_ml[(warp * 16 + row) * 2 + 1] = l[h];
+                for (int n = 0; n < D / 8; ++n)
+                    *reinterpret_cast<float2*>(red_o + (warp * 16 + row) * kRedStride + n * 8 + t4 * 2) =
+                        make_float2(o[n][2 * h], o[n][2 * h + 1]);
+                if (t4 == 0) *reinterpret_cast<float2*>(red_ml + (warp * 16 + row) * 2) = make_float2(m[h], l[h]);
             }
         }
         __syncthreads();
@@ -693,21 +710,21 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
 #pragma unroll
             for (int w = 0; w < 4; ++w) {
                 const float c = exp2f(red_ml[(w * 16 + row) * 2] - m_use);
-                const float4 part = *reinterpret_cast<const float4*>(red_o + (w * 16 + row) * D + d);
+                const float4 part = *reinterpret_cast<const float4*>(red_o + (w * 16 + row) * kRedStride + d);
                 acc.x += c * part.x; acc.y += c * part.y; acc.z += c * part.z; acc.w += c * part.w;
                 sum += c * red_ml[(w * 16 + row) * 2 + 1];
             }
             if (clustered) {
                 // to the owner of these columns: [sender][row][column in the owner's share], then [sender][row][m, l]
                 constexpr int kRows = 8;
-                const int share = D / cluster_size;
+                constexpr int share = D / kDecodeCluster;
                 const uint32_t owner = (uint32_t)(d / share);
                 const uint32_t base = dec_cluster_map(q_s, owner);
                 const int me = (int)dec_cluster_rank();
                 const uint32_t o_at = base + (uint32_t)(((me * kRows + row) * share + d % share) * 4);
                 asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};\n" ::"r"(o_at), "f"(acc.x), "f"(acc.y), "f"(acc.z), "f"(acc.w) : "memory");
                 if (d % share == 0) {
-                    const uint32_t ml_at = base + (uint32_t)((cluster_size * kRows * share + (me * kRows + row) * 2) * 4);
+                    const uint32_t ml_at = base + (uint32_t)((kDecodeCluster * kRows * share + (me * kRows + row) * 2) * 4);
                     asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};\n" ::"r"(ml_at), "f"(mx), "f"(sum) : "memory");
                 }
             } else if (whole) {
@@ -725,18 +742,20 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
             dec_cluster_arrive();
             dec_cluster_wait();
             constexpr int kRows = 8;
-            const int share = D / cluster_size;
+            constexpr int share = D / kDecodeCluster;
             const float* recv_o = reinterpret_cast<const float*>(q_s);
-            const float* recv_ml = recv_o + cluster_size * kRows * share;
+            const float* recv_ml = recv_o + kDecodeCluster * kRows * share;
             const int me = (int)dec_cluster_rank();
             for (int i = threadIdx.x; i < group * (share / 4); i += kThreads) {
                 const int row = i / (share / 4), dl = (i % (share / 4)) * 4;
                 float mx = -INFINITY;
-                for (int j = 0; j < cluster_size; ++j) mx = fmaxf(mx, recv_ml[(j * kRows + row) * 2]);
+#pragma unroll
+                for (int j = 0; j < kDecodeCluster; ++j) mx = fmaxf(mx, recv_ml[(j * kRows + row) * 2]);
                 const float m_use = mx == -INFINITY ? 0.f : mx;
                 float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
                 float sum = 0.f;
-                for (int j = 0; j < cluster_size; ++j) {          // in the order of the parts' pages
+#pragma unroll
+                for (int j = 0; j < kDecodeCluster; ++j) {          // in the order of the parts' pages
                     const float w = exp2f(recv_ml[(j * kRows + row) * 2] - m_use);
                     const float4 part = *reinterpret_cast<const float4*>(recv_o + (j * kRows + row) * share + dl);
                     acc.x += w * part.x; acc.y += w * part.y; acc.z += w * part.z; acc.w += w * part.w;
@@ -749,8 +768,6 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
             }
         } else if (!whole) {
             __syncthreads();
-            const int c_first = dec_cta_of_unit(run, group_first_unit);
-            const int c_last = dec_cta_of_unit(run, group_first_unit + seq_tiles - 1);
             atrace(5);
             if (threadIdx.x == 0) {
                 // one acquire-release add at GPU scope: this CTA's part (ordered before it by the barrier
@@ -762,7 +779,6 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
             if (ticket_s == c_last - c_first) {
                 // a part lies in its CTA's first place if the group is the first of its run: true for
                 // every part after the first, whose runs begin inside the group
-                const int first_slot = dec_run_begin(run, c_first) >= group_first_unit ? 0 : 1;
                 const int n_parts = c_last - c_first + 1;       // at most kMaxGroupParts by the choice of run length
                 // four neighbouring elements of a row per thread; the parts come in rounds of kMaxParts, the loads
                 // of a round issued before any is used, and are added in the order of their pages
@@ -816,7 +832,7 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
 
 constexpr int kPrefillSmem = (64 + 4 * kPage) * kStride * (int)sizeof(bf16);
 constexpr int kDecodeTiles = (16 + 2 * kKvStages * kPage) * kStride * (int)sizeof(bf16);
-constexpr int kDecodeReduce = 16 * kStride * (int)sizeof(bf16) + (4 * 16 * D + 4 * 16 * 2) * (int)sizeof(float);
+constexpr int kDecodeReduce = 16 * kStride * (int)sizeof(bf16) + (4 * 16 * kRedStride + 4 * 16 * 2) * (int)sizeof(float);
 constexpr int kDecodeSmem = kDecodeTiles > kDecodeReduce ? kDecodeTiles : kDecodeReduce;
 
 }  // namespace dfi

@@ -249,6 +249,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     unsigned char* ring = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     float* staging = reinterpret_cast<float*>(ring + (size_t)Cfg::kStages * Cfg::kStageBytes);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int cl_stride = 0, cl_owned = 0, cl_pad_log2 = 2;      // CLUSTER: set by the epilogue threads before they wait
     const int cta = blockIdx.x;
     const int u_begin = sk_run_begin(s, cta), u_end = sk_run_begin(s, cta + 1);
     const int n_units = u_end - u_begin;
@@ -356,6 +357,21 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         const int t = quarter * 32 + lane;
         int rb = first_rb, seg_first_kc = first_kc, done = 0, segment = 0;
         bool ok = true;
+        uint32_t cl_dest = 0;
+        if (CLUSTER) {
+            // Where this thread's sums go in the cluster, and what the CTA owns: divisions by the number of
+            // parts, done now, while the weights stream, and not between the last MMA and the stores.
+            constexpr bool kTurn = BN > 16;
+            const int parts = s.parts, rank = (int)cluster_rank();
+            cl_stride = ((kTileM / 4 + parts - 1) / parts) * 4;
+            cl_owned = owned_groups(rank, parts, kTileM / 4);
+            while ((parts << cl_pad_log2) < kTileM / 4) ++cl_pad_log2;
+            // a group is four neighbouring rows of the block: a thread sends its own row's sums, or (turned) a whole group's
+            const int group = kTurn ? (t & 31) : (t >> 2);
+            cl_dest = cluster_map(s32(staging), (uint32_t)(group % parts)) +
+                      (uint32_t)((rank * BN * cl_stride + (group / parts) * 4 + (kTurn ? 0 : (t & 3))) * 4);
+            asm volatile("" : "+r"(cl_stride), "+r"(cl_owned), "+r"(cl_pad_log2), "+r"(cl_dest));      // computed here, not later
+        }
         if (fusion.in_ssq != nullptr || fusion.residual != nullptr) {
             pdl_wait();          // these threads read what the kernel before wrote
             if (fusion.in_ssq != nullptr) {
@@ -376,17 +392,11 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             // travels as one 16-byte store.
             constexpr bool kTurn = BN > 16;
             float* turn = reinterpret_cast<float*>(ring);
-            const int parts = s.parts;
-            const int stride = ((kTileM / 4 + parts - 1) / parts) * 4;       // floats per (sender, row) in an owner
-            const uint32_t mine = (uint32_t)((int)cluster_rank() * BN * stride * 4);
             ok = mbar_wait(&acc_full[0], 0, 3);
             if (t == 0) trace(3);
             if (ok) {
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                 const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-                const int group_of_t = t >> 2;
-                const uint32_t direct = cluster_map(s32(staging), (uint32_t)(group_of_t % parts)) + mine +
-                                        (uint32_t)(((group_of_t / parts) * 4 + (t & 3)) * 4);
 #pragma unroll
                 for (int c = 0; c < BN; c += 16) {
                     uint32_t d[16];
@@ -395,7 +405,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                     for (int e = 0; e < 16; ++e) {
                         if (c + e < s.M) {
                             if (kTurn) turn[(c + e) * kTileM + t] = __uint_as_float(d[e]);
-                            else cluster_store(direct + (uint32_t)((c + e) * stride * 4), __uint_as_float(d[e]));
+                            else cluster_store(cl_dest + (uint32_t)((c + e) * cl_stride * 4), __uint_as_float(d[e]));
                         }
                     }
                 }
@@ -405,10 +415,8 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 epilogue_barrier();
                 if (ok) {
                     const int group = t & 31;                                    // the same in every pass: 128 = 4 x 32
-                    const uint32_t base = cluster_map(s32(staging), (uint32_t)(group % parts)) + mine +
-                                          (uint32_t)((group / parts) * 16);
                     for (int b = t >> 5; b < s.M; b += 4)
-                        cluster_store4(base + (uint32_t)(b * stride * 4),
+                        cluster_store4(cl_dest + (uint32_t)(b * cl_stride * 4),
                                        *reinterpret_cast<const float4*>(turn + b * kTileM + group * 4));
                 }
             }
@@ -513,11 +521,8 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         if (warp >= 2) {
             const int t = (warp & 3) * 32 + lane;
             const int parts = s.parts, rank = (int)cluster_rank();
-            const int stride = ((kTileM / 4 + parts - 1) / parts) * 4;
-            const int n_owned = owned_groups(rank, parts, kTileM / 4);
-            int pad_log2 = 2;                                   // lanes per row: a power of two that holds the owned groups
-            while ((parts << pad_log2) < kTileM / 4) ++pad_log2;
-            const int pad = 1 << pad_log2;
+            const int stride = cl_stride, n_owned = cl_owned, pad_log2 = cl_pad_log2;
+            const int pad = 1 << pad_log2;                      // lanes per row: a power of two that holds the owned groups
             const int total = s.M << pad_log2;
             const int rounded = (total + 31) & ~31;        // whole warps: the lanes of a row share its sum of squares
             const int ssq_part = first_rb * parts + rank;
