@@ -266,32 +266,38 @@ __global__ void qk_norm_rope_write_kernel(T* __restrict__ qkv, int row_stride, i
     }
 }
 
-// The same with half a warp per head and four neighbouring elements of each half per lane, for
-// head sizes that are multiples of 8 up to 256: fewer, wider loads when there are many rows.
-struct Quad { float v[4]; };
-__device__ __forceinline__ Quad load4(const float* p) {
-    const float4 f = *reinterpret_cast<const float4*>(p);
-    return Quad{{f.x, f.y, f.z, f.w}};
+// The same with eight lanes per head (four heads per warp) and eight neighbouring elements of each half
+// of a head per lane, for head sizes that are multiples of 16 up to 256: with many rows the kernel is
+// bound by the instructions around each load, so every lane takes a 16-byte load's worth of a head.
+constexpr int kWideSteps = 2;  // 8 lanes x 8 elements x 2 steps cover half a head of up to 128 (one step: up to 64)
+
+struct Oct { float v[8]; };
+__device__ __forceinline__ Oct load8(const float* p) {
+    const float4 f = *reinterpret_cast<const float4*>(p), g = *reinterpret_cast<const float4*>(p + 4);
+    return Oct{{f.x, f.y, f.z, f.w, g.x, g.y, g.z, g.w}};
 }
-__device__ __forceinline__ Quad load4(const bf16* p) {
-    const uint2 u = *reinterpret_cast<const uint2*>(p);
+__device__ __forceinline__ Oct load8(const bf16* p) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
     const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
     const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
-    return Quad{{a.x, a.y, b.x, b.y}};
+    const float2 c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.z));
+    const float2 d = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.w));
+    return Oct{{a.x, a.y, b.x, b.y, c.x, c.y, d.x, d.y}};
 }
-__device__ __forceinline__ void store4(float* p, const Quad& q) {
+__device__ __forceinline__ void store8(float* p, const Oct& q) {
     *reinterpret_cast<float4*>(p) = make_float4(q.v[0], q.v[1], q.v[2], q.v[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(q.v[4], q.v[5], q.v[6], q.v[7]);
 }
-__device__ __forceinline__ void store4(bf16* p, const Quad& q) {
-    uint2 u;
+__device__ __forceinline__ void store8(bf16* p, const Oct& q) {
+    uint4 u;
     *reinterpret_cast<__nv_bfloat162*>(&u.x) = __floats2bfloat162_rn(q.v[0], q.v[1]);
     *reinterpret_cast<__nv_bfloat162*>(&u.y) = __floats2bfloat162_rn(q.v[2], q.v[3]);
-    *reinterpret_cast<uint2*>(p) = u;
+    *reinterpret_cast<__nv_bfloat162*>(&u.z) = __floats2bfloat162_rn(q.v[4], q.v[5]);
+    *reinterpret_cast<__nv_bfloat162*>(&u.w) = __floats2bfloat162_rn(q.v[6], q.v[7]);
+    *reinterpret_cast<uint4*>(p) = u;
 }
 
-constexpr int kWideSteps = 2;  // 16 lanes x 4 elements x 2 steps cover half a head of up to 128
-
-template <typename T>
+template <typename T, int STEPS>
 __global__ void qk_norm_rope_write_wide_kernel(T* __restrict__ qkv, int row_stride, int n_q, int n_kv, int D,
                                                const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
                                                const float* __restrict__ cos_t, const float* __restrict__ sin_t,
@@ -301,8 +307,8 @@ __global__ void qk_norm_rope_write_wide_kernel(T* __restrict__ qkv, int row_stri
                                                int ring_tokens, int write_cache) {
     pdl_launch_next();
     pdl_wait();
-    const int lane = threadIdx.x & 15;
-    const int head = blockIdx.y * (blockDim.x >> 4) + (threadIdx.x >> 4);
+    const int lane = threadIdx.x & 7;
+    const int head = blockIdx.y * (blockDim.x >> 3) + (threadIdx.x >> 3);
     const int row = blockIdx.x;
     const bool is_q = head < n_q;
     const bool is_k = !is_q && head < n_q + n_kv;
@@ -312,6 +318,16 @@ __global__ void qk_norm_rope_write_wide_kernel(T* __restrict__ qkv, int row_stri
     T* src = qkv + (size_t)row * row_stride + (size_t)(active ? head : 0) * D;
     const int pos = row_pos[row];
 
+    Oct lo[STEPS], hi[STEPS];
+#pragma unroll
+    for (int j = 0; j < STEPS; ++j) {
+        const int i = 8 * lane + 64 * j;
+        if (active && i < half) {
+            lo[j] = load8(src + i);
+            hi[j] = load8(src + i + half);
+        }
+    }
+    // where keys and values go: looked up after the row has been asked for, which does not wait for it
     T* dst = src;
     if (active && !is_q) {
         const int place = place_of(pos, ring_tokens);
@@ -320,56 +336,44 @@ __global__ void qk_norm_rope_write_wide_kernel(T* __restrict__ qkv, int row_stri
         T* cache = is_k ? k_cache : v_cache;
         dst = cache + (((size_t)page * n_kv + kv_head) * page_size + place % page_size) * D;
     }
-
-    Quad lo[kWideSteps], hi[kWideSteps];
+    const float* w = is_q ? q_w : (is_k ? k_w : nullptr);
+    const bool rotate = (is_q || is_k) && cos_t != nullptr;
     float ssq = 0.f;
 #pragma unroll
-    for (int j = 0; j < kWideSteps; ++j) {
-        const int i = 4 * lane + 64 * j;
-        if (active && i < half) {
-            lo[j] = load4(src + i);
-            hi[j] = load4(src + i + half);
+    for (int j = 0; j < STEPS; ++j) {
+        if (active && 8 * lane + 64 * j < half) {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) ssq += lo[j].v[e] * lo[j].v[e] + hi[j].v[e] * hi[j].v[e];
+            for (int e = 0; e < 8; ++e) ssq += lo[j].v[e] * lo[j].v[e] + hi[j].v[e] * hi[j].v[e];
         }
     }
-    const float* w = is_q ? q_w : (is_k ? k_w : nullptr);
 #pragma unroll
-    for (int o = 8; o > 0; o >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, o);
+    for (int o = 4; o > 0; o >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, o);
     if (!active) return;
-    if (w != nullptr) {
-        const float scale = 1.0f / sqrtf(ssq / (float)D + eps);
+    const float scale = w != nullptr ? 1.0f / sqrtf(ssq / (float)D + eps) : 1.0f;
 #pragma unroll
-        for (int j = 0; j < kWideSteps; ++j) {
-            const int i = 4 * lane + 64 * j;
-            if (i < half) {
-                const Quad wl = load4(w + i), wh = load4(w + i + half);
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    lo[j].v[e] *= scale * wl.v[e];
-                    hi[j].v[e] *= scale * wh.v[e];
-                }
-            }
-        }
-    }
-    const bool rotate = (is_q || is_k) && cos_t != nullptr;
-    const float* c = rotate ? cos_t + (size_t)pos * half : nullptr;
-    const float* s = rotate ? sin_t + (size_t)pos * half : nullptr;
-#pragma unroll
-    for (int j = 0; j < kWideSteps; ++j) {
-        const int i = 4 * lane + 64 * j;
+    for (int j = 0; j < STEPS; ++j) {
+        const int i = 8 * lane + 64 * j;
         if (i < half) {
-            Quad a = lo[j], b = hi[j];
-            if (rotate) {
-                const Quad cv = load4(c + i), sv = load4(s + i);
+            Oct a = lo[j], b = hi[j];
+            if (w != nullptr) {
+                const Oct wl = load8(w + i), wh = load8(w + i + half);
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    a.v[e] = lo[j].v[e] * cv.v[e] - hi[j].v[e] * sv.v[e];
-                    b.v[e] = hi[j].v[e] * cv.v[e] + lo[j].v[e] * sv.v[e];
+                for (int e = 0; e < 8; ++e) {
+                    a.v[e] *= scale * wl.v[e];
+                    b.v[e] *= scale * wh.v[e];
                 }
             }
-            store4(dst + i, a);
-            store4(dst + i + half, b);
+            if (rotate) {
+                const Oct cv = load8(cos_t + (size_t)pos * half + i), sv = load8(sin_t + (size_t)pos * half + i);
+                const Oct a0 = a, b0 = b;
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    a.v[e] = a0.v[e] * cv.v[e] - b0.v[e] * sv.v[e];
+                    b.v[e] = b0.v[e] * cv.v[e] + a0.v[e] * sv.v[e];
+                }
+            }
+            store8(dst + i, a);
+            store8(dst + i + half, b);
         }
     }
 }
@@ -502,19 +506,21 @@ DFI_EXPORT int dfi_qk_norm_rope_write(void* qkv, int rows, int row_stride, int n
     cudaStream_t st = (cudaStream_t)stream;
     const int warps = 4;
     const int heads = n_q + 2 * n_kv;
-    const bool wide = rows >= 64 && head_dim % 8 == 0 && head_dim <= 128 * kWideSteps && row_stride % 4 == 0 &&
+    const bool wide = rows >= 64 && head_dim % 16 == 0 && head_dim <= 128 * kWideSteps && row_stride % 8 == 0 &&
                       aligned16(qkv) && aligned16(k_cache) && aligned16(v_cache) && aligned16(q_w) && aligned16(k_w) &&
                       aligned16(cos_t) && aligned16(sin_t);
     if (wide) {
-        dim3 wide_grid(rows, (heads + 2 * warps - 1) / (2 * warps));
-        if (dtype == DFI_DTYPE_F32)
-            launch(qk_norm_rope_write_wide_kernel<float>, wide_grid, warps * 32, 0, st,
-                (float*)qkv, row_stride, n_q, n_kv, head_dim, q_w, k_w, eps, cos_t, sin_t, row_pos, row_seq,
-                (float*)k_cache, (float*)v_cache, block_table, table_width, page_size, ring_tokens, write_cache);
-        else if (dtype == DFI_DTYPE_BF16)
-            launch(qk_norm_rope_write_wide_kernel<bf16>, wide_grid, warps * 32, 0, st,
-                (bf16*)qkv, row_stride, n_q, n_kv, head_dim, q_w, k_w, eps, cos_t, sin_t, row_pos, row_seq,
-                (bf16*)k_cache, (bf16*)v_cache, block_table, table_width, page_size, ring_tokens, write_cache);
+        dim3 wide_grid(rows, (heads + 4 * warps - 1) / (4 * warps));
+#define DFI_WIDE(TYPE, STEPS)                                                                                       \
+    launch(qk_norm_rope_write_wide_kernel<TYPE, STEPS>, wide_grid, warps * 32, 0, st, (TYPE*)qkv, row_stride, n_q,       \
+           n_kv, head_dim, q_w, k_w, eps, cos_t, sin_t, row_pos, row_seq, (TYPE*)k_cache, (TYPE*)v_cache, block_table,  \
+           table_width, page_size, ring_tokens, write_cache)
+        if (dtype == DFI_DTYPE_F32) {
+            if (head_dim <= 128) DFI_WIDE(float, 1); else DFI_WIDE(float, 2);
+        } else if (dtype == DFI_DTYPE_BF16) {
+            if (head_dim <= 128) DFI_WIDE(bf16, 1); else DFI_WIDE(bf16, 2);
+        }
+#undef DFI_WIDE
         else return DFI_ERR_DTYPE;
         DFI_CHECK_LAUNCH();
         return DFI_OK;

@@ -84,9 +84,10 @@ def paged_cache(n_seqs, lengths, n_kv, dim, dtype, ring_tokens=0, seed=0, page_s
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("n_q, n_kv, dim", [(6, 3, 48), (4, 4, 16), (16, 2, 128), (5, 1, 256), (3, 1, 20)])
-@pytest.mark.parametrize("lengths, starts", [([70, 3, 130], [60, 0, 127]), ([170, 3, 130], [60, 0, 127])])
+@pytest.mark.parametrize("lengths, starts", [([70, 3, 130], [60, 0, 127]), ([170, 3, 130], [60, 0, 127]), ([171, 3, 130], [60, 0, 127])])
 def test_qk_norm_rope_write(dtype, n_q, n_kv, dim, lengths, starts):
-    """Few rows take the kernel with a warp per head, many rows the one with half a warp per head."""
+    """Few rows take the kernel with a warp per head, many rows the one with half a warp per head and
+    four rows per thread (116 rows fill its threads, 117 leave three of the last four without a row)."""
     from dryft_flash_infer_b200.ops import kernels
     from dryft_flash_infer_b200.parts.rotary import RotaryEmbedding
 
