@@ -111,7 +111,7 @@ class Engine:
         if max_context > self._positions_ready:
             self.model.prepare(max_context)
             self._positions_ready = max_context
-        self.stepper = Stepper(self.model, self.cache, self.options.step_tokens)
+        self.stepper = Stepper(self.model, self.cache, self.options.step_tokens, self.options.cuda_graph)
         self.decoder = Decoder(self.model, self.cache, self.options.cuda_graph)
 
     def _ensure_room(self, lengths: list[int]) -> None:

@@ -6,6 +6,7 @@ import torch
 
 from ..cache import SequenceCache
 from .context import StepContext, StepEntry
+from .prefill import PrefillGraphs
 
 
 class Stepper:
@@ -22,9 +23,11 @@ class Stepper:
     shares are cut into passes here, which changes no result.
     """
 
-    def __init__(self, model, cache: SequenceCache, step_tokens: int):
+    def __init__(self, model, cache: SequenceCache, step_tokens: int, use_graph: bool = False):
         self.model, self.cache = model, cache
         self.step_tokens = step_tokens
+        # short prompt steps run as CUDA graphs at a few fixed shapes, if every mixer can be captured
+        self.graphs = PrefillGraphs(model, cache) if use_graph and model.graph_safe else None
         self.has_ring = any(g.ring_tokens for g in cache.groups)
         self.device = model.device
 
@@ -70,8 +73,10 @@ class Stepper:
     def _pass(self, entries: list[StepEntry]):
         for e in entries:
             self.cache.book.reserve(e.slot, len(e.tokens))
-        ctx = StepContext(entries, self.cache, self.device)
-        logits = self.model.forward(ctx, self.cache)
+        logits = self.graphs.run(entries) if self.graphs is not None else None
+        if logits is None:
+            ctx = StepContext(entries, self.cache, self.device)
+            logits = self.model.forward(ctx, self.cache)
         for e in entries:
             self.cache.book.advance(e.slot, len(e.tokens))
         return logits

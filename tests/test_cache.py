@@ -117,3 +117,41 @@ def test_groups_by_need_and_state_area():
     assert (table[0, :2] > 0).all() and (table[0, 2:] == 0).all()
     view = cache.layer_view(2, [torch.zeros(1, 4, dtype=torch.int32)] * 3, True)
     assert view.k.data_ptr() == by_ids[(0, 2)].k[1].data_ptr() and view.ring_tokens == 0
+
+
+def test_a_step_laid_out_at_a_larger_shape_keeps_its_spare_rows_away_from_live_pages():
+    """The layout that lets short prompt steps share buffers: rows past the step's own belong to no
+    sequence and point at the null page; the step's own numbers are where they are without padding."""
+    from dryft_flash_infer_b200.engine import StepContext, StepEntry
+    from dryft_flash_infer_b200.engine.prefill import shape_for
+
+    cache = SequenceCache({0: KVNeed(2, 16)}, {}, max_tokens=640, max_seqs=4, max_context=320, step_tokens=64,
+                          dtype=torch.float32, device="cpu")
+    a, b = cache.open_slot(), cache.open_slot()
+    cache.book.reserve(a, 70)
+    cache.book.advance(a, 70)           # a has 70 tokens already: its share of the step starts there
+    entries = [StepEntry(a, [5, 6, 7], [2]), StepEntry(b, list(range(1, 101)), [0, 99])]
+    for e in entries:
+        cache.book.reserve(e.slot, len(e.tokens))
+    assert shape_for(entries) == (128, 4, 4)
+    assert shape_for([StepEntry(a, [1], [0]), StepEntry(b, [2], [0])]) is None            # a decode step
+    assert shape_for([StepEntry(a, list(range(2000)), [0])]) is None                     # too long
+    assert shape_for([StepEntry(a, [1, 2], [])]) is None                                 # nothing wanted
+    plain = StepContext(entries, cache, "cpu")
+    buffer = torch.full((4096,), -7, dtype=torch.int32)
+    padded = StepContext(entries, cache, "cpu", table_widths=[5], shape=(128, 4, 4), into=buffer)
+    assert (padded.n_rows, padded.n_seqs, padded.n_wanted) == (128, 4, 4)
+    assert (padded.own_rows, padded.own_seqs, padded.own_wanted) == (103, 2, 3)
+    assert not padded.all_decode and not padded.wants_every_row and padded.max_q_len == 128
+    assert torch.equal(padded.tokens[:103], plain.tokens) and (padded.tokens[103:] == 0).all()
+    assert torch.equal(padded.row_pos[:103], plain.row_pos) and (padded.row_pos[103:] == 0).all()
+    assert torch.equal(padded.row_seq[:103], plain.row_seq) and (padded.row_seq[103:] == 3).all()
+    assert padded.cu_rows.tolist() == [0, 3, 103, 103, 103]
+    assert padded.seq_start.tolist() == [70, 0, 0, 0] and padded.seq_qlen.tolist() == [3, 100, 0, 0]
+    assert padded.wanted_rows.tolist() == [2, 3, 102, 0]
+    table = padded.block_tables[0]
+    assert table.shape == (4, 5) and (table[2:] == 0).all()                # the spare sequences: the null page only
+    assert torch.equal(table[:2, :2], plain.block_tables[0][:, :2]) and (table[:2, :2] > 0).all()
+    assert padded.block_tables[0].data_ptr() >= buffer.data_ptr()          # it lives in the buffer it was given
+    with pytest.raises(ValueError, match="does not fit the shape"):
+        StepContext(entries, cache, "cpu", table_widths=[5], shape=(128, 2, 4), into=buffer)   # no sequence to spare

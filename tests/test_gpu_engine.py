@@ -415,3 +415,50 @@ def test_head_size_64_with_prompts_of_several_hundred_tokens(tmp_path, dtype):
     logits = engine.step([StepEntry(slot, p[300:], [0, len(p) - 301])])
     assert_close(logits[0], want[0][300], dtype, "second share, first place")
     assert_close(logits[1], want[0][len(p) - 1], dtype, "second share, last place")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_short_prompt_steps_replayed_as_graphs(folders, name, dtype):
+    """Prompt steps of unequal sizes that share one padded shape: the first runs kernel by kernel, the
+    second is captured, the others are replays of that graph on the same buffers.  Every one of them
+    must give the logits of the plain implementation, whatever the step before left in the buffers;
+    one sequence stays live throughout, so a stray write of a spare row into its pages would show in
+    its later share; and with graphs switched off the engine must agree too."""
+    from dryft_flash_infer_b200 import StepEntry
+
+    folder, cfg, weights = folders[name]
+    ref_w = reference_weights(weights, dtype)
+    engine = make_engine(folder, dtype, max_tokens=64 * 24)
+    assert engine.stepper.graphs is not None
+    plain_engine = make_engine(folder, dtype, max_tokens=64 * 24, cuda_graph=False)
+    assert plain_engine.stepper.graphs is None
+    long_prompt = prompts_for(cfg, [130], seed=77)[0]
+    want_long = plain_model.forward(cfg, ref_w, long_prompt)
+    keeper = engine.open_slot()
+    fed = 0
+    # every round: 3 fresh prompts and a share of the long one, 4 sequences and 4 wanted places in 128 rows
+    for round_, (lengths, share) in enumerate([((5, 40, 31), 20), ((20, 30, 33), 9), ((1, 2, 60), 50), ((64, 3, 7), 51)]):
+        prompts = prompts_for(cfg, lengths, seed=200 + round_)
+        slots = [engine.open_slot() for _ in prompts]
+        entries = [StepEntry(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)]
+        entries.insert(1, StepEntry(keeper, long_prompt[fed:fed + share], [share - 1]))
+        logits = engine.step(entries)
+        assert logits.shape[0] == 4
+        rows = [0, 2, 3]
+        for row, p in zip(rows, prompts):
+            assert_close(logits[row], plain_model.forward(cfg, ref_w, p)[len(p) - 1], dtype, f"round {round_}, {len(p)} tokens")
+        assert_close(logits[1], want_long[fed + share - 1], dtype, f"round {round_}, the long prompt's share")
+        fed += share
+        other_slots = [plain_engine.open_slot() for _ in prompts]
+        other = plain_engine.step([StepEntry(s, p, [len(p) - 1]) for s, p in zip(other_slots, prompts)])
+        assert_close(logits[rows], other, dtype, f"round {round_}, against the engine without graphs")
+        for s in slots:
+            engine.close_slot(s)
+        for s in other_slots:
+            plain_engine.close_slot(s)
+    assert fed == 130
+    assert engine.stepper.graphs.replays == 3 and len(engine.stepper.graphs.shapes) == 1
+    engine.close_slot(keeper)
+    engine.cache.book.check()
+    assert engine.cache.live_slots == 0
