@@ -8,7 +8,7 @@ as the reference has none).
 ``generate`` prints one JSON line per output step (the list that ``Engine.generate`` yields)
 and a last line with tokens per second.  The reference engine is configured through
 environment variables; the one that applies here keeps its name and meaning:
-``DRYFT_GRAPH=on|off`` (capture the decode step in a CUDA graph), also ``--cuda-graph``.
+``DRYFT_GRAPH=on|off`` (capture the decode step, and short prompt steps, in CUDA graphs), also ``--cuda-graph``.
 """
 
 from __future__ import annotations
