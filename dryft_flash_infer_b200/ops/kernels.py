@@ -473,6 +473,11 @@ def pair_error(reset: bool = True) -> int:
 #: rows from which the pair kernel is used for the SwiGLU product (below, the library product + SwiGLU kernel is as fast or faster)
 PAIR_MIN_ROWS = 1024
 
+#: Which kernel takes a prompt's plain bfloat16 products (more than 64 rows): "library" (the default: the
+#: library's GEMM, as in the reference's prefill, which measured faster on these shapes) or "own" (the
+#: pair kernel for every one of them, so that the whole step runs on this package's kernels).
+PREFILL_GEMM = os.environ.get("DRYFT_PREFILL_GEMM", "library")
+
 
 class ScaledRows:
     """Rows ``w (.) r`` of an RMS norm that still lack their factor ``1 / rms(r)``: the product that
@@ -578,6 +583,9 @@ def linear(x, weight: torch.Tensor, out_dtype: torch.dtype | None = None, add_no
         return decode_linear(x, weight, out_dtype)
     if out_dtype is not None and out_dtype != x.dtype:
         return torch.mm(x, weight.t(), out_dtype=out_dtype)
+    if (PREFILL_GEMM == "own" and x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and x.is_contiguous()
+            and weight.is_contiguous()):
+        return pair_linear(x, weight)
     return torch.mm(x, weight.t())
 
 
@@ -590,6 +598,6 @@ def linear_swiglu(x, gate_up: torch.Tensor) -> torch.Tensor:
     if x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and x.is_contiguous():
         if x.shape[0] <= SKINNY_MAX_ROWS:
             return decode_linear(x, gate_up, swiglu=True)
-        if x.shape[0] >= PAIR_MIN_ROWS and gate_up.is_contiguous():
+        if (x.shape[0] >= PAIR_MIN_ROWS or PREFILL_GEMM == "own") and gate_up.is_contiguous():
             return pair_linear(x, gate_up, swiglu=True)          # prompts: the activation on the accumulator
     return swiglu(linear(x, gate_up))

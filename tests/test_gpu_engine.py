@@ -462,3 +462,29 @@ def test_short_prompt_steps_replayed_as_graphs(folders, name, dtype):
     engine.close_slot(keeper)
     engine.cache.book.check()
     assert engine.cache.live_slots == 0
+
+
+def test_prompts_with_every_product_on_our_own_kernels(tmp_path, monkeypatch):
+    """``DRYFT_PREFILL_GEMM=own``: a prompt's qkv, o, gate_up and down products all run on the pair kernel
+    (the library's product is the default only because it is faster on these shapes).  Same logits."""
+    from dryft_flash_infer_b200 import StepEntry
+    from dryft_flash_infer_b200.ops import kernels
+
+    weights = plain_model.random_weights(TINY_D, seed=5, matrix_std=0.05, norm_std=0.1)
+    folder = write_model(tmp_path, TINY_D, weights)
+    ref_w = reference_weights(weights, "bfloat16")
+    prompts = prompts_for(TINY_D, [300, 70, 129], seed=3)
+    monkeypatch.setattr(kernels, "PREFILL_GEMM", "own")
+    calls = []
+    real = kernels.pair_linear
+    monkeypatch.setattr(kernels, "pair_linear", lambda x, w, swiglu=False: (calls.append(swiglu), real(x, w, swiglu))[1])
+    engine = make_engine(folder, "bfloat16", max_tokens=64 * 12, cuda_graph=False)
+    slots = [engine.open_slot() for _ in prompts]
+    logits = engine.step([StepEntry(s, p, [0, len(p) - 1]) for s, p in zip(slots, prompts)])
+    layers = TINY_D["num_hidden_layers"]
+    assert calls.count(True) == layers and calls.count(False) == 3 * layers        # gate_up; qkv, o, down
+    assert kernels.pair_error() == 0
+    for i, p in enumerate(prompts):
+        want = plain_model.forward(TINY_D, ref_w, p)
+        assert_close(logits[2 * i], want[0], "bfloat16", f"prompt {i}, first place")
+        assert_close(logits[2 * i + 1], want[len(p) - 1], "bfloat16", f"prompt {i}, last place")
