@@ -1,7 +1,5 @@
 """The engine on a GPU against the plain implementation, in float32 and in bfloat16."""
 
-import math
-
 import pytest
 import torch
 

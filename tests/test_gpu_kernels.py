@@ -1,8 +1,6 @@
 """Each CUDA kernel alone against a plain float32 statement of the same operation,
 at sizes other than the engine's tiny models use."""
 
-import math
-
 import pytest
 import torch
 

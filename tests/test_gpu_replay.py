@@ -3,7 +3,6 @@ by one, and in batches of unequal lengths whose slots are used again, in both pr
 
 import json
 import subprocess
-import sys
 from pathlib import Path
 
 import numpy as np
