@@ -65,13 +65,14 @@ class PrefillGraphs:
         shape = shape_for(entries)
         if shape is None:
             return None
-        held = self.shapes.get(shape)
+        held = self.shapes.pop(shape, None)
         if held is None:
             if len(self.shapes) >= MAX_GRAPHS:
-                self.shapes.pop(next(iter(self.shapes)))
+                self.shapes.pop(next(iter(self.shapes)))        # the one whose last use is the longest ago
             rows, seqs, wanted = shape
             words = 3 * rows + 3 * seqs + (seqs + 1) + wanted + sum(seqs * w for w in self.widths) + 64
-            held = self.shapes[shape] = _Shape(words, self.model.device)
+            held = _Shape(words, self.model.device)
+        self.shapes[shape] = held                               # the dictionary keeps the order of last use
         ctx = StepContext(entries, self.cache, self.model.device, table_widths=self.widths, shape=shape,
                           into=held.buffer)
         held.uses += 1

@@ -486,3 +486,31 @@ def test_prompts_with_every_product_on_our_own_kernels(tmp_path, monkeypatch):
         want = plain_model.forward(TINY_D, ref_w, p)
         assert_close(logits[2 * i], want[0], "bfloat16", f"prompt {i}, first place")
         assert_close(logits[2 * i + 1], want[len(p) - 1], "bfloat16", f"prompt {i}, last place")
+
+
+def test_graphs_of_several_shapes_take_turns_and_the_oldest_goes(folders, monkeypatch):
+    """Shapes used in turn share one memory pool for their graphs, and only a few are kept: a shape that was
+    dropped starts again from its first use.  Every step still gives the plain implementation's logits."""
+    from dryft_flash_infer_b200 import StepEntry
+    from dryft_flash_infer_b200.engine import prefill
+
+    folder, cfg, weights = folders["B"]
+    ref_w = reference_weights(weights, "bfloat16")
+    monkeypatch.setattr(prefill, "MAX_GRAPHS", 2)
+    engine = make_engine(folder, "bfloat16", max_tokens=64 * 16)
+    graphs = engine.stepper.graphs
+    turns = [(70,), (140,), (70,), (140,), (70, 3), (140,), (70,), (70,), (70, 5), (70, 3)]
+    for turn, lengths in enumerate(turns):
+        prompts = prompts_for(cfg, lengths, seed=400 + turn)
+        slots = [engine.open_slot() for _ in prompts]
+        logits = engine.step([StepEntry(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)])
+        for row, p in enumerate(prompts):
+            assert_close(logits[row], plain_model.forward(cfg, ref_w, p)[len(p) - 1], "bfloat16", f"turn {turn}, {len(p)} tokens")
+        for s in slots:
+            engine.close_slot(s)
+        assert len(graphs.shapes) <= 2
+    # with room for two shapes, the one whose last use is the longest ago goes: (128, 2, 1) at turn 4,
+    # (128, 4, 2) at turn 6, (256, 2, 1) at turn 8; a shape that comes back starts from its first use.
+    # Replays (every use of a shape after its first since it came): turns 2, 3, 5, 7 and 9.
+    assert graphs.replays == 5
+    engine.cache.book.check()
