@@ -427,7 +427,7 @@ def test_short_prompt_steps_replayed_as_graphs(folders, name, dtype):
 
     folder, cfg, weights = folders[name]
     ref_w = reference_weights(weights, dtype)
-    engine = make_engine(folder, dtype, max_tokens=64 * 24)
+    engine = make_engine(folder, dtype, max_tokens=64 * 24, cuda_graph=True)
     assert engine.stepper.graphs is not None
     plain_engine = make_engine(folder, dtype, max_tokens=64 * 24, cuda_graph=False)
     assert plain_engine.stepper.graphs is None
@@ -497,7 +497,7 @@ def test_graphs_of_several_shapes_take_turns_and_the_oldest_goes(folders, monkey
     folder, cfg, weights = folders["B"]
     ref_w = reference_weights(weights, "bfloat16")
     monkeypatch.setattr(prefill, "MAX_GRAPHS", 2)
-    engine = make_engine(folder, "bfloat16", max_tokens=64 * 16)
+    engine = make_engine(folder, "bfloat16", max_tokens=64 * 16, cuda_graph=True)
     graphs = engine.stepper.graphs
     turns = [(70,), (140,), (70,), (140,), (70, 3), (140,), (70,), (70,), (70, 5), (70, 3)]
     for turn, lengths in enumerate(turns):
