@@ -5,8 +5,8 @@
 
 Prints one JSON line.  ``value`` is decoded tokens per second at batch 8 with every
 sequence at the benchmark context length (the last timed step ends there), timed on the
-device over K decode steps after W warm-up steps (each step launched before the tokens of the
-step before it are read, as generation does).  ``e2e`` is the same through
+device over K decode steps (default 256, the benchmark configuration's generated tokens) after W
+warm-up steps (each step launched before the tokens of the step before it are read, as generation does).  ``e2e`` is the same through
 ``Engine.generate`` with host token lists in and out.  ``prefill`` is one prompt of 2,048
 tokens; ``points`` are decode at batch 1 and 64; ``roofline`` compares the bytes a decode
 step has to read (every weight once, the live requests' cache) with the HBM peak.
@@ -206,7 +206,8 @@ def generation_run(shape: str) -> int:
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=64)
+    parser.add_argument("--steps", type=int, default=256,
+                        help="timed decode steps (default: the 256 generated tokens of the benchmark configuration)")
     parser.add_argument("--warmup", type=int, default=4)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--layers", type=int, default=QWEN3_4B["num_hidden_layers"],
