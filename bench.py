@@ -8,7 +8,8 @@ sequence at the benchmark context length (the last timed step ends there), timed
 device over K decode steps (default 256, the benchmark configuration's generated tokens) after W
 warm-up steps (each step launched before the tokens of the step before it are read, as generation does).  ``e2e`` is the same through
 ``Engine.generate`` with host token lists in and out.  ``prefill`` is one prompt of 2,048
-tokens; ``points`` are decode at batch 1 and 64; ``roofline`` compares the bytes a decode
+tokens; ``points`` are decode at batch 1 and 64 at that context, and at batch 1, 8 and 64 right after
+prompts of 512 tokens; ``roofline`` compares the bytes a decode
 step has to read (every weight once, the live requests' cache) with the HBM peak.
 """
 
@@ -40,6 +41,7 @@ QWEN3_14B = dict(QWEN3_4B, num_hidden_layers=40, hidden_size=5120, num_attention
 CONTEXT = 4096
 BATCH = 8
 PREFILL_TOKENS = 2048
+PROMPT_OF_POINTS = 512      # the prompts of the benchmark configuration's decode runs
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
 
@@ -317,6 +319,10 @@ def main() -> int:
     if not args.quick:
         for name, n in (("decode_b1", 1), ("decode_b64", 64)):
             point_ms, _ = time_decode(engine, n, CONTEXT, max(8, steps // 4), warmup)
+            points[name] = round(n / point_ms * 1e3, 1)
+        # the benchmark configuration's other reading: prompts of 512 tokens, then the generated tokens
+        for name, n in (("decode_b1_prompt512", 1), ("decode_b8_prompt512", BATCH), ("decode_b64_prompt512", 64)):
+            point_ms, _ = time_decode(engine, n, PROMPT_OF_POINTS + steps + warmup + 1, steps, warmup)
             points[name] = round(n / point_ms * 1e3, 1)
         # ---- end to end through Engine.generate: host token lists in, host token lists out
         prompts = [torch.randint(0, cfg["vocab_size"], (CONTEXT - steps - 1,), generator=g).tolist() for _ in range(BATCH)]
