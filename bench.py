@@ -302,6 +302,7 @@ def main() -> int:
         if i >= 2:
             times.append(a.elapsed_time(b))
     prefill_ms = statistics.median(times)
+    print("prefill runs (ms):", " ".join(f"{t:.2f}" for t in times), file=sys.stderr)
     flops = prefill_flops(cfg, args.layers, PREFILL_TOKENS)
     prefill = {"value": round(PREFILL_TOKENS / prefill_ms * 1e3, 1), "tokens": PREFILL_TOKENS, "ms": round(prefill_ms, 3),
                "frac": round(flops / (prefill_ms * 1e-3) / (peak["bf16_tflops"] * 1e12), 4)}
