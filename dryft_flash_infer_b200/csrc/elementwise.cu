@@ -267,8 +267,8 @@ __global__ void qk_norm_rope_write_kernel(T* __restrict__ qkv, int row_stride, i
 }
 
 // The same with eight lanes per head (four heads per warp) and eight neighbouring elements of each half
-// of a head per lane, for head sizes that are multiples of 16 up to 256: with many rows the kernel is
-// bound by the instructions around each load, so every lane takes a 16-byte load's worth of a head.
+// of a head per lane, for head sizes that are multiples of 16 up to 256: with many rows a warp mostly
+// waits for its loads, so every lane takes a 16-byte load's worth of a head (half the warps per row).
 constexpr int kWideSteps = 2;  // 8 lanes x 8 elements x 2 steps cover half a head of up to 128 (one step: up to 64)
 
 struct Oct { float v[8]; };
