@@ -205,6 +205,89 @@ def generation_run(shape: str) -> int:
     return 0
 
 
+def headline_config(layers: int) -> dict:
+    cfg = QWEN3_4B
+    return {"model": "Qwen3-4B sizes", "layers": layers, "layers_of_config": cfg["num_hidden_layers"],
+            "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+            "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
+            "global_batch": BATCH, "seq_len": CONTEXT, "prefill_tokens": PREFILL_TOKENS, "parallelism": "none",
+            "cuda_graph": True, "l2": "weights read per step (8 GB) exceed L2 (126 MB)"}
+
+
+def reference_run(steps: int, warmup: int, quick: bool) -> int:
+    """The reference arm: the unmodified reference engine (its ``engine/`` folder copied to
+    ``baseline/_ref/engine``) on the headline's decode step, through ``Engine(model_path).generate``.
+
+    This process only writes the model folder (Qwen3-4B sizes, random weights, this package's writer) and
+    starts ``baseline/reference_arm.py`` twice, in processes of their own because the reference reads its
+    settings from the environment at import: once with its stock settings (8-bit decode weights where
+    they win its warm-up race) and once with ``DRYFT_FP8=off`` (its pure bfloat16 engine)."""
+    import os
+    import tempfile
+
+    def unavailable(why: str) -> int:
+        print(json.dumps({"impl": "reference", "unavailable": why}))
+        return 0
+
+    arm = ROOT / "baseline" / "reference_arm.py"
+    if not (ROOT / "baseline" / "_ref" / "engine" / "engine.py").is_file():
+        return unavailable("no copy of the reference under baseline/_ref/engine (copy its engine/ folder there; "
+                           "pip cannot install it: it has neither setup.py nor pyproject.toml)")
+    try:
+        import torch
+        from dryft_flash_infer_b200.config import config_from_dict
+        from dryft_flash_infer_b200.weights import write_random_model
+
+        if not torch.cuda.is_available():
+            return unavailable("no CUDA device is visible")
+        with tempfile.TemporaryDirectory(prefix="dfi_reference_model_") as folder:
+            print("reference arm: writing a Qwen3-4B-sized random model folder", file=sys.stderr, flush=True)
+            write_random_model(config_from_dict(QWEN3_4B), 0, folder, torch.bfloat16, device="cuda:0")
+            torch.cuda.empty_cache()
+            results = {}
+            with ClockSampler() as clocks:
+                for name, env, extra in (("stock", {}, [] if quick else ["--points", "--prefill"]),
+                                         ("bf16", {"DRYFT_FP8": "off"}, [])):
+                    environment = {k: v for k, v in os.environ.items() if not k.startswith("DRYFT_")}
+                    environment.update(env)
+                    print(f"reference arm: running the reference with {env or 'its stock settings'}", file=sys.stderr,
+                          flush=True)
+                    done = subprocess.run([sys.executable, str(arm), "--model", folder, "--steps", str(steps),
+                                           "--warmup", str(warmup), *extra], env=environment, stdout=subprocess.PIPE,
+                                          text=True, timeout=1500)
+                    lines = [ln for ln in done.stdout.splitlines() if ln.startswith("{")]
+                    if done.returncode != 0 or not lines:
+                        results[name] = {"unavailable": f"the reference's process ended with code {done.returncode} "
+                                                        f"and no result line"}
+                    else:
+                        results[name] = json.loads(lines[-1])
+    except Exception as exc:                                   # noqa: BLE001 - the arm reports, it does not raise
+        return unavailable(f"{type(exc).__name__}: {exc}"[:400])
+    stock, bf16 = results["stock"], results["bf16"]
+    if "unavailable" in stock:
+        return unavailable(f"the reference raised on this image: {stock['unavailable']}; "
+                           f"its last lines: {' | '.join(stock.get('engine_lines', []))}"[:600])
+    path = "the reference's own engine" if stock.get("fast_path") and not stock.get("fell_back_to_native") \
+        else "NOT the reference's engine: it fell back to its native Transformers loop"
+    line = {
+        "metric": "decode tokens/s at batch 8 (Qwen3-4B sizes, bf16, random weights)",
+        "value": stock["value"], "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+        "ms_per_step": stock["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: random weights, random token ids", "impl": "reference",
+        "path": path, "weights_of_decode_products": stock.get("decode_projections"),
+        "config": headline_config(QWEN3_4B["num_hidden_layers"]),
+        "e2e": {"value": stock["e2e_value"], "unit": "tokens/s", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": BATCH * 8},
+        "bf16_weights": ({"value": bf16["value"], "ms_per_step": bf16["ms_per_step"], "e2e_value": bf16["e2e_value"],
+                          "fast_path": bf16.get("fast_path"), "settings": bf16.get("settings")}
+                         if "unavailable" not in bf16 else {"unavailable": bf16["unavailable"]}),
+        "points": stock.get("points", {}), "prefill": stock.get("prefill"),
+        "engine_lines": stock.get("engine_lines", [])[-6:], "clocks": clocks.summary(),
+    }
+    print(json.dumps(line))
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -224,13 +307,10 @@ def main() -> int:
     if args.gpus != 1:
         print(f"bench.py measures a single-GPU engine: --gpus {args.gpus} is not supported, run it with --gpus 1")
         return 2
-    if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "the reference is not an installable package (pip: neither setup.py nor pyproject.toml), "
-                          "and its engine loads a checkpoint through Transformers, which this box does not hold"}))
-        return 0
     warmup = max(3, args.warmup)
     steps = max(1, args.steps)
+    if args.impl == "reference":
+        return reference_run(steps, warmup, args.quick)
     if args.shape != "4b":
         return generation_run(args.shape)
 
@@ -336,8 +416,8 @@ def main() -> int:
         elapsed = time.perf_counter() - begin
         batch = next(iter(b for b in engine.decoder.batches.values() if b.n == BATCH))
         e2e = {"value": round(BATCH * produced / elapsed, 1), "unit": "tokens/s",
-               "h2d_bytes_per_step": int((batch.host.numel() - batch.first_refreshed) * 4),
-               "d2h_bytes_per_step": BATCH * 4}
+               "h2d_bytes_per_step": int(batch.h2d_bytes_per_step),
+               "d2h_bytes_per_step": BATCH * 4 + 32}
 
     line = {
         "metric": "decode tokens/s at batch 8 (Qwen3-4B sizes, bf16, random weights)",
@@ -345,11 +425,7 @@ def main() -> int:
         "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: random weights, random token ids, random cache content",
         "impl": "ours",
-        "config": {"model": "Qwen3-4B sizes", "layers": args.layers, "layers_of_config": QWEN3_4B["num_hidden_layers"],
-                   "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
-                   "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
-                   "global_batch": BATCH, "seq_len": CONTEXT, "prefill_tokens": PREFILL_TOKENS, "parallelism": "none",
-                   "cuda_graph": True, "l2": "weights read per step (8 GB) exceed L2 (126 MB)"},
+        "config": headline_config(args.layers),
         "prefill": prefill, "roofline": roofline, "points": points, "e2e": e2e,
         "gpu_launches": int(launches * steps), "clocks": clocks.summary(),
     }

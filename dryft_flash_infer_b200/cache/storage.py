@@ -12,7 +12,8 @@ at place ``p`` (or ``p % ring_tokens`` in a group with a window), i.e. in page
 ``table[place // page_size]`` at row ``place % page_size``.
 
 Beside the groups, every schedule entry whose mixer asks for it has a fixed-size
-float32 state per slot, ``[slots, *shape]``, zeroed when a slot is opened.
+state per slot, ``[slots, *shape]``, in the dtype the mixer names (float32 or bfloat16),
+set to the mixer's start value when a slot is opened.
 """
 
 from __future__ import annotations
@@ -25,6 +26,7 @@ from ..parts.base import KVNeed, StateNeed
 from .allocator import GroupPages, SlotBook
 
 PAGE_SIZE = 64
+_STATE_DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16}
 
 
 @dataclass
@@ -91,16 +93,20 @@ class SequenceCache:
             for position, cache_id in enumerate(ids):
                 self.group_of[cache_id] = (index, position)
         self.book = SlotBook(max_seqs, [g.pages for g in self.groups], max_context)
-        self.state: dict[int, torch.Tensor] = {
-            position: torch.zeros((max_seqs,) + tuple(need.shape), dtype=torch.float32, device=device)
-            for position, need in state_needs.items()
-        }
+        self.state: dict[int, torch.Tensor] = {}
+        self.state_init: dict[int, float] = {}
+        for position, need in state_needs.items():
+            if need.dtype not in _STATE_DTYPES:
+                raise ValueError(f"a state is held in one of {sorted(_STATE_DTYPES)}, not {need.dtype!r}")
+            self.state[position] = torch.full((max_seqs,) + tuple(need.shape), float(need.init),
+                                              dtype=_STATE_DTYPES[need.dtype], device=device)
+            self.state_init[position] = float(need.init)
 
     # ------------------------------------------------------------------ slots
     def open_slot(self) -> int:
         slot = self.book.open()
-        for area in self.state.values():
-            area[slot].zero_()
+        for position, area in self.state.items():
+            area[slot].fill_(self.state_init[position])        # a slot used again starts as a new one does
         return slot
 
     def close_slot(self, slot: int) -> None:
@@ -139,4 +145,4 @@ class SequenceCache:
 
     def bytes(self) -> int:
         return sum(g.k.numel() * g.k.element_size() * 2 for g in self.groups) + \
-            sum(a.numel() * 4 for a in self.state.values())
+            sum(a.numel() * a.element_size() for a in self.state.values())

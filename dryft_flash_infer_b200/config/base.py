@@ -25,6 +25,8 @@ class ModelConfig:
     """
 
     architecture: ClassVar[str] = ""
+    #: the checkpoint format's ``model_type`` key, written beside ``architectures`` by ``save``
+    model_type: ClassVar[str] = ""
 
     @classmethod
     def from_dict(cls, raw: dict[str, Any]) -> "ModelConfig":
@@ -32,6 +34,8 @@ class ModelConfig:
 
     def to_dict(self) -> dict[str, Any]:
         out = {"architectures": [self.architecture]}
+        if self.model_type:
+            out["model_type"] = self.model_type
         for f in fields(self):
             out[f.name] = getattr(self, f.name)
         return out

@@ -3,7 +3,7 @@
 The keys and their defaults follow what the reference engine reads from the
 checkpoint's configuration (engine/engine.py:223-234): ``head_dim`` defaults to
 ``hidden_size // num_attention_heads`` and is otherwise independent of them;
-``rope_theta`` defaults to 5e6.  The reference insists on tied embeddings
+``rope_theta`` must be given (as such, or under ``rope_parameters``).  The reference insists on tied embeddings
 (engine/engine.py:233-234); here both tied and untied heads are accepted.
 Features of the checkpoint format that the reference engine does not implement
 (rope scaling, sliding windows, attention biases, an activation other than SiLU)
@@ -16,6 +16,24 @@ from dataclasses import dataclass
 from typing import Any, ClassVar
 
 from .base import ConfigError, ModelConfig, take
+
+
+def _rope_theta(raw: dict[str, Any]) -> float:
+    """The rotation base: ``rope_theta``, or ``rope_parameters.rope_theta`` where a newer checkpoint keeps
+    it (whose ``rope_type`` must then be the default one).  A file with neither is refused: the reference
+    falls back to 5e6 only when the configuration object lacks the attribute (engine/engine.py:230), which
+    a file read through its library never does, so a guess here would rotate with a base nobody chose."""
+    parameters = raw.get("rope_parameters")
+    if isinstance(parameters, dict):
+        kind = parameters.get("rope_type", parameters.get("type", "default"))
+        if kind not in (None, "default"):
+            raise ConfigError(f"config.json: 'rope_parameters.rope_type' = {kind!r} is not supported for "
+                              f"Qwen3ForCausalLM (only the default rotation is)")
+        if raw.get("rope_theta") is None and parameters.get("rope_theta") is not None:
+            return take(parameters, "rope_theta", float)
+    if raw.get("rope_theta") is None:
+        raise ConfigError("config.json: missing key 'rope_theta' (and no 'rope_parameters.rope_theta')")
+    return take(raw, "rope_theta", float)
 
 
 @dataclass(frozen=True)
@@ -35,6 +53,7 @@ class Qwen3Config(ModelConfig):
     torch_dtype: str = "bfloat16"
 
     architecture: ClassVar[str] = "Qwen3ForCausalLM"
+    model_type: ClassVar[str] = "qwen3"
 
     @classmethod
     def from_dict(cls, raw: dict[str, Any]) -> "Qwen3Config":
@@ -51,13 +70,15 @@ class Qwen3Config(ModelConfig):
             num_key_value_heads=take(raw, "num_key_value_heads", int, heads),
             head_dim=take(raw, "head_dim", int, hidden // heads),
             rms_norm_eps=take(raw, "rms_norm_eps", float, 1e-6),
-            rope_theta=take(raw, "rope_theta", float, 5_000_000.0),
+            rope_theta=_rope_theta(raw),
             tie_word_embeddings=take(raw, "tie_word_embeddings", bool, False),
             max_position_embeddings=take(raw, "max_position_embeddings", int, 32768),
             hidden_act=take(raw, "hidden_act", str, "silu"),
             torch_dtype=take(raw, "torch_dtype", str, take(raw, "dtype", str, "bfloat16")),
         )
-        if raw.get("rope_scaling") not in (None, {}):
+        scaling = raw.get("rope_scaling")
+        if scaling not in (None, {}) and not (isinstance(scaling, dict) and
+                                              scaling.get("rope_type", scaling.get("type")) in (None, "default")):
             raise ConfigError("config.json: 'rope_scaling' is not supported for Qwen3ForCausalLM")
         if raw.get("use_sliding_window"):
             raise ConfigError("config.json: 'use_sliding_window' = true is not supported for Qwen3ForCausalLM")
@@ -75,8 +96,9 @@ class Qwen3Config(ModelConfig):
             raise ConfigError(
                 f"config.json: 'num_attention_heads' ({self.num_attention_heads}) must be a multiple of "
                 f"'num_key_value_heads' ({self.num_key_value_heads})")
-        if self.head_dim % 2:
-            raise ConfigError(f"config.json: 'head_dim' must be even for rotary embedding, got {self.head_dim}")
+        if self.head_dim % 16 or self.head_dim > 256:
+            raise ConfigError(f"config.json: 'head_dim' must be a multiple of 16 and at most 256 (the attention "
+                              f"kernels' head sizes), got {self.head_dim}")
         if self.hidden_act != "silu":
             raise ConfigError(f"config.json: 'hidden_act' must be 'silu', got {self.hidden_act!r}")
         if not (self.rms_norm_eps > 0 and self.rope_theta > 0):

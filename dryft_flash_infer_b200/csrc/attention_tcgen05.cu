@@ -653,15 +653,7 @@ attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __
 
 using namespace dfi;
 
-DFI_EXPORT int dfi_attention_prefill_tc_error(int reset) {
-    int value = 0;
-    if (cudaMemcpyFromSymbol(&value, g_tc_error, sizeof(int)) != cudaSuccess) return -1;
-    if (reset && value != 0) {
-        const int zero = 0;
-        cudaMemcpyToSymbol(g_tc_error, &zero, sizeof(int));
-    }
-    return value;
-}
+DFI_TCGEN05_STATUS_ENTRIES(attention_prefill_tc)
 
 #ifdef DFI_TRACE
 DFI_EXPORT int dfi_attention_prefill_trace(unsigned long long* host) {

@@ -27,6 +27,31 @@ __global__ void embedding_kernel(const T* __restrict__ table, const int* __restr
     }
 }
 
+// ------------------------------------------------------------------ a * scale + b, and the cap on logits
+// a[i] = a[i] * scale + (b ? b[i] : 0), in float32, in place: the factor some architectures put on the
+// embedded rows, and the residual sum of a model without a final norm.
+template <typename T>
+__global__ void scale_add_kernel(T* __restrict__ a, const T* __restrict__ b, long long n, float scale) {
+    pdl_launch_next();
+    pdl_wait();
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        float v = to_float(a[i]) * scale;
+        if (b != nullptr) v += to_float(b[i]);
+        a[i] = from_float<T>(v);
+    }
+}
+
+// x = x * scale, then (cap > 0) x = cap * tanh(x / cap), in place on float32 logits.
+__global__ void scale_cap_kernel(float* __restrict__ x, long long n, float scale, float cap) {
+    pdl_launch_next();
+    pdl_wait();
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        float v = x[i] * scale;
+        if (cap > 0.f) v = cap * tanhf(v / cap);
+        x[i] = v;
+    }
+}
+
 // ------------------------------------------------------------------ gather rows
 template <typename T, bool VEC>
 __global__ void gather_rows_kernel(const T* __restrict__ x, const int* __restrict__ rows, T* __restrict__ out, int dim) {
@@ -266,6 +291,65 @@ __global__ void qk_norm_rope_write_kernel(T* __restrict__ qkv, int row_stride, i
     }
 }
 
+// The same for a rotation of only the first R < D elements of a head (pairs i and i + R/2 for i < R/2;
+// the elements from R on are normalised but not rotated; cos/sin are [max_positions, R/2]).  One warp per
+// (row, head); a lane takes the elements lane, lane + 32, ... and finds each one's partner, which
+// another lane holds, in the warp's shared-memory copy of the normalised head.
+constexpr int kPartialWarps = 4;
+
+template <typename T>
+__global__ void qk_norm_rope_write_partial_kernel(T* __restrict__ qkv, int row_stride, int n_q, int n_kv, int D, int R,
+                                                  const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
+                                                  const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                                  const int* __restrict__ row_pos, const int* __restrict__ row_seq,
+                                                  T* __restrict__ k_cache, T* __restrict__ v_cache,
+                                                  const int* __restrict__ block_table, int table_width, int page_size,
+                                                  int ring_tokens, int write_cache) {
+    __shared__ float normed[kPartialWarps][64 * kMaxPairsPerLane];
+    pdl_launch_next();
+    pdl_wait();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int head = blockIdx.y * kPartialWarps + warp;
+    if (head >= n_q + 2 * n_kv) return;
+    const int row = blockIdx.x;
+    const bool is_q = head < n_q;
+    const bool is_k = !is_q && head < n_q + n_kv;
+    if (!is_q && !write_cache) return;
+    T* src = qkv + (size_t)row * row_stride + (size_t)head * D;
+    T* dst = src;
+    const int pos = row_pos[row];
+    if (!is_q) {
+        const int place = place_of(pos, ring_tokens);
+        const int page = block_table[(size_t)row_seq[row] * table_width + place / page_size];
+        const int kv_head = is_k ? head - n_q : head - n_q - n_kv;
+        dst = (is_k ? k_cache : v_cache) + (((size_t)page * n_kv + kv_head) * page_size + place % page_size) * D;
+    }
+    float ssq = 0.f;
+    for (int i = lane; i < D; i += 32) {
+        const float v = to_float(src[i]);
+        normed[warp][i] = v;
+        ssq += v * v;
+    }
+    const float* w = is_q ? q_w : (is_k ? k_w : nullptr);
+    if (w != nullptr) {
+        ssq = warp_sum(ssq);
+        const float scale = 1.0f / sqrtf(ssq / (float)D + eps);
+        for (int i = lane; i < D; i += 32) normed[warp][i] *= scale * w[i];
+    }
+    __syncwarp();
+    const bool rotate = (is_q || is_k) && cos_t != nullptr;
+    const int half = R >> 1;
+    for (int i = lane; i < D; i += 32) {
+        float v = normed[warp][i];
+        if (rotate && i < R) {
+            const int pair = i < half ? i : i - half;
+            const float c = cos_t[(size_t)pos * half + pair], sn = sin_t[(size_t)pos * half + pair];
+            v = i < half ? v * c - normed[warp][i + half] * sn : v * c + normed[warp][i - half] * sn;
+        }
+        dst[i] = from_float<T>(v);
+    }
+}
+
 // The same with eight lanes per head (four heads per warp) and eight neighbouring elements of each half
 // of a head per lane, for head sizes that are multiples of 16 up to 256: with many rows a warp mostly
 // waits for its loads, so every lane takes a 16-byte load's worth of a head (half the warps per row).
@@ -457,6 +541,25 @@ DFI_EXPORT int dfi_embedding(const void* table, const int* ids, void* out, int r
     return DFI_OK;
 }
 
+DFI_EXPORT int dfi_scale_add(void* a, const void* b, long long n, float scale, int dtype, void* stream) {
+    if (n <= 0) return DFI_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int blocks = (int)((n + 255) / 256 < 2048 ? (n + 255) / 256 : 2048);
+    if (dtype == DFI_DTYPE_F32) launch(scale_add_kernel<float>, blocks, 256, 0, st, (float*)a, (const float*)b, n, scale);
+    else if (dtype == DFI_DTYPE_BF16) launch(scale_add_kernel<bf16>, blocks, 256, 0, st, (bf16*)a, (const bf16*)b, n, scale);
+    else return DFI_ERR_DTYPE;
+    DFI_CHECK_LAUNCH();
+    return DFI_OK;
+}
+
+DFI_EXPORT int dfi_scale_cap(float* x, long long n, float scale, float cap, void* stream) {
+    if (n <= 0) return DFI_OK;
+    const int blocks = (int)((n + 255) / 256 < 2048 ? (n + 255) / 256 : 2048);
+    launch(scale_cap_kernel, blocks, 256, 0, (cudaStream_t)stream, x, n, scale, cap);
+    DFI_CHECK_LAUNCH();
+    return DFI_OK;
+}
+
 DFI_EXPORT int dfi_gather_rows(const void* x, const int* rows_idx, void* out, int rows, int dim, int dtype,
                                void* stream) {
     if (rows <= 0) return DFI_OK;
@@ -496,16 +599,33 @@ DFI_EXPORT int dfi_swiglu(const void* gate_up, void* out, int rows, int inter, i
 
 DFI_EXPORT int dfi_qk_norm_rope_write(void* qkv, int rows, int row_stride, int n_q, int n_kv, int head_dim,
                                       const float* q_w, const float* k_w, float eps, const float* cos_t,
-                                      const float* sin_t, const int* row_pos, const int* row_seq, void* k_cache,
-                                      void* v_cache, const int* block_table, int table_width, int page_size,
-                                      int ring_tokens, int write_cache, int dtype, void* stream) {
+                                      const float* sin_t, int rotary_dim, const int* row_pos, const int* row_seq,
+                                      void* k_cache, void* v_cache, const int* block_table, int table_width,
+                                      int page_size, int ring_tokens, int write_cache, int dtype, void* stream) {
     if (rows <= 0) return DFI_OK;
     if (head_dim <= 0 || head_dim % 4 || head_dim > 64 * kMaxPairsPerLane) return DFI_ERR_SHAPE;
     if (row_stride % 2) return DFI_ERR_ALIGN;
     if (n_q < 0 || n_kv < 0 || page_size <= 0 || table_width <= 0) return DFI_ERR_SHAPE;
+    if (cos_t != nullptr && (rotary_dim <= 0 || rotary_dim % 2 || rotary_dim > head_dim)) return DFI_ERR_SHAPE;
     cudaStream_t st = (cudaStream_t)stream;
     const int warps = 4;
     const int heads = n_q + 2 * n_kv;
+    if (cos_t != nullptr && rotary_dim != head_dim) {
+        // only part of each head rotates: the pairing differs from the kernels below
+        dim3 grid(rows, (heads + kPartialWarps - 1) / kPartialWarps);
+        if (grid.y > 65535) return DFI_ERR_LIMIT;
+        if (dtype == DFI_DTYPE_F32)
+            launch(qk_norm_rope_write_partial_kernel<float>, grid, kPartialWarps * 32, 0, st, (float*)qkv, row_stride, n_q,
+                   n_kv, head_dim, rotary_dim, q_w, k_w, eps, cos_t, sin_t, row_pos, row_seq, (float*)k_cache,
+                   (float*)v_cache, block_table, table_width, page_size, ring_tokens, write_cache);
+        else if (dtype == DFI_DTYPE_BF16)
+            launch(qk_norm_rope_write_partial_kernel<bf16>, grid, kPartialWarps * 32, 0, st, (bf16*)qkv, row_stride, n_q,
+                   n_kv, head_dim, rotary_dim, q_w, k_w, eps, cos_t, sin_t, row_pos, row_seq, (bf16*)k_cache,
+                   (bf16*)v_cache, block_table, table_width, page_size, ring_tokens, write_cache);
+        else return DFI_ERR_DTYPE;
+        DFI_CHECK_LAUNCH();
+        return DFI_OK;
+    }
     const bool wide = rows >= 64 && head_dim % 16 == 0 && head_dim <= 128 * kWideSteps && row_stride % 8 == 0 &&
                       aligned16(qkv) && aligned16(k_cache) && aligned16(v_cache) && aligned16(q_w) && aligned16(k_w) &&
                       aligned16(cos_t) && aligned16(sin_t);

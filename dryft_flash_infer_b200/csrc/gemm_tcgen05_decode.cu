@@ -678,15 +678,7 @@ DFI_EXPORT int dfi_gemm_decode_trace(unsigned long long* host_out) {
 }
 #endif
 
-DFI_EXPORT int dfi_gemm_decode_error(int reset) {
-    int value = 0;
-    if (cudaMemcpyFromSymbol(&value, g_tc_error, sizeof(int)) != cudaSuccess) return -1;
-    if (reset && value != 0) {
-        const int zero = 0;
-        cudaMemcpyToSymbol(g_tc_error, &zero, sizeof(int));
-    }
-    return value;
-}
+DFI_TCGEN05_STATUS_ENTRIES(gemm_decode)
 
 // Scratch: two parts of 128 x (padded batch) floats for each CTA, and the launch may use up to twice the
 // CTAs it was asked for; one counter per row block (zero

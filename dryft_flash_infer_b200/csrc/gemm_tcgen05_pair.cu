@@ -315,15 +315,7 @@ static int launch_pair(const void* x, const void* w, void* out, PairShape s, cud
 
 using namespace dfi;
 
-DFI_EXPORT int dfi_gemm_pair_error(int reset) {
-    int value = 0;
-    if (cudaMemcpyFromSymbol(&value, g_tc_error, sizeof(int)) != cudaSuccess) return -1;
-    if (reset && value != 0) {
-        const int zero = 0;
-        cudaMemcpyToSymbol(g_tc_error, &zero, sizeof(int));
-    }
-    return value;
-}
+DFI_TCGEN05_STATUS_ENTRIES(gemm_pair)
 
 // out[M, N] bfloat16 (row stride ldo) = x[M, K] . w[N, K]^T, or with swiglu: silu(x . gate^T) * (x . up^T)
 // for w = [gate; up] of 2N rows.  K a multiple of 8; x and w 16-byte aligned.

@@ -325,6 +325,8 @@ DFI_EXPORT int dfi_skinny_gemm(const void* x, const void* w, void* out, int M, i
 
 // ------------------------------------------------------------------ the allocation-free entry point
 // See skinny_gemm_static.h for who needs it and what it promises.
+#include <mutex>
+
 #include "skinny_gemm_static.h"
 
 namespace dfi {
@@ -343,6 +345,7 @@ struct StaticScratch {
 static __device__ __align__(256) StaticScratch g_static_scratch;
 
 static StaticScratch* g_static_ptr[kMaxDevices] = {};
+static std::mutex g_static_setup;          // first calls made by several host threads at once take turns
 
 }  // namespace dfi
 
@@ -366,20 +369,24 @@ int dfi_skinny_gemm_static(const void* x, const void* w, void* out, int M, int N
     int device = 0;
     if (cudaGetDevice(&device) != cudaSuccess) return DFI_ERR_LAUNCH;
     if (device < 0 || device >= kMaxDevices) return DFI_ERR_LIMIT;
-    if (g_static_ptr[device] == nullptr) {
-        // set-up, once per device, with that device current
-        StaticScratch* ptr = nullptr;
-        if (cudaGetSymbolAddress((void**)&ptr, g_static_scratch) != cudaSuccess || ptr == nullptr) {
-            cudaGetLastError();
-            return DFI_ERR_LAUNCH;
+    StaticScratch* scratch = nullptr;
+    {
+        // set-up, once per device, with that device current; threads that arrive together take turns
+        std::lock_guard<std::mutex> lock(g_static_setup);
+        if (g_static_ptr[device] == nullptr) {
+            StaticScratch* ptr = nullptr;
+            if (cudaGetSymbolAddress((void**)&ptr, g_static_scratch) != cudaSuccess || ptr == nullptr) {
+                cudaGetLastError();
+                return DFI_ERR_LAUNCH;
+            }
+            if (cudaMemsetAsync(ptr->counters, 0, sizeof(ptr->counters), (cudaStream_t)stream) != cudaSuccess) {
+                cudaGetLastError();
+                return DFI_ERR_LAUNCH;
+            }
+            g_static_ptr[device] = ptr;
         }
-        if (cudaMemsetAsync(ptr->counters, 0, sizeof(ptr->counters), (cudaStream_t)stream) != cudaSuccess) {
-            cudaGetLastError();
-            return DFI_ERR_LAUNCH;
-        }
-        g_static_ptr[device] = ptr;
+        scratch = g_static_ptr[device];
     }
-    StaticScratch* scratch = g_static_ptr[device];
     int n_ctas = dfi_sm_count();
     if (n_ctas <= 0) return DFI_ERR_LAUNCH;
     if (n_ctas > kStaticCtas) n_ctas = kStaticCtas;

@@ -26,7 +26,11 @@
 // First call on a device.  The first call made while a given device is current looks up
 // the array's device address (cudaGetSymbolAddress) and clears the counters with a
 // cudaMemsetAsync on the caller's stream.  Make that first call during set-up, before any
-// stream capture is begun on that stream.  Later calls on the device only launch.
+// stream capture is begun on that stream.  Later calls on the device only launch.  Host
+// threads that make their first calls at the same moment are taken one after the other
+// (a lock around the set-up); the clearing is ordered before the first product only on the
+// stream of the thread that did the set-up, so a second thread on another stream must
+// order its first call after that one, as it must anyway (see Sharing).
 //
 // Sharing.  All calls on a device use the same array, and it keeps what the last call left
 // in it.  The partial sums are overwritten before they are read; the counters are left at

@@ -17,8 +17,18 @@ constexpr uint32_t kSpinLimit = 1u << 22;     // tries of mbarrier.try_wait befo
 
 enum { MODE_NORMAL = 0, MODE_SWIGLU = 1, MODE_SWAP = 2, MODE_NN = 3 };
 
-// one error word per translation unit (each .cu that includes this header reads its own)
+// One error word per translation unit (each .cu that includes this header reads its own), and, if the
+// host has named one, a word in the host's own status buffer that receives the same code: the host
+// reads that buffer together with a step's results, so a wait that ran out is noticed without a
+// synchronisation of its own.
 static __device__ int g_tc_error = 0;
+static __device__ int* g_status_word = nullptr;
+
+__device__ __forceinline__ void record_error(int code) {
+    atomicCAS(&g_tc_error, 0, code);
+    int* word = g_status_word;
+    if (word != nullptr) atomicCAS(word, 0, code);
+}
 
 __device__ __forceinline__ uint32_t s32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -29,8 +39,8 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(s32(bar)), "r"(bytes) : "memory");
 }
 // Waits for the phase with the given parity to complete; false if the bound ran out.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int code) {
-    for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int code, uint32_t limit = kSpinLimit) {
+    for (uint32_t spin = 0; spin < limit; ++spin) {
         uint32_t done;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
@@ -39,7 +49,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int co
             : "=r"(done) : "r"(s32(bar)), "r"(parity) : "memory");
         if (done) return true;
     }
-    atomicCAS(&g_tc_error, 0, code);
+    record_error(code);
     return false;
 }
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
@@ -103,4 +113,50 @@ static inline bool make_tile_map(CUtensorMap* map, const void* base, int rows, i
                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+
+// What a kernel of this header does when a wait runs out, alone: one warp takes 32 columns of tensor
+// memory, waits `limit` tries on a barrier that nothing ever arrives on, records `code`, gives the
+// tensor memory back and returns.  It exists so that the path from the error word to the host's
+// exception can be tested without any other kernel failing.
+static __global__ void wait_selftest_kernel(uint32_t limit, int code) {
+    __shared__ __align__(8) uint64_t bar;
+    __shared__ uint32_t tmem_base_s;
+    if (threadIdx.x == 0) mbar_init(&bar, 1);
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(s32(&tmem_base_s)), "r"(32) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const uint32_t tmem_base = tmem_base_s;
+    if (threadIdx.x == 0) mbar_wait(&bar, 0, code, limit);
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(32) : "memory");
+}
+
 }  // namespace dfi
+
+// The three host entry points every translation unit of this header exports under its own name:
+//   dfi_<name>_error(reset)            the unit's error word (synchronises), optionally reset to 0
+//   dfi_<name>_set_status_word(ptr)    a device word of the host's that receives the codes too (or null)
+//   dfi_<name>_wait_selftest(limit, code, stream)   the self-test kernel above
+#define DFI_TCGEN05_STATUS_ENTRIES(name)                                                              \
+    DFI_EXPORT int dfi_##name##_error(int reset) {                                                    \
+        int value = 0;                                                                                \
+        if (cudaMemcpyFromSymbol(&value, dfi::g_tc_error, sizeof(int)) != cudaSuccess) return -1;     \
+        if (reset && value != 0) {                                                                    \
+            const int zero = 0;                                                                       \
+            cudaMemcpyToSymbol(dfi::g_tc_error, &zero, sizeof(int));                                  \
+        }                                                                                             \
+        return value;                                                                                 \
+    }                                                                                                 \
+    DFI_EXPORT int dfi_##name##_set_status_word(int* word) {                                          \
+        return cudaMemcpyToSymbol(dfi::g_status_word, &word, sizeof(int*)) == cudaSuccess ? DFI_OK    \
+                                                                                           : DFI_ERR_LAUNCH; \
+    }                                                                                                 \
+    DFI_EXPORT int dfi_##name##_wait_selftest(unsigned limit, int code, void* stream) {               \
+        dfi::wait_selftest_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(limit, code);                   \
+        DFI_CHECK_LAUNCH();                                                                           \
+        return DFI_OK;                                                                                \
+    }

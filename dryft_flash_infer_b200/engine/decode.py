@@ -52,15 +52,23 @@ class DecodeBatch:
         for name, size in sections.items():
             self.offsets[name] = total
             total += _pad4(size)
-        self.host = torch.zeros(total, dtype=torch.int32).pin_memory()
-        self.host_np = self.host.numpy()
+        # A step's numbers travel through pinned staging buffers used in turn: the copy to the device is
+        # asynchronous, and the next step (launched before this one's tokens are read) must not rewrite a
+        # buffer whose copy has not run yet.  Each buffer has an event recorded after its copy.
+        self.staging = [torch.zeros(total, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self.staging_np = [t.numpy() for t in self.staging]
+        self.tokens_staging = [torch.zeros(n, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self.staging_event: list[torch.cuda.Event | None] = [None, None]
         self.device_buffer = torch.zeros(total, dtype=torch.int32, device=device)
-        self.tokens_host = torch.zeros(n, dtype=torch.int32).pin_memory()
         # results come back through two pinned buffers in turn, so that the host can read one step's
-        # tokens while the next step is already running
+        # tokens while the next step is already running; the kernels' status words ride along
         self.result_host = [torch.zeros(n, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self.status_host = [torch.zeros(kernels.STATUS_WORDS, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self.status_device = kernels.status_words(device)
         self.result_event = [torch.cuda.Event() for _ in range(2)]
         self.launched = 0
+        #: float32 logits ``[n, vocab]`` of the step launched last (a fixed buffer once the graph exists)
+        self.logits: torch.Tensor | None = None
 
         def dev(name, size):
             return self.device_buffer[self.offsets[name]: self.offsets[name] + size]
@@ -70,12 +78,13 @@ class DecodeBatch:
         self.cu_rows, self.wanted_rows = dev("cu_rows", n + 1), dev("wanted_rows", n)
         self.uniforms = dev("uniforms", n).view(torch.float32)
         self.block_tables = [dev(f"table{g}", n * w).view(n, w) for g, w in enumerate(table_widths)]
-        h = self.host_np
-        h[self.offsets["row_seq"]: self.offsets["row_seq"] + n] = np.arange(n)
-        h[self.offsets["seq_qlen"]: self.offsets["seq_qlen"] + n] = 1
-        h[self.offsets["cu_rows"]: self.offsets["cu_rows"] + n + 1] = np.arange(n + 1)
-        h[self.offsets["wanted_rows"]: self.offsets["wanted_rows"] + n] = np.arange(n)
+        for h in self.staging_np:
+            h[self.offsets["row_seq"]: self.offsets["row_seq"] + n] = np.arange(n)
+            h[self.offsets["seq_qlen"]: self.offsets["seq_qlen"] + n] = 1
+            h[self.offsets["cu_rows"]: self.offsets["cu_rows"] + n + 1] = np.arange(n + 1)
+            h[self.offsets["wanted_rows"]: self.offsets["wanted_rows"] + n] = np.arange(n)
         self.first_refreshed = self.offsets["row_seq"]
+        self.h2d_bytes_per_step = (total - self.first_refreshed) * 4
         self.graph = None
         self.slots: list[int] = []
         self.starts: list[int] = []
@@ -83,14 +92,20 @@ class DecodeBatch:
         self.last_out: list[int] | None = None
 
     def _body(self) -> None:
-        logits = self.model.forward(self, self.cache)
+        logits = self.logits = self.model.forward(self, self.cache)
         if self.temperature == 0.0:
             kernels.argmax(logits, out=self.tokens)
         else:
             kernels.sample_temperature(logits, self.uniforms, self.temperature, out=self.tokens)
 
-    def _refresh(self, slots: list[int], uniforms) -> None:
-        n, h, off = self.n, self.host_np, self.offsets
+    def _refresh(self, slots: list[int], tokens: list[int] | None, uniforms) -> None:
+        turn = self.launched & 1
+        if self.staging_event[turn] is not None:
+            self.staging_event[turn].synchronize()          # the copy that last read this buffer has run
+        if tokens is not None:
+            self.tokens_staging[turn][:] = torch.tensor(tokens, dtype=torch.int32)
+            self.tokens.copy_(self.tokens_staging[turn], non_blocking=True)
+        n, h, off = self.n, self.staging_np[turn], self.offsets
         self.slots = slots
         self.starts = starts = [self.cache.length(s) for s in slots]
         h[off["row_pos"]: off["row_pos"] + n] = starts
@@ -102,7 +117,10 @@ class DecodeBatch:
             self.cache.fill_block_table(h[off[f"table{g}"]: off[f"table{g}"] + n * width].reshape(n, width),
                                         slots, g, width)
         first = self.first_refreshed
-        self.device_buffer[first:].copy_(self.host[first:], non_blocking=True)
+        self.device_buffer[first:].copy_(self.staging[turn][first:], non_blocking=True)
+        if self.staging_event[turn] is None:
+            self.staging_event[turn] = torch.cuda.Event()
+        self.staging_event[turn].record()
 
     def launch(self, slots: list[int], tokens: list[int] | None, uniforms=None) -> int:
         """Starts one decode step for ``slots`` and returns a ticket for ``fetch``.  ``tokens`` None
@@ -110,10 +128,7 @@ class DecodeBatch:
         book = self.cache.book
         for slot in slots:
             book.reserve(slot, 1)
-        if tokens is not None:
-            self.tokens_host[:] = torch.tensor(tokens, dtype=torch.int32)
-            self.tokens.copy_(self.tokens_host, non_blocking=True)
-        self._refresh(slots, uniforms)
+        self._refresh(slots, tokens, uniforms)
         if not self.use_graph:
             self._body()
         elif self.graph is None:
@@ -137,6 +152,7 @@ class DecodeBatch:
         ticket = self.launched
         self.launched += 1
         self.result_host[ticket & 1].copy_(self.tokens, non_blocking=True)
+        self.status_host[ticket & 1].copy_(self.status_device, non_blocking=True)
         self.result_event[ticket & 1].record()
         return ticket
 
@@ -146,6 +162,8 @@ class DecodeBatch:
         if ticket < self.launched - 2:
             raise RuntimeError("the result of this decode step has been overwritten by later steps")
         self.result_event[ticket & 1].synchronize()
+        # a bounded wait that ran out in one of the step's kernels: the tokens are not to be trusted
+        kernels.raise_for_status(self.status_host[ticket & 1].tolist(), self.model.device)
         return self.result_host[ticket & 1].tolist()
 
     def run(self, slots: list[int], tokens: list[int] | None, uniforms=None) -> list[int]:
@@ -188,6 +206,16 @@ class Decoder:
         ticket = batch.launch(list(slots), None if tokens is None else list(tokens), uniforms)
         self.last = (key, tuple(slots))
         return DecodeHandle(batch, ticket)
+
+    def step_logits(self, slots: list[int], tokens: list[int]) -> torch.Tensor:
+        """One decode step for ``slots`` fed ``tokens`` on the fixed buffers (and through the graph) that
+        generation uses, waited for; returns the step's float32 logits ``[len(slots), vocab]``, which stay
+        valid until the next step of this batch size.  The tokens the sampler chose are thrown away."""
+        key, batch = self._batch_for(len(slots), SamplingParams())
+        batch.fetch(batch.launch(list(slots), list(tokens)))
+        self.last = None                  # the next decode step is fed from the host again
+        batch.last_out = None
+        return batch.logits
 
     def decode(self, slots: list[int], tokens: list[int], requests: list[int], step_index: int,
                params: SamplingParams) -> list[int]:

@@ -19,6 +19,7 @@ import torch
 from .. import models  # noqa: F401  (registers the architectures)
 from ..cache import PAGE_SIZE, SequenceCache
 from ..config import ModelConfig, architecture_named, config_from_dict, load_config
+from ..ops import kernels
 from ..sampling import SamplingParams, select_tokens
 from ..weights import fill_random, load_weights
 from .context import StepEntry
@@ -111,8 +112,8 @@ class Engine:
         if max_context > self._positions_ready:
             self.model.prepare(max_context)
             self._positions_ready = max_context
-        self.stepper = Stepper(self.model, self.cache, self.options.step_tokens, self.options.cuda_graph)
         self.decoder = Decoder(self.model, self.cache, self.options.cuda_graph)
+        self.stepper = Stepper(self.model, self.cache, self.options.step_tokens, self.options.cuda_graph, self.decoder)
 
     def _ensure_room(self, lengths: list[int]) -> None:
         """Makes the cache fit a batch whose sequences reach ``lengths`` tokens."""
@@ -158,7 +159,15 @@ class Engine:
         return self.decoder.decode_launch(slots, tokens, requests, step_index, params)
 
     def select(self, logits, requests: list[int], step_index: int, params: SamplingParams) -> list[int]:
-        return select_tokens(logits, params, requests, step_index).tolist()
+        chosen = select_tokens(logits, params, requests, step_index).tolist()
+        self.check_status()               # the tokens are on the host: so is anything the step's kernels recorded
+        return chosen
+
+    def check_status(self) -> None:
+        """Raises ``KernelError`` if a bounded wait ran out in a kernel launched since the last check (the
+        results computed since are then not valid).  It synchronises; ``select`` and the decode steps'
+        ``result()`` check for themselves, a caller of ``step`` alone calls it once its logits are on the host."""
+        kernels.check_status(self.device)
 
     # ------------------------------------------------------------------ generation
     def generate(self, input_ids: list[list[int]], max_new_tokens: int, *, temperature: float = 0.0, seed: int = 0,

@@ -37,9 +37,8 @@ class DecoderModel:
             self.blocks.append(block_class(
                 build_part("mixer", layer.mixer, spec.hidden_size),
                 build_part("feed_forward", layer.feed_forward, spec.hidden_size),
-                build_part("norm", layer.mixer_norm, spec.hidden_size),
-                build_part("norm", layer.ffn_norm, spec.hidden_size)))
-        self.final_norm = build_part("norm", spec.final_norm, spec.hidden_size)
+                {name: build_part("norm", norm, spec.hidden_size) for name, norm in layer.norms.items()}))
+        self.final_norm = build_part("norm", spec.final_norm, spec.hidden_size) if spec.final_norm is not None else None
         self.embedding = None   # [vocab, hidden]
         self.head = None        # [vocab, hidden]; the embedding itself when tied
         self.dtype = None
@@ -58,8 +57,9 @@ class DecoderModel:
                     if key not in layer.tensor_names:
                         raise ValueError(f"the architecture gives no file name for tensor '{key}'")
                     out.append(ExpectedTensor(layer.tensor_names[key], decl, part))
-        for local, decl in self.final_norm.tensors().items():
-            out.append(ExpectedTensor(spec.final_norm_names[local], decl, self.final_norm))
+        if self.final_norm is not None:
+            for local, decl in self.final_norm.tensors().items():
+                out.append(ExpectedTensor(spec.final_norm_names[local], decl, self.final_norm))
         if spec.head_name is not None:
             out.append(ExpectedTensor(spec.head_name, TensorDecl((spec.vocab_size, spec.hidden_size), "head"), self))
         names = [t.name for t in out]
@@ -71,7 +71,8 @@ class DecoderModel:
         parts: list[Part] = []
         for block in self.blocks:
             parts.extend(block.parts().values())
-        parts.append(self.final_norm)
+        if self.final_norm is not None:
+            parts.append(self.final_norm)
         return parts
 
     @property
@@ -141,7 +142,8 @@ class DecoderModel:
             return self._forward(ctx, cache)
 
     def _forward(self, ctx, cache) -> torch.Tensor | None:
-        residual = kernels.embedding(self.embedding, ctx.tokens)
+        spec = self.spec
+        residual = kernels.embedding(self.embedding, ctx.tokens, scale=spec.embedding_scale)
         pending = None
         schedule = self.spec.schedule
         for position, entry in enumerate(schedule):
@@ -153,18 +155,28 @@ class DecoderModel:
                 # the norm that reads this block's result, if its reader takes rows that lack their factor
                 if position + 1 < len(schedule):
                     follower = self.blocks[schedule[position + 1].layer]
-                    next_norm = follower.mixer_norm if follower.takes_scaled_pending else None
+                    next_norm = follower.first_norm if follower.takes_scaled_pending else None
                 else:
-                    next_norm = self.final_norm if ctx.wants_every_row and ctx.n_wanted > 0 else None
+                    next_norm = self.final_norm if ctx.wants_every_row and ctx.n_wanted > 0 \
+                        and self.final_norm is not None else None
                 residual, pending = block.forward(residual, pending, ctx, view, state, next_norm=next_norm)
             else:
                 residual, pending = block.forward(residual, pending, ctx, view, state)
         if ctx.n_wanted == 0:
             return None
         if isinstance(pending, kernels.ScaledRows):
-            return kernels.linear(pending, self.head, out_dtype=torch.float32)
+            return self._logits(pending)
         if not ctx.wants_every_row:
             residual = kernels.gather_rows(residual, ctx.wanted_rows)
             pending = kernels.gather_rows(pending, ctx.wanted_rows) if pending is not None else None
+        if self.final_norm is None:
+            return self._logits(residual if pending is None else kernels.add_rows(residual, pending))
         normed = self.final_norm.forward(residual) if pending is None else self.final_norm.add_forward(residual, pending)
-        return kernels.linear(normed, self.head, out_dtype=torch.float32)
+        return self._logits(normed)
+
+    def _logits(self, rows) -> torch.Tensor:
+        """The output head, float32, with the architecture's factor and cap on the logits if it has them."""
+        logits = kernels.linear(rows, self.head, out_dtype=torch.float32)
+        if self.spec.logit_scale != 1.0 or self.spec.logit_softcap != 0.0:
+            kernels.transform_logits(logits, self.spec.logit_scale, self.spec.logit_softcap)
+        return logits

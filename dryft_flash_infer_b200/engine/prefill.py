@@ -2,8 +2,8 @@
 
 A step of a few hundred tokens launches some three hundred kernels whose work on the
 device takes less time than the host needs to launch them.  Such steps are laid out at
-one of a few fixed shapes (rows in multiples of 128, sequences and wanted places in powers
-of two; see ``StepContext``'s ``shape``), so that every step of a shape runs on the same
+one of a few fixed shapes (16, 32 or 64 rows or a multiple of 128, sequences and wanted places
+in powers of two; see ``StepContext``'s ``shape``), so that every step of a shape runs on the same
 buffers, and the kernels of a shape are captured once and replayed.  What lies past a
 step's own rows is computed and thrown away: it reaches no live page of the cache and no
 other row, so it changes no result.  Steps that fit no shape (more than ``MAX_ROWS`` rows,
@@ -17,6 +17,7 @@ import torch
 from .context import StepContext, StepEntry
 
 ROW_UNIT = 128
+SMALL_ROWS = 64        # the most rows the decode products take
 MAX_ROWS = 1024
 MAX_SEQS = 64          # of a shape, the spare one included
 MAX_WANTED = 64
@@ -38,7 +39,10 @@ def shape_for(entries: list[StepEntry]) -> tuple[int, int, int] | None:
         return None
     if all(len(e.tokens) == 1 for e in entries):
         return None            # decode steps have fixed buffers of their own
-    return (-(-rows // ROW_UNIT) * ROW_UNIT, _power_of_two(len(entries) + 1), _power_of_two(wanted))
+    # up to 64 rows the products run the decode kernels (which read the weights at a higher rate than the
+    # library's 128-row tiles): such steps are padded to 16, 32 or 64 rows, not to 128
+    padded = max(16, _power_of_two(rows)) if rows <= SMALL_ROWS else -(-rows // ROW_UNIT) * ROW_UNIT
+    return (padded, _power_of_two(len(entries) + 1), _power_of_two(wanted))
 
 
 class _Shape:

@@ -23,9 +23,12 @@ class Stepper:
     shares are cut into passes here, which changes no result.
     """
 
-    def __init__(self, model, cache: SequenceCache, step_tokens: int, use_graph: bool = False):
+    def __init__(self, model, cache: SequenceCache, step_tokens: int, use_graph: bool = False, decoder=None):
         self.model, self.cache = model, cache
         self.step_tokens = step_tokens
+        # with graphs on, a step of one token per sequence runs where generation's decode steps run: on
+        # the decoder's fixed buffers, through its CUDA graph
+        self.decoder = decoder if decoder is not None and decoder.use_graph else None
         # short prompt steps run as CUDA graphs at a few fixed shapes, if every mixer can be captured
         self.graphs = PrefillGraphs(model, cache) if use_graph and model.graph_safe else None
         self.has_ring = any(g.ring_tokens for g in cache.groups)
@@ -45,6 +48,8 @@ class Stepper:
                 if not 0 <= t < vocab:
                     raise ValueError(f"token id {t} is outside the vocabulary of {vocab}")
         longest = max(len(e.tokens) for e in entries)
+        if longest == 1 and self.decoder is not None:
+            return self._decode_pass(entries)
         if not self.has_ring or longest <= self.step_tokens:
             return self._pass(entries)
         # cut long shares into passes of at most step_tokens per sequence
@@ -69,6 +74,18 @@ class Stepper:
         logits = torch.cat(pieces)
         rank = sorted(range(len(order)), key=lambda i: order[i])
         return logits[torch.tensor(rank, device=logits.device)]
+
+    def _decode_pass(self, entries: list[StepEntry]):
+        for e in entries:
+            if any(w != 0 for w in e.want):
+                raise ValueError(f"wanted place {e.want} is outside the 1 token given for slot {e.slot}")
+        logits = self.decoder.step_logits([e.slot for e in entries], [e.tokens[0] for e in entries])
+        rows = [i for i, e in enumerate(entries) for _ in e.want]
+        if not rows:
+            return None
+        if rows == list(range(len(entries))):
+            return logits.clone()
+        return logits[torch.tensor(rows, device=logits.device)]
 
     def _pass(self, entries: list[StepEntry]):
         for e in entries:

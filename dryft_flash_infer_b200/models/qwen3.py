@@ -42,7 +42,7 @@ def build_qwen3(config: Qwen3Config) -> ModelSpec:
             "feed_forward.up_proj": p + "mlp.up_proj.weight",
             "feed_forward.down_proj": p + "mlp.down_proj.weight",
         }
-        layers.append(LayerSpec("pre_norm", mixer, feed_forward, norm, norm, names))
+        layers.append(LayerSpec("pre_norm", mixer, feed_forward, {"mixer_norm": norm, "ffn_norm": norm}, names))
     return ModelSpec(
         architecture=config.architecture,
         vocab_size=config.vocab_size,
@@ -54,6 +54,8 @@ def build_qwen3(config: Qwen3Config) -> ModelSpec:
         embedding_name="model.embed_tokens.weight",
         final_norm_names={"weight": "model.norm.weight"},
         head_name=None if config.tie_word_embeddings else "lm_head.weight",
+        # a tied model's file may still carry a copy of the head: it is the embedding, so it is skipped
+        ignorable_tensors=("lm_head.weight",) if config.tie_word_embeddings else (),
     )
 
 

@@ -30,7 +30,7 @@ ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
 
 #: sources of the core library; further modules (built per head size) name their own
-CORE_SOURCES = ["elementwise.cu", "attention_generic.cu", "sampling.cu", "skinny_gemm.cu", "gemm_tcgen05.cu", "gemm_tcgen05_decode.cu", "gemm_tcgen05_pair.cu"]
+CORE_SOURCES = ["elementwise.cu", "attention_generic.cu", "sampling.cu", "skinny_gemm.cu", "gemm_simt.cu", "gemm_tcgen05_decode.cu", "gemm_tcgen05_pair.cu"]
 #: the tensor-core attention, built once per head size (-DDFI_HEAD_DIM=...)
 ATTENTION_SOURCES = ["attention_mma.cu", "attention_tcgen05.cu"]
 #: head sizes compiled ahead by ``all_libraries`` (others compile at first use)

@@ -51,8 +51,77 @@ def set_pdl(enabled: bool) -> None:
     _PDL_APPLIED.clear()
 
 
+#: The tcgen05 kernels bound every wait on an mbarrier; a wait that runs out records a code, the CTA
+#: frees its tensor memory and returns, and the step's numbers are not valid.  Each device has one
+#: small int32 buffer that receives these codes (one word per kernel family), so that the host can
+#: read it with a step's results instead of synchronising for it.
+STATUS_WORDS = 8
+_STATUS_UNITS = {"gemm_decode": 0, "gemm_pair": 1, "attention_prefill_tc": 2}
+_STATUS: dict[int, torch.Tensor] = {}
+_STATUS_BOUND: set = set()
+_STATUS_LIBRARIES: list = []          # (library, units) of every library that was handed a status word
+
+
+def status_words(device=None) -> torch.Tensor:
+    """The int32 status buffer of ``device`` (default: the current one); all zero while nothing failed."""
+    index = torch.cuda.current_device() if device is None else torch.device(device).index or 0
+    held = _STATUS.get(index)
+    if held is None:
+        held = _STATUS[index] = torch.zeros(STATUS_WORDS, dtype=torch.int32, device=f"cuda:{index}")
+    return held
+
+
+def _bind_status(lib, units: tuple[str, ...]):
+    """Tells ``lib``'s kernels (on the current device) which words of the status buffer are theirs."""
+    index = torch.cuda.current_device()
+    if (id(lib), index) not in _STATUS_BOUND:
+        words = status_words(index)
+        for unit in units:
+            rc = getattr(lib, f"dfi_{unit}_set_status_word")(ctypes.c_void_p(words.data_ptr() + 4 * _STATUS_UNITS[unit]))
+            if rc != 0:
+                raise KernelError(f"could not hand the status word to {unit}")
+        _STATUS_BOUND.add((id(lib), index))
+        if not any(held is lib for held, _ in _STATUS_LIBRARIES):
+            _STATUS_LIBRARIES.append((lib, units))
+    return lib
+
+
+def raise_for_status(values, device=None) -> None:
+    """``values``: a host copy of ``status_words``.  If any word is set, clears the words and every
+    stream-K counter of the device (a kernel that gave up may have left tickets behind) and raises."""
+    values = [int(v) for v in values]
+    if not any(values):
+        return
+    if torch.cuda.is_available():
+        index = torch.cuda.current_device() if device is None else torch.device(device).index or 0
+        torch.cuda.synchronize(index)
+        status_words(index).zero_()
+        for lib, units in _STATUS_LIBRARIES:
+            for unit in units:
+                getattr(lib, f"dfi_{unit}_error")(1)
+        for table in (_ATTENTION_SCRATCH, _DECODE_SCRATCH, _GEMM_SCRATCH):
+            for device_key, held in table.items():
+                if torch.device(device_key).index == index:
+                    held[1].zero_()
+    names = {v: k for k, v in _STATUS_UNITS.items()}
+    failed = ", ".join(f"{names.get(i, f'word {i}')} (wait code {v})" for i, v in enumerate(values) if v)
+    raise KernelError(f"a bounded wait ran out in a tcgen05 kernel: {failed}; the results of the step are not valid")
+
+
+def check_status(device=None) -> None:
+    """Reads the status buffer (this synchronises) and raises ``KernelError`` if a wait ran out."""
+    raise_for_status(status_words(device).tolist(), device)
+
+
+def wait_selftest(unit: str, limit: int = 1, code: int = 77, head_dim: int = 128) -> None:
+    """Launches ``unit``'s one-CTA self-test kernel: it waits ``limit`` tries on a barrier that nothing
+    arrives on, records ``code`` as a real kernel's wait would, frees its tensor memory and returns."""
+    lib = _attention_library(head_dim) if unit == "attention_prefill_tc" else _core()
+    _check(getattr(lib, f"dfi_{unit}_wait_selftest")(ctypes.c_uint(limit), int(code), _stream()), f"{unit} self-test")
+
+
 def _core():
-    return _with_pdl(load_library("dfi_core", CORE_SOURCES), "dfi_set_pdl")
+    return _bind_status(_with_pdl(load_library("dfi_core", CORE_SOURCES), "dfi_set_pdl"), ("gemm_decode", "gemm_pair"))
 
 
 def _code(t: torch.Tensor) -> int:
@@ -113,15 +182,40 @@ def _f(x: float):
     return ctypes.c_float(x)
 
 
-def embedding(table: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
-    """``table[ids]`` for int32 ``ids [rows]``."""
+def embedding(table: torch.Tensor, ids: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    """``table[ids] * scale`` for int32 ``ids [rows]``."""
     _need_cuda(table, ids)
     assert ids.dtype == torch.int32 and table.is_contiguous()
     rows, (vocab, hidden) = ids.numel(), table.shape
     out = torch.empty((rows, hidden), dtype=table.dtype, device=table.device)
     _check(_core().dfi_embedding(_ptr(table), _ptr(ids), _ptr(out), rows, hidden, vocab, _code(table), _stream()),
            "embedding")
+    if scale != 1.0:
+        scale_add(out, None, scale)
     return out
+
+
+def scale_add(a: torch.Tensor, b: torch.Tensor | None, scale: float = 1.0) -> torch.Tensor:
+    """``a = a * scale + b`` in place (float32 arithmetic, one rounding); ``b`` may be None."""
+    _need_cuda(a, b)
+    assert a.is_contiguous() and (b is None or (b.is_contiguous() and b.shape == a.shape and b.dtype == a.dtype))
+    _check(_core().dfi_scale_add(_ptr(a), _ptr(b), ctypes.c_longlong(a.numel()), _f(scale), _code(a), _stream()),
+           "scale_add")
+    return a
+
+
+def add_rows(residual: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
+    """``residual += delta`` in place: the residual sum where no norm follows it."""
+    return scale_add(residual, delta, 1.0)
+
+
+def transform_logits(logits: torch.Tensor, scale: float = 1.0, softcap: float = 0.0) -> torch.Tensor:
+    """``logits * scale`` and then, with ``softcap`` c > 0, ``c * tanh(x / c)``: in place, float32."""
+    _need_cuda(logits)
+    assert logits.dtype == torch.float32 and logits.is_contiguous()
+    _check(_core().dfi_scale_cap(_ptr(logits), ctypes.c_longlong(logits.numel()), _f(scale), _f(softcap), _stream()),
+           "transform_logits")
+    return logits
 
 
 def gather_rows(x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
@@ -170,7 +264,8 @@ def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
 
 def qk_norm_rope_write(qkv: torch.Tensor, n_q: int, n_kv: int, head_dim: int, q_weight, k_weight, eps: float,
                        cos, sin, row_pos: torch.Tensor, row_seq: torch.Tensor, cache) -> torch.Tensor:
-    """Per-head RMSNorm (if weights are given) and rotation (if tables are given) of the
+    """Per-head RMSNorm (if weights are given) and rotation (if tables are given: ``cos``/``sin
+    [positions, rotary_dim / 2]`` rotate the first ``rotary_dim <= head_dim`` elements of a head) of the
     query and key heads of ``qkv [rows, (n_q + 2 n_kv) * head_dim]``; queries are
     rewritten in place, keys and values go to ``cache`` (a ``LayerCache``) at each row's
     position unless ``cache.writes`` is false.  Returns the query view ``[rows, n_q * head_dim]``.
@@ -185,11 +280,16 @@ def qk_norm_rope_write(qkv: torch.Tensor, n_q: int, n_kv: int, head_dim: int, q_
         raise KernelError(f"qk_norm_rope_write: head_dim {head_dim} must be a multiple of 4 and at most 256")
     for w in (q_weight, k_weight):
         assert w is None or (w.dtype == torch.float32 and w.numel() == head_dim)
+    rotary_dim = head_dim
     if cos is not None:
-        assert cos.dtype == torch.float32 and sin.dtype == torch.float32 and cos.shape[1] == head_dim // 2
+        assert cos.dtype == torch.float32 and sin.dtype == torch.float32 and cos.shape == sin.shape
+        assert cos.is_contiguous() and sin.is_contiguous()
+        rotary_dim = 2 * cos.shape[1]
+        if rotary_dim > head_dim:
+            raise KernelError(f"qk_norm_rope_write: tables for {rotary_dim} rotating elements, heads of {head_dim}")
     _check(_core().dfi_qk_norm_rope_write(
         _ptr(qkv), rows, width, n_q, n_kv, head_dim, _ptr(q_weight), _ptr(k_weight), _f(eps), _ptr(cos), _ptr(sin),
-        _ptr(row_pos), _ptr(row_seq), _ptr(cache.k), _ptr(cache.v), _ptr(cache.block_table),
+        rotary_dim, _ptr(row_pos), _ptr(row_seq), _ptr(cache.k), _ptr(cache.v), _ptr(cache.block_table),
         cache.block_table.shape[1], cache.page_size, cache.ring_tokens, 1 if cache.writes else 0, _code(qkv),
         _stream()), "qk_norm_rope_write", f"head_dim {head_dim}")
     return qkv[:, : n_q * head_dim]
@@ -217,8 +317,27 @@ def attention_generic(q: torch.Tensor, cache, row_seq: torch.Tensor, row_pos: to
 
 
 def _attention_library(head_dim: int):
-    return _with_pdl(load_library(f"dfi_attention_d{head_dim}", ATTENTION_SOURCES, [f"-DDFI_HEAD_DIM={head_dim}"]),
-                     "dfi_attention_set_pdl")
+    return _bind_status(_with_pdl(load_library(f"dfi_attention_d{head_dim}", ATTENTION_SOURCES,
+                                               [f"-DDFI_HEAD_DIM={head_dim}"]), "dfi_attention_set_pdl"),
+                        ("attention_prefill_tc",))
+
+
+_RETIRED_SCRATCH: list = []
+
+
+def _scratch(table: dict, device, floats: int, counters: int):
+    """The scratch of one kernel family on ``device``: room for partial sums and zeroed counters, made
+    once at the size its first caller asks for (the engine always asks for the same: one wave of CTAs,
+    65,536 counters).  A later call that needs more gets a new one; the old one is kept for good, because
+    CUDA graphs captured earlier still name its address."""
+    held = table.get(device)
+    if held is None or held[0].numel() < floats or held[1].numel() < counters:
+        if held is not None:
+            _RETIRED_SCRATCH.append(held)
+        held = (torch.empty(max(floats, held[0].numel() if held else 0), dtype=torch.float32, device=device),
+                torch.zeros(max(counters, 65536, held[1].numel() if held else 0), dtype=torch.int32, device=device))
+        table[device] = held
+    return held
 
 
 DECODE_ATTENTION_MAX_SEQS = 1024
@@ -271,11 +390,11 @@ class TokenPrep:
         self.qkv, self.q_weight, self.k_weight, self.eps, self.cos, self.sin = qkv, q_weight, k_weight, eps, cos, sin
 
 
-def decode_prepares_tokens(qkv: torch.Tensor, ctx, n_q: int, n_kv: int, head_dim: int) -> bool:
+def decode_prepares_tokens(qkv: torch.Tensor, ctx, n_q: int, n_kv: int, head_dim: int, cos=None) -> bool:
     """True if ``attention_decode`` can take this step's raw projection (``prep=``) instead of queries
     prepared by ``qk_norm_rope_write``: a bfloat16 step of one token per sequence with a head size that
-    is a power of two."""
-    return (qkv.is_cuda and qkv.dtype == torch.bfloat16 and ctx.all_decode and head_dim in (16, 32, 64, 128)
+    is a power of two, whose rotation (if any) takes the whole head."""
+    return (qkv.is_cuda and (cos is None or 2 * cos.shape[1] == head_dim) and qkv.dtype == torch.bfloat16 and ctx.all_decode and head_dim in (16, 32, 64, 128)
             and n_q // n_kv <= 16 and ctx.n_seqs <= DECODE_ATTENTION_MAX_SEQS and qkv.stride(1) == 1
             and qkv.stride(0) % 4 == 0 and bool(_attention_library(head_dim).dfi_attention_decode_prepares()))
 
@@ -302,11 +421,7 @@ def attention_decode(q, cache, ctx, n_q: int, n_kv: int, head_dim: int, scale: f
     n_ctas = min(n_ctas, 4096)
     lib.dfi_attention_decode_scratch_floats.restype = ctypes.c_longlong
     floats, n_counters = lib.dfi_attention_decode_scratch_floats(n_ctas), ctx.n_seqs * n_kv
-    held = _ATTENTION_SCRATCH.get(q.device)
-    if held is None or held[0].numel() < floats or held[1].numel() < n_counters:
-        held = (torch.empty(max(floats, held[0].numel() if held else 0), dtype=torch.float32, device=q.device),
-                torch.zeros(max(n_counters, 8192, held[1].numel() if held else 0), dtype=torch.int32, device=q.device))
-        _ATTENTION_SCRATCH[q.device] = held
+    held = _scratch(_ATTENTION_SCRATCH, q.device, floats, n_counters)
     out = torch.empty((q.shape[0], n_q * head_dim), dtype=q.dtype, device=q.device)
     if prep is not None:
         _check(lib.dfi_attention_decode_prepared(
@@ -377,12 +492,7 @@ def _gemm_scratch(device, n_ctas: int, counters: int):
     lib = _core()
     lib.dfi_skinny_gemm_partial_floats.restype = ctypes.c_longlong
     floats = lib.dfi_skinny_gemm_partial_floats(n_ctas)
-    held = _GEMM_SCRATCH.get(device)
-    if held is None or held[0].numel() < floats or held[1].numel() < counters:
-        partials = torch.empty(max(floats, held[0].numel() if held else 0), dtype=torch.float32, device=device)
-        count = torch.zeros(max(counters, 8192, held[1].numel() if held else 0), dtype=torch.int32, device=device)
-        _GEMM_SCRATCH[device] = held = (partials, count)
-    return held
+    return _scratch(_GEMM_SCRATCH, device, floats, counters)
 
 
 def skinny_linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None,
@@ -409,40 +519,9 @@ def skinny_linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype 
     return out
 
 
-TC_NORMAL, TC_SWIGLU, TC_SWAP, TC_NN = 0, 1, 2, 3
-
-
-def tc_linear(x: torch.Tensor, weight: torch.Tensor, mode: int = TC_NORMAL,
-              out_dtype: torch.dtype | None = None) -> torch.Tensor:
-    """``x @ weight.T`` on the tcgen05 tensor cores (TMA-fed, accumulator in tensor memory).
-
-    ``TC_NORMAL``: the rows of ``x`` take the 128-row side of the instruction (prefill).
-    ``TC_SWIGLU``: ``weight = [gate; up]``; returns ``silu(x @ gate.T) * (x @ up.T)``.
-    ``TC_SWAP``: the same product as normal with the weights on the 128-row side (up to 256 rows of ``x``).
-    """
-    _need_cuda(x, weight)
-    m, k = x.shape
-    assert x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
-    assert x.is_contiguous() and weight.is_contiguous()
-    if mode == TC_NN:                       # weight is [K, N]
-        assert weight.shape[0] == k
-        n = weight.shape[1]
-    else:
-        assert weight.shape[1] == k
-        n = weight.shape[0] // 2 if mode == TC_SWIGLU else weight.shape[0]
-    if k % 8 or (mode != TC_SWAP and n % 8):
-        raise KernelError(f"tc_linear takes K and N in steps of 8, got K={k}, N={n}")
-    out_dtype = out_dtype or x.dtype
-    out = torch.empty((m, n), dtype=out_dtype, device=x.device)
-    _check(_core().dfi_gemm_tcgen05(_ptr(x), _ptr(weight), _ptr(out), m, n, k, mode, _DTYPE_CODE[out_dtype], _stream()),
-           "tc_linear", f"{m} x {k} by {weight.shape[0]} x {k}, mode {mode}")
-    return out
-
-
 def tc_error(reset: bool = True) -> int:
-    """0, or the code of the first bounded wait that ran out in a tcgen05 kernel (synchronises)."""
-    lib = _core()
-    return lib.dfi_gemm_tcgen05_error(int(reset)) or lib.dfi_gemm_decode_error(int(reset))
+    """0, or the code of the first bounded wait that ran out in the decode product's kernel (synchronises)."""
+    return _core().dfi_gemm_decode_error(int(reset))
 
 
 _DECODE_SCRATCH: dict = {}
@@ -531,11 +610,7 @@ def decode_linear(x, weight: torch.Tensor, out_dtype: torch.dtype | None = None,
         n_ctas = lib.dfi_sm_count()
     lib.dfi_gemm_decode_partial_floats.restype = ctypes.c_longlong
     floats, counters = lib.dfi_gemm_decode_partial_floats(n_ctas), lib.dfi_gemm_decode_counters(n, int(swiglu))
-    held = _DECODE_SCRATCH.get(x.device)
-    if held is None or held[0].numel() < floats or held[1].numel() < counters:
-        held = (torch.empty(max(floats, held[0].numel() if held else 0), dtype=torch.float32, device=x.device),
-                torch.zeros(max(counters, 8192, held[1].numel() if held else 0), dtype=torch.int32, device=x.device))
-        _DECODE_SCRATCH[x.device] = held
+    held = _scratch(_DECODE_SCRATCH, x.device, floats, counters)
     out = torch.empty((m, n), dtype=out_dtype, device=x.device)
     what = f"{m} x {k} by {weight.shape[0]} x {k}"
     if scaled is None and add_norm is None:
@@ -565,26 +640,45 @@ def decode_linear(x, weight: torch.Tensor, out_dtype: torch.dtype | None = None,
     return out
 
 
+def simt_linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """``x @ weight.T`` on the float32 pipes (``csrc/gemm_simt.cu``): every product and sum in float32 in
+    the order of k.  Any sizes; float32 operands, or bfloat16 ones with a bfloat16 or float32 result."""
+    _need_cuda(x, weight)
+    assert x.dim() == 2 and weight.dim() == 2 and x.shape[1] == weight.shape[1] and x.dtype == weight.dtype
+    x, weight = x.contiguous(), weight.contiguous()
+    out_dtype = out_dtype or x.dtype
+    if out_dtype not in _DTYPE_CODE or (x.dtype == torch.float32 and out_dtype != torch.float32):
+        raise KernelError(f"simt_linear: {x.dtype} operands cannot give a {out_dtype} result")
+    out = torch.empty((x.shape[0], weight.shape[0]), dtype=out_dtype, device=x.device)
+    _check(_core().dfi_gemm_simt(_ptr(x), _ptr(weight), _ptr(out), x.shape[0], weight.shape[0], x.shape[1], _code(x),
+                                 _DTYPE_CODE[out_dtype], _stream()), "simt_linear",
+           f"{x.shape[0]} x {x.shape[1]} by {weight.shape[0]} x {weight.shape[1]}")
+    return out
+
+
 def linear(x, weight: torch.Tensor, out_dtype: torch.dtype | None = None, add_norm=None):
     """``x @ weight.T`` for ``weight [out, in]`` as stored in the model file.
 
     bfloat16 with at most 64 rows (decoding) runs the hand-written stream-K tcgen05 kernel; larger
-    products go to the library's GEMM, as the reference's prefill does
-    (engine/engine.py:881-884).  float32 operands take the library's float32 product with
-    no reduced-precision mode.  ``out_dtype=torch.float32`` keeps bfloat16 products
-    unrounded (used for logits).  ``ScaledRows`` in and ``add_norm`` are those of ``decode_linear``.
+    bfloat16 products go to the library's GEMM, as the reference's prefill does
+    (engine/engine.py:881-884), or with ``DRYFT_PREFILL_GEMM=own`` to the pair kernel.  float32
+    operands, and bfloat16 matrices whose width is no multiple of 8 (which the TMA-fed kernels do not
+    take), run the plain float32-pipe kernel of this package: true 32-bit, no library, no
+    reduced-precision mode.  ``out_dtype=torch.float32`` keeps bfloat16 products unrounded (used for
+    logits).  ``ScaledRows`` in and ``add_norm`` are those of ``decode_linear``.
     """
     if isinstance(x, ScaledRows) or add_norm is not None:
         # only made and asked for where the decode kernel runs (add_norm_fusable)
         return decode_linear(x, weight, out_dtype, add_norm=add_norm)
     _need_cuda(x, weight)
     assert x.dim() == 2 and weight.dim() == 2 and x.shape[1] == weight.shape[1] and x.dtype == weight.dtype
-    if x.dtype == torch.bfloat16 and x.shape[0] <= SKINNY_MAX_ROWS and x.shape[1] % 8 == 0 and x.is_contiguous():
+    if x.dtype == torch.float32 or x.shape[1] % 8:
+        return simt_linear(x, weight, out_dtype)
+    if x.shape[0] <= SKINNY_MAX_ROWS and x.is_contiguous():
         return decode_linear(x, weight, out_dtype)
     if out_dtype is not None and out_dtype != x.dtype:
         return torch.mm(x, weight.t(), out_dtype=out_dtype)
-    if (PREFILL_GEMM == "own" and x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and x.is_contiguous()
-            and weight.is_contiguous()):
+    if PREFILL_GEMM == "own" and x.is_contiguous() and weight.is_contiguous():
         return pair_linear(x, weight)
     return torch.mm(x, weight.t())
 

@@ -18,6 +18,11 @@ class Attention(Mixer):
     key/value head ``h // (n_q / n_kv)``, scores scaled by ``scale`` (default
     ``head_dim ** -0.5``, engine/kernels/attention.py:210).  ``window`` > 0 limits each
     query to the latest ``window`` keys.  ``qk_norm`` and ``position`` may be absent.
+
+    What the mixer asks of its position part: float32 tables ``cos`` and ``sin`` of shape
+    ``[positions, r / 2]`` with ``r <= head_dim`` even, made by ``prepare``; element ``i < r / 2`` of a
+    head is rotated with element ``i + r / 2`` by the angle whose cosine and sine stand at ``[position,
+    i]``, and elements from ``r`` on are left as they are.
     """
 
     kind = "attention"
@@ -65,7 +70,7 @@ class Attention(Mixer):
         qkv = kernels.linear(x, self.qkv)
         cos = self.position.cos if self.position is not None else None
         sin = self.position.sin if self.position is not None else None
-        if kernels.decode_prepares_tokens(qkv, ctx, self.n_heads, self.n_kv_heads, self.head_dim):
+        if kernels.decode_prepares_tokens(qkv, ctx, self.n_heads, self.n_kv_heads, self.head_dim, cos):
             # decoding: the attention kernel normalises, rotates and stores the new token itself
             prep = kernels.TokenPrep(qkv, self.q_norm, self.k_norm, self.qk_norm_eps, cos, sin)
             attended = kernels.attention_decode(None, cache, ctx, self.n_heads, self.n_kv_heads, self.head_dim,

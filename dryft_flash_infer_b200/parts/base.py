@@ -12,7 +12,7 @@ Position      ``prepare(max_positions, device)``; what the mixer reads from it i
               between the two of them (rotary: ``cos``/``sin`` tables).
 Mixer         ``cache_need()``, ``state_need()``, ``forward(x, ctx, cache, state)``.
 FeedForward   ``forward(x, ctx)``.
-Block         ``forward(residual, pending, ctx, cache, state) -> (residual, pending)``.
+Block         ``norm_names``; ``forward(residual, pending, ctx, cache, state) -> (residual, pending)``.
 """
 
 from __future__ import annotations
@@ -54,9 +54,12 @@ class KVNeed:
 
 @dataclass(frozen=True)
 class StateNeed:
-    """A mixer that keeps a fixed-size float32 state per sequence, zero at the start."""
+    """A mixer that keeps a state of fixed size per sequence: its shape, the dtype it is held in
+    (``float32`` or ``bfloat16``) and the value every element has when a sequence starts."""
 
     shape: tuple[int, ...]
+    dtype: str = "float32"
+    init: float = 0.0
 
 
 class Part:
@@ -130,7 +133,8 @@ class FeedForward(Part):
 
 
 class Block:
-    """An arrangement of a mixer, a feed-forward and their norms around the residual stream.
+    """An arrangement of a mixer, a feed-forward and norms around the residual stream.  How many norms
+    there are and where they stand is the block kind's business: it names them in ``norm_names``.
 
     The residual stream travels between blocks as ``(residual, pending)``: ``pending``
     is a delta not yet added, so that the next norm can add and normalise in one pass.
@@ -141,13 +145,23 @@ class Block:
     #: then return ``pending`` as ``kernels.ScaledRows`` of that norm, the sum already in ``residual``
     fuses_next_norm = False
 
-    def __init__(self, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm, ffn_norm: Norm):
+    #: the names of the norms this arrangement has; the layer's spec must give exactly these
+    norm_names: tuple[str, ...] = ()
+
+    def __init__(self, mixer: Mixer, feed_forward: FeedForward, norms: dict[str, Norm]):
+        if set(norms) != set(self.norm_names):
+            raise ValueError(f"a '{self.kind}' block has the norms {sorted(self.norm_names)}, the layer gives "
+                             f"{sorted(norms)}")
         self.mixer, self.feed_forward = mixer, feed_forward
-        self.mixer_norm, self.ffn_norm = mixer_norm, ffn_norm
+        self.norms = dict(norms)
 
     def parts(self) -> dict[str, Part]:
-        return {"mixer": self.mixer, "feed_forward": self.feed_forward,
-                "mixer_norm": self.mixer_norm, "ffn_norm": self.ffn_norm}
+        return {"mixer": self.mixer, "feed_forward": self.feed_forward, **self.norms}
+
+    @property
+    def first_norm(self) -> Norm | None:
+        """The norm that reads the residual stream as it enters the block, if the block starts with one."""
+        return None
 
     @property
     def graph_safe(self) -> bool:

@@ -17,7 +17,16 @@ class PreNormBlock(Block):
     """
 
     kind = "pre_norm"
+    norm_names = ("mixer_norm", "ffn_norm")
     fuses_next_norm = True
+
+    def __init__(self, mixer, feed_forward, norms):
+        super().__init__(mixer, feed_forward, norms)
+        self.mixer_norm, self.ffn_norm = self.norms["mixer_norm"], self.norms["ffn_norm"]
+
+    @property
+    def first_norm(self):
+        return self.mixer_norm
 
     @property
     def takes_scaled_pending(self) -> bool:

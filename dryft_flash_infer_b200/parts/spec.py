@@ -21,17 +21,19 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One layer: the arrangement (``block``) of a mixer, a feed-forward and their norms.
+    """One layer: the arrangement (``block``) of a mixer, a feed-forward and the block's norms.
 
-    ``tensor_names`` maps each tensor of the layer, written ``<part>.<tensor>`` with
-    part in {mixer, feed_forward, mixer_norm, ffn_norm}, to its name in the model file.
+    ``norms`` maps the names the block kind gives its norms to their specs: the block
+    decides how many it has and where they stand (``pre_norm`` has ``mixer_norm`` and
+    ``ffn_norm``).  ``tensor_names`` maps each tensor of the layer, written
+    ``<part>.<tensor>`` with part in {mixer, feed_forward} or a norm's name, to its name
+    in the model file.
     """
 
     block: str
     mixer: PartSpec
     feed_forward: PartSpec
-    mixer_norm: PartSpec
-    ffn_norm: PartSpec
+    norms: dict[str, PartSpec]
     tensor_names: dict[str, str]
 
 
@@ -59,11 +61,19 @@ class ModelSpec:
     max_positions: int
     layers: tuple[LayerSpec, ...]
     schedule: tuple[ScheduleEntry, ...]
-    final_norm: PartSpec
+    #: the norm between the last block and the output head, or None for a model without one
+    final_norm: PartSpec | None
     embedding_name: str
     final_norm_names: dict[str, str]
     #: name of the output head's matrix, or None when it is the embedding table
     head_name: str | None
+    #: what surrounds the blocks, for architectures that have it: a factor on the embedded rows, a
+    #: factor on the logits, and a cap ``c`` that turns logits ``x`` into ``c * tanh(x / c)`` (0: none)
+    embedding_scale: float = 1.0
+    logit_scale: float = 1.0
+    logit_softcap: float = 0.0
+    #: tensors that a model file may hold beside the expected ones without being an error
+    ignorable_tensors: tuple[str, ...] = ()
 
     def check(self) -> None:
         owners = {}

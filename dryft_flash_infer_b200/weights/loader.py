@@ -84,9 +84,7 @@ def load_weights(model, folder: str | Path) -> None:
     """Copies every expected tensor from ``folder`` into ``model``'s allocated buffers."""
     files = ModelFiles(folder)
     expected = model.expected_tensors()
-    # a tied model's file may still carry a copy of the head: it is the embedding, so it is skipped
-    ignorable = ("lm_head.weight",) if model.spec.head_name is None else ()
-    check_tensors(folder, files, expected, ignorable)
+    check_tensors(folder, files, expected, model.spec.ignorable_tensors)
     staging = None
     for e in expected:
         dest = model.destination(e)

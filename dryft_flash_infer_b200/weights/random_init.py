@@ -41,8 +41,11 @@ def fill_random(model, seed: int) -> None:
     model.bind()
 
 
-def write_random_model(config: ModelConfig, seed: int, folder: str | Path, dtype: torch.dtype = torch.bfloat16) -> Path:
-    """Writes ``config.json`` and ``model.safetensors`` with random weights stored in ``dtype``."""
+def write_random_model(config: ModelConfig, seed: int, folder: str | Path, dtype: torch.dtype = torch.bfloat16,
+                       device="cpu") -> Path:
+    """Writes ``config.json`` and ``model.safetensors`` with random weights stored in ``dtype``.  The
+    numbers are drawn on ``device`` (a CUDA device draws a model of billions of weights in seconds; its
+    generator gives other numbers than the CPU's for the same seed)."""
     from ..engine.model import DecoderModel
 
     folder = Path(folder)
@@ -56,6 +59,7 @@ def write_random_model(config: ModelConfig, seed: int, folder: str | Path, dtype
     model = DecoderModel(architecture_named(config.architecture).build(config))
     expected = model.expected_tensors()
     plan = [(e.name, dtype, tuple(e.decl.shape)) for e in expected]
-    stream = ((e.name, random_tensor(e.name, e.decl.shape, e.decl.init, seed).to(dtype)) for e in expected)
+    stream = ((e.name, random_tensor(e.name, e.decl.shape, e.decl.init, seed, device).to(dtype).cpu())
+              for e in expected)
     write_safetensors(folder / "model.safetensors", stream, plan, metadata={"format": "pt", "seed": str(seed)})
     return folder

@@ -28,3 +28,15 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+def pytest_terminal_summary(terminalreporter):
+    """The largest logit error each family of comparisons showed: what the bounds in ``helpers.py`` rest on."""
+    try:
+        import helpers
+    except Exception:
+        return
+    for (dtype, family), (err, what) in sorted(helpers.SEEN.items()):
+        terminalreporter.write_line(f"largest logit error, {dtype} / {family}: {err:.3e} ({what})")
+    for name, text in sorted(helpers.NOTES.items()):
+        terminalreporter.write_line(f"{name}: {text}")

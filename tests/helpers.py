@@ -10,8 +10,18 @@ from dryft_flash_infer_b200.weights import write_safetensors
 
 #: float32 logits may differ from the plain implementation by summation order only
 F32_ATOL = 2e-4
-#: bfloat16: 8 significant bits per rounding, a few dozen roundings on the way to a logit
-BF16_REL = 0.03
+#: bfloat16 bounds on the largest logit error, per family of tests: about twice the largest error that the
+#: family's tests showed on a B200 (printed at the end of a GPU run, see ``conftest.py``), on logits with a
+#: standard deviation of 0.5 to 0.6.  "tiny": the configurations A to D of the tests; "wide": the layers
+#: at the widths of Qwen3-4B, whose logits are sums over 2,560 terms.
+BF16_ATOL = {"tiny": 0.06, "wide": 0.12}
+#: how far below the plain implementation's best logit a token chosen by the bfloat16 engine may lie
+BF16_TIE_GAP = 0.05
+
+#: the largest error each family has shown in this run, for the summary at the end
+SEEN: dict[tuple[str, str], tuple[float, str]] = {}
+#: other measured numbers that bounds rest on, ``name -> text``, printed with the summary
+NOTES: dict[str, str] = {}
 
 
 def write_model(folder, cfg: dict, weights: dict, store: torch.dtype = torch.float32):
@@ -20,18 +30,18 @@ def write_model(folder, cfg: dict, weights: dict, store: torch.dtype = torch.flo
     return folder
 
 
-def tolerance(dtype: str, reference: torch.Tensor) -> float:
-    if dtype == "float32":
-        return F32_ATOL
-    return BF16_REL * max(1.0, float(reference.abs().max()))
+def tolerance(dtype: str, family: str = "tiny") -> float:
+    return F32_ATOL if dtype == "float32" else BF16_ATOL[family]
 
 
-def assert_close(got: torch.Tensor, want: torch.Tensor, dtype: str, what: str = ""):
+def assert_close(got: torch.Tensor, want: torch.Tensor, dtype: str, what: str = "", family: str = "tiny"):
     got, want = got.float().cpu(), want.float().cpu()
     assert got.shape == want.shape, f"{what}: shape {tuple(got.shape)} != {tuple(want.shape)}"
     assert torch.isfinite(got).all(), f"{what}: not finite"
     err = float((got - want).abs().max())
-    tol = tolerance(dtype, want)
+    if err > SEEN.get((dtype, family), (-1.0, ""))[0]:
+        SEEN[(dtype, family)] = (err, what)
+    tol = tolerance(dtype, family)
     assert err <= tol, f"{what}: max error {err:.3e} > {tol:.3e} ({dtype})"
 
 

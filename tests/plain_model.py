@@ -148,8 +148,9 @@ def normalise_config(cfg: dict) -> dict:
     return out
 
 
-def forward(cfg: dict, weights: dict, tokens, dtype=torch.float32, windows=None) -> torch.Tensor:
-    """Logits ``[T, vocab]`` at every position of one sequence.
+def forward(cfg: dict, weights: dict, tokens, dtype=torch.float32, windows=None, places=None) -> torch.Tensor:
+    """Logits ``[T, vocab]`` at every position of one sequence (or ``[len(places), vocab]`` at the
+    positions ``places``: the head is a large product when the vocabulary is).
 
     embed -> layers -> final norm -> head, the head being the embedding table when
     ``tie_word_embeddings`` (engine/engine.py:236-239, :1019-1025).  ``windows``
@@ -163,6 +164,8 @@ def forward(cfg: dict, weights: dict, tokens, dtype=torch.float32, windows=None)
     for index in range(cfg["num_hidden_layers"]):
         window = windows[index] if windows else 0
         x = decoder_layer(x, w, index, cfg, positions, window)
+    if places is not None:
+        x = x[torch.as_tensor(list(places), dtype=torch.int64)]
     x = rms_norm(x, w["model.norm.weight"], cfg["rms_norm_eps"])
     head = w["model.embed_tokens.weight"] if cfg["tie_word_embeddings"] else w["lm_head.weight"]
     return x @ head.T

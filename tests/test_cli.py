@@ -53,8 +53,16 @@ def test_bench_measures_one_gpu_only_and_says_so():
     assert len(lines) == 1 and "--gpus 2" in lines[0]
 
 
-def test_bench_reference_arm_is_unavailable_and_exits_zero():
+def test_bench_reference_arm_without_a_gpu_says_why_in_one_line():
+    """On a machine without a CUDA device neither arm can run; the reference arm then prints its
+    one-line reason and exits 0 (with a device it runs the reference, which takes minutes: not here)."""
+    import torch
+
+    if torch.cuda.is_available():
+        import pytest
+
+        pytest.skip("with a CUDA device the arm runs the reference itself")
     done = bench("--impl", "reference", "--gpus", "1", "--steps", "2", "--warmup", "1")
     assert done.returncode == 0
     line = json.loads(done.stdout.strip().splitlines()[-1])
-    assert line["impl"] == "reference" and "unavailable" in line and "\n" not in line["unavailable"]
+    assert line["impl"] == "reference" and "\n" not in line["unavailable"]

@@ -21,10 +21,22 @@ def test_reads_the_keys_of_config_json():
 
 def test_defaults_follow_the_reference():
     raw = dict(plain_model.TINY_A)
-    del raw["head_dim"], raw["rope_theta"], raw["rms_norm_eps"]
+    del raw["head_dim"], raw["rms_norm_eps"]
     cfg = config_from_dict(raw)
     assert cfg.head_dim == raw["hidden_size"] // raw["num_attention_heads"]
-    assert cfg.rope_theta == 5_000_000.0 and cfg.rms_norm_eps == 1e-6
+    assert cfg.rms_norm_eps == 1e-6
+
+
+def test_the_rotation_base_is_read_where_the_file_keeps_it_and_never_guessed():
+    raw = dict(plain_model.TINY_A)
+    del raw["rope_theta"]
+    with pytest.raises(ConfigError, match="rope_theta"):
+        config_from_dict(raw)
+    newer = dict(raw, rope_parameters={"rope_type": "default", "rope_theta": 123456.0})
+    assert config_from_dict(newer).rope_theta == 123456.0
+    with pytest.raises(ConfigError, match="rope_type"):
+        config_from_dict(dict(raw, rope_parameters={"rope_type": "yarn", "rope_theta": 1e6, "factor": 4.0}))
+    assert json.loads(json.dumps(config_from_dict(plain_model.TINY_A).to_dict()))["model_type"] == "qwen3"
 
 
 def test_round_trip_through_a_folder(tmp_path):
@@ -45,6 +57,8 @@ def test_round_trip_through_a_folder(tmp_path):
     ({"use_sliding_window": True}, "use_sliding_window"),
     ({"attention_bias": True}, "attention_bias"),
     ({"head_dim": 15}, "head_dim"),
+    ({"head_dim": 24}, "head_dim"),
+    ({"head_dim": 272}, "head_dim"),
     ({"num_hidden_layers": 0}, "num_hidden_layers"),
 ])
 def test_bad_configurations_are_named(change, word):
@@ -80,7 +94,7 @@ def test_spec_follows_the_configuration_layer_by_layer():
     assert mixer.kind == "attention" and mixer.params["head_dim"] == 32 and mixer.params["n_kv_heads"] == 2
     assert mixer.params["position"].params["theta"] == 1e6
     assert spec.layers[0].feed_forward.params["intermediate_size"] == 200
-    assert spec.layers[0].mixer_norm.params["eps"] == 1e-5
+    assert sorted(spec.layers[0].norms) == ["ffn_norm", "mixer_norm"] and spec.layers[0].norms["mixer_norm"].params["eps"] == 1e-5
     model = DecoderModel(spec)
     names = {t.name: t.decl.shape for t in model.expected_tensors()}
     assert names["model.layers.2.self_attn.q_proj.weight"] == (256, 96)

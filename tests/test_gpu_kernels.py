@@ -401,21 +401,6 @@ def test_skinny_gemm_with_swiglu(m, inter, k):
     assert got.dtype == torch.bfloat16 and torch.allclose(got.float().cpu(), want, atol=3e-2, rtol=1e-2)
 
 
-@pytest.mark.parametrize("m, n, k", [(128, 128, 64), (300, 320, 200), (2048, 256, 2560), (1, 128, 128), (130, 6144, 96)])
-def test_tcgen05_gemm_normal(m, n, k):
-    from dryft_flash_infer_b200.ops import kernels
-
-    g = torch.Generator().manual_seed(m + n + k)
-    x = torch.randn(m, k, generator=g).to(torch.bfloat16)
-    w = (torch.randn(n, k, generator=g) * 0.05).to(torch.bfloat16)
-    want = x.float() @ w.float().T
-    got = kernels.tc_linear(x.cuda(), w.cuda(), kernels.TC_NORMAL, torch.float32)
-    assert kernels.tc_error() == 0
-    assert torch.allclose(got.cpu(), want, atol=2e-3, rtol=1e-3), float((got.cpu() - want).abs().max())
-    got16 = kernels.tc_linear(x.cuda(), w.cuda())
-    assert torch.allclose(got16.float().cpu(), want, atol=2e-2, rtol=1e-2)
-
-
 @pytest.mark.parametrize("m, n, k", [(256, 256, 64), (300, 320, 200), (2048, 2560, 4096), (1, 8, 8), (700, 6144, 96),
                                      (5000, 520, 264)])
 def test_tcgen05_pair_gemm(m, n, k):
@@ -445,36 +430,6 @@ def test_tcgen05_pair_gemm_swiglu(m, inter, k):
     got = kernels.pair_linear(x.cuda(), w.cuda(), swiglu=True)
     assert kernels.pair_error() == 0
     assert torch.allclose(got.float().cpu(), want, atol=0.02 * float(want.abs().max()), rtol=2e-2)
-
-
-@pytest.mark.parametrize("m, inter, k", [(128, 128, 64), (300, 200, 96), (2048, 9728, 2560), (5, 72, 40)])
-def test_tcgen05_gemm_swiglu(m, inter, k):
-    from dryft_flash_infer_b200.ops import kernels
-
-    g = torch.Generator().manual_seed(m + inter + k)
-    x = torch.randn(m, k, generator=g).to(torch.bfloat16)
-    w = (torch.randn(2 * inter, k, generator=g) * 0.1).to(torch.bfloat16)
-    gu = x.float() @ w.float().T
-    want = gu[:, :inter] / (1 + torch.exp(-gu[:, :inter])) * gu[:, inter:]
-    got = kernels.tc_linear(x.cuda(), w.cuda(), kernels.TC_SWIGLU, torch.float32)
-    assert kernels.tc_error() == 0
-    assert torch.allclose(got.cpu(), want, atol=3e-3, rtol=2e-3), float((got.cpu() - want).abs().max())
-    got16 = kernels.tc_linear(x.cuda(), w.cuda(), kernels.TC_SWIGLU)
-    assert torch.allclose(got16.float().cpu(), want, atol=3e-2, rtol=1e-2)
-
-
-@pytest.mark.parametrize("m", [1, 8, 17, 33, 64, 100, 256])
-@pytest.mark.parametrize("n, k", [(128, 64), (320, 200), (2560, 4096), (100, 96)])
-def test_tcgen05_gemm_swapped(m, n, k):
-    from dryft_flash_infer_b200.ops import kernels
-
-    g = torch.Generator().manual_seed(m * n + k)
-    x = torch.randn(m, k, generator=g).to(torch.bfloat16)
-    w = (torch.randn(n, k, generator=g) * 0.05).to(torch.bfloat16)
-    want = x.float() @ w.float().T
-    got = kernels.tc_linear(x.cuda(), w.cuda(), kernels.TC_SWAP, torch.float32)
-    assert kernels.tc_error() == 0
-    assert torch.allclose(got.cpu(), want, atol=2e-3, rtol=1e-3), float((got.cpu() - want).abs().max())
 
 
 @pytest.mark.parametrize("m", [1, 3, 8, 17, 33, 64])
@@ -551,20 +506,6 @@ def test_tcgen05_decode_gemm_with_the_norm_fused_around_it(m, hidden, k, n2):
         kernels.decode_linear(x.cuda(), w.cuda(), torch.float32, add_norm=(residual.cuda(), norm_w.cuda(), eps))
 
 
-@pytest.mark.parametrize("m, n, k", [(128, 128, 64), (300, 320, 200), (256, 256, 1024)])
-def test_tcgen05_gemm_with_a_row_major_second_operand(m, n, k):
-    """out = x @ w for w stored [K, N]: the operand layout the value product of attention uses."""
-    from dryft_flash_infer_b200.ops import kernels
-
-    g = torch.Generator().manual_seed(m + n + k)
-    x = torch.randn(m, k, generator=g).to(torch.bfloat16)
-    w = (torch.randn(k, n, generator=g) * 0.05).to(torch.bfloat16)
-    want = x.float() @ w.float()
-    got = kernels.tc_linear(x.cuda(), w.cuda(), kernels.TC_NN, torch.float32)
-    assert kernels.tc_error() == 0
-    assert torch.allclose(got.cpu(), want, atol=2e-3, rtol=1e-3), float((got.cpu() - want).abs().max())
-
-
 @pytest.mark.parametrize("n_q, n_kv, dim", [(8, 2, 128), (3, 1, 64), (4, 4, 128), (32, 8, 128)])
 def test_attention_tcgen05_prefill(n_q, n_kv, dim):
     from dryft_flash_infer_b200.ops import kernels
@@ -585,3 +526,28 @@ def test_attention_tcgen05_prefill(n_q, n_kv, dim):
         assert kernels.attention_tc_error(dim) == 0
         assert torch.isfinite(got).all()
         assert torch.allclose(got.float().cpu(), want, atol=tol(dtype, 2), rtol=tol(dtype)), window
+
+
+@pytest.mark.parametrize("m, n, k", [(1, 1, 1), (7, 130, 100), (64, 64, 16), (65, 63, 17), (300, 320, 200), (3, 1000, 2563)])
+def test_plain_float32_pipe_gemm(m, n, k):
+    """The product of the true 32-bit path, and of bfloat16 matrices whose width is no multiple of 8:
+    float32 operands against a float64 product (no reduced-precision mode would pass this bound),
+    bfloat16 operands with bfloat16 and float32 results."""
+    from dryft_flash_infer_b200.ops import kernels
+
+    g = torch.Generator().manual_seed(m + n + k)
+    x = torch.randn(m, k, generator=g)
+    w = torch.randn(n, k, generator=g) * 0.1
+    want = (x.double() @ w.double().T)
+    got = kernels.simt_linear(x.cuda(), w.cuda())
+    assert got.dtype == torch.float32
+    assert float((got.cpu().double() - want).abs().max()) <= 2e-6 * max(1.0, k ** 0.5) * float(want.abs().max() + 1)
+    assert torch.equal(kernels.linear(x.cuda(), w.cuda()), got)            # float32 operands always run this kernel
+    x16, w16 = x.to(torch.bfloat16), w.to(torch.bfloat16)
+    want16 = x16.double() @ w16.double().T
+    unrounded = kernels.simt_linear(x16.cuda(), w16.cuda(), torch.float32)
+    assert float((unrounded.cpu().double() - want16).abs().max()) <= 2e-6 * max(1.0, k ** 0.5) * float(want16.abs().max() + 1)
+    rounded = kernels.simt_linear(x16.cuda(), w16.cuda())
+    assert rounded.dtype == torch.bfloat16 and torch.equal(rounded, unrounded.to(torch.bfloat16))
+    if k % 8:
+        assert torch.equal(kernels.linear(x16.cuda(), w16.cuda()), rounded)  # widths the TMA kernels do not take

@@ -17,9 +17,12 @@ pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parent.parent
 
 
-def replay(model, dtype, out, steps, max_tokens):
-    proc = subprocess.Popen([str(ROOT / "bin" / "trace_run"), "--model", str(model), "--dtype", dtype, "--out", str(out),
-                             "--max-tokens", str(max_tokens)], stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True)
+def replay(model, dtype, out, steps, max_tokens, graph):
+    command = [str(ROOT / "bin" / "trace_run"), "--model", str(model), "--dtype", dtype, "--out", str(out),
+               "--max-tokens", str(max_tokens)]
+    if graph != "default":
+        command += ["--cuda-graph", graph]
+    proc = subprocess.Popen(command, stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True)
     for record in steps:
         proc.stdin.write(json.dumps(record) + "\n")
         proc.stdin.flush()
@@ -32,9 +35,12 @@ def read(out, step, vocab):
     return torch.from_numpy(np.fromfile(Path(out) / f"{step}.f32", dtype="<f4").reshape(-1, vocab))
 
 
+@pytest.mark.parametrize("graph", ["default", "off"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["A", "B"])
-def test_three_ways_of_cutting_the_same_requests(tmp_path, name, dtype):
+def test_three_ways_of_cutting_the_same_requests(tmp_path, name, dtype, graph):
+    """``graph`` default (on): single-token steps run on generation's fixed decode buffers through its CUDA
+    graph and short prompt steps through the prompt graphs; off: every step launch by launch."""
     cfg = CONFIGS[name]
     weights = plain_model.random_weights(cfg, seed=91, matrix_std=0.06, norm_std=0.1)
     model = write_model(tmp_path / "model", cfg, weights)
@@ -46,7 +52,7 @@ def test_three_ways_of_cutting_the_same_requests(tmp_path, name, dtype):
     # 1. each request alone and whole; every place wanted
     steps = [{"step": i, "entries": [{"id": k, "tokens": p, "want": list(range(len(p)))}], "end": [k]}
              for i, (k, p) in enumerate(requests.items())]
-    replay(model, dtype, tmp_path / "whole", steps, max_tokens=192)
+    replay(model, dtype, tmp_path / "whole", steps, 192, graph)
     for i, k in enumerate(requests):
         assert_close(read(tmp_path / "whole", i, vocab), want[k], dtype, f"whole {k}")
 
@@ -62,7 +68,7 @@ def test_three_ways_of_cutting_the_same_requests(tmp_path, name, dtype):
                           "end": [k] if t == len(p) - 1 else []})
             expect[n] = want[k][t: t + 1]
             n += 1
-    replay(model, dtype, tmp_path / "tail", steps, max_tokens=192)
+    replay(model, dtype, tmp_path / "tail", steps, 192, graph)
     for step, rows in expect.items():
         assert_close(read(tmp_path / "tail", step, vocab), rows, dtype, f"tail step {step}")
 
@@ -84,7 +90,7 @@ def test_three_ways_of_cutting_the_same_requests(tmp_path, name, dtype):
             if t % 2 == 0:
                 expect[n] = torch.stack([want[k][len(requests[k]) - tails[k] + t] for k in live])
             n += 1
-    replay(model, dtype, tmp_path / "batches", steps, max_tokens=64 + 64 + 128 + 64)
+    replay(model, dtype, tmp_path / "batches", steps, 64 + 64 + 128 + 64, graph)
     for step, rows in expect.items():
         assert_close(read(tmp_path / "batches", step, vocab), rows, dtype, f"batch step {step}")
     assert not (tmp_path / "batches" / "2.f32").exists()          # nothing wanted, nothing written
