@@ -163,6 +163,15 @@ def time_decode(engine, n_seqs: int, context: int, steps: int, warmup: int, samp
     return ms, per_step
 
 
+def long_engine(engine, context: int):
+    """``engine`` with its cache made anew for one sequence of ``context`` tokens (the weights stay)."""
+    engine._make_cache(context, 1, context)
+    for group in engine.cache.groups:
+        group.k.normal_(0.0, 1.0)
+        group.v.normal_(0.0, 1.0)
+    return engine
+
+
 def generation_run(shape: str) -> int:
     """Generation through ``Engine.generate`` at the 8B shape (16 unequal prompts of 128..2,048 tokens, 256
     greedy steps) or the 14B shape (32 prompts of 1,024 tokens, 128 steps): tokens per second, prefill included."""
@@ -192,11 +201,22 @@ def generation_run(shape: str) -> int:
         results.append((end - begin, first - begin, produced))
     total, ttft, produced = min(results)
     nums = model_numbers(cfg, cfg["num_hidden_layers"])
+    peak = peaks()
+    tpot = (total - ttft) / max(1, produced - 1)
+    # a decode step reads every weight once and the cache of the live sequences (on average half the new tokens in)
+    step_bytes = nums["weight_bytes"] + (sum(lengths) + batch * produced / 2) * nums["kv_bytes_per_token"]
+    achieved = step_bytes / tpot / 1e9
+    flops = sum(prefill_flops(cfg, cfg["num_hidden_layers"], n) for n in lengths)      # each prompt: its products, its own causal attention, one head row
     print(json.dumps({
         "metric": f"generation tokens/s, prefill included (Qwen3-{shape.upper()} sizes, bf16, random weights)",
         "value": round(batch * produced / total, 1), "unit": "tokens/s", "n_gpus": 1, "impl": "ours",
         "ttft_ms": round(ttft * 1e3, 2), "tpot_ms": round((total - ttft) / max(1, produced - 1) * 1e3, 3),
         "prefill_tokens_per_s": round(sum(lengths) / ttft, 1),
+        "prefill": {"value": round(sum(lengths) / ttft, 1), "tokens": sum(lengths), "ms": round(ttft * 1e3, 2),
+                    "frac": round(flops / ttft / (peak["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / peak["hbm_gbs"], 4), "peaks": peak["source"],
+                     "bytes_per_step_gb": round(step_bytes / 1e9, 2)},
         "config": {"model": f"Qwen3-{shape.upper()} sizes", "layers": cfg["num_hidden_layers"], "hidden": cfg["hidden_size"],
                    "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
                    "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "global_batch": batch,
@@ -418,6 +438,10 @@ def main() -> int:
         e2e = {"value": round(BATCH * produced / elapsed, 1), "unit": "tokens/s",
                "h2d_bytes_per_step": int(batch.h2d_bytes_per_step),
                "d2h_bytes_per_step": BATCH * 4 + 32}
+        # last, because they make the cache anew: one sequence at 16,384 and at 32,768 tokens
+        for name, context in (("decode_b1_context16k", 16384), ("decode_b1_context32k", 32768)):
+            point_ms, _ = time_decode(long_engine(engine, context), 1, context, max(8, steps // 8), warmup)
+            points[name] = round(1 / point_ms * 1e3, 1)
 
     line = {
         "metric": "decode tokens/s at batch 8 (Qwen3-4B sizes, bf16, random weights)",

@@ -3,6 +3,7 @@ as the reference has none).
 
     python -m dryft_flash_infer_b200 generate --model DIR --prompt-ids prompts.json --max-new-tokens 32
     python -m dryft_flash_infer_b200 generate --model DIR --random-prompts 4:128 --max-new-tokens 16 --temperature 0.8 --seed 1
+    python -m dryft_flash_infer_b200 generate --random-config config.json --random-prompts 8:512 --max-new-tokens 64
     python -m dryft_flash_infer_b200 random-model --config config.json --seed 0 --out DIR
 
 ``generate`` prints one JSON line per output step (the list that ``Engine.generate`` yields)
@@ -27,7 +28,14 @@ def _generate(args) -> int:
     options = {"dtype": args.dtype}
     if args.cuda_graph is not None:
         options["cuda_graph"] = args.cuda_graph == "on"
-    engine = Engine(args.model, **options)
+    if (args.model is None) == (args.random_config is None):
+        raise SystemExit("give either --model DIR or --random-config CONFIG_JSON")
+    if args.model is not None:
+        engine = Engine(args.model, **options)
+    else:
+        # a model of random weights made on the device from a configuration file: no folder is written
+        with open(args.random_config) as fh:
+            engine = Engine(config=json.load(fh), random_weights=True, seed=args.seed, **options)
     if args.prompt_ids:
         with open(args.prompt_ids) as fh:
             prompts = json.load(fh)
@@ -70,7 +78,9 @@ def main(argv=None) -> int:
                                      formatter_class=argparse.RawDescriptionHelpFormatter)
     sub = parser.add_subparsers(dest="command", required=True)
     gen = sub.add_parser("generate", help="continue prompts given as token ids")
-    gen.add_argument("--model", required=True, help="folder with config.json and model.safetensors")
+    gen.add_argument("--model", help="folder with config.json and model.safetensors")
+    gen.add_argument("--random-config", metavar="CONFIG_JSON",
+                     help="instead of --model: a config.json of the architecture; the weights are random (--seed)")
     gen.add_argument("--prompt-ids", help="JSON file: a list of lists of token ids")
     gen.add_argument("--random-prompts", metavar="BATCH:LENGTH", help="seeded uniform-random prompts instead")
     gen.add_argument("--max-new-tokens", type=int, required=True)

@@ -156,8 +156,8 @@ __device__ __forceinline__ FinishInput finish_begin(const RowFusion& fusion, con
     in.norm_weight = make_float4(0.f, 0.f, 0.f, 0.f);
     in.inside = col < s.N;       // N is a multiple of 4 with an add-norm output: a group is inside the matrix or outside it
     if (!SWIGLU && fusion.residual != nullptr && in.inside) {
-        in.residual = *reinterpret_cast<const uint2*>(fusion.residual + (size_t)b * s.N + col);
-        in.norm_weight = *reinterpret_cast<const float4*>(fusion.norm_weight + col);
+        in.residual = __ldcg(reinterpret_cast<const uint2*>(fusion.residual + (size_t)b * s.N + col));
+        in.norm_weight = __ldg(reinterpret_cast<const float4*>(fusion.norm_weight + col));
     }
     return in;
 }
@@ -515,16 +515,34 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     if (CLUSTER) {
         // every thread of every CTA of the cluster comes here, whatever happened to it before
         __syncwarp();
+        const int ep_t = (warp & 3) * 32 + lane;
+        const int ep_parts = s.parts, ep_rank = (int)cluster_rank();
+        const int ep_pad = 1 << cl_pad_log2;                    // lanes per row: a power of two that holds the owned groups
+        const int ep_total = s.M << cl_pad_log2;
+        const int ep_rounded = (ep_total + 31) & ~31;      // whole warps: the lanes of a row share its sum of squares
+        // What the first pass of the epilogue needs from memory besides the sums (the old residual, the norm's
+        // weight) depends on no other CTA of the cluster: it is asked for before the barrier and travels
+        // while the CTAs meet.
+        FinishInput ahead[2] = {};
+        if (warp >= 2) {
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const int item = ep_t + u * 128;
+                const int j = item & (ep_pad - 1);
+                if ((u == 0 || ep_t + 128 < ep_rounded) && item < ep_total && j < cl_owned)
+                    ahead[u] = finish_begin<false>(fusion, s, first_rb * kTileM + (ep_rank + ep_parts * j) * 4, item >> cl_pad_log2);
+            }
+        }
         if (threadIdx.x == 64) trace(4);
         cluster_sync_all();
         if (threadIdx.x == 64) trace(5);
         if (warp >= 2) {
-            const int t = (warp & 3) * 32 + lane;
-            const int parts = s.parts, rank = (int)cluster_rank();
+            const int t = ep_t;
+            const int parts = ep_parts, rank = ep_rank;
             const int stride = cl_stride, n_owned = cl_owned, pad_log2 = cl_pad_log2;
-            const int pad = 1 << pad_log2;                      // lanes per row: a power of two that holds the owned groups
-            const int total = s.M << pad_log2;
-            const int rounded = (total + 31) & ~31;        // whole warps: the lanes of a row share its sum of squares
+            const int pad = ep_pad;
+            const int total = ep_total;
+            const int rounded = ep_rounded;
             const int ssq_part = first_rb * parts + rank;
             const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
             // two items per pass: the second one's loads from memory travel with the first one's
@@ -541,7 +559,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                     row[u] = item >> pad_log2;
                     active[u] = (u == 0 || two) && item < total && j < n_owned;
                     col[u] = first_rb * kTileM + (rank + parts * j) * 4;
-                    if (active[u]) in[u] = finish_begin<false>(fusion, s, col[u], row[u]);
+                    if (active[u]) in[u] = first == t ? ahead[u] : finish_begin<false>(fusion, s, col[u], row[u]);
                 }
 #pragma unroll
                 for (int u = 0; u < 2; ++u) {

@@ -42,6 +42,22 @@ def test_generate_prints_one_line_per_step(tmp_path):
     assert [json.loads(l) for l in again.stdout.strip().splitlines()][:5] == lines[:5]
 
 
+@pytest.mark.gpu
+def test_generate_from_a_configuration_alone(tmp_path):
+    """``--random-config``: a model of random weights without a folder on disk; the same seed, the same tokens."""
+    (tmp_path / "c.json").write_text(json.dumps(plain_model.TINY_A))
+    args = ("generate", "--random-config", str(tmp_path / "c.json"), "--random-prompts", "3:9", "--max-new-tokens", "4",
+            "--seed", "7", "--dtype", "float32")
+    first, second = run(*args), run(*args)
+    assert first.returncode == 0, first.stderr
+    rows = [json.loads(l) for l in first.stdout.strip().splitlines()]
+    assert len(rows) == 5 and all(len(r) == 3 for r in rows[:4]) and first.stdout == second.stdout.replace(
+        second.stdout.strip().splitlines()[-1], first.stdout.strip().splitlines()[-1])
+    both = run("generate", "--random-config", str(tmp_path / "c.json"), "--model", str(tmp_path), "--random-prompts", "1:2",
+               "--max-new-tokens", "1")
+    assert both.returncode != 0 and "either" in both.stderr
+
+
 def bench(*args):
     return subprocess.run([sys.executable, str(ROOT / "bench.py"), *args], cwd=ROOT, capture_output=True, text=True)
 
