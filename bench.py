@@ -426,14 +426,21 @@ def main() -> int:
             point_ms, _ = time_decode(engine, n, PROMPT_OF_POINTS + steps + warmup + 1, steps, warmup)
             points[name] = round(n / point_ms * 1e3, 1)
         # ---- end to end through Engine.generate: host token lists in, host token lists out
-        prompts = [torch.randint(0, cfg["vocab_size"], (CONTEXT - steps - 1,), generator=g).tolist() for _ in range(BATCH)]
-        stream = engine.generate(prompts, steps + 1)
-        next(stream)                                   # the prefill and the first token
+        # (as for ``value`` and for the reference arm: W untimed decode steps first, then K timed ones that end
+        # at the benchmark context.  The stream runs one step ahead of its reader, so after the first token
+        # and W more rows W + 1 steps have been launched and K are left.)
+        new = steps + warmup + 2
+        prompts = [torch.randint(0, cfg["vocab_size"], (CONTEXT - new,), generator=g).tolist() for _ in range(BATCH)]
+        stream = engine.generate(prompts, new)
+        for _ in range(1 + warmup):
+            next(stream)                               # the prefill and the first token, then the warm-up steps
         torch.cuda.synchronize()
         begin = time.perf_counter()
-        produced = sum(1 for _ in stream)
+        rows = sum(1 for _ in stream)
         torch.cuda.synchronize()
         elapsed = time.perf_counter() - begin
+        assert rows == steps + 1
+        produced = steps
         batch = next(iter(b for b in engine.decoder.batches.values() if b.n == BATCH))
         e2e = {"value": round(BATCH * produced / elapsed, 1), "unit": "tokens/s",
                "h2d_bytes_per_step": int(batch.h2d_bytes_per_step),

@@ -7,7 +7,9 @@
 // by row block and dealt to the CTAs in equal contiguous runs (stream-K), so that every SM reads
 // the same number of bytes even when W has few rows.  Inside a CTA: warp 0 feeds a ring of
 // shared-memory stages with TMA, warp 1 issues the MMAs into one of two TMEM accumulators, warps
-// 2-5 drain the other.  A CTA whose run covers a whole row block stores the result itself;
+// 2-9 drain the other (two warps for each quarter of the lanes, which share its columns) and run the
+// epilogue: its chains of dependent instructions are what a step of many rows waits for, so they are
+// spread over eight warps, two to a scheduler.  A CTA whose run covers a whole row block stores the result itself;
 // otherwise it leaves float32 partial sums in scratch memory and takes a ticket from the row
 // block's counter, and the CTA that draws the last ticket adds the parts in the order of their k
 // ranges (the result does not depend on who finished when), applies the epilogue and resets the
@@ -39,7 +41,8 @@
 
 namespace dfi {
 
-constexpr int kDecThreads = 192;
+constexpr int kEpThreads = 256;              // the epilogue's threads: eight warps, two for each quarter of the TMEM lanes
+constexpr int kDecThreads = 64 + kEpThreads; // producer warp, issuing warp, epilogue warps
 constexpr int kDecSmemBudget = 110 * 1024;   // two CTAs fit an SM: the next kernel sets up and loads weights beside this one
 
 struct StreamShape {
@@ -85,7 +88,7 @@ __device__ __forceinline__ int sk_cta_of_unit(const StreamShape& s, int u) {
     while (c > 0 && sk_run_begin(s, c) > u) --c;
     return c;
 }
-__device__ __forceinline__ void epilogue_barrier() { asm volatile("bar.sync 1, 128;\n" ::: "memory"); }
+__device__ __forceinline__ void epilogue_barrier() { asm volatile("bar.sync 1, %0;\n" ::"n"(kEpThreads) : "memory"); }
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(s32(bar)) : "memory");
 }
@@ -230,7 +233,7 @@ __device__ __forceinline__ void finish_group(const RowFusion& fusion, const Stre
 }
 
 template <int BN, bool SWIGLU, bool CLUSTER>
-__global__ void __launch_bounds__(kDecThreads, 1)
+__global__ void __launch_bounds__(kDecThreads, 2)
 gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                    void* __restrict__ out, StreamShape s, float* __restrict__ partials, int* __restrict__ counters,
                    int out_dtype, RowFusion fusion) {
@@ -279,7 +282,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(&acc_full[i], 1);
-            mbar_init(&acc_empty[i], 128);
+            mbar_init(&acc_empty[i], kEpThreads);
         }
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         // The weights depend on no earlier kernel and on no other thread of this CTA: the first
@@ -352,9 +355,15 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             }
         }
     } else {
-        // warps 2..5: thread t of the 128 holds row `t` of the row block (TMEM lane t)
+        // warps 2..9: thread t of a set of four warps holds row `t` of the row block (TMEM lane t); the two sets
+        // share the batch's columns when there are 32 or more, and the work of the epilogue always
         const int quarter = warp & 3;
         const int t = quarter * 32 + lane;
+        const int half = (warp - 2) >> 2;
+        const int t2 = half * 128 + t;                         // 0..255: this thread's place in the epilogue's work
+        constexpr bool kSplitCols = BN >= 32;
+        const int c_begin = kSplitCols ? half * (BN / 2) : 0;
+        const int c_end = kSplitCols ? c_begin + BN / 2 : (half == 0 ? BN : 0);
         int rb = first_rb, seg_first_kc = first_kc, done = 0, segment = 0;
         bool ok = true;
         uint32_t cl_dest = 0;
@@ -375,11 +384,11 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         if (fusion.in_ssq != nullptr || fusion.residual != nullptr) {
             pdl_wait();          // these threads read what the kernel before wrote
             if (fusion.in_ssq != nullptr) {
-                if (t < BN) {
+                if (t2 < BN) {
                     float ssq = 0.f;
-                    if (t < s.M)
-                        for (int p = 0; p < fusion.in_parts; ++p) ssq += fusion.in_ssq[p * kSsqStride + t];
-                    row_scale[t] = 1.0f / sqrtf(ssq * fusion.in_inv_dim + fusion.in_eps);
+                    if (t2 < s.M)
+                        for (int p = 0; p < fusion.in_parts; ++p) ssq += fusion.in_ssq[p * kSsqStride + t2];
+                    row_scale[t2] = 1.0f / sqrtf(ssq * fusion.in_inv_dim + fusion.in_eps);
                 }
                 epilogue_barrier();
             }
@@ -393,12 +402,12 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             constexpr bool kTurn = BN > 16;
             float* turn = reinterpret_cast<float*>(ring);
             ok = mbar_wait(&acc_full[0], 0, 3);
-            if (t == 0) trace(3);
+            if (t2 == 0) trace(3);
             if (ok) {
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                 const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-#pragma unroll
-                for (int c = 0; c < BN; c += 16) {
+                for (int c = c_begin; c < c_end; c += 16) {
+                    if (c >= s.M) break;                 // the same for a whole warp: columns past the batch hold nothing
                     uint32_t d[16];
                     tmem_load16(taddr + c, d);
 #pragma unroll
@@ -414,8 +423,9 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             if (kTurn) {
                 epilogue_barrier();
                 if (ok) {
-                    const int group = t & 31;                                    // the same in every pass: 128 = 4 x 32
-                    for (int b = t >> 5; b < s.M; b += 4)
+                    // (cl_dest was made from t: the same group for t2 and t2 + 128, since 128 = 4 x 32)
+                    const int group = t2 & 31;
+                    for (int b = t2 >> 5; b < s.M; b += kEpThreads / 32)
                         cluster_store4(cl_dest + (uint32_t)(b * cl_stride * 4),
                                        *reinterpret_cast<const float4*>(turn + b * kTileM + group * 4));
                 }
@@ -427,7 +437,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             const int buf = segment & 1;
             ok = mbar_wait(&acc_full[buf], (segment >> 1) & 1, 3);
             if (!ok) break;
-            if (t == 0 && done + seg_units >= n_units) trace(3);
+            if (t2 == 0 && done + seg_units >= n_units) trace(3);
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN;
             // D[t][b] goes, transposed, either to the staging buffer (this CTA summed the whole row
@@ -435,8 +445,8 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             // reads along the row block
             float* dest = complete ? staging
                                    : partials + ((size_t)cta * 2 + (rb == first_rb ? 0 : 1)) * Cfg::kSlotFloats;
-#pragma unroll
-            for (int c = 0; c < BN; c += 16) {
+            for (int c = c_begin; c < c_end; c += 16) {
+                if (c >= s.M) break;                     // the same for a whole warp
                 uint32_t d[16];
                 tmem_load16(taddr + c, d);
 #pragma unroll
@@ -454,7 +464,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 c_first = sk_cta_of_unit(s, rb_first_unit);
                 c_last = sk_cta_of_unit(s, rb_first_unit + s.k_chunks - 1);
                 first_slot = sk_run_begin(s, c_first) >= rb_first_unit ? 0 : 1;
-                if (t == 0) {
+                if (t2 == 0) {
                     if (done + seg_units >= n_units) trace(4);
                     // one acquire-release add at GPU scope: this CTA's part (ordered before it by the barrier
                     // above) is visible to whoever reads a later ticket, and the earlier parts are visible here
@@ -473,7 +483,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                                                    : partials + ((size_t)c_first * 2 + first_slot) * Cfg::kSlotFloats;
                 const float* next_part = partials + ((size_t)c_first * 2 + 2) * Cfg::kSlotFloats;
                 const int n_more = complete ? 0 : c_last - c_first;
-                for (int item = t; item < s.M * kGroups; item += 128) {
+                for (int item = t2; item < s.M * kGroups; item += kEpThreads) {
                     const int b = item / kGroups, c4 = (item % kGroups) * 4;
                     const int offset = b * kTileM + c4;
                     const FinishInput in = finish_begin<SWIGLU>(fusion, s, rb * kCols + c4, b);
@@ -502,9 +512,9 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                     // a warp holds one row's columns of this row block: 32 lanes share a sum of squares
                     finish_group<SWIGLU>(fusion, s, out, out_dtype, row_scale, in, rb * kCols + c4, b, v, u, true, 32, rb, lane);
                 }
-                if (!complete && t == 0) counters[rb] = 0;   // ready for the next call
+                if (!complete && t2 == 0) counters[rb] = 0;   // ready for the next call
             }
-            if (t == 0 && done + seg_units >= n_units) trace(6);
+            if (t2 == 0 && done + seg_units >= n_units) trace(6);
             epilogue_barrier();          // staging is free for the next row block
             done += seg_units;
             seg_first_kc = 0;
@@ -515,7 +525,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     if (CLUSTER) {
         // every thread of every CTA of the cluster comes here, whatever happened to it before
         __syncwarp();
-        const int ep_t = (warp & 3) * 32 + lane;
+        const int ep_t = warp >= 2 ? ((warp - 2) >> 2) * 128 + (warp & 3) * 32 + lane : 0;
         const int ep_parts = s.parts, ep_rank = (int)cluster_rank();
         const int ep_pad = 1 << cl_pad_log2;                    // lanes per row: a power of two that holds the owned groups
         const int ep_total = s.M << cl_pad_log2;
@@ -527,9 +537,9 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         if (warp >= 2) {
 #pragma unroll
             for (int u = 0; u < 2; ++u) {
-                const int item = ep_t + u * 128;
+                const int item = ep_t + u * kEpThreads;
                 const int j = item & (ep_pad - 1);
-                if ((u == 0 || ep_t + 128 < ep_rounded) && item < ep_total && j < cl_owned)
+                if ((u == 0 || ep_t + kEpThreads < ep_rounded) && item < ep_total && j < cl_owned)
                     ahead[u] = finish_begin<false>(fusion, s, first_rb * kTileM + (ep_rank + ep_parts * j) * 4, item >> cl_pad_log2);
             }
         }
@@ -546,15 +556,15 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             const int ssq_part = first_rb * parts + rank;
             const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
             // two items per pass: the second one's loads from memory travel with the first one's
-            for (int first = t; first < rounded; first += 256) {
-                const bool two = first + 128 < rounded;     // the same for a whole warp
+            for (int first = t; first < rounded; first += 2 * kEpThreads) {
+                const bool two = first + kEpThreads < rounded;     // the same for a whole warp
                 FinishInput in[2] = {};
                 float4 v[2] = {zero4, zero4};
                 int col[2], row[2];
                 bool active[2];
 #pragma unroll
                 for (int u = 0; u < 2; ++u) {
-                    const int item = first + u * 128;
+                    const int item = first + u * kEpThreads;
                     const int j = item & (pad - 1);
                     row[u] = item >> pad_log2;
                     active[u] = (u == 0 || two) && item < total && j < n_owned;
@@ -564,7 +574,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 #pragma unroll
                 for (int u = 0; u < 2; ++u) {
                     if (active[u]) {
-                        const float* from = staging + row[u] * stride + ((first + u * 128) & (pad - 1)) * 4;
+                        const float* from = staging + row[u] * stride + ((first + u * kEpThreads) & (pad - 1)) * 4;
 #pragma unroll
                         for (int p = 0; p < 8; ++p) {
                             if (p < parts) {
