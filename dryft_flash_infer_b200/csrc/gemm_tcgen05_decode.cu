@@ -16,12 +16,12 @@
 // counter.  No CTA waits for another CTA; waits inside a CTA (on its own mbarriers) are bounded.
 //
 // CLUSTER variant, for a matrix with few row blocks cut into 2 to 8 parts each: the CTAs of a row
-// block form a thread-block cluster and add their parts through distributed shared memory instead
-// of scratch memory and tickets.  Every CTA owns the columns c of the row block with (c / 4) mod
-// parts equal to its rank; each CTA stores its sums for a column straight into the owner's shared
-// memory (for a batch above 16 rows four columns at a time, after turning them in its own shared
-// memory), all CTAs meet once at the cluster barrier, and every owner adds the parts in the order
-// of their k ranges and applies the epilogue to its columns.
+// block form a thread-block cluster and meet once at the cluster barrier instead of taking tickets.
+// Every CTA owns the columns c of the row block with (c / 4) mod parts equal to its rank.  With a
+// batch of at most 16 rows each CTA stores its sums for a column straight into the owner's shared
+// memory; with more rows it writes its part to scratch memory and the owners read their columns
+// from there after the barrier (the barrier's release and acquire order both).  Every owner adds
+// the parts in the order of their k ranges and applies the epilogue to its columns.
 //
 // Two optional fusions with the RMS norm around the product, both in the adding CTA's epilogue:
 // * scaled input: x holds rows w (.) r that still lack their 1/rms factor; the sums of squares of r
@@ -131,18 +131,18 @@ __device__ __forceinline__ void trace(int slot) {
 __device__ __forceinline__ void trace(int) {}
 #endif
 
-template <int BN> struct DecConfig {
+template <int BN, bool CLUSTER> struct DecConfig {
     static constexpr int kABytes = kTileM * kTileK * 2;
     static constexpr int kBBytes = BN * kTileK * 2;
     static constexpr int kStageBytes = kABytes + kBBytes;
-    static constexpr int kStagingBytes = BN * 144 * 4;               // float [BN][128] for the epilogue; in a cluster
-                                                                     // [parts][BN][owned columns], at most 144 BN floats
+    // float [BN][128] for the epilogue; in a cluster [parts][BN][owned columns], at most 144 BN floats; none in a
+    // cluster with more than 16 rows, whose parts meet through scratch memory
+    static constexpr int kStagingBytes = (CLUSTER && BN > 16) ? 0 : BN * 144 * 4;
     static constexpr int kStagesRaw = (kDecSmemBudget - 1024 - kStagingBytes) / kStageBytes;
     static constexpr int kStages = kStagesRaw > 10 ? 10 : kStagesRaw;
     static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;      // two accumulators
     static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024;
     static constexpr int kSlotFloats = BN * kTileM;                  // one part of one row block
-    static_assert(kStagesRaw < 2 || kStages * kStageBytes >= BN * kTileM * 4, "the ring also holds a CTA's sums, turned, at the end");
 };
 
 // What the epilogue of one group of four columns needs from memory besides the sums: asked for
@@ -237,7 +237,7 @@ __global__ void __launch_bounds__(kDecThreads, 2)
 gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                    void* __restrict__ out, StreamShape s, float* __restrict__ partials, int* __restrict__ counters,
                    int out_dtype, RowFusion fusion) {
-    using Cfg = DecConfig<BN>;
+    using Cfg = DecConfig<BN, CLUSTER>;
     if (threadIdx.x == 0) trace(0);
     pdl_launch_next();
     extern __shared__ unsigned char smem_raw[];
@@ -395,12 +395,13 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         }
         if (CLUSTER) {
             // The run is one part of row block first_rb: every sum goes to the CTA that owns its column.
-            // A thread holds one row of the block, a group is four neighbouring rows.  With few rows in
-            // the batch every sum travels on its own; with many, the sums are turned in this CTA's shared
-            // memory first (the ring is free: every MMA that read it is complete), so that a group
-            // travels as one 16-byte store.
+            // A thread holds one row of the block, a group is four neighbouring rows.  With at most 16 rows
+            // in the batch every sum travels on its own into the owner's shared memory.  With more, the
+            // remote stores (32 KB a CTA at 64 rows) took longer to land than the whole stream of a small
+            // matrix takes: the CTA writes its part to scratch memory instead, rows of the batch along the
+            // row block (512 contiguous bytes a warp), and the owners read their columns from L2.
             constexpr bool kTurn = BN > 16;
-            float* turn = reinterpret_cast<float*>(ring);
+            float* turn = partials + (size_t)cta * 2 * Cfg::kSlotFloats;      // this CTA's part, [row of the batch][row of the block]
             ok = mbar_wait(&acc_full[0], 0, 3);
             if (t2 == 0) trace(3);
             if (ok) {
@@ -420,16 +421,8 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 }
                 asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
             }
-            if (kTurn) {
-                epilogue_barrier();
-                if (ok) {
-                    // (cl_dest was made from t: the same group for t2 and t2 + 128, since 128 = 4 x 32)
-                    const int group = t2 & 31;
-                    for (int b = t2 >> 5; b < s.M; b += kEpThreads / 32)
-                        cluster_store4(cl_dest + (uint32_t)(b * cl_stride * 4),
-                                       *reinterpret_cast<const float4*>(turn + b * kTileM + group * 4));
-                }
-            }
+            // (kTurn: the sums lie in scratch memory now; the cluster barrier below, with its release and acquire at
+            // cluster scope, makes them visible to the CTAs that own their columns)
         }
         while (!CLUSTER && done < n_units && ok) {
             const int seg_units = min(s.k_chunks - seg_first_kc, n_units - done);
@@ -574,12 +567,25 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 #pragma unroll
                 for (int u = 0; u < 2; ++u) {
                     if (active[u]) {
-                        const float* from = staging + row[u] * stride + ((first + u * kEpThreads) & (pad - 1)) * 4;
+                        if (BN > 16) {
+                            // the parts lie in scratch memory, one slot per CTA of the cluster (neighbours in the grid)
+                            const float* from = partials + (size_t)(cta - rank) * 2 * Cfg::kSlotFloats + row[u] * kTileM +
+                                                (rank + parts * ((first + u * kEpThreads) & (pad - 1))) * 4;
+                            float4 w4[8];
 #pragma unroll
-                        for (int p = 0; p < 8; ++p) {
-                            if (p < parts) {
-                                const float4 w4 = *reinterpret_cast<const float4*>(from + p * BN * stride);
-                                v[u].x += w4.x; v[u].y += w4.y; v[u].z += w4.z; v[u].w += w4.w;
+                            for (int p = 0; p < 8; ++p)
+                                w4[p] = p < parts ? __ldcg(reinterpret_cast<const float4*>(from + (size_t)p * 2 * Cfg::kSlotFloats))
+                                                  : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                            for (int p = 0; p < 8; ++p) { v[u].x += w4[p].x; v[u].y += w4[p].y; v[u].z += w4[p].z; v[u].w += w4[p].w; }
+                        } else {
+                            const float* from = staging + row[u] * stride + ((first + u * kEpThreads) & (pad - 1)) * 4;
+#pragma unroll
+                            for (int p = 0; p < 8; ++p) {
+                                if (p < parts) {
+                                    const float4 w4 = *reinterpret_cast<const float4*>(from + p * BN * stride);
+                                    v[u].x += w4.x; v[u].y += w4.y; v[u].z += w4.z; v[u].w += w4.w;
+                                }
                             }
                         }
                     }
@@ -623,7 +629,7 @@ static int dec_sm_count() {
 template <int BN, bool SWIGLU, bool CLUSTER>
 static int launch_decode(const void* x, const void* w, void* out, StreamShape s, float* partials, int* counters,
                          int out_dtype, const RowFusion& fusion, cudaStream_t st) {
-    using Cfg = DecConfig<BN>;
+    using Cfg = DecConfig<BN, CLUSTER>;
     static_assert(Cfg::kStages >= 2, "the ring needs at least two stages");
     static bool configured = false;
     if (!configured) {
