@@ -98,7 +98,10 @@ __device__ __forceinline__ void tmem_load16(uint32_t taddr, uint32_t (&r)[16]) {
         : "r"(taddr));
     asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 }
-__device__ __forceinline__ float silu_times(float gate, float up) { return gate / (1.0f + expf(-gate)) * up; }
+// silu(gate) * up for an epilogue whose result is rounded to bfloat16: the fast exponential and division
+// (a few units in the last place of float32) cost a quarter of the instructions of the exact ones, and the
+// epilogue of a step of many rows is a chain of such instructions.
+__device__ __forceinline__ float silu_times(float gate, float up) { return __fdividef(gate, 1.0f + __expf(-gate)) * up; }
 
 
 // A [rows, K] bfloat16 matrix (row stride K) as a TMA map with boxes of box_rows x 64, 128-byte swizzle.
