@@ -13,7 +13,11 @@ constexpr int kTileK = 64;                    // 64 bfloat16 = 128 bytes: one sw
 constexpr int kUmmaK = 16;
 constexpr int kTcThreads = 192;
 constexpr int kSmemBudget = 200 * 1024;
-constexpr uint32_t kSpinLimit = 1u << 22;     // tries of mbarrier.try_wait before giving up
+// Tries of mbarrier.try_wait before a wait gives up.  A try that does not succeed returns after a few
+// microseconds (the hardware's own time limit), so this bound is about a second: no wait of these kernels
+// lasts longer than microseconds unless something is broken, and a broken kernel then ends in a second
+// (measured: a deadlock built by mistake ended after 16 s with a bound of 2^22) with its code recorded.
+constexpr uint32_t kSpinLimit = 1u << 18;
 
 enum { MODE_NORMAL = 0, MODE_SWIGLU = 1, MODE_SWAP = 2, MODE_NN = 3 };
 
