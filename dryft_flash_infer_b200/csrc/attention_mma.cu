@@ -590,9 +590,15 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
                                      : head_load(raw, nullptr, nullptr, nullptr, pos, lane);
             }
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
-                head_finish(rows_in[i], prep.q_weight != nullptr, prep.eps, prep.cos_table != nullptr,
-                            q_s + (warp + 4 * i) * kStride, nullptr, lane);
+            for (int i = 0; i < 4; ++i) {
+                // rows past the group are the padding of the 16-row MMA tile: zeros, without the norm's and the
+                // rotation's chains of shuffles (with four query heads a group, three of a warp's four rows)
+                if (warp + 4 * i < group)
+                    head_finish(rows_in[i], prep.q_weight != nullptr, prep.eps, prep.cos_table != nullptr,
+                                q_s + (warp + 4 * i) * kStride, nullptr, lane);
+                else if (lane < D / 4)
+                    *reinterpret_cast<uint2*>(q_s + (warp + 4 * i) * kStride + 4 * lane) = make_uint2(0u, 0u);
+            }
         } else {
             for (int i = threadIdx.x; i < 16 * kChunks; i += kThreads) {
                 const int row = i / kChunks, c = i % kChunks;
