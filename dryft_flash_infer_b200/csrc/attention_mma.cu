@@ -291,11 +291,16 @@ struct DecodeRun {
     int n_ctas;
     int parts;      // > 0: every group has `tiles` pages and is cut into this many parts, one CTA each
     int tiles;
+    int whole;      // > 0: every group has `tiles` pages, there are this many groups, and a CTA takes whole groups
 };
 // First unit of a CTA's run: equal contiguous runs over all units, or (when every sequence brings
 // the same number of pages) the same number of parts for every group, so that no run crosses from
-// one group into the next.
+// one group into the next, or (many short groups) whole groups only, so that nothing is merged.
 __device__ __forceinline__ int dec_run_begin(const DecodeRun& r, int cta) {
+    if (r.whole > 0) {
+        if (cta >= r.n_ctas) return r.total;
+        return (int)((long long)r.whole * cta / r.n_ctas) * r.tiles;
+    }
     if (r.parts > 0) {
         if (cta >= r.n_ctas) return r.total;
         return (cta / r.parts) * r.tiles + r.tiles * (cta % r.parts) / r.parts;
@@ -304,7 +309,8 @@ __device__ __forceinline__ int dec_run_begin(const DecodeRun& r, int cta) {
 }
 __device__ __forceinline__ int dec_cta_of_unit(const DecodeRun& r, int u) {
     int c;
-    if (r.parts > 0) c = (u / r.tiles) * r.parts + min(r.parts - 1, (u % r.tiles) * r.parts / r.tiles);
+    if (r.whole > 0) c = (int)((long long)(u / r.tiles) * r.n_ctas / r.whole);
+    else if (r.parts > 0) c = (u / r.tiles) * r.parts + min(r.parts - 1, (u % r.tiles) * r.parts / r.tiles);
     else c = (int)((unsigned long long)u * (unsigned)r.n_ctas / (unsigned)r.total);
     while (c + 1 < r.n_ctas && dec_run_begin(r, c + 1) <= u) ++c;
     while (c > 0 && dec_run_begin(r, c) > u) --c;
@@ -486,6 +492,7 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
     const int least = max(4, (longest + kMaxGroupParts - 3) / (kMaxGroupParts - 2));
     run.n_ctas = max(1, min((int)gridDim.x, run.total / least));
     run.parts = 0;
+    run.whole = 0;
     run.tiles = longest;
     if (shortest == longest) {
         // every group has the same number of pages: the same number of parts for each, none crossing over
@@ -496,6 +503,16 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
         if (n_seqs * n_kv * parts <= (int)gridDim.x && n_seqs * n_kv * parts * 100 >= run.n_ctas * 80) {
             run.parts = parts;
             run.n_ctas = n_seqs * n_kv * parts;
+        } else if (n_seqs * n_kv >= (int)gridDim.x) {
+            // more groups than CTAs (many short sequences): equal runs would cut most groups in two, and every
+            // cut costs a preparation of the queries, two stores of partial results, a ticket and a merge,
+            // about three pages' worth of time.  Whole groups per CTA cost the busiest CTA a few pages more.
+            const int groups = n_seqs * n_kv;
+            const int busiest = (groups + (int)gridDim.x - 1) / (int)gridDim.x;
+            if (busiest * longest <= run.total / (int)gridDim.x + 3) {
+                run.whole = groups;
+                run.n_ctas = (int)gridDim.x;
+            }
         }
     }
     // When the launch groups CTAs into clusters and every group of this step is cut into exactly that

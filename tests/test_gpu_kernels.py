@@ -278,6 +278,26 @@ def test_attention_tensor_core_decode_dealt_to_any_number_of_ctas(n_q, n_kv, dim
         assert torch.equal(again, got)                 # the counters were left ready; the order of the merge is fixed
 
 
+@pytest.mark.parametrize("n_q, n_kv, dim", [(8, 2, 128), (4, 4, 32)])
+def test_attention_decode_with_more_groups_than_ctas_takes_whole_groups(n_q, n_kv, dim):
+    """Many short sequences of one length: with more (sequence, head) groups than CTAs a CTA takes whole groups,
+    one after another, and nothing is merged.  The CTA counts are chosen so that the busiest CTA holds two
+    or three groups and some hold one fewer; a count that does not qualify (few CTAs, long runs) runs beside them."""
+    from dryft_flash_infer_b200.ops import kernels
+
+    dtype = torch.bfloat16
+    n_seqs = 40
+    lengths, new = [170] * n_seqs, [1] * n_seqs                  # three pages each, the last one a third full
+    q, cache, row_seq, row_pos, scale, want = attention_case(dtype, n_q, n_kv, dim, lengths, new, seed=dim + 1, sharp=60)
+    ctx = step_like(lengths, new)
+    groups = n_seqs * n_kv
+    for ctas in (groups, groups // 2, groups // 2 + 7, groups // 3 + 1, 5):
+        got = kernels.attention_decode(q, cache, ctx, n_q, n_kv, dim, scale, n_ctas=ctas)
+        assert torch.isfinite(got).all()
+        assert torch.allclose(got.float().cpu(), want, atol=tol(dtype, 2), rtol=tol(dtype)), ctas
+        assert torch.equal(kernels.attention_decode(q, cache, ctx, n_q, n_kv, dim, scale, n_ctas=ctas), got)
+
+
 @pytest.mark.parametrize("n_q, n_kv, dim", [(4, 4, 16), (16, 1, 32), (3, 1, 64), (32, 8, 128)])
 @pytest.mark.parametrize("qk_norm, rotary, window, ring", [(True, True, 0, 0), (False, False, 0, 0), (True, True, 100, 192)])
 def test_attention_decode_that_prepares_the_tokens_itself(n_q, n_kv, dim, qk_norm, rotary, window, ring):
