@@ -321,6 +321,7 @@ def main() -> int:
     parser.add_argument("--profile", choices=["decode", "prefill", "timeline"],
                         help="run only a few plain (graph-less) decode steps or one prefill, for a profiler; prints no JSON")
     parser.add_argument("--batch", type=int, default=BATCH, help="batch of the --profile decode steps")
+    parser.add_argument("--context", type=int, default=CONTEXT, help="context length of the --profile decode steps")
     parser.add_argument("--shape", choices=["4b", "8b", "14b"], default="4b",
                         help="8b / 14b: the end-to-end generation runs of the larger shapes instead of the headline run")
     args = parser.parse_args()
@@ -349,15 +350,16 @@ def main() -> int:
     g = torch.Generator().manual_seed(0)
     if args.profile == "decode":
         engine.decoder.use_graph = False
-        ms, launches = time_decode(engine, args.batch, CONTEXT, steps, warmup)
-        print(f"profile run: {steps} plain decode steps at batch {args.batch}, {ms:.3f} ms and {launches} launches per step")
+        ms, launches = time_decode(engine, args.batch, args.context, steps, warmup)
+        print(f"profile run: {steps} plain decode steps at batch {args.batch} and context {args.context}, {ms:.3f} ms and "
+              f"{launches} launches per step")
         return 0
     if args.profile == "timeline":
         # kernel records of one graph replay: when each kernel of a layer ends after the one before it
         from torch.profiler import ProfilerActivity, profile
         from dryft_flash_infer_b200.sampling import SamplingParams
 
-        slots = fill_context(engine, args.batch, CONTEXT - 64)
+        slots = fill_context(engine, args.batch, args.context - 64)
         tokens = [3] * args.batch
         for i in range(5):
             tokens = engine.decode(slots, tokens, list(range(args.batch)), 1 + i, SamplingParams())

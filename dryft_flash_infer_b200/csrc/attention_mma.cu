@@ -497,7 +497,14 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
     if (shortest == longest) {
         // every group has the same number of pages: the same number of parts for each, none crossing over
         const int per_cta = max(least, (run.total + (int)gridDim.x - 1) / (int)gridDim.x);
-        const int parts = max(1, longest / per_cta);
+        int parts = max(1, longest / per_cta);
+        // Short groups with CTAs to spare: four parts each, although that leaves a CTA fewer than four pages.
+        // Four parts meet in a cluster, which costs less than the pages saved (at batch 1 and 8 with some 700
+        // keys a sequence the kernel took 20 us with two parts of five or six pages that met through scratch
+        // memory and a ticket).
+        if (parts < kDecodeCluster && longest >= kDecodeCluster && cluster_size == kDecodeCluster &&
+            n_seqs * n_kv * kDecodeCluster <= (int)gridDim.x)
+            parts = kDecodeCluster;
         // (not if there are more parts than CTAs, nor if they would keep fewer than 80 % of the CTAs busy
         // that equal runs crossing from group to group would: then those runs are used)
         if (n_seqs * n_kv * parts <= (int)gridDim.x && n_seqs * n_kv * parts * 100 >= run.n_ctas * 80) {

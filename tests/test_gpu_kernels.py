@@ -571,3 +571,22 @@ def test_plain_float32_pipe_gemm(m, n, k):
     assert rounded.dtype == torch.bfloat16 and torch.equal(rounded, unrounded.to(torch.bfloat16))
     if k % 8:
         assert torch.equal(kernels.linear(x16.cuda(), w16.cuda()), rounded)  # widths the TMA kernels do not take
+
+
+@pytest.mark.parametrize("n_q, n_kv, dim", [(8, 2, 128), (32, 8, 128), (4, 1, 64)])
+@pytest.mark.parametrize("length", [200, 330, 700, 960])
+def test_attention_decode_of_short_sequences_in_four_parts(n_q, n_kv, dim, length):
+    """Few short sequences of one length (4 to 15 pages): with CTAs to spare every group is cut into four
+    parts of one to four pages, which meet in a cluster."""
+    from dryft_flash_infer_b200.ops import kernels
+
+    dtype = torch.bfloat16
+    n_seqs = 2
+    lengths, new = [length] * n_seqs, [1] * n_seqs
+    q, cache, row_seq, row_pos, scale, want = attention_case(dtype, n_q, n_kv, dim, lengths, new, seed=dim + length, sharp=length // 3)
+    ctx = step_like(lengths, new)
+    for ctas in (None, 4 * n_seqs * n_kv, 4 * n_seqs * n_kv + 8, 7):
+        got = kernels.attention_decode(q, cache, ctx, n_q, n_kv, dim, scale, n_ctas=ctas)
+        assert torch.isfinite(got).all()
+        assert torch.allclose(got.float().cpu(), want, atol=tol(dtype, 2), rtol=tol(dtype)), ctas
+        assert torch.equal(kernels.attention_decode(q, cache, ctx, n_q, n_kv, dim, scale, n_ctas=ctas), got)
