@@ -18,15 +18,18 @@
 // Both follow the online softmax of the reference's split kernel
 // (engine/kernels/attention.py:40-137; merge :140-177): float32 scores, maximum, sum and
 // accumulator; probabilities rounded to bfloat16 for the product with V.  Keys and values
-// come one page (64 tokens) at a time through cp.async into padded shared memory; the
-// tensor-core instruction is mma.sync m16n8k16 (operands in registers via ldmatrix).
+// come one page (64 tokens) at a time; the tensor-core instruction is mma.sync m16n8k16 (operands
+// in registers via ldmatrix).  The decode kernel, for head sizes 64 and 128, fetches a page as TMA
+// boxes of 64 tokens x 64 elements with the 128-byte swizzle (one thread asks, an mbarrier says when
+// the page has landed; ldmatrix applies the same swizzle, which keeps it free of bank conflicts
+// without padding); the other head sizes and the prompt kernel use cp.async into padded rows.
 //
 // Places of the cache that no token was written to may hold anything (NaN included):
 // scores of masked keys are replaced, not added to, and value rows past the sequence's
 // end are zero-filled on load, so such places never reach a result.
 #include <stdlib.h>
 
-#include "common.cuh"
+#include "tcgen05.cuh"
 
 #ifndef DFI_HEAD_DIM
 #define DFI_HEAD_DIM 128
@@ -42,6 +45,16 @@ constexpr int kPage = 64;           // keys per tile = tokens per cache page
 constexpr int kChunks = D / 8;      // 16-byte chunks per row
 constexpr int kThreads = 128;
 constexpr float kLog2e = 1.4426950408889634f;
+constexpr bool kTmaPages = D % 64 == 0;                               // the decode kernel's pages come by TMA
+constexpr int kDecTile = kTmaPages ? kPage * D : kPage * kStride;     // elements of one tile of its ring
+
+// Address of the 16-byte chunk at (row, col), col a multiple of 8, of a tile of 64 rows: padded rows, or
+// (SW) column blocks of 64 elements, each [64 rows][128 bytes] with the chunk index XORed by row mod 8.
+template <bool SW>
+__device__ __forceinline__ const bf16* tile_chunk(const bf16* tile, int row, int col) {
+    if (SW) return tile + (col >> 6) * (kPage * 64) + row * 64 + ((((col & 63) >> 3) ^ (row & 7)) << 3);
+    return tile + row * kStride + col;
+}
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -88,7 +101,7 @@ __device__ __forceinline__ const bf16* page_ptr(const bf16* cache, const int* ta
 }
 
 // S[16 x 8*NT] += Q[16 x D] . K[keys x D]^T for the NT key tiles starting at row `key0` of k_s.
-template <int NT>
+template <int NT, bool SW = false>
 __device__ __forceinline__ void scores(float (&s)[NT][4], const uint32_t (&qf)[D / 16][4], const bf16* k_s, int key0,
                                        int lane) {
     static_assert(NT % 2 == 0, "key tiles come in pairs");
@@ -102,7 +115,7 @@ __device__ __forceinline__ void scores(float (&s)[NT][4], const uint32_t (&qf)[D
 #pragma unroll
         for (int j = 0; j < NT; j += 2) {
             uint32_t b[4];
-            ldmatrix_x4(b, k_s + (key0 + j * 8 + r + (mi >> 1) * 8) * kStride + kk * 16 + (mi & 1) * 8);
+            ldmatrix_x4(b, tile_chunk<SW>(k_s, key0 + j * 8 + r + (mi >> 1) * 8, kk * 16 + (mi & 1) * 8));
             mma_bf16(s[j], qf[kk], b[0], b[1]);
             mma_bf16(s[j + 1], qf[kk], b[2], b[3]);
         }
@@ -110,7 +123,7 @@ __device__ __forceinline__ void scores(float (&s)[NT][4], const uint32_t (&qf)[D
 }
 
 // O[16 x D] += P[16 x 8*NT] . V[keys x D] for the keys starting at row `key0` of v_s.
-template <int NT>
+template <int NT, bool SW = false>
 __device__ __forceinline__ void weighted_values(float (&o)[D / 8][4], const float (&p)[NT][4], const bf16* v_s, int key0,
                                                 int lane) {
     const int mi = lane >> 3, r = lane & 7;
@@ -124,7 +137,7 @@ __device__ __forceinline__ void weighted_values(float (&o)[D / 8][4], const floa
 #pragma unroll
         for (int n = 0; n < D / 8; n += 2) {
             uint32_t b[4];
-            ldmatrix_x4_trans(b, v_s + (key0 + c * 16 + r + (mi & 1) * 8) * kStride + n * 8 + (mi >> 1) * 8);
+            ldmatrix_x4_trans(b, tile_chunk<SW>(v_s, key0 + c * 16 + r + (mi & 1) * 8, n * 8 + (mi >> 1) * 8));
             mma_bf16(o[n], a, b[0], b[1]);
             mma_bf16(o[n + 1], a, b[2], b[3]);
         }
@@ -387,8 +400,9 @@ __device__ __forceinline__ HeadInput head_load(const bf16* src, const float* wei
     }
     return in;
 }
+// `sw_row` >= 0: dst is a swizzled tile (see tile_chunk) and the vector is its row sw_row.
 __device__ __forceinline__ void head_finish(const HeadInput& in, bool norm, float eps, bool rotate, bf16* dst, bf16* dst2,
-                                            int lane) {
+                                            int lane, int sw_row = -1) {
     constexpr int kLanes = D / 4;
     const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&in.raw.x));
     const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&in.raw.y));
@@ -414,7 +428,9 @@ __device__ __forceinline__ void head_finish(const HeadInput& in, bool norm, floa
         uint2 packed;
         *reinterpret_cast<__nv_bfloat162*>(&packed.x) = __floats2bfloat162_rn(v[0], v[1]);
         *reinterpret_cast<__nv_bfloat162*>(&packed.y) = __floats2bfloat162_rn(v[2], v[3]);
-        *reinterpret_cast<uint2*>(dst + 4 * lane) = packed;
+        bf16* at = sw_row < 0 ? dst + 4 * lane
+                              : const_cast<bf16*>(tile_chunk<true>(dst, sw_row, (4 * lane) & ~7)) + ((4 * lane) & 7);
+        *reinterpret_cast<uint2*>(at) = packed;
         if (dst2 != nullptr) *reinterpret_cast<uint2*>(dst2 + 4 * lane) = packed;
     }
 }
@@ -425,7 +441,8 @@ constexpr int kMaxGroupParts = 64;      // CTAs that may share one (sequence, he
 constexpr int kMaxDecodeSeqs = 1024;    // sequences per launch (their page counts sit in shared memory)
 
 __global__ void __launch_bounds__(kThreads)
-attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, int out_stride,
+attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                        const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, int out_stride,
                         const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                         const int* __restrict__ block_table, int table_width, const int* __restrict__ seq_start,
                         int n_seqs, int n_q, int n_kv, int ring_tokens, int window, float scale_log2,
@@ -434,9 +451,36 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
     atrace(0);
     pdl_launch_next();
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    bf16* q_s = reinterpret_cast<bf16*>(smem_raw);   // [16][kStride]
-    bf16* k_s = q_s + 16 * kStride;                  // [kKvStages][64][kStride]
-    bf16* v_s = k_s + kKvStages * kPage * kStride;   // [kKvStages][64][kStride]
+    // the tiles first, on a 1024-byte boundary (the swizzle's period); the query tile behind them
+    bf16* k_s = reinterpret_cast<bf16*>((reinterpret_cast<uintptr_t>(smem_raw) + (kTmaPages ? 1023 : 0)) &
+                                        ~uintptr_t(kTmaPages ? 1023 : 0));   // [kKvStages][tile]
+    bf16* v_s = k_s + kKvStages * kDecTile;          // [kKvStages][tile]
+    bf16* q_s = v_s + kKvStages * kDecTile;          // [16][kStride]
+    __shared__ __align__(8) uint64_t page_bar[kKvStages];     // a page's keys and values have landed (TMA)
+    uint32_t page_parity = 0;                        // bit s: the parity of the next wait on stage s
+    if (kTmaPages && threadIdx.x == 0) {
+        for (int i = 0; i < kKvStages; ++i) mbar_init(&page_bar[i], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    // One page into a stage of the ring: by TMA one thread asks for the boxes (two column blocks of keys, two
+    // of values), else every thread copies its chunks.  `zero_from` is the first key index that holds nothing.
+    auto fetch_page = [&](int stage, const int* table, int t, int kv_head, int live_keys) {
+        if (kTmaPages) {
+            if (threadIdx.x == 0) {
+                const int place = place_of(t * kPage, ring_tokens);
+                const int row = (table[place / kPage] * n_kv + kv_head) * kPage;
+                mbar_expect_tx(&page_bar[stage], 2 * kPage * D * (int)sizeof(bf16));
+#pragma unroll
+                for (int h = 0; h < D / 64; ++h) {
+                    tma_load_2d(k_s + stage * kDecTile + h * kPage * 64, &map_k, h * 64, row, &page_bar[stage]);
+                    tma_load_2d(v_s + stage * kDecTile + h * kPage * 64, &map_v, h * 64, row, &page_bar[stage]);
+                }
+            }
+        } else {
+            load_page(k_s + stage * kDecTile, page_ptr(k_cache, table, t, ring_tokens, n_kv, kv_head), t * kPage, live_keys, false);
+            load_page(v_s + stage * kDecTile, page_ptr(v_cache, table, t, ring_tokens, n_kv, kv_head), t * kPage, live_keys, true);
+        }
+    };
     __shared__ int cum_s[kMaxDecodeSeqs + 1];        // pages of the sequences before each one
     __shared__ int warp_tot_s[4];
     __shared__ int warp_max_s[4];
@@ -561,8 +605,7 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
         for (int i = 0; i < kKvStages - 1; ++i) {
             const int t = t_begin + i;
             if (t <= t_end && t < pos / kPage) {
-                load_page(k_s + i * kPage * kStride, page_ptr(k_cache, table, t, ring_tokens, n_kv, kv_head), t * kPage, pos + 1, false);
-                load_page(v_s + i * kPage * kStride, page_ptr(v_cache, table, t, ring_tokens, n_kv, kv_head), t * kPage, pos + 1, true);
+                fetch_page(i, table, t, kv_head, pos + 1);
                 preloaded |= 1u << i;
             }
         }
@@ -632,11 +675,7 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
             }
         }
         // a ring of kKvStages pages of keys and values: kKvStages - 1 of them are on their way while one is used
-        auto load_tile = [&](int t) {
-            const int stage = (t - t_begin) % kKvStages;
-            load_page(k_s + stage * kPage * kStride, page_ptr(k_cache, table, t, ring_tokens, n_kv, kv_head), t * kPage, kv_len, false);
-            load_page(v_s + stage * kPage * kStride, page_ptr(v_cache, table, t, ring_tokens, n_kv, kv_head), t * kPage, kv_len, true);
-        };
+        auto load_tile = [&](int t) { fetch_page((t - t_begin) % kKvStages, table, t, kv_head, kv_len); };
 #pragma unroll
         for (int i = 0; i < kKvStages - 1; ++i) {
             if (t_begin + i <= t_end && !(first_segment && ((preloaded >> i) & 1u))) load_tile(t_begin + i);
@@ -661,6 +700,10 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
         for (int t = t_begin; t <= t_end; ++t) {
             const int stage = (t - t_begin) % kKvStages;
             cp_async_wait<kKvStages - 2>();
+            if (kTmaPages) {
+                mbar_wait(&page_bar[stage], (page_parity >> stage) & 1u, 31);      // bounded; a wait that runs out is recorded
+                page_parity ^= 1u << stage;
+            }
             __syncthreads();     // page t has landed for everyone, and everyone is done with the stage refilled next
             if (clustered && t == t_begin + 1) {
                 dec_cluster_arrive();      // every warp has its queries in registers: the query tile's space is free
@@ -668,16 +711,29 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
             }
             if (t + kKvStages - 1 <= t_end) load_tile(t + kKvStages - 1);
             cp_async_commit();
-            if (kPrepHeadDim && prep.qkv != nullptr && prep.write_cache && t == pos / kPage) {
+            const bool own_token_here = kPrepHeadDim && prep.qkv != nullptr && prep.write_cache && t == pos / kPage;
+            if (own_token_here || (kTmaPages && t == pos / kPage)) {
+                if (kTmaPages) {
+                    // a page that came by TMA came whole: the value rows of keys past the sequence's end may hold
+                    // anything and are zeroed here (their probabilities are zero, but zero times NaN is not)
+                    const int first_dead = pos % kPage + 1;
+                    bf16* v_tile = v_s + stage * kDecTile;
+                    for (int i = threadIdx.x; i < (kPage - first_dead) * (D / 8); i += kThreads) {
+                        const int row = first_dead + i / (D / 8), c = i % (D / 8);
+                        *reinterpret_cast<uint4*>(v_tile + (c >> 3) * (kPage * 64) + row * 64 + (c & 7) * 8) = make_uint4(0u, 0u, 0u, 0u);
+                    }
+                }
                 // this page holds the step's own token: its key (normalised, rotated) and value go into
                 // the page in shared memory and into the cache
-                if (warp < 2) {
+                if (own_token_here && warp < 2) {
                     const int row = pos % kPage;
-                    bf16* tile = (warp == 0 ? k_s : v_s) + stage * kPage * kStride + row * kStride;
+                    bf16* tile = (warp == 0 ? k_s : v_s) + stage * kDecTile + (kTmaPages ? 0 : row * kStride);
                     bf16* cached = const_cast<bf16*>(page_ptr(warp == 0 ? prep.k_cache : prep.v_cache, table, t, ring_tokens, n_kv, kv_head)) + (size_t)row * D;
-                    if (warp == 0) head_finish(token_in, prep.k_weight != nullptr, prep.eps, prep.cos_table != nullptr, tile, cached, lane);
-                    else head_finish(token_in, false, 0.f, false, tile, cached, lane);
+                    if (warp == 0) head_finish(token_in, prep.k_weight != nullptr, prep.eps, prep.cos_table != nullptr, tile, cached, lane, kTmaPages ? row : -1);
+                    else head_finish(token_in, false, 0.f, false, tile, cached, lane, kTmaPages ? row : -1);
                 }
+                // (the stage's next page comes through the async proxy: these writes are ordered before it)
+                if (kTmaPages) asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
                 __syncthreads();
             }
             if (t == t_begin) {
@@ -687,11 +743,11 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
                 for (int kk = 0; kk < D / 16; ++kk)
                     ldmatrix_x4(qf[kk], q_s + (r + (mi & 1) * 8) * kStride + kk * 16 + (mi >> 1) * 8);
             }
-            const bf16* k_t = k_s + stage * kPage * kStride;
-            const bf16* v_t = v_s + stage * kPage * kStride;
+            const bf16* k_t = k_s + stage * kDecTile;
+            const bf16* v_t = v_s + stage * kDecTile;
             // each warp takes 16 of the tile's 64 keys
             float sc[2][4];
-            scores<2>(sc, qf, k_t, warp * 16, lane);
+            scores<2, kTmaPages>(sc, qf, k_t, warp * 16, lane);
             const int key_base = t * kPage + warp * 16;
 #pragma unroll
             for (int j = 0; j < 2; ++j)
@@ -702,7 +758,7 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
                     sc[j][e] = seen ? sc[j][e] * scale_log2 : -INFINITY;
                 }
             softmax_update<2>(sc, m, l, o);
-            weighted_values<2>(o, sc, v_t, warp * 16, lane);
+            weighted_values<2, kTmaPages>(o, sc, v_t, warp * 16, lane);
         }
         atrace(4);
         cp_async_wait<0>();
@@ -854,6 +910,8 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
             }
         }
         atrace(6);
+        // (the next group's pages come through the async proxy into memory this group's merge wrote)
+        if (kTmaPages) asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
         __syncthreads();     // the reduction buffers alias the tile buffers of the next group
         u += t_b - t_a;
         first_segment = false;
@@ -861,8 +919,8 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
 }
 
 constexpr int kPrefillSmem = (64 + 4 * kPage) * kStride * (int)sizeof(bf16);
-constexpr int kDecodeTiles = (16 + 2 * kKvStages * kPage) * kStride * (int)sizeof(bf16);
-constexpr int kDecodeReduce = 16 * kStride * (int)sizeof(bf16) + (4 * 16 * kRedStride + 4 * 16 * 2) * (int)sizeof(float);
+constexpr int kDecodeTiles = (16 * kStride + 2 * kKvStages * kDecTile) * (int)sizeof(bf16) + (kTmaPages ? 1024 : 0);
+constexpr int kDecodeReduce = 16 * kStride * (int)sizeof(bf16) + (4 * 16 * kRedStride + 4 * 16 * 2) * (int)sizeof(float) + (kTmaPages ? 1024 : 0);
 constexpr int kDecodeSmem = kDecodeTiles > kDecodeReduce ? kDecodeTiles : kDecodeReduce;
 
 }  // namespace dfi
@@ -884,6 +942,9 @@ DFI_EXPORT int dfi_attention_trace(unsigned long long* host_out) {
 #endif
 
 DFI_EXPORT int dfi_attention_head_dim() { return D; }
+
+// the decode kernel's waits for its pages are bounded like those of the tcgen05 kernels
+DFI_TCGEN05_STATUS_ENTRIES(attention_decode)
 
 // Scratch of the decode kernel for a launch of `n_ctas` CTAs: floats for part_o, then for part_ml.
 DFI_EXPORT long long dfi_attention_decode_scratch_floats(int n_ctas) { return (long long)n_ctas * 2 * 16 * (D + 2); }
@@ -958,7 +1019,7 @@ DFI_EXPORT int dfi_attention_prefill(const void* q, int q_stride, void* out, int
 // dfi_attention_decode_scratch_floats(n_ctas) floats; `counters` holds n_seqs * n_kv ints, zero
 // before the first call and left zero by every call.  n_ctas <= 0: as many as run at once.
 static int attention_decode(const void* q, int q_stride, void* out, int out_stride, const void* k_cache,
-                            const void* v_cache, const int* block_table, int table_width,
+                            const void* v_cache, long long cache_pages, const int* block_table, int table_width,
                             const int* seq_start, int n_seqs, int n_q, int n_kv, int page_size,
                             int ring_tokens, int window, float scale, int n_ctas, float* scratch,
                             int* counters, const DecodePrep& prep, void* stream) {
@@ -981,6 +1042,14 @@ static int attention_decode(const void* q, int q_stride, void* out, int out_stri
     if (n_ctas > 4096) n_ctas = 4096;
     float* part_o = scratch;
     float* part_ml = scratch + (size_t)n_ctas * 2 * 16 * D;
+    // the caches as TMA maps of boxes of 64 rows x 64 elements (rows: page, head, token)
+    CUtensorMap map_k = {}, map_v = {};
+    if (kTmaPages) {
+        const long long rows = cache_pages * n_kv * kPage;
+        if (cache_pages <= 0 || rows > 0x7fffffffLL) return DFI_ERR_LIMIT;
+        if (!make_tile_map(&map_k, k_cache, (int)rows, D, kPage) || !make_tile_map(&map_v, v_cache, (int)rows, D, kPage))
+            return DFI_ERR_LAUNCH;
+    }
     // clusters only where the kernel can use them: every group cut into kDecodeCluster parts needs that many CTAs
     const int cluster = (decode_clusters_enabled() && n_ctas % kDecodeCluster == 0 &&
                          (long long)n_seqs * n_kv * kDecodeCluster <= n_ctas) ? kDecodeCluster : 1;
@@ -1005,7 +1074,7 @@ static int attention_decode(const void* q, int q_stride, void* out, int out_stri
     }
     config.attrs = attr;
     config.numAttrs = n_attr;
-    if (cudaLaunchKernelEx(&config, attention_decode_kernel, (const bf16*)q, q_stride, (bf16*)out, out_stride,
+    if (cudaLaunchKernelEx(&config, attention_decode_kernel, map_k, map_v, (const bf16*)q, q_stride, (bf16*)out, out_stride,
                            (const bf16*)k_cache, (const bf16*)v_cache, block_table, table_width, seq_start, n_seqs, n_q,
                            n_kv, ring_tokens, window, scale * kLog2e, part_o, part_ml, counters, prep, cluster) != cudaSuccess) {
         cudaGetLastError();
@@ -1016,13 +1085,14 @@ static int attention_decode(const void* q, int q_stride, void* out, int out_stri
 }
 
 DFI_EXPORT int dfi_attention_decode(const void* q, int q_stride, void* out, int out_stride, const void* k_cache,
-                                    const void* v_cache, const int* block_table, int table_width,
+                                    const void* v_cache, long long cache_pages, const int* block_table, int table_width,
                                     const int* seq_start, int n_seqs, int n_q, int n_kv, int page_size,
                                     int ring_tokens, int window, float scale, int n_ctas, float* scratch,
                                     int* counters, void* stream) {
     DecodePrep none = {};
-    return attention_decode(q, q_stride, out, out_stride, k_cache, v_cache, block_table, table_width, seq_start, n_seqs,
-                            n_q, n_kv, page_size, ring_tokens, window, scale, n_ctas, scratch, counters, none, stream);
+    return attention_decode(q, q_stride, out, out_stride, k_cache, v_cache, cache_pages, block_table, table_width,
+                            seq_start, n_seqs, n_q, n_kv, page_size, ring_tokens, window, scale, n_ctas, scratch, counters,
+                            none, stream);
 }
 
 // 1 if this build (head size) has the variant that prepares the step's token itself.
@@ -1035,7 +1105,8 @@ DFI_EXPORT int dfi_attention_decode_prepares() { return kPrepHeadDim ? 1 : 0; }
 DFI_EXPORT int dfi_attention_decode_prepared(const void* qkv, int qkv_stride, const float* q_weight,
                                              const float* k_weight, float eps, const float* cos_table,
                                              const float* sin_table, int write_cache, void* out, int out_stride,
-                                             void* k_cache, void* v_cache, const int* block_table, int table_width,
+                                             void* k_cache, void* v_cache, long long cache_pages,
+                                             const int* block_table, int table_width,
                                              const int* seq_start, int n_seqs, int n_q, int n_kv, int page_size,
                                              int ring_tokens, int window, float scale, int n_ctas, float* scratch,
                                              int* counters, void* stream) {
@@ -1054,6 +1125,7 @@ DFI_EXPORT int dfi_attention_decode_prepared(const void* qkv, int qkv_stride, co
     prep.k_cache = (bf16*)k_cache;
     prep.v_cache = (bf16*)v_cache;
     prep.write_cache = write_cache;
-    return attention_decode(nullptr, 0, out, out_stride, k_cache, v_cache, block_table, table_width, seq_start, n_seqs,
-                            n_q, n_kv, page_size, ring_tokens, window, scale, n_ctas, scratch, counters, prep, stream);
+    return attention_decode(nullptr, 0, out, out_stride, k_cache, v_cache, cache_pages, block_table, table_width,
+                            seq_start, n_seqs, n_q, n_kv, page_size, ring_tokens, window, scale, n_ctas, scratch, counters,
+                            prep, stream);
 }

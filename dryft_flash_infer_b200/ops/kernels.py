@@ -56,7 +56,7 @@ def set_pdl(enabled: bool) -> None:
 #: small int32 buffer that receives these codes (one word per kernel family), so that the host can
 #: read it with a step's results instead of synchronising for it.
 STATUS_WORDS = 8
-_STATUS_UNITS = {"gemm_decode": 0, "gemm_pair": 1, "attention_prefill_tc": 2}
+_STATUS_UNITS = {"gemm_decode": 0, "gemm_pair": 1, "attention_prefill_tc": 2, "attention_decode": 3}
 _STATUS: dict[int, torch.Tensor] = {}
 _STATUS_BOUND: set = set()
 _STATUS_LIBRARIES: list = []          # (library, units) of every library that was handed a status word
@@ -319,7 +319,7 @@ def attention_generic(q: torch.Tensor, cache, row_seq: torch.Tensor, row_pos: to
 def _attention_library(head_dim: int):
     return _bind_status(_with_pdl(load_library(f"dfi_attention_d{head_dim}", ATTENTION_SOURCES,
                                                [f"-DDFI_HEAD_DIM={head_dim}"]), "dfi_attention_set_pdl"),
-                        ("attention_prefill_tc",))
+                        ("attention_prefill_tc", "attention_decode"))
 
 
 _RETIRED_SCRATCH: list = []
@@ -426,13 +426,15 @@ def attention_decode(q, cache, ctx, n_q: int, n_kv: int, head_dim: int, scale: f
     if prep is not None:
         _check(lib.dfi_attention_decode_prepared(
             _ptr(q), q.stride(0), _ptr(prep.q_weight), _ptr(prep.k_weight), _f(prep.eps), _ptr(prep.cos), _ptr(prep.sin),
-            int(cache.writes), _ptr(out), out.stride(0), _ptr(cache.k), _ptr(cache.v), _ptr(cache.block_table),
+            int(cache.writes), _ptr(out), out.stride(0), _ptr(cache.k), _ptr(cache.v), ctypes.c_longlong(cache.k.shape[0]),
+            _ptr(cache.block_table),
             cache.block_table.shape[1], _ptr(ctx.seq_start), ctx.n_seqs, n_q, n_kv, cache.page_size, cache.ring_tokens,
             window, _f(scale), n_ctas, _ptr(held[0]), _ptr(held[1]), _stream()), "attention_decode",
             f"head_dim {head_dim}, {n_q}/{n_kv} heads, tokens prepared inside")
         return out
     _check(lib.dfi_attention_decode(
-        _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cache.k), _ptr(cache.v), _ptr(cache.block_table),
+        _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cache.k), _ptr(cache.v), ctypes.c_longlong(cache.k.shape[0]),
+        _ptr(cache.block_table),
         cache.block_table.shape[1], _ptr(ctx.seq_start), ctx.n_seqs, n_q, n_kv, cache.page_size, cache.ring_tokens,
         window, _f(scale), n_ctas, _ptr(held[0]), _ptr(held[1]), _stream()), "attention_decode",
         f"head_dim {head_dim}, {n_q}/{n_kv} heads")
