@@ -116,7 +116,7 @@ def check_status(device=None) -> None:
 def wait_selftest(unit: str, limit: int = 1, code: int = 77, head_dim: int = 128) -> None:
     """Launches ``unit``'s one-CTA self-test kernel: it waits ``limit`` tries on a barrier that nothing
     arrives on, records ``code`` as a real kernel's wait would, frees its tensor memory and returns."""
-    lib = _attention_library(head_dim) if unit == "attention_prefill_tc" else _core()
+    lib = _attention_library(head_dim) if unit.startswith("attention") else _core()
     _check(getattr(lib, f"dfi_{unit}_wait_selftest")(ctypes.c_uint(limit), int(code), _stream()), f"{unit} self-test")
 
 

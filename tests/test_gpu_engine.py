@@ -593,7 +593,8 @@ def test_a_wait_that_runs_out_reaches_the_host_as_an_exception(folders):
     folder, cfg, weights = folders["B"]
     engine = make_engine(folder, "bfloat16", max_tokens=512, cuda_graph=True)
     engine.check_status()
-    for unit, head_dim, code in (("gemm_decode", 128, 41), ("gemm_pair", 128, 42), ("attention_prefill_tc", 64, 43)):
+    for unit, head_dim, code in (("gemm_decode", 128, 41), ("gemm_pair", 128, 42), ("attention_prefill_tc", 64, 43),
+                                 ("attention_decode", 32, 45)):
         kernels.wait_selftest(unit, limit=2, code=code, head_dim=head_dim)
         with pytest.raises(kernels.KernelError, match=f"{unit} .wait code {code}."):
             engine.check_status()
@@ -616,8 +617,8 @@ def test_a_wait_that_runs_out_reaches_the_host_as_an_exception(folders):
     got = [r[0] for r in engine.generate([prompt], 4)]
     assert _teacher_forced_gap(cfg, bf16_weights(weights), prompt, got) <= BF16_TIE_GAP
     # a word set by the host shows the same way
-    kernels.status_words()[3] = 9
-    with pytest.raises(kernels.KernelError, match="word 3"):
+    kernels.status_words()[6] = 9
+    with pytest.raises(kernels.KernelError, match="word 6"):
         engine.check_status()
 
 
