@@ -32,6 +32,10 @@
 //   next product's scaled input and this row block's sum of r^2 per row.
 // With both, the add + norm kernel between two products disappears.
 //
+// A word about the next product (NextStream, tcgen05.cuh): when the producer has asked for the last tile of
+// its CTA's run it asks a few tiles of the product that the step runs next into L2, for the time in which
+// this kernel's epilogue and the next kernel's wait leave the memory idle.
+//
 // SWIGLU variant: W = [gate; up] of 2N rows; a row block is 64 gate rows and the 64 up rows that
 // belong to them, and the epilogue writes silu(gate) * up (engine/kernels/reference.py:74-79;
 // the fusion follows the idea of engine/kernels/cuda_mlp.py:39-125).
@@ -70,11 +74,7 @@ struct RowFusion {
 // whole matrix (stream-K), or, for a matrix with few row blocks, each row block cut into the same
 // number of parts, so that no CTA's run crosses from one row block into the next.
 __device__ __forceinline__ int sk_run_begin(const StreamShape& s, int cta) {
-    if (s.parts > 0) {
-        if (cta >= s.n_ctas) return s.units;
-        return (cta / s.parts) * s.k_chunks + s.k_chunks * (cta % s.parts) / s.parts;
-    }
-    return (int)((unsigned)s.units * (unsigned)cta / (unsigned)s.n_ctas);
+    return deal_begin(UnitDeal{s.units, s.k_chunks, s.n_ctas, s.parts}, cta);
 }
 __device__ __forceinline__ int sk_cta_of_unit(const StreamShape& s, int u) {
     int c;
@@ -236,7 +236,7 @@ template <int BN, bool SWIGLU, bool CLUSTER>
 __global__ void __launch_bounds__(kDecThreads, 2)
 gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                    void* __restrict__ out, StreamShape s, float* __restrict__ partials, int* __restrict__ counters,
-                   int out_dtype, RowFusion fusion) {
+                   int out_dtype, RowFusion fusion, const __grid_constant__ NextStream next) {
     using Cfg = DecConfig<BN, CLUSTER>;
     if (threadIdx.x == 0) trace(0);
     pdl_launch_next();
@@ -319,6 +319,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 load_x(st, prod_kc);
                 if (++prod_kc == s.k_chunks) { prod_kc = 0; ++prod_rb; }
             }
+            prefetch_next_stream(next, cta, (int)gridDim.x);      // this CTA's own stream has been asked for
         }
     } else if (warp == 1) {
         if (lane == 0) {
@@ -628,7 +629,7 @@ static int dec_sm_count() {
 
 template <int BN, bool SWIGLU, bool CLUSTER>
 static int launch_decode(const void* x, const void* w, void* out, StreamShape s, float* partials, int* counters,
-                         int out_dtype, const RowFusion& fusion, cudaStream_t st) {
+                         int out_dtype, const RowFusion& fusion, cudaStream_t st, const NextStream& next) {
     using Cfg = DecConfig<BN, CLUSTER>;
     static_assert(Cfg::kStages >= 2, "the ring needs at least two stages");
     static bool configured = false;
@@ -657,11 +658,11 @@ static int launch_decode(const void* x, const void* w, void* out, StreamShape s,
         config.attrs = attr;
         config.numAttrs = pdl_enabled() ? 2 : 1;
         if (cudaLaunchKernelEx(&config, gemm_decode_kernel<BN, SWIGLU, CLUSTER>, map_w, map_x, out, s, partials, counters,
-                               out_dtype, fusion) != cudaSuccess)
+                               out_dtype, fusion, next) != cudaSuccess)
             return DFI_ERR_LAUNCH;
         return DFI_OK;
     }
-    launch(gemm_decode_kernel<BN, SWIGLU, CLUSTER>, s.n_ctas, kDecThreads, Cfg::kSmemBytes, st, map_w, map_x, out, s, partials, counters, out_dtype, fusion);
+    launch(gemm_decode_kernel<BN, SWIGLU, CLUSTER>, s.n_ctas, kDecThreads, Cfg::kSmemBytes, st, map_w, map_x, out, s, partials, counters, out_dtype, fusion, next);
     return DFI_OK;
 }
 
@@ -726,7 +727,8 @@ DFI_EXPORT int dfi_gemm_decode_counters(int N, int swiglu) {
 // out[M, N] (row stride N) = x[M, K] . w[N, K]^T, or with swiglu: silu(x . gate^T) * (x . up^T) for
 // w = [gate; up] of 2N rows.  M <= 64; K a multiple of 8.  n_ctas <= 0: one per SM.
 static int gemm_decode(const void* x, const void* w, void* out, int M, int N, int K, int swiglu, int n_ctas,
-                       float* partials, int* counters, int out_dtype, const RowFusion& fusion, void* stream) {
+                       float* partials, int* counters, int out_dtype, const RowFusion& fusion, const void* next_hint,
+                       void* stream) {
     if (M <= 0 || N <= 0) return DFI_OK;
     if (M > 64 || K <= 0 || K % 8) return DFI_ERR_SHAPE;
     if (out_dtype != DFI_DTYPE_F32 && out_dtype != DFI_DTYPE_BF16) return DFI_ERR_DTYPE;
@@ -741,11 +743,12 @@ static int gemm_decode(const void* x, const void* w, void* out, int M, int N, in
     s.wide_out = (N % 4 == 0 && aligned16(out)) ? 1 : 0;
     const bool cluster = plan_uses_cluster(s, swiglu);
     cudaStream_t st = (cudaStream_t)stream;
+    const NextStream next = next_stream_arg(next_hint);
     int rc;
 #define DFI_DEC(BNV)                                                                                       \
-    rc = swiglu ? launch_decode<BNV, true, false>(x, w, out, s, partials, counters, out_dtype, fusion, st)  \
-         : cluster ? launch_decode<BNV, false, true>(x, w, out, s, partials, counters, out_dtype, fusion, st) \
-                   : launch_decode<BNV, false, false>(x, w, out, s, partials, counters, out_dtype, fusion, st)
+    rc = swiglu ? launch_decode<BNV, true, false>(x, w, out, s, partials, counters, out_dtype, fusion, st, next)  \
+         : cluster ? launch_decode<BNV, false, true>(x, w, out, s, partials, counters, out_dtype, fusion, st, next) \
+                   : launch_decode<BNV, false, false>(x, w, out, s, partials, counters, out_dtype, fusion, st, next)
     if (M <= 16) DFI_DEC(16);
     else if (M <= 32) DFI_DEC(32);
     else DFI_DEC(64);
@@ -755,10 +758,37 @@ static int gemm_decode(const void* x, const void* w, void* out, int M, int N, in
     return DFI_OK;
 }
 
+// next_hint: null, or what dfi_gemm_decode_next_stream wrote about the product that the step runs after this one.
 DFI_EXPORT int dfi_gemm_decode(const void* x, const void* w, void* out, int M, int N, int K, int swiglu, int n_ctas,
-                               float* partials, int* counters, int out_dtype, void* stream) {
+                               float* partials, int* counters, int out_dtype, const void* next_hint, void* stream) {
     RowFusion none = {};
-    return gemm_decode(x, w, out, M, N, K, swiglu, n_ctas, partials, counters, out_dtype, none, stream);
+    return gemm_decode(x, w, out, M, N, K, swiglu, n_ctas, partials, counters, out_dtype, none, next_hint, stream);
+}
+
+// The hint that a decode kernel takes about the product out = x[M, K] . w^T that follows it (same meaning of
+// N, K, swiglu and n_ctas as in dfi_gemm_decode): written to `hint` (dfi_next_stream_bytes() bytes of host
+// memory).  `tiles`: how many tiles per CTA to ask into L2.  The hint names w: it is good for as long as w
+// stays where it is.
+DFI_EXPORT int dfi_next_stream_bytes() { return (int)sizeof(NextStream); }
+DFI_EXPORT int dfi_gemm_decode_next_stream(void* hint, const void* w, int M, int N, int K, int swiglu, int n_ctas, int tiles) {
+    if (hint == nullptr || w == nullptr || M <= 0 || M > 64 || N <= 0 || K <= 0 || K % 8 || !aligned16(w)) return DFI_ERR_SHAPE;
+    if (n_ctas <= 0) n_ctas = dec_sm_count();
+    if (n_ctas <= 0) return DFI_ERR_LAUNCH;
+    if (n_ctas > 512) n_ctas = 512;
+    StreamShape s;
+    if (!plan_decode(s, M, N, K, swiglu, n_ctas)) return DFI_ERR_LIMIT;
+    NextStream next;
+    memset(&next, 0, sizeof(next));
+    if (!make_tile_map(&next.map, w, swiglu ? 2 * N : N, K, swiglu ? kTileM / 2 : kTileM)) return DFI_ERR_LAUNCH;
+    next.deal = UnitDeal{s.units, s.k_chunks, s.n_ctas, s.parts};
+    next.up_row0 = swiglu ? N : -1;
+    const bool cluster = plan_uses_cluster(s, swiglu);
+    next.skip = M <= 16 ? (cluster ? DecConfig<16, true>::kStages : DecConfig<16, false>::kStages)
+              : M <= 32 ? (cluster ? DecConfig<32, true>::kStages : DecConfig<32, false>::kStages)
+                        : (cluster ? DecConfig<64, true>::kStages : DecConfig<64, false>::kStages);
+    next.count = tiles > 0 ? tiles : 0;
+    memcpy(hint, &next, sizeof(next));
+    return DFI_OK;
 }
 
 // Floats per part of a sum-of-squares array, and the number of parts a product with N output
@@ -780,7 +810,7 @@ DFI_EXPORT int dfi_gemm_decode_ssq_parts(int M, int N, int K, int n_ctas) {
 DFI_EXPORT int dfi_gemm_decode_fused(const void* x, const void* w, void* out, int M, int N, int K, int swiglu,
                                      int n_ctas, float* partials, int* counters, int out_dtype, const float* in_ssq,
                                      int in_parts, int in_dim, float in_eps, void* residual, const float* norm_weight,
-                                     float* out_ssq, void* stream) {
+                                     float* out_ssq, const void* next_hint, void* stream) {
     RowFusion fusion = {};
     if (in_ssq != nullptr) {
         if (in_parts <= 0 || in_dim <= 0) return DFI_ERR_SHAPE;
@@ -796,5 +826,5 @@ DFI_EXPORT int dfi_gemm_decode_fused(const void* x, const void* w, void* out, in
         fusion.norm_weight = norm_weight;
         fusion.out_ssq = out_ssq;
     }
-    return gemm_decode(x, w, out, M, N, K, swiglu, n_ctas, partials, counters, out_dtype, fusion, stream);
+    return gemm_decode(x, w, out, M, N, K, swiglu, n_ctas, partials, counters, out_dtype, fusion, next_hint, stream);
 }

@@ -3,6 +3,7 @@
 #pragma once
 
 #include <cuda.h>
+#include <string.h>
 
 #include "common.cuh"
 
@@ -120,6 +121,63 @@ static inline bool make_tile_map(CUtensorMap* map, const void* base, int rows, i
                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+
+// ---- a word about the matrix product that the step runs next
+// How a decode product deals its units of 128 rows x 64 k to its CTAs: equal contiguous runs over the whole
+// matrix (parts == 0), or every row block cut into the same number of parts, one CTA each.
+struct UnitDeal {
+    int units, k_chunks, n_ctas, parts;
+};
+__host__ __device__ __forceinline__ int deal_begin(const UnitDeal& d, int cta) {
+    if (d.parts > 0) {
+        if (cta >= d.n_ctas) return d.units;
+        return (cta / d.parts) * d.k_chunks + d.k_chunks * (cta % d.parts) / d.parts;
+    }
+    return (int)((unsigned)d.units * (unsigned)cta / (unsigned)d.n_ctas);
+}
+// A decode kernel may be told which weights the step streams after it.  Between the moment a CTA has asked
+// for the last of its own stream and the moment the next product can use its first tiles, the memory has
+// nothing to do (the epilogue, the end of the grid and the next product's activations take about 4 us); the
+// next product already holds its first ring (it loads it before it waits for this kernel), so the CTA asks
+// the `count` tiles that follow that ring, for the next product's CTA of the same number, into L2.  A hint
+// only: nothing waits for these tiles, and a wrong hint costs a little bandwidth.  More than a few tiles
+// were measured slower than none: the epilogue's own dependent loads then queue behind them.  The products
+// take the hint; decode attention does not (given one for the output projection it ran slower, hint or no hint).
+struct alignas(64) NextStream {
+    CUtensorMap map;        // the next product's weights with the boxes that product loads
+    UnitDeal deal;
+    int up_row0;            // >= 0: [gate; up] weights in boxes of 64 rows, the up rows starting at this row
+    int skip;               // tiles of a CTA's run that its first ring holds
+    int count;              // tiles to ask for after those; 0: no hint
+    int reserved;
+};
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int x, int y) {
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];\n" ::"l"(map), "r"(x), "r"(y) : "memory");
+}
+// Called by one thread of CTA `cta` of `n_here`.
+__device__ __forceinline__ void prefetch_next_stream(const NextStream& next, int cta, int n_here) {
+    if (next.count <= 0) return;
+    for (int c = cta; c < next.deal.n_ctas; c += n_here) {
+        const int first = deal_begin(next.deal, c) + next.skip;
+        const int last = min(deal_begin(next.deal, c + 1), first + next.count);
+        for (int u = first; u < last; ++u) {
+            const int rb = u / next.deal.k_chunks, kc = u % next.deal.k_chunks;
+            if (next.up_row0 >= 0) {
+                tma_prefetch_2d(&next.map, kc * kTileK, rb * (kTileM / 2));
+                tma_prefetch_2d(&next.map, kc * kTileK, next.up_row0 + rb * (kTileM / 2));
+            } else {
+                tma_prefetch_2d(&next.map, kc * kTileK, rb * kTileM);
+            }
+        }
+    }
+}
+// The kernel argument from the host's copy of a hint (any alignment), or no hint.
+static inline NextStream next_stream_arg(const void* host_hint) {
+    NextStream next;
+    memset(&next, 0, sizeof(next));
+    if (host_hint != nullptr) memcpy(&next, host_hint, sizeof(next));
+    return next;
+}
 
 // What a kernel of this header does when a wait runs out, alone: one warp takes 32 columns of tensor
 // memory, waits `limit` tries on a barrier that nothing ever arrives on, records `code`, gives the

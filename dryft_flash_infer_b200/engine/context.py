@@ -41,6 +41,9 @@ class StepContext:
 
     def __init__(self, entries: list[StepEntry], cache, device, table_widths: list[int] | None = None,
                  shape: tuple[int, int, int] | None = None, into: torch.Tensor | None = None):
+        #: ``kernels.NextWeights`` of the matrix that the step streams after the part that is running, or
+        #: None: the model and the blocks keep it up to date, a part may give it to its last kernel
+        self.upcoming = None
         self.slots = [e.slot for e in entries]
         self.q_lens = [len(e.tokens) for e in entries]
         self.starts = [cache.length(e.slot) for e in entries]

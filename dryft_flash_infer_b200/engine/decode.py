@@ -33,6 +33,7 @@ class DecodeBatch:
     all_decode = True
     wants_every_row = True
     max_q_len = 1
+    upcoming = None          # as in StepContext: what the step streams after the part that is running
 
     def __init__(self, model, cache, n: int, table_widths: list[int], max_context: int, temperature: float,
                  use_graph: bool):

@@ -151,6 +151,11 @@ class DecoderModel:
             view = cache.layer_view(entry.cache, ctx.block_tables, entry.writes_cache) \
                 if block.mixer.cache_need() is not None else None
             state = cache.state.get(position)
+            # what the step streams after this block: the next block's first matrix, or the output head
+            if position + 1 < len(schedule):
+                ctx.upcoming = self.blocks[schedule[position + 1].layer].mixer.first_weights()
+            else:
+                ctx.upcoming = kernels.next_weights(self.head) if ctx.n_wanted > 0 else None
             if block.fuses_next_norm:
                 # the norm that reads this block's result, if its reader takes rows that lack their factor
                 if position + 1 < len(schedule):
@@ -162,6 +167,7 @@ class DecoderModel:
                 residual, pending = block.forward(residual, pending, ctx, view, state, next_norm=next_norm)
             else:
                 residual, pending = block.forward(residual, pending, ctx, view, state)
+        ctx.upcoming = None
         if ctx.n_wanted == 0:
             return None
         if isinstance(pending, kernels.ScaledRows):

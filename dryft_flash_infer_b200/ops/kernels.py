@@ -9,6 +9,7 @@ from __future__ import annotations
 
 import ctypes
 import os
+import weakref
 
 import torch
 
@@ -488,6 +489,10 @@ def sample_temperature(logits: torch.Tensor, uniforms: torch.Tensor, temperature
 _GEMM_SCRATCH: dict = {}
 SKINNY_MAX_ROWS = 64
 
+#: Tiles of 128 rows x 64 k per CTA that a decode kernel asks into L2 for the product after it (``NextWeights``).
+#: Measured at Qwen3-4B sizes, batch 8: 4 tiles take 2 % off the step, 8 tiles 0.6 %, 16 tiles add 2.6 %.  0: none.
+NEXT_TILES = int(os.environ.get("DRYFT_NEXT_TILES", "4"))
+
 
 def _gemm_scratch(device, n_ctas: int, counters: int):
     """The stream-K scratch of a device: room for every CTA's partial sums, and zeroed counters."""
@@ -586,8 +591,62 @@ def add_norm_fusable(rows: torch.Tensor) -> bool:
             and rows.shape[1] % 8 == 0 and rows.is_contiguous())
 
 
+class NextWeights:
+    """A word about the weights a decode step streams next: ``weight [N, K]`` (with ``swiglu``: ``[gate; up]``
+    of ``2 N`` rows) of the product that follows the kernel this is given to (``then=``).  The kernel asks
+    the first tiles behind that product's opening ring into L2 once its own stream has been asked for.  A
+    hint: results never depend on it, and kernels that cannot use it ignore it.  It does not keep the
+    matrix alive."""
+
+    __slots__ = ("_weight", "swiglu", "_hints", "__weakref__")
+
+    def __init__(self, weight: torch.Tensor, swiglu: bool = False):
+        self._weight, self.swiglu = weakref.ref(weight), bool(swiglu)
+        self._hints: dict = {}
+
+    @property
+    def weight(self) -> torch.Tensor | None:
+        return self._weight()
+
+    def hint(self, rows: int):
+        """The kernels' form of the hint for a step of ``rows`` rows (a host buffer), or None."""
+        w = self.weight
+        if w is None or NEXT_TILES <= 0 or not w.is_cuda or w.dtype != torch.bfloat16 \
+                or not 0 < rows <= SKINNY_MAX_ROWS or w.dim() != 2 or w.shape[1] % 8 or not w.is_contiguous():
+            return None
+        key = (w.data_ptr(), rows)
+        held = self._hints.get(key)
+        if held is None:
+            lib = _core()
+            held = ctypes.create_string_buffer(lib.dfi_next_stream_bytes())
+            n = w.shape[0] // 2 if self.swiglu else w.shape[0]
+            rc = lib.dfi_gemm_decode_next_stream(held, _ptr(w), rows, n, w.shape[1], int(self.swiglu), 0, NEXT_TILES)
+            held = held if rc == 0 else False
+            self._hints = {key: held}            # one entry: a part's weights stay where they are between steps
+        return held or None
+
+
+_NEXT_WEIGHTS: dict = {}
+
+
+def next_weights(weight: torch.Tensor | None, swiglu: bool = False) -> NextWeights | None:
+    """The ``NextWeights`` of a matrix, made once for each tensor object (None for None)."""
+    if weight is None:
+        return None
+    key = (id(weight), bool(swiglu))
+    held = _NEXT_WEIGHTS.get(key)
+    if held is None or held.weight is not weight:
+        held = _NEXT_WEIGHTS[key] = NextWeights(weight, swiglu)
+        weakref.finalize(weight, _NEXT_WEIGHTS.pop, key, None)
+    return held
+
+
+def _hint(then: NextWeights | None, rows: int):
+    return then.hint(rows) if then is not None else None
+
+
 def decode_linear(x, weight: torch.Tensor, out_dtype: torch.dtype | None = None,
-                  swiglu: bool = False, n_ctas: int | None = None, add_norm=None):
+                  swiglu: bool = False, n_ctas: int | None = None, add_norm=None, then: NextWeights | None = None):
     """``x @ weight.T`` (with ``swiglu``: ``silu(x @ gate.T) * (x @ up.T)`` for ``weight = [gate; up]``)
     for at most 64 rows of bfloat16 ``x``: the decode step's product as a persistent stream-K kernel on
     tcgen05, with TMA loads and the accumulator in tensor memory.  ``n_ctas``: CTAs that share the
@@ -595,7 +654,8 @@ def decode_linear(x, weight: torch.Tensor, out_dtype: torch.dtype | None = None,
 
     ``x`` may be ``ScaledRows``: their factor is applied to the result.  ``add_norm = (residual,
     norm_weight, eps)``: the product is a residual delta; ``residual`` is updated in place and the call
-    returns the ``ScaledRows`` of ``rms_norm(residual) * norm_weight`` for the next product."""
+    returns the ``ScaledRows`` of ``rms_norm(residual) * norm_weight`` for the next product.  ``then``: the
+    weights of the product that the step runs after this one (see ``NextWeights``)."""
     scaled = x if isinstance(x, ScaledRows) else None
     if scaled is not None:
         x = scaled.rows
@@ -615,9 +675,10 @@ def decode_linear(x, weight: torch.Tensor, out_dtype: torch.dtype | None = None,
     held = _scratch(_DECODE_SCRATCH, x.device, floats, counters)
     out = torch.empty((m, n), dtype=out_dtype, device=x.device)
     what = f"{m} x {k} by {weight.shape[0]} x {k}"
+    hint = _hint(then, m)
     if scaled is None and add_norm is None:
         _check(lib.dfi_gemm_decode(_ptr(x), _ptr(weight), _ptr(out), m, n, k, int(swiglu), n_ctas, _ptr(held[0]),
-                                   _ptr(held[1]), _DTYPE_CODE[out_dtype], _stream()), "decode_linear", what)
+                                   _ptr(held[1]), _DTYPE_CODE[out_dtype], hint, _stream()), "decode_linear", what)
         return out
     in_ssq, in_parts, in_dim, in_eps = None, 0, 0, 0.0
     if scaled is not None:
@@ -635,7 +696,7 @@ def decode_linear(x, weight: torch.Tensor, out_dtype: torch.dtype | None = None,
         residual, norm_weight, out_ssq = _ptr(res), _ptr(norm_w), _ptr(ssq)
     _check(lib.dfi_gemm_decode_fused(_ptr(x), _ptr(weight), _ptr(out), m, n, k, int(swiglu), n_ctas, _ptr(held[0]),
                                      _ptr(held[1]), _DTYPE_CODE[out_dtype], in_ssq, in_parts, in_dim,
-                                     ctypes.c_float(in_eps), residual, norm_weight, out_ssq, _stream()),
+                                     ctypes.c_float(in_eps), residual, norm_weight, out_ssq, hint, _stream()),
            "decode_linear", what)
     if add_norm is not None:
         return ScaledRows(out, ssq, n, float(add_norm[2]))
@@ -658,7 +719,8 @@ def simt_linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | 
     return out
 
 
-def linear(x, weight: torch.Tensor, out_dtype: torch.dtype | None = None, add_norm=None):
+def linear(x, weight: torch.Tensor, out_dtype: torch.dtype | None = None, add_norm=None,
+           then: NextWeights | None = None):
     """``x @ weight.T`` for ``weight [out, in]`` as stored in the model file.
 
     bfloat16 with at most 64 rows (decoding) runs the hand-written stream-K tcgen05 kernel; larger
@@ -667,17 +729,18 @@ def linear(x, weight: torch.Tensor, out_dtype: torch.dtype | None = None, add_no
     operands, and bfloat16 matrices whose width is no multiple of 8 (which the TMA-fed kernels do not
     take), run the plain float32-pipe kernel of this package: true 32-bit, no library, no
     reduced-precision mode.  ``out_dtype=torch.float32`` keeps bfloat16 products unrounded (used for
-    logits).  ``ScaledRows`` in and ``add_norm`` are those of ``decode_linear``.
+    logits).  ``ScaledRows`` in, ``add_norm`` and ``then`` are those of ``decode_linear``; the other
+    kernels ignore ``then``.
     """
     if isinstance(x, ScaledRows) or add_norm is not None:
         # only made and asked for where the decode kernel runs (add_norm_fusable)
-        return decode_linear(x, weight, out_dtype, add_norm=add_norm)
+        return decode_linear(x, weight, out_dtype, add_norm=add_norm, then=then)
     _need_cuda(x, weight)
     assert x.dim() == 2 and weight.dim() == 2 and x.shape[1] == weight.shape[1] and x.dtype == weight.dtype
     if x.dtype == torch.float32 or x.shape[1] % 8:
         return simt_linear(x, weight, out_dtype)
     if x.shape[0] <= SKINNY_MAX_ROWS and x.is_contiguous():
-        return decode_linear(x, weight, out_dtype)
+        return decode_linear(x, weight, out_dtype, then=then)
     if out_dtype is not None and out_dtype != x.dtype:
         return torch.mm(x, weight.t(), out_dtype=out_dtype)
     if PREFILL_GEMM == "own" and x.is_contiguous() and weight.is_contiguous():
@@ -685,15 +748,15 @@ def linear(x, weight: torch.Tensor, out_dtype: torch.dtype | None = None, add_no
     return torch.mm(x, weight.t())
 
 
-def linear_swiglu(x, gate_up: torch.Tensor) -> torch.Tensor:
+def linear_swiglu(x, gate_up: torch.Tensor, then: NextWeights | None = None) -> torch.Tensor:
     """``silu(x @ gate.T) * (x @ up.T)`` for the fused matrix ``gate_up = [gate; up]``: one kernel
     for bfloat16 (the decode kernel for few rows, the pair kernel for many), else the product followed by
     the SwiGLU kernel."""
     if isinstance(x, ScaledRows):
-        return decode_linear(x, gate_up, swiglu=True)
+        return decode_linear(x, gate_up, swiglu=True, then=then)
     if x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and x.is_contiguous():
         if x.shape[0] <= SKINNY_MAX_ROWS:
-            return decode_linear(x, gate_up, swiglu=True)
+            return decode_linear(x, gate_up, swiglu=True, then=then)
         if (x.shape[0] >= PAIR_MIN_ROWS or PREFILL_GEMM == "own") and gate_up.is_contiguous():
             return pair_linear(x, gate_up, swiglu=True)          # prompts: the activation on the accumulator
     return swiglu(linear(x, gate_up))

@@ -66,6 +66,9 @@ class Attention(Mixer):
         if self.position is not None:
             self.position.prepare(max_positions, device)
 
+    def first_weights(self):
+        return kernels.next_weights(self.qkv)
+
     def forward(self, x, ctx, cache, state, add_norm=None):
         qkv = kernels.linear(x, self.qkv)
         cos = self.position.cos if self.position is not None else None
@@ -75,12 +78,12 @@ class Attention(Mixer):
             prep = kernels.TokenPrep(qkv, self.q_norm, self.k_norm, self.qk_norm_eps, cos, sin)
             attended = kernels.attention_decode(None, cache, ctx, self.n_heads, self.n_kv_heads, self.head_dim,
                                                 self.scale, self.window, prep=prep)
-            return kernels.linear(attended, self.o, add_norm=add_norm)
+            return kernels.linear(attended, self.o, add_norm=add_norm, then=getattr(ctx, "upcoming", None))
         q = kernels.qk_norm_rope_write(qkv, self.n_heads, self.n_kv_heads, self.head_dim, self.q_norm, self.k_norm,
                                        self.qk_norm_eps, cos, sin, ctx.row_pos, ctx.row_seq, cache)
         attended = kernels.attention(q, cache, ctx, self.n_heads, self.n_kv_heads, self.head_dim, self.scale,
                                      self.window)
-        return kernels.linear(attended, self.o, add_norm=add_norm)
+        return kernels.linear(attended, self.o, add_norm=add_norm, then=getattr(ctx, "upcoming", None))
 
 
 register_part("mixer", Attention.kind, Attention)

@@ -83,6 +83,12 @@ class Part:
         for name, tensor in buffers.items():
             setattr(self, name, tensor)
 
+    def first_weights(self):
+        """``kernels.NextWeights`` of the matrix that ``forward`` streams first, or None.  Whoever runs
+        this part after another one may leave it in ``ctx.upcoming``, where the part before finds it and
+        hands it to its last kernel (``then=``): a hint for decode steps that changes no result."""
+        return None
+
     def buffer_shapes(self) -> dict[str, tuple[tuple[int, ...], str]]:
         out: dict[str, tuple[tuple[int, ...], str]] = {}
         for decl in self.tensors().values():

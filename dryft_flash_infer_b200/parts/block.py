@@ -33,6 +33,14 @@ class PreNormBlock(Block):
         return self.mixer.accepts_scaled_rows and self.mixer_norm.scale_fusion() is not None
 
     def forward(self, residual, pending, ctx, cache, state, next_norm=None):
+        after = ctx.upcoming                     # what follows this block; the mixer is followed by the feed-forward
+        ctx.upcoming = self.feed_forward.first_weights()
+        try:
+            return self._forward(residual, pending, ctx, cache, state, next_norm, after)
+        finally:
+            ctx.upcoming = after
+
+    def _forward(self, residual, pending, ctx, cache, state, next_norm, after):
         fusable = kernels.add_norm_fusable(residual)
         if isinstance(pending, kernels.ScaledRows):
             normed = pending                     # the block before added its result and prepared this norm
@@ -47,6 +55,7 @@ class PreNormBlock(Block):
         else:
             mixed = self.mixer.forward(normed, ctx, cache, state)
             normed = self.ffn_norm.add_forward(residual, mixed)
+        ctx.upcoming = after
         fusion = next_norm.scale_fusion() if next_norm is not None and fusable and self.feed_forward.fuses_add_norm else None
         if fusion is not None:
             return residual, self.feed_forward.forward(normed, ctx, add_norm=(residual, *fusion))

@@ -30,9 +30,12 @@ class SwiGLU(FeedForward):
             "down_proj": TensorDecl((hidden, inter), "down"),
         }
 
+    def first_weights(self):
+        return kernels.next_weights(self.gate_up, swiglu=True)
+
     def forward(self, x, ctx, add_norm=None):
-        inner = kernels.linear_swiglu(x, self.gate_up)
-        return kernels.linear(inner, self.down, add_norm=add_norm)
+        inner = kernels.linear_swiglu(x, self.gate_up, then=kernels.next_weights(self.down))
+        return kernels.linear(inner, self.down, add_norm=add_norm, then=getattr(ctx, "upcoming", None))
 
 
 register_part("feed_forward", SwiGLU.kind, SwiGLU)

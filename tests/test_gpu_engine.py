@@ -693,3 +693,33 @@ def test_prompt_steps_of_a_few_rows_keep_the_decode_products(folders, dtype):
     assert [shape[0] for shape in shapes] == [16, 32, 64] and engine.stepper.graphs.replays >= 3
     engine.close_slot(keeper)
     engine.cache.book.check()
+
+
+def test_the_words_about_the_next_product_change_no_logit(wide_model, monkeypatch):
+    """Decode kernels are told which weights the step streams after them (the feed-forward's after the
+    mixer's, the next layer's after that, the output head's at the end) and ask some of them into L2.
+    With the hints off the step's logits are the same bit for bit, launch by launch and through the graph."""
+    from dryft_flash_infer_b200 import StepEntry
+    from dryft_flash_infer_b200.ops import kernels
+
+    folder, prompts, _, _ = wide_model            # widths at which the products have tiles beyond their first ring
+    prompts = [p[:70] for p in prompts[:3]]
+    seen = {}
+    for tiles in (4, 0):
+        monkeypatch.setattr(kernels, "NEXT_TILES", tiles)
+        given = []
+        real = kernels.NextWeights.hint
+        monkeypatch.setattr(kernels.NextWeights, "hint", lambda self, rows: given.append(real(self, rows)) or given[-1])
+        for graph in (False, True):
+            engine = make_engine(folder, "bfloat16", max_tokens=64 * 8, cuda_graph=graph)
+            assert engine.decoder.use_graph == graph
+            slots = [engine.open_slot() for _ in prompts]
+            rows = [engine.step([StepEntry(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)])]
+            for t in range(3):
+                rows.append(engine.step([StepEntry(s, [7 + t + i], [0]) for i, s in enumerate(slots)]))
+            seen[tiles, graph] = torch.cat([r.float().cpu() for r in rows])
+        monkeypatch.setattr(kernels.NextWeights, "hint", real)
+        # hints were given (and were real ones) exactly when they are on
+        assert any(h is not None for h in given) == (tiles > 0)
+    assert torch.equal(seen[4, False], seen[0, False])
+    assert torch.equal(seen[4, True], seen[0, True])

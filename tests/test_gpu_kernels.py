@@ -590,3 +590,34 @@ def test_attention_decode_of_short_sequences_in_four_parts(n_q, n_kv, dim, lengt
         assert torch.isfinite(got).all()
         assert torch.allclose(got.float().cpu(), want, atol=tol(dtype, 2), rtol=tol(dtype)), ctas
         assert torch.equal(kernels.attention_decode(q, cache, ctx, n_q, n_kv, dim, scale, n_ctas=ctas), got)
+
+
+@pytest.mark.parametrize("m", [1, 8, 33, 64])
+def test_a_word_about_the_next_product_changes_no_result(m):
+    """``then=`` names the weights that the step streams next; the kernel asks some of them into L2.  Whatever
+    those weights are (few tiles or many, SwiGLU rows, a matrix that ends inside a tile), the product's
+    result is the same bit for bit, with every number of CTAs."""
+    from dryft_flash_infer_b200.ops import kernels
+
+    g = torch.Generator().manual_seed(m)
+    x = torch.randn(m, 200, generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn(300, 200, generator=g) * 0.05).to(torch.bfloat16).cuda()
+    gate_up = (torch.randn(2 * 72, 200, generator=g) * 0.1).to(torch.bfloat16).cuda()
+    plain = kernels.decode_linear(x, w, torch.float32)
+    plain_act = kernels.decode_linear(x, gate_up, swiglu=True)
+    followers = [(torch.randn(n, k, generator=g).to(torch.bfloat16).cuda(), sw)
+                 for n, k, sw in ((37, 72, False), (2560, 4096, False), (2 * 9728, 2560, True), (2 * 40, 40, True), (128, 64, False))]
+    for follower, sw in followers:
+        then = kernels.next_weights(follower, swiglu=sw)
+        assert then.hint(m) is not None and then is kernels.next_weights(follower, swiglu=sw)
+        for ctas in (None, 1, 3, 500):
+            assert torch.equal(kernels.decode_linear(x, w, torch.float32, n_ctas=ctas, then=then),
+                               kernels.decode_linear(x, w, torch.float32, n_ctas=ctas))
+        assert torch.equal(kernels.decode_linear(x, w, torch.float32, then=then), plain)
+        assert torch.equal(kernels.decode_linear(x, gate_up, swiglu=True, then=then), plain_act)
+        assert kernels.tc_error() == 0
+    # weights that the decode kernel would not take give no hint, and no hint is taken for more than 64 rows
+    assert kernels.next_weights(torch.zeros(16, 12, dtype=torch.bfloat16, device="cuda")).hint(m) is None
+    assert kernels.next_weights(torch.zeros(16, 16, dtype=torch.float32, device="cuda")).hint(m) is None
+    assert kernels.next_weights(followers[1][0]).hint(65) is None
+    assert kernels.next_weights(None) is None
