@@ -672,11 +672,13 @@ DFI_EXPORT int dfi_attention_prefill_tc_available() { return DFI_FA_ENABLED; }
 
 // q [rows, q_stride] (the head's columns start at head * head_dim), out [rows, out_stride];
 // k_cache, v_cache [pages, n_kv, 64, head_dim]; cache_pages = number of pages in them.
+// tiles_per_cta: 1 or 2 query tiles of 128 rows per CTA, or 0 to let the launch choose.
 DFI_EXPORT int dfi_attention_prefill_tc(const void* q, int q_rows, int q_stride, void* out, int out_stride,
                                         const void* k_cache, const void* v_cache, long long cache_pages,
                                         const int* block_table, int table_width, const int* cu_rows,
                                         const int* seq_start, int n_seqs, int max_q_len, int n_q, int n_kv,
-                                        int page_size, int ring_tokens, int window, float scale, void* stream) {
+                                        int page_size, int ring_tokens, int window, float scale, int tiles_per_cta,
+                                        void* stream) {
 #if DFI_FA_ENABLED
     if (n_seqs <= 0 || max_q_len <= 0) return DFI_OK;
     if (page_size != kFaKeys || n_q <= 0 || n_kv <= 0 || n_q % n_kv || ring_tokens % kFaKeys) return DFI_ERR_SHAPE;
@@ -695,7 +697,20 @@ DFI_EXPORT int dfi_attention_prefill_tc(const void* q, int q_rows, int q_stride,
     if (!make_tile_map(&map_q, q, q_rows, n_q * kFaD, kFaRows, q_stride)) return DFI_ERR_LAUNCH;
     if (!make_tile_map(&map_k, k_cache, (int)cache_rows, kFaD, kFaKeys)) return DFI_ERR_LAUNCH;
     if (!make_tile_map(&map_v, v_cache, (int)cache_rows, kFaD, kFaKeys)) return DFI_ERR_LAUNCH;
-    if (max_q_len > kFaRows) {
+    static int sms = 0;
+    if (sms == 0) {
+        int device = 0;
+        if (cudaGetDevice(&device) != cudaSuccess ||
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess)
+            sms = 1;
+    }
+    // CTAs of two tiles each; if they would leave half the SMs idle (one prompt of up to 512 tokens with 32 heads),
+    // CTAs of one tile do better although a tile alone runs its pages more slowly (measured at 512 tokens:
+    // 16.4 against 19.3 us; at 768 tokens 29.4 against 25.2)
+    // (counted from the rows there are: a step laid out at a larger shape has sequences without rows)
+    const long long ctas2 = (long long)n_q * ((q_rows + 2 * kFaRows - 1) / (2 * kFaRows));
+    if (tiles_per_cta < 0 || tiles_per_cta > 2) return DFI_ERR_SHAPE;
+    if (max_q_len > kFaRows && (tiles_per_cta == 2 || (tiles_per_cta == 0 && ctas2 * 2 > sms))) {
         // long shares: two query tiles per CTA, each with softmax warps of its own
         static bool configured2 = false;
         if (!configured2) {

@@ -358,9 +358,12 @@ def attention_prefill(q, cache, ctx, n_q: int, n_kv: int, head_dim: int, scale: 
     return out
 
 
-def attention_prefill_tc(q, cache, ctx, n_q: int, n_kv: int, head_dim: int, scale: float, window: int = 0):
+def attention_prefill_tc(q, cache, ctx, n_q: int, n_kv: int, head_dim: int, scale: float, window: int = 0,
+                         tiles_per_cta: int = 0):
     """Flash attention for prompts on tcgen05 (head sizes 64 and 128): TMA-fed pages of keys and values,
-    scores and the page's output in tensor memory, one thread per query row for the softmax."""
+    scores and the page's output in tensor memory, one thread per query row for the softmax.
+    ``tiles_per_cta``: 1 or 2 query tiles of 128 rows a CTA; 0 lets the launch choose (two, unless the
+    shares are short or that would leave half the SMs without a CTA)."""
     _need_cuda(q, cache.k)
     assert q.dtype == torch.bfloat16 and q.stride(1) == 1 and q.shape[1] == n_q * head_dim
     lib = _attention_library(head_dim)
@@ -371,7 +374,7 @@ def attention_prefill_tc(q, cache, ctx, n_q: int, n_kv: int, head_dim: int, scal
         _ptr(q), q.shape[0], q.stride(0), _ptr(out), out.stride(0), _ptr(cache.k), _ptr(cache.v),
         ctypes.c_longlong(cache.k.shape[0]), _ptr(cache.block_table), cache.block_table.shape[1], _ptr(ctx.cu_rows),
         _ptr(ctx.seq_start), ctx.n_seqs, ctx.max_q_len, n_q, n_kv, cache.page_size, cache.ring_tokens, window,
-        _f(scale), _stream()), "attention_prefill_tc", f"head_dim {head_dim}, {n_q}/{n_kv} heads")
+        _f(scale), int(tiles_per_cta), _stream()), "attention_prefill_tc", f"head_dim {head_dim}, {n_q}/{n_kv} heads")
     return out
 
 

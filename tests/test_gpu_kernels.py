@@ -534,18 +534,20 @@ def test_attention_tcgen05_prefill(n_q, n_kv, dim):
     for lengths, new in (([70, 3, 130], [70, 3, 130]), ([70, 3, 200], [10, 3, 67]), ([257, 64, 1], [1, 1, 1]),
                          ([300], [300]), ([700, 129], [257, 128])):
         q, cache, row_seq, row_pos, scale, want = attention_case(dtype, n_q, n_kv, dim, lengths, new, seed=dim, sharp=5)
-        got = kernels.attention_prefill_tc(q, cache, step_like(lengths, new), n_q, n_kv, dim, scale)
-        assert kernels.attention_tc_error(dim) == 0
-        assert torch.isfinite(got).all(), (lengths, new)
-        assert torch.allclose(got.float().cpu(), want, atol=tol(dtype, 2), rtol=tol(dtype)), (lengths, new)
+        for tiles in (0, 1, 2):          # the launch's choice, one query tile a CTA, two
+            got = kernels.attention_prefill_tc(q, cache, step_like(lengths, new), n_q, n_kv, dim, scale, tiles_per_cta=tiles)
+            assert kernels.attention_tc_error(dim) == 0
+            assert torch.isfinite(got).all(), (lengths, new, tiles)
+            assert torch.allclose(got.float().cpu(), want, atol=tol(dtype, 2), rtol=tol(dtype)), (lengths, new, tiles)
     for window, ring in ((100, 192), (64, 128), (130, 320)):
         lengths, new = [500, 131, 40], [3, 2, 40]
         q, cache, row_seq, row_pos, scale, want = attention_case(dtype, n_q, n_kv, dim, lengths, new, window=window,
                                                                  ring_tokens=ring, seed=window)
-        got = kernels.attention_prefill_tc(q, cache, step_like(lengths, new), n_q, n_kv, dim, scale, window)
-        assert kernels.attention_tc_error(dim) == 0
-        assert torch.isfinite(got).all()
-        assert torch.allclose(got.float().cpu(), want, atol=tol(dtype, 2), rtol=tol(dtype)), window
+        for tiles in (1, 2):
+            got = kernels.attention_prefill_tc(q, cache, step_like(lengths, new), n_q, n_kv, dim, scale, window, tiles_per_cta=tiles)
+            assert kernels.attention_tc_error(dim) == 0
+            assert torch.isfinite(got).all()
+            assert torch.allclose(got.float().cpu(), want, atol=tol(dtype, 2), rtol=tol(dtype)), (window, tiles)
 
 
 @pytest.mark.parametrize("m, n, k", [(1, 1, 1), (7, 130, 100), (64, 64, 16), (65, 63, 17), (300, 320, 200), (3, 1000, 2563)])
