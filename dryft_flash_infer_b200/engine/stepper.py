@@ -36,6 +36,9 @@ class Stepper:
 
     @torch.no_grad()
     def step(self, entries: list[StepEntry]):
+        for e in entries:
+            if len(e.tokens) == 0 and len(e.want) > 0:
+                raise ValueError(f"wanted places {list(e.want)} of slot {e.slot}, which brings no tokens to this step")
         entries = [e for e in entries if len(e.tokens) > 0]
         if not entries:
             return None

@@ -13,7 +13,6 @@ class SwiGLU(FeedForward):
 
     kind = "swiglu"
     accepts_scaled_rows = True
-    fuses_add_norm = True
     graph_safe = True
 
     def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "silu"):
@@ -21,6 +20,12 @@ class SwiGLU(FeedForward):
             raise ValueError(f"SwiGLU feed-forward knows the 'silu' activation only, got {activation!r}")
         self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
         self.gate_up = self.down = None
+
+    @property
+    def fuses_add_norm(self) -> bool:
+        # the product that would add and prepare the next norm is the down projection, whose inner size is the
+        # intermediate one: the decode kernel takes it in steps of 8 (other sizes run the plain kernels)
+        return self.intermediate_size % 8 == 0
 
     def tensors(self):
         inter, hidden = self.intermediate_size, self.hidden_size

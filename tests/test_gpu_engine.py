@@ -255,6 +255,10 @@ def test_engine_errors_are_loud(folders):
         engine.step([StepEntry(a, [cfg["vocab_size"]], [0])])
     with pytest.raises(ValueError, match="twice"):
         engine.step([StepEntry(a, [1], [0]), StepEntry(a, [2], [0])])
+    with pytest.raises(ValueError, match="brings no tokens"):
+        engine.step([StepEntry(a, [1], [0]), StepEntry(b, [], [-1])])
+    with pytest.raises(ValueError, match="outside the 1 token"):
+        engine.step([StepEntry(a, [1], [1])])
     engine.close_slot(a)
     with pytest.raises(CacheError, match="freed twice"):
         engine.close_slot(a)
@@ -723,3 +727,37 @@ def test_the_words_about_the_next_product_change_no_logit(wide_model, monkeypatc
         assert any(h is not None for h in given) == (tiles > 0)
     assert torch.equal(seen[4, False], seen[0, False])
     assert torch.equal(seen[4, True], seen[0, True])
+
+
+TINY_E = {
+    "architectures": ["Qwen3ForCausalLM"], "num_hidden_layers": 2, "hidden_size": 72, "num_attention_heads": 6,
+    "num_key_value_heads": 3, "head_dim": 80, "intermediate_size": 100, "vocab_size": 257, "rope_theta": 700.0,
+    "rms_norm_eps": 2e-5, "tie_word_embeddings": True, "hidden_act": "silu", "max_position_embeddings": 2048,
+}
+
+
+@pytest.mark.parametrize("graph", [True, False])
+@pytest.mark.parametrize("hidden, inter", [(72, 100), (100, 56), (100, 100)])
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_widths_that_are_no_multiples_of_eight(tmp_path, dtype, hidden, inter, graph):
+    """An intermediate size or a width of 100: the TMA-fed products take inner sizes in steps of 8 only, so
+    these products run on the plain kernel, and a product before a norm must not be asked to fuse with it
+    when its own inner size is not one of those (the down projection after a width that is)."""
+    from dryft_flash_infer_b200 import Engine, StepEntry
+
+    cfg = dict(TINY_E, hidden_size=hidden, intermediate_size=inter)
+    weights = plain_model.random_weights(cfg, seed=hidden + inter, matrix_std=0.06, norm_std=0.1)
+    folder = write_model(tmp_path, cfg, weights)
+    ref_w = reference_weights(weights, dtype)
+    engine = Engine(folder, dtype=dtype, max_tokens=64 * 12, cuda_graph=graph)
+    prompts = prompts_for(cfg, [65, 3, 63, 17], seed=5)
+    want = [plain_model.forward(cfg, ref_w, p) for p in prompts]
+    slots = [engine.open_slot() for _ in prompts]
+    logits = engine.step([StepEntry(s, p[:-2], [len(p) - 3]) for s, p in zip(slots, prompts)])
+    for i, p in enumerate(prompts):
+        assert_close(logits[i], want[i][len(p) - 3], dtype, f"prefill {i}")
+    for t in (2, 1):
+        logits = engine.step([StepEntry(s, [p[len(p) - t]], [0]) for s, p in zip(slots, prompts)])
+        for i, p in enumerate(prompts):
+            assert_close(logits[i], want[i][len(p) - t], dtype, f"decode {i} -{t}")
+    engine.check_status()
