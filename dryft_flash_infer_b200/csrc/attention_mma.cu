@@ -342,8 +342,59 @@ __device__ __forceinline__ uint32_t dec_cluster_map(const void* own, uint32_t ra
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(out) : "r"((uint32_t)__cvta_generic_to_shared(own)), "r"(rank));
     return out;
 }
+constexpr int kDecodeClusterWide = 8;   // ... or eight, when the groups are few and small (up to four query heads each)
+constexpr bool kWideClusterFits = (D / kDecodeClusterWide) % 4 == 0;     // a CTA's share of the columns in fours
+constexpr int kWideMostPages = 80;      // a group of more pages than this is cut into more than eight parts
 __device__ __forceinline__ void dec_cluster_arrive() { asm volatile("barrier.cluster.arrive.aligned;\n" ::: "memory"); }
 __device__ __forceinline__ void dec_cluster_wait() { asm volatile("barrier.cluster.wait.aligned;\n" ::: "memory"); }
+// The merge of a group's parts inside a cluster of CL CTAs.  Every CTA owns D / CL columns of the head and
+// receives, in the space of its query tile, [sender][row][its columns] of the others' sums and then
+// [sender][row][maximum, sum]; the space holds 32 / CL rows of a group (8 query heads with four CTAs, 4 with
+// eight), kRows * D * 4 + CL * kRows * 8 bytes, which the query tile's 16 rows always cover.
+template <int CL>
+__device__ __forceinline__ void dec_cluster_send(const bf16* q_s, int row, int d, float4 acc, float mx, float sum) {
+    constexpr int kRows = 32 / CL;
+    constexpr int share = D / CL;
+    const uint32_t owner = (uint32_t)(d / share);
+    const uint32_t base = dec_cluster_map(q_s, owner);
+    const int me = (int)dec_cluster_rank();
+    const uint32_t o_at = base + (uint32_t)(((me * kRows + row) * share + d % share) * 4);
+    asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};\n" ::"r"(o_at), "f"(acc.x), "f"(acc.y), "f"(acc.z), "f"(acc.w) : "memory");
+    if (d % share == 0) {
+        const uint32_t ml_at = base + (uint32_t)((CL * kRows * share + (me * kRows + row) * 2) * 4);
+        asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};\n" ::"r"(ml_at), "f"(mx), "f"(sum) : "memory");
+    }
+}
+// All parts have arrived (the caller has passed the cluster barrier): this CTA adds them, in the order of the
+// parts' pages, for its share of the columns and writes the group's rows; `dst` is the group's first row.
+template <int CL>
+__device__ __forceinline__ void dec_cluster_finish(const bf16* q_s, bf16* dst_group, int group) {
+    constexpr int kRows = 32 / CL;
+    constexpr int share = D / CL;
+    const float* recv_o = reinterpret_cast<const float*>(q_s);
+    const float* recv_ml = recv_o + CL * kRows * share;
+    const int me = (int)dec_cluster_rank();
+    for (int i = threadIdx.x; i < group * (share / 4); i += kThreads) {
+        const int row = i / (share / 4), dl = (i % (share / 4)) * 4;
+        float mx = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < CL; ++j) mx = fmaxf(mx, recv_ml[(j * kRows + row) * 2]);
+        const float m_use = mx == -INFINITY ? 0.f : mx;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        float sum = 0.f;
+#pragma unroll
+        for (int j = 0; j < CL; ++j) {
+            const float w = exp2f(recv_ml[(j * kRows + row) * 2] - m_use);
+            const float4 part = *reinterpret_cast<const float4*>(recv_o + (j * kRows + row) * share + dl);
+            acc.x += w * part.x; acc.y += w * part.y; acc.z += w * part.z; acc.w += w * part.w;
+            sum += w * recv_ml[(j * kRows + row) * 2 + 1];
+        }
+        const float inv = sum > 0.f ? 1.0f / sum : 0.f;
+        bf16* dst = dst_group + (size_t)row * D + me * share + dl;
+        *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
+        *reinterpret_cast<__nv_bfloat162*>(dst + 2) = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
+    }
+}
 
 #ifdef DFI_TRACE
 __device__ unsigned long long g_attn_trace[4096 * 8];
@@ -549,9 +600,18 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         if (parts < kDecodeCluster && longest >= kDecodeCluster && cluster_size == kDecodeCluster &&
             n_seqs * n_kv * kDecodeCluster <= (int)gridDim.x)
             parts = kDecodeCluster;
+        // A launch in clusters of eight (few groups of up to four query heads): eight parts each as long as a
+        // part stays at ten pages or fewer, so that they meet in the cluster and not through scratch memory
+        // and a ticket.
+        bool by_cluster = false;          // fewer CTAs than equal runs would use, on purpose
+        if (cluster_size == kDecodeClusterWide && longest >= kDecodeClusterWide && longest <= kWideMostPages &&
+            n_seqs * n_kv * kDecodeClusterWide <= (int)gridDim.x) {
+            parts = kDecodeClusterWide;
+            by_cluster = true;
+        }
         // (not if there are more parts than CTAs, nor if they would keep fewer than 80 % of the CTAs busy
         // that equal runs crossing from group to group would: then those runs are used)
-        if (n_seqs * n_kv * parts <= (int)gridDim.x && n_seqs * n_kv * parts * 100 >= run.n_ctas * 80) {
+        if (n_seqs * n_kv * parts <= (int)gridDim.x && (by_cluster || n_seqs * n_kv * parts * 100 >= run.n_ctas * 80)) {
             run.parts = parts;
             run.n_ctas = n_seqs * n_kv * parts;
         } else if (n_seqs * n_kv >= (int)gridDim.x) {
@@ -573,7 +633,8 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     // says so), and a second barrier tells it that all parts have arrived.  All CTAs of a cluster
     // take the same decision, since they compute it from the same numbers.
     // (the cluster's size is a constant of this file, so that the shares of the columns below are divided by a constant)
-    const bool clustered = cluster_size == kDecodeCluster && run.parts == kDecodeCluster && group <= 8 && (D / kDecodeCluster) % 4 == 0;
+    const bool clustered = cluster_size > 1 && run.parts == cluster_size && group <= 32 / cluster_size &&
+                           (D / kDecodeCluster) % 4 == 0 && (cluster_size == kDecodeCluster || kWideClusterFits);
     const int cta = blockIdx.x;
     const bool idle = cta >= run.n_ctas;
     const int u_begin = idle ? 0 : dec_run_begin(run, cta), u_end = idle ? 0 : dec_run_begin(run, cta + 1);
@@ -801,17 +862,11 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                 sum += c * red_ml[(w * 16 + row) * 2 + 1];
             }
             if (clustered) {
-                // to the owner of these columns: [sender][row][column in the owner's share], then [sender][row][m, l]
-                constexpr int kRows = 8;
-                constexpr int share = D / kDecodeCluster;
-                const uint32_t owner = (uint32_t)(d / share);
-                const uint32_t base = dec_cluster_map(q_s, owner);
-                const int me = (int)dec_cluster_rank();
-                const uint32_t o_at = base + (uint32_t)(((me * kRows + row) * share + d % share) * 4);
-                asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};\n" ::"r"(o_at), "f"(acc.x), "f"(acc.y), "f"(acc.z), "f"(acc.w) : "memory");
-                if (d % share == 0) {
-                    const uint32_t ml_at = base + (uint32_t)((kDecodeCluster * kRows * share + (me * kRows + row) * 2) * 4);
-                    asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};\n" ::"r"(ml_at), "f"(mx), "f"(sum) : "memory");
+                if constexpr (kWideClusterFits) {
+                    if (run.parts == kDecodeClusterWide) dec_cluster_send<kDecodeClusterWide>(q_s, row, d, acc, mx, sum);
+                    else dec_cluster_send<kDecodeCluster>(q_s, row, d, acc, mx, sum);
+                } else {
+                    dec_cluster_send<kDecodeCluster>(q_s, row, d, acc, mx, sum);
                 }
             } else if (whole) {
                 const float inv = sum > 0.f ? 1.0f / sum : 0.f;
@@ -827,30 +882,12 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
             // all parts have arrived; this CTA finishes its share of the columns
             dec_cluster_arrive();
             dec_cluster_wait();
-            constexpr int kRows = 8;
-            constexpr int share = D / kDecodeCluster;
-            const float* recv_o = reinterpret_cast<const float*>(q_s);
-            const float* recv_ml = recv_o + kDecodeCluster * kRows * share;
-            const int me = (int)dec_cluster_rank();
-            for (int i = threadIdx.x; i < group * (share / 4); i += kThreads) {
-                const int row = i / (share / 4), dl = (i % (share / 4)) * 4;
-                float mx = -INFINITY;
-#pragma unroll
-                for (int j = 0; j < kDecodeCluster; ++j) mx = fmaxf(mx, recv_ml[(j * kRows + row) * 2]);
-                const float m_use = mx == -INFINITY ? 0.f : mx;
-                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-                float sum = 0.f;
-#pragma unroll
-                for (int j = 0; j < kDecodeCluster; ++j) {          // in the order of the parts' pages
-                    const float w = exp2f(recv_ml[(j * kRows + row) * 2] - m_use);
-                    const float4 part = *reinterpret_cast<const float4*>(recv_o + (j * kRows + row) * share + dl);
-                    acc.x += w * part.x; acc.y += w * part.y; acc.z += w * part.z; acc.w += w * part.w;
-                    sum += w * recv_ml[(j * kRows + row) * 2 + 1];
-                }
-                const float inv = sum > 0.f ? 1.0f / sum : 0.f;
-                bf16* dst = out + (size_t)seq * out_stride + (size_t)(kv_head * group + row) * D + me * share + dl;
-                *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
-                *reinterpret_cast<__nv_bfloat162*>(dst + 2) = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
+            bf16* dst = out + (size_t)seq * out_stride + (size_t)(kv_head * group) * D;
+            if constexpr (kWideClusterFits) {
+                if (run.parts == kDecodeClusterWide) dec_cluster_finish<kDecodeClusterWide>(q_s, dst, group);
+                else dec_cluster_finish<kDecodeCluster>(q_s, dst, group);
+            } else {
+                dec_cluster_finish<kDecodeCluster>(q_s, dst, group);
             }
         } else if (!whole) {
             __syncthreads();
@@ -959,6 +996,15 @@ static int decode_clusters_enabled() {
     return enabled;
 }
 
+static int wide_clusters_enabled() {
+    static int enabled = -1;
+    if (enabled < 0) {
+        const char* text = getenv("DRYFT_ATTENTION_CLUSTER");      // "4": never clusters of eight
+        enabled = (text != nullptr && text[0] == '4') ? 0 : 1;
+    }
+    return enabled;
+}
+
 DFI_EXPORT int dfi_attention_decode_wave() {
     static int wave = -1;
     if (wave >= 0) return wave;
@@ -1022,7 +1068,7 @@ static int attention_decode(const void* q, int q_stride, void* out, int out_stri
                             const void* v_cache, long long cache_pages, const int* block_table, int table_width,
                             const int* seq_start, int n_seqs, int n_q, int n_kv, int page_size,
                             int ring_tokens, int window, float scale, int n_ctas, float* scratch,
-                            int* counters, const DecodePrep& prep, void* stream) {
+                            int* counters, const DecodePrep& prep, int max_kv_len, void* stream) {
     if (n_seqs <= 0) return DFI_OK;
     if (page_size != kPage || n_q <= 0 || n_kv <= 0 || n_q % n_kv || n_q / n_kv > 16 || ring_tokens % kPage)
         return DFI_ERR_SHAPE;
@@ -1051,10 +1097,24 @@ static int attention_decode(const void* q, int q_stride, void* out, int out_stri
             return DFI_ERR_LAUNCH;
     }
     // clusters only where the kernel can use them: every group cut into kDecodeCluster parts needs that many CTAs
-    const int cluster = (decode_clusters_enabled() && n_ctas % kDecodeCluster == 0 &&
-                         (long long)n_seqs * n_kv * kDecodeCluster <= n_ctas) ? kDecodeCluster : 1;
+    int cluster = (decode_clusters_enabled() && n_ctas % kDecodeCluster == 0 &&
+                   (long long)n_seqs * n_kv * kDecodeCluster <= n_ctas) ? kDecodeCluster : 1;
+    // eight CTAs a cluster where that still covers every group and a group's rows fit the receive space
+    // (the grid is then a whole number of them: up to seven CTAs fewer, none of which would have had pages)
+    int grid = n_ctas;
+    const int wide_grid = n_ctas / kDecodeClusterWide * kDecodeClusterWide;
+    // Measured at 32/8 heads of 128: a launch in clusters of eight gains 1.4 to 4.9 % of the step for one or two
+    // sequences of up to 4,096 keys, and loses 1 to 4 % for four sequences or for longer ones, whose parts do
+    // not meet in the cluster and whose CTAs the wider clusters place less evenly.  Hence: at most 16 groups,
+    // and only if the caller says that no sequence of this launch can be longer than the kernel's limit.
+    if (cluster > 1 && kWideClusterFits && wide_clusters_enabled() && n_q / n_kv <= 32 / kDecodeClusterWide &&
+        n_seqs * n_kv <= 16 && max_kv_len > 0 && max_kv_len <= kWideMostPages * kPage &&
+        (long long)n_seqs * n_kv * kDecodeClusterWide <= wide_grid) {
+        cluster = kDecodeClusterWide;
+        grid = wide_grid;
+    }
     cudaLaunchConfig_t config = {};
-    config.gridDim = dim3(n_ctas);
+    config.gridDim = dim3(grid);
     config.blockDim = dim3(kThreads);
     config.dynamicSmemBytes = kDecodeSmem;
     config.stream = (cudaStream_t)stream;
@@ -1084,15 +1144,17 @@ static int attention_decode(const void* q, int q_stride, void* out, int out_stri
     return DFI_OK;
 }
 
+// max_kv_len: no sequence of this launch, or of any later replay of it in a CUDA graph, holds more keys than this
+// (0: not known).  It only chooses between launch shapes.
 DFI_EXPORT int dfi_attention_decode(const void* q, int q_stride, void* out, int out_stride, const void* k_cache,
                                     const void* v_cache, long long cache_pages, const int* block_table, int table_width,
                                     const int* seq_start, int n_seqs, int n_q, int n_kv, int page_size,
                                     int ring_tokens, int window, float scale, int n_ctas, float* scratch,
-                                    int* counters, void* stream) {
+                                    int* counters, int max_kv_len, void* stream) {
     DecodePrep none = {};
     return attention_decode(q, q_stride, out, out_stride, k_cache, v_cache, cache_pages, block_table, table_width,
                             seq_start, n_seqs, n_q, n_kv, page_size, ring_tokens, window, scale, n_ctas, scratch, counters,
-                            none, stream);
+                            none, max_kv_len, stream);
 }
 
 // 1 if this build (head size) has the variant that prepares the step's token itself.
@@ -1109,7 +1171,7 @@ DFI_EXPORT int dfi_attention_decode_prepared(const void* qkv, int qkv_stride, co
                                              const int* block_table, int table_width,
                                              const int* seq_start, int n_seqs, int n_q, int n_kv, int page_size,
                                              int ring_tokens, int window, float scale, int n_ctas, float* scratch,
-                                             int* counters, void* stream) {
+                                             int* counters, int max_kv_len, void* stream) {
     if (!kPrepHeadDim) return DFI_ERR_SHAPE;
     if (qkv == nullptr || qkv_stride % 4 || (reinterpret_cast<uintptr_t>(qkv) & 7)) return DFI_ERR_ALIGN;
     if (!aligned16(q_weight) || !aligned16(k_weight) || !aligned16(cos_table) || !aligned16(sin_table)) return DFI_ERR_ALIGN;
@@ -1127,5 +1189,5 @@ DFI_EXPORT int dfi_attention_decode_prepared(const void* qkv, int qkv_stride, co
     prep.write_cache = write_cache;
     return attention_decode(nullptr, 0, out, out_stride, k_cache, v_cache, cache_pages, block_table, table_width,
                             seq_start, n_seqs, n_q, n_kv, page_size, ring_tokens, window, scale, n_ctas, scratch, counters,
-                            prep, stream);
+                            prep, max_kv_len, stream);
 }

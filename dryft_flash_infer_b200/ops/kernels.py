@@ -433,15 +433,15 @@ def attention_decode(q, cache, ctx, n_q: int, n_kv: int, head_dim: int, scale: f
             int(cache.writes), _ptr(out), out.stride(0), _ptr(cache.k), _ptr(cache.v), ctypes.c_longlong(cache.k.shape[0]),
             _ptr(cache.block_table),
             cache.block_table.shape[1], _ptr(ctx.seq_start), ctx.n_seqs, n_q, n_kv, cache.page_size, cache.ring_tokens,
-            window, _f(scale), n_ctas, _ptr(held[0]), _ptr(held[1]), _stream()), "attention_decode",
-            f"head_dim {head_dim}, {n_q}/{n_kv} heads, tokens prepared inside")
+            window, _f(scale), n_ctas, _ptr(held[0]), _ptr(held[1]), int(getattr(ctx, "max_kv_len", 0) or 0), _stream()),
+            "attention_decode", f"head_dim {head_dim}, {n_q}/{n_kv} heads, tokens prepared inside")
         return out
     _check(lib.dfi_attention_decode(
         _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cache.k), _ptr(cache.v), ctypes.c_longlong(cache.k.shape[0]),
         _ptr(cache.block_table),
         cache.block_table.shape[1], _ptr(ctx.seq_start), ctx.n_seqs, n_q, n_kv, cache.page_size, cache.ring_tokens,
-        window, _f(scale), n_ctas, _ptr(held[0]), _ptr(held[1]), _stream()), "attention_decode",
-        f"head_dim {head_dim}, {n_q}/{n_kv} heads")
+        window, _f(scale), n_ctas, _ptr(held[0]), _ptr(held[1]), int(getattr(ctx, "max_kv_len", 0) or 0), _stream()),
+        "attention_decode", f"head_dim {head_dim}, {n_q}/{n_kv} heads")
     return out
 
 

@@ -623,3 +623,25 @@ def test_a_word_about_the_next_product_changes_no_result(m):
     assert kernels.next_weights(torch.zeros(16, 16, dtype=torch.float32, device="cuda")).hint(m) is None
     assert kernels.next_weights(followers[1][0]).hint(65) is None
     assert kernels.next_weights(None) is None
+
+
+@pytest.mark.parametrize("n_q, n_kv, dim", [(32, 8, 128), (8, 2, 64), (3, 1, 96), (4, 4, 32), (2, 2, 128)])
+@pytest.mark.parametrize("length", [500, 513, 1270, 2049, 4100, 5100, 5200])
+def test_attention_decode_of_few_groups_in_clusters_of_eight(n_q, n_kv, dim, length):
+    """Few groups of up to four query heads and 8 to 80 pages each (a small batch at a middle context): the
+    launch forms clusters of eight CTAs and every group is cut into eight parts that meet in their cluster;
+    with more pages (5,200 keys) or with too few CTAs for that the parts meet as before."""
+    from dryft_flash_infer_b200.ops import kernels
+
+    dtype = torch.bfloat16
+    n_seqs = max(1, 8 // n_kv) if length < 3000 else 1
+    lengths, new = [length] * n_seqs, [1] * n_seqs
+    q, cache, row_seq, row_pos, scale, want = attention_case(dtype, n_q, n_kv, dim, lengths, new, seed=dim + length,
+                                                             sharp=length // 3)
+    ctx = step_like(lengths, new)
+    for ctas in (None, 64, 16):
+        got = kernels.attention_decode(q, cache, ctx, n_q, n_kv, dim, scale, n_ctas=ctas)
+        assert torch.isfinite(got).all()
+        assert torch.allclose(got.float().cpu(), want, atol=tol(dtype, 2), rtol=tol(dtype)), ctas
+        assert torch.equal(kernels.attention_decode(q, cache, ctx, n_q, n_kv, dim, scale, n_ctas=ctas), got)
+    kernels.check_status()
