@@ -305,6 +305,7 @@ struct DecodeRun {
     int parts;      // > 0: every group has `tiles` pages and is cut into this many parts, one CTA each
     int tiles;
     int whole;      // > 0: every group has `tiles` pages, there are this many groups, and a CTA takes whole groups
+    int uneven;     // with parts > 0: the groups differ in length; each is cut into `parts` parts of its own pages
 };
 // First unit of a CTA's run: equal contiguous runs over all units, or (when every sequence brings
 // the same number of pages) the same number of parts for every group, so that no run crosses from
@@ -344,6 +345,7 @@ __device__ __forceinline__ uint32_t dec_cluster_map(const void* own, uint32_t ra
 }
 constexpr int kDecodeClusterWide = 8;   // ... or eight, when the groups are few and small (up to four query heads each)
 constexpr bool kWideClusterFits = (D / kDecodeClusterWide) % 4 == 0;     // a CTA's share of the columns in fours
+constexpr int kCutCost = 12;            // what a group cut by the end of an equal run costs, in pages of a CTA's time
 constexpr int kWideMostPages = 80;      // a group of more pages than this is cut into more than eight parts
 __device__ __forceinline__ void dec_cluster_arrive() { asm volatile("barrier.cluster.arrive.aligned;\n" ::: "memory"); }
 __device__ __forceinline__ void dec_cluster_wait() { asm volatile("barrier.cluster.wait.aligned;\n" ::: "memory"); }
@@ -588,6 +590,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     run.n_ctas = max(1, min((int)gridDim.x, run.total / least));
     run.parts = 0;
     run.whole = 0;
+    run.uneven = 0;
     run.tiles = longest;
     if (shortest == longest) {
         // every group has the same number of pages: the same number of parts for each, none crossing over
@@ -626,6 +629,22 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
             }
         }
     }
+    else if (cluster_size > 1 && n_seqs * n_kv * cluster_size <= (int)gridDim.x && group <= 32 / cluster_size &&
+             (D / kDecodeCluster) % 4 == 0 && (cluster_size == kDecodeCluster || kWideClusterFits)) {
+        // Sequences of different lengths and few groups: every group is cut into as many parts as a cluster has
+        // CTAs, each part a share of its own group's pages (none, for a group with fewer pages than parts), and
+        // the parts meet in the cluster.  The CTAs of the longest sequence then hold more pages than an equal
+        // share; equal runs over all pages instead cut groups wherever a run ends, and every cut costs a second
+        // preparation of queries, a second start of the page ring, partial results through scratch memory and a
+        // ticket: about kCutCost pages' worth (batch 8 near 3,900 keys: 3.42 ms a step with equal runs, 2.85 ms
+        // with sequences of one length).
+        const int per_part = (longest + cluster_size - 1) / cluster_size;
+        if (per_part <= run.total / run.n_ctas + kCutCost) {
+            run.parts = cluster_size;
+            run.uneven = 1;
+            run.n_ctas = n_seqs * n_kv * cluster_size;
+        }
+    }
     // When the launch groups CTAs into clusters and every group of this step is cut into exactly that
     // many parts, the CTAs of a cluster hold the parts of one group and merge them through distributed
     // shared memory: each owns a share of the head's columns and receives the others' sums for them in
@@ -637,11 +656,19 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                            (D / kDecodeCluster) % 4 == 0 && (cluster_size == kDecodeCluster || kWideClusterFits);
     const int cta = blockIdx.x;
     const bool idle = cta >= run.n_ctas;
-    const int u_begin = idle ? 0 : dec_run_begin(run, cta), u_end = idle ? 0 : dec_run_begin(run, cta + 1);
+    int u_begin = idle ? 0 : dec_run_begin(run, cta), u_end = idle ? 0 : dec_run_begin(run, cta + 1);
 
     // the sequence that holds unit u_begin: the last one whose first unit is not past it
     int seq;
-    {
+    if (run.uneven && !idle) {
+        // part `cta % parts` of group `cta / parts`: a share of that group's own pages (it may be empty)
+        const int gi = cta / run.parts, part = cta % run.parts;
+        seq = gi / n_kv;
+        const int seq_tiles = cum_s[seq + 1] - cum_s[seq];
+        const int first = cum_s[seq] * n_kv + (gi % n_kv) * seq_tiles;
+        u_begin = first + seq_tiles * part / run.parts;
+        u_end = first + seq_tiles * (part + 1) / run.parts;
+    } else {
         int lo = 0, hi = n_seqs - 1;
         while (lo < hi) {
             const int mid = (lo + hi + 1) >> 1;
@@ -677,7 +704,10 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     atrace(2);
     int u = u_begin;
     bool first_segment = true;
-    while (u < u_end) {
+    // (a part without pages still takes its place in the cluster's merge: one pass with nothing to attend to)
+    bool empty_part = run.uneven && u_begin == u_end;
+    while (u < u_end || empty_part) {
+        empty_part = false;
         while (cum_s[seq + 1] * n_kv <= u) ++seq;
         const int seq_tiles = cum_s[seq + 1] - cum_s[seq];
         const int in_seq = u - cum_s[seq] * n_kv;
