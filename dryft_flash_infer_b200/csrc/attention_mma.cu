@@ -344,18 +344,20 @@ __device__ __forceinline__ uint32_t dec_cluster_map(const void* own, uint32_t ra
     return out;
 }
 constexpr int kDecodeClusterWide = 8;   // ... or eight, when the groups are few and small (up to four query heads each)
+constexpr int kDecodeClusterPair = 2;   // ... or two, when there are too many groups for four CTAs each
 constexpr bool kWideClusterFits = (D / kDecodeClusterWide) % 4 == 0;     // a CTA's share of the columns in fours
 constexpr int kCutCost = 12;            // what a group cut by the end of an equal run costs, in pages of a CTA's time
 constexpr int kWideMostPages = 80;      // a group of more pages than this is cut into more than eight parts
 __device__ __forceinline__ void dec_cluster_arrive() { asm volatile("barrier.cluster.arrive.aligned;\n" ::: "memory"); }
 __device__ __forceinline__ void dec_cluster_wait() { asm volatile("barrier.cluster.wait.aligned;\n" ::: "memory"); }
-// The merge of a group's parts inside a cluster of CL CTAs.  Every CTA owns D / CL columns of the head and
-// receives, in the space of its query tile, [sender][row][its columns] of the others' sums and then
-// [sender][row][maximum, sum]; the space holds 32 / CL rows of a group (8 query heads with four CTAs, 4 with
-// eight), kRows * D * 4 + CL * kRows * 8 bytes, which the query tile's 16 rows always cover.
+// The merge of a group's parts inside a cluster of CL CTAs (2, 4 or 8).  Every CTA owns D / CL columns of the
+// head and receives, in the space of its query tile, [sender][row][its columns] of the others' sums and then
+// [sender][row][maximum, sum]; the space holds dec_cluster_rows(CL) rows of a group (8 query heads, 4 with
+// eight CTAs), kRows * D * 4 + CL * kRows * 8 bytes, which the query tile's 16 rows always cover.
+__host__ __device__ constexpr int dec_cluster_rows(int cl) { return cl == 8 ? 4 : 8; }
 template <int CL>
 __device__ __forceinline__ void dec_cluster_send(const bf16* q_s, int row, int d, float4 acc, float mx, float sum) {
-    constexpr int kRows = 32 / CL;
+    constexpr int kRows = dec_cluster_rows(CL);
     constexpr int share = D / CL;
     const uint32_t owner = (uint32_t)(d / share);
     const uint32_t base = dec_cluster_map(q_s, owner);
@@ -371,7 +373,7 @@ __device__ __forceinline__ void dec_cluster_send(const bf16* q_s, int row, int d
 // parts' pages, for its share of the columns and writes the group's rows; `dst` is the group's first row.
 template <int CL>
 __device__ __forceinline__ void dec_cluster_finish(const bf16* q_s, bf16* dst_group, int group) {
-    constexpr int kRows = 32 / CL;
+    constexpr int kRows = dec_cluster_rows(CL);
     constexpr int share = D / CL;
     const float* recv_o = reinterpret_cast<const float*>(q_s);
     const float* recv_ml = recv_o + CL * kRows * share;
@@ -629,8 +631,8 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
             }
         }
     }
-    else if (cluster_size > 1 && n_seqs * n_kv * cluster_size <= (int)gridDim.x && group <= 32 / cluster_size &&
-             (D / kDecodeCluster) % 4 == 0 && (cluster_size == kDecodeCluster || kWideClusterFits)) {
+    else if (cluster_size > 1 && n_seqs * n_kv * cluster_size <= (int)gridDim.x && group <= dec_cluster_rows(cluster_size) &&
+             (D / kDecodeCluster) % 4 == 0 && (cluster_size != kDecodeClusterWide || kWideClusterFits)) {
         // Sequences of different lengths and few groups: every group is cut into as many parts as a cluster has
         // CTAs, each part a share of its own group's pages (none, for a group with fewer pages than parts), and
         // the parts meet in the cluster.  The CTAs of the longest sequence then hold more pages than an equal
@@ -645,6 +647,25 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
             run.n_ctas = n_seqs * n_kv * cluster_size;
         }
     }
+    // The same with whole groups, one a CTA, where there are too many groups to cut each (and no more than CTAs):
+    // nothing is merged, and the longest group is the kernel's length.
+    if (shortest != longest && run.parts == 0 && n_seqs * n_kv <= (int)gridDim.x &&
+        longest <= run.total / run.n_ctas + kCutCost) {
+        run.parts = 1;
+        run.uneven = 1;
+        run.n_ctas = n_seqs * n_kv;
+    }
+    // More groups than CTAs: the same number of whole groups for every CTA (one more for some), if the busiest
+    // CTA's pages stay within the cost of the cuts that equal runs would make.
+    if (shortest != longest && run.parts == 0 && n_seqs * n_kv > (int)gridDim.x) {
+        const int groups = n_seqs * n_kv;
+        const int busiest = (groups + (int)gridDim.x - 1) / (int)gridDim.x;
+        if (busiest * longest <= run.total / (int)gridDim.x + kCutCost) {
+            run.whole = groups;
+            run.uneven = 1;
+            run.n_ctas = (int)gridDim.x;
+        }
+    }
     // When the launch groups CTAs into clusters and every group of this step is cut into exactly that
     // many parts, the CTAs of a cluster hold the parts of one group and merge them through distributed
     // shared memory: each owns a share of the head's columns and receives the others' sums for them in
@@ -652,15 +673,22 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     // says so), and a second barrier tells it that all parts have arrived.  All CTAs of a cluster
     // take the same decision, since they compute it from the same numbers.
     // (the cluster's size is a constant of this file, so that the shares of the columns below are divided by a constant)
-    const bool clustered = cluster_size > 1 && run.parts == cluster_size && group <= 32 / cluster_size &&
-                           (D / kDecodeCluster) % 4 == 0 && (cluster_size == kDecodeCluster || kWideClusterFits);
+    const bool clustered = cluster_size > 1 && run.parts == cluster_size && group <= dec_cluster_rows(cluster_size) &&
+                           (D / kDecodeCluster) % 4 == 0 && (cluster_size != kDecodeClusterWide || kWideClusterFits);
     const int cta = blockIdx.x;
     const bool idle = cta >= run.n_ctas;
     int u_begin = idle ? 0 : dec_run_begin(run, cta), u_end = idle ? 0 : dec_run_begin(run, cta + 1);
 
     // the sequence that holds unit u_begin: the last one whose first unit is not past it
     int seq;
-    if (run.uneven && !idle) {
+    if (run.uneven && run.whole > 0 && !idle) {
+        // whole groups g_a .. g_b - 1 of different lengths: from the first unit of the one to that of the other
+        const int g_a = (int)((long long)cta * run.whole / run.n_ctas), g_b = (int)((long long)(cta + 1) * run.whole / run.n_ctas);
+        seq = g_a / n_kv;
+        u_begin = cum_s[seq] * n_kv + (g_a % n_kv) * (cum_s[seq + 1] - cum_s[seq]);
+        const int seq_b = g_b / n_kv;
+        u_end = g_b >= run.whole ? run.total : cum_s[seq_b] * n_kv + (g_b % n_kv) * (cum_s[seq_b + 1] - cum_s[seq_b]);
+    } else if (run.uneven && !idle) {
         // part `cta % parts` of group `cta / parts`: a share of that group's own pages (it may be empty)
         const int gi = cta / run.parts, part = cta % run.parts;
         seq = gi / n_kv;
@@ -705,7 +733,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     int u = u_begin;
     bool first_segment = true;
     // (a part without pages still takes its place in the cluster's merge: one pass with nothing to attend to)
-    bool empty_part = run.uneven && u_begin == u_end;
+    bool empty_part = run.uneven && run.parts > 0 && u_begin == u_end;
     while (u < u_end || empty_part) {
         empty_part = false;
         while (cum_s[seq + 1] * n_kv <= u) ++seq;
@@ -892,9 +920,10 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                 sum += c * red_ml[(w * 16 + row) * 2 + 1];
             }
             if (clustered) {
-                if constexpr (kWideClusterFits) {
-                    if (run.parts == kDecodeClusterWide) dec_cluster_send<kDecodeClusterWide>(q_s, row, d, acc, mx, sum);
-                    else dec_cluster_send<kDecodeCluster>(q_s, row, d, acc, mx, sum);
+                if (run.parts == kDecodeClusterPair) {
+                    dec_cluster_send<kDecodeClusterPair>(q_s, row, d, acc, mx, sum);
+                } else if (kWideClusterFits && run.parts == kDecodeClusterWide) {
+                    if constexpr (kWideClusterFits) dec_cluster_send<kDecodeClusterWide>(q_s, row, d, acc, mx, sum);
                 } else {
                     dec_cluster_send<kDecodeCluster>(q_s, row, d, acc, mx, sum);
                 }
@@ -913,9 +942,10 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
             dec_cluster_arrive();
             dec_cluster_wait();
             bf16* dst = out + (size_t)seq * out_stride + (size_t)(kv_head * group) * D;
-            if constexpr (kWideClusterFits) {
-                if (run.parts == kDecodeClusterWide) dec_cluster_finish<kDecodeClusterWide>(q_s, dst, group);
-                else dec_cluster_finish<kDecodeCluster>(q_s, dst, group);
+            if (run.parts == kDecodeClusterPair) {
+                dec_cluster_finish<kDecodeClusterPair>(q_s, dst, group);
+            } else if (kWideClusterFits && run.parts == kDecodeClusterWide) {
+                if constexpr (kWideClusterFits) dec_cluster_finish<kDecodeClusterWide>(q_s, dst, group);
             } else {
                 dec_cluster_finish<kDecodeCluster>(q_s, dst, group);
             }
@@ -1129,6 +1159,10 @@ static int attention_decode(const void* q, int q_stride, void* out, int out_stri
     // clusters only where the kernel can use them: every group cut into kDecodeCluster parts needs that many CTAs
     int cluster = (decode_clusters_enabled() && n_ctas % kDecodeCluster == 0 &&
                    (long long)n_seqs * n_kv * kDecodeCluster <= n_ctas) ? kDecodeCluster : 1;
+    // too many groups for four CTAs each, but not for two
+    if (cluster == 1 && decode_clusters_enabled() && wide_clusters_enabled() && n_ctas % kDecodeClusterPair == 0 &&
+        (long long)n_seqs * n_kv * kDecodeClusterPair <= n_ctas)
+        cluster = kDecodeClusterPair;
     // eight CTAs a cluster where that still covers every group and a group's rows fit the receive space
     // (the grid is then a whole number of them: up to seven CTAs fewer, none of which would have had pages)
     int grid = n_ctas;
@@ -1137,7 +1171,7 @@ static int attention_decode(const void* q, int q_stride, void* out, int out_stri
     // sequences of up to 4,096 keys, and loses 1 to 4 % for four sequences or for longer ones, whose parts do
     // not meet in the cluster and whose CTAs the wider clusters place less evenly.  Hence: at most 16 groups,
     // and only if the caller says that no sequence of this launch can be longer than the kernel's limit.
-    if (cluster > 1 && kWideClusterFits && wide_clusters_enabled() && n_q / n_kv <= 32 / kDecodeClusterWide &&
+    if (cluster == kDecodeCluster && kWideClusterFits && wide_clusters_enabled() && n_q / n_kv <= dec_cluster_rows(kDecodeClusterWide) &&
         n_seqs * n_kv <= 16 && max_kv_len > 0 && max_kv_len <= kWideMostPages * kPage &&
         (long long)n_seqs * n_kv * kDecodeClusterWide <= wide_grid) {
         cluster = kDecodeClusterWide;

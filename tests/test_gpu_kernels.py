@@ -645,3 +645,48 @@ def test_attention_decode_of_few_groups_in_clusters_of_eight(n_q, n_kv, dim, len
         assert torch.allclose(got.float().cpu(), want, atol=tol(dtype, 2), rtol=tol(dtype)), ctas
         assert torch.equal(kernels.attention_decode(q, cache, ctx, n_q, n_kv, dim, scale, n_ctas=ctas), got)
     kernels.check_status()
+
+
+@pytest.mark.parametrize("n_seqs, n_kv, group, dim", [(2, 8, 4, 128), (9, 8, 4, 128), (16, 8, 4, 128), (40, 4, 2, 64), (33, 8, 1, 32),
+                                                     (70, 8, 4, 128), (70, 5, 3, 48), (3, 1, 16, 64), (20, 2, 8, 16)])
+@pytest.mark.parametrize("spread", ["mild", "wild"])
+def test_attention_decode_of_sequences_of_different_lengths(n_seqs, n_kv, group, dim, spread):
+    """Lengths that differ, for every way the kernel deals them: few groups -> each cut into the parts of a
+    cluster of 8, 4 or 2 CTAs (a sequence of one or two pages leaves parts empty); up to as many groups as
+    CTAs -> one whole group a CTA; more -> several whole groups a CTA; and, where the longest group would
+    hold a CTA too long, equal runs across groups with tickets.  With token preparation inside and without."""
+    from dryft_flash_infer_b200.ops import kernels
+    from dryft_flash_infer_b200.parts.rotary import RotaryEmbedding
+
+    dtype = torch.bfloat16
+    g = torch.Generator().manual_seed(n_seqs * 131 + dim)
+    if spread == "mild":
+        lengths = [int(x) for x in torch.randint(520, 700, (n_seqs,), generator=g)]
+    else:
+        lengths = [int(x) for x in torch.randint(1, 1400, (n_seqs,), generator=g)]
+        lengths[0], lengths[-1] = 1, 65
+    new = [1] * n_seqs
+    n_q = n_kv * group
+    q, cache, row_seq, row_pos, scale, want = attention_case(dtype, n_q, n_kv, dim, lengths, new, seed=dim + n_seqs)
+    ctx = step_like(lengths, new)
+    for ctas in (None, 40):
+        got = kernels.attention_decode(q, cache, ctx, n_q, n_kv, dim, scale, n_ctas=ctas)
+        assert torch.isfinite(got).all()
+        assert torch.allclose(got.float().cpu(), want, atol=tol(dtype, 2), rtol=tol(dtype)), ctas
+        assert torch.equal(kernels.attention_decode(q, cache, ctx, n_q, n_kv, dim, scale, n_ctas=ctas), got)
+    if dim in (16, 32, 64, 128) and group <= 16:
+        # the raw projection in, norm + rotation + cache write inside: against the two kernels one after the other
+        qkv = torch.randn(n_seqs, (n_q + 2 * n_kv) * dim, generator=g).to(dtype).cuda()
+        qw, kw = (1 + 0.3 * torch.randn(dim, generator=g)).cuda(), (1 + 0.3 * torch.randn(dim, generator=g)).cuda()
+        rot = RotaryEmbedding(0, dim, 4321.0)
+        rot.prepare(2048, "cuda")
+        two = LayerCache(cache.k.clone(), cache.v.clone(), cache.block_table, 64, 0, True)
+        prepared = kernels.qk_norm_rope_write(qkv.clone(), n_q, n_kv, dim, qw, kw, 1e-5, rot.cos, rot.sin, row_pos, row_seq, two)
+        want2 = kernels.attention_decode(prepared, two, ctx, n_q, n_kv, dim, scale, n_ctas=7)
+        one = LayerCache(cache.k.clone(), cache.v.clone(), cache.block_table, 64, 0, True)
+        got2 = kernels.attention_decode(None, one, ctx, n_q, n_kv, dim, scale,
+                                        prep=kernels.TokenPrep(qkv, qw, kw, 1e-5, rot.cos, rot.sin))
+        assert torch.allclose(got2.float(), want2.float(), atol=tol(dtype, 2), rtol=tol(dtype))
+        assert torch.allclose(one.k.float(), two.k.float(), atol=tol(dtype), rtol=tol(dtype), equal_nan=True)
+        assert torch.equal(one.v.float().nan_to_num(7.0), two.v.float().nan_to_num(7.0))
+    kernels.check_status()
