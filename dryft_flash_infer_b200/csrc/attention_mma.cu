@@ -495,6 +495,138 @@ constexpr int kMaxParts = 16;           // parts of a group that the merge holds
 constexpr int kMaxGroupParts = 64;      // CTAs that may share one (sequence, head) group
 constexpr int kMaxDecodeSeqs = 1024;    // sequences per launch (their page counts sit in shared memory)
 
+// How a launch deals its pages, and what this CTA gets: worked out by one thread of the CTA (in a function of
+// its own, so that its divisions and branches stay out of the registers and the schedule of the page loop) and
+// handed to the others through shared memory.
+struct DecodePlan {
+    DecodeRun run;
+    int first_unit, end_unit, first_seq;
+};
+template <int CL>
+__device__ __noinline__ void dec_plan(DecodePlan* plan, const int* cum_s, int longest, int shortest, int n_seqs, int n_kv,
+                                      int group, int grid, int cta) {
+    constexpr int cluster_size = CL;
+    constexpr bool kClusterMerge = CL > 1 && (D / (CL > 1 ? CL : 1)) % 4 == 0;
+    DecodeRun run;
+    run.total = cum_s[n_seqs] * n_kv;
+    // A CTA takes at least four pages, and enough of them that no sequence is spread over more than
+    // kMaxGroupParts CTAs.
+    const int least = max(4, (longest + kMaxGroupParts - 3) / (kMaxGroupParts - 2));
+    run.n_ctas = max(1, min(grid, run.total / least));
+    run.parts = 0;
+    run.whole = 0;
+    run.uneven = 0;
+    run.tiles = longest;
+    if (shortest == longest) {
+        // every group has the same number of pages: the same number of parts for each, none crossing over
+        const int per_cta = max(least, (run.total + grid - 1) / grid);
+        int parts = max(1, longest / per_cta);
+        // Short groups with CTAs to spare: four parts each, although that leaves a CTA fewer than four pages.
+        // Four parts meet in a cluster, which costs less than the pages saved (at batch 1 and 8 with some 700
+        // keys a sequence the kernel took 20 us with two parts of five or six pages that met through scratch
+        // memory and a ticket).
+        if (parts < kDecodeCluster && longest >= kDecodeCluster && cluster_size == kDecodeCluster &&
+            n_seqs * n_kv * kDecodeCluster <= grid)
+            parts = kDecodeCluster;
+        // A launch in clusters of eight (few groups of up to four query heads): eight parts each as long as a
+        // part stays at ten pages or fewer, so that they meet in the cluster and not through scratch memory
+        // and a ticket.
+        bool by_cluster = false;          // fewer CTAs than equal runs would use, on purpose
+        if (cluster_size == kDecodeClusterWide && longest >= kDecodeClusterWide && longest <= kWideMostPages &&
+            n_seqs * n_kv * kDecodeClusterWide <= grid) {
+            parts = kDecodeClusterWide;
+            by_cluster = true;
+        }
+        // (not if there are more parts than CTAs, nor if they would keep fewer than 80 % of the CTAs busy
+        // that equal runs crossing from group to group would: then those runs are used)
+        if (n_seqs * n_kv * parts <= grid && (by_cluster || n_seqs * n_kv * parts * 100 >= run.n_ctas * 80)) {
+            run.parts = parts;
+            run.n_ctas = n_seqs * n_kv * parts;
+        } else if (n_seqs * n_kv >= grid) {
+            // more groups than CTAs (many short sequences): equal runs would cut most groups in two, and every
+            // cut costs a preparation of the queries, two stores of partial results, a ticket and a merge,
+            // about three pages' worth of time.  Whole groups per CTA cost the busiest CTA a few pages more.
+            const int groups = n_seqs * n_kv;
+            const int busiest = (groups + grid - 1) / grid;
+            if (busiest * longest <= run.total / grid + 3) {
+                run.whole = groups;
+                run.n_ctas = grid;
+            }
+        }
+    }
+    else if (kClusterMerge && n_seqs * n_kv * cluster_size <= grid && group <= dec_cluster_rows(cluster_size)) {
+        // Sequences of different lengths and few groups: every group is cut into as many parts as a cluster has
+        // CTAs, each part a share of its own group's pages (none, for a group with fewer pages than parts), and
+        // the parts meet in the cluster.  The CTAs of the longest sequence then hold more pages than an equal
+        // share; equal runs over all pages instead cut groups wherever a run ends, and every cut costs a second
+        // preparation of queries, a second start of the page ring, partial results through scratch memory and a
+        // ticket: about kCutCost pages' worth (batch 8 near 3,900 keys: 3.42 ms a step with equal runs, 2.85 ms
+        // with sequences of one length).
+        const int per_part = (longest + cluster_size - 1) / cluster_size;
+        if (per_part <= run.total / run.n_ctas + kCutCost) {
+            run.parts = cluster_size;
+            run.uneven = 1;
+            run.n_ctas = n_seqs * n_kv * cluster_size;
+        }
+    }
+    // The same with whole groups, one a CTA, where there are too many groups to cut each (and no more than CTAs):
+    // nothing is merged, and the longest group is the kernel's length.
+    if (shortest != longest && run.parts == 0 && n_seqs * n_kv <= grid &&
+        longest <= run.total / run.n_ctas + kCutCost) {
+        run.parts = 1;
+        run.uneven = 1;
+        run.n_ctas = n_seqs * n_kv;
+    }
+    // More groups than CTAs: the same number of whole groups for every CTA (one more for some), if the busiest
+    // CTA's pages stay within the cost of the cuts that equal runs would make.
+    if (shortest != longest && run.parts == 0 && n_seqs * n_kv > grid) {
+        const int groups = n_seqs * n_kv;
+        const int busiest = (groups + grid - 1) / grid;
+        if (busiest * longest <= run.total / grid + kCutCost) {
+            run.whole = groups;
+            run.uneven = 1;
+            run.n_ctas = grid;
+        }
+    }
+    const bool idle = cta >= run.n_ctas;
+    // this CTA's units and the sequence that holds the first of them
+    int first_unit = 0, end_unit = 0, first_seq = 0;
+    if (idle) {
+    } else if (run.uneven && run.whole > 0) {
+        // whole groups g_a .. g_b - 1 of different lengths: from the first unit of the one to that of the other
+        const int g_a = (int)((long long)cta * run.whole / run.n_ctas), g_b = (int)((long long)(cta + 1) * run.whole / run.n_ctas);
+        first_seq = g_a / n_kv;
+        first_unit = cum_s[first_seq] * n_kv + (g_a % n_kv) * (cum_s[first_seq + 1] - cum_s[first_seq]);
+        const int seq_b = g_b / n_kv;
+        end_unit = g_b >= run.whole ? run.total : cum_s[seq_b] * n_kv + (g_b % n_kv) * (cum_s[seq_b + 1] - cum_s[seq_b]);
+    } else if (run.uneven) {
+        // part `cta % parts` of group `cta / parts`: a share of that group's own pages (it may be empty)
+        const int gi = cta / run.parts, part = cta % run.parts;
+        first_seq = gi / n_kv;
+        const int seq_tiles = cum_s[first_seq + 1] - cum_s[first_seq];
+        const int first = cum_s[first_seq] * n_kv + (gi % n_kv) * seq_tiles;
+        first_unit = first + seq_tiles * part / run.parts;
+        end_unit = first + seq_tiles * (part + 1) / run.parts;
+    } else {
+        first_unit = dec_run_begin(run, cta);
+        end_unit = dec_run_begin(run, cta + 1);
+        // the last sequence whose first unit is not past first_unit
+        int lo = 0, hi = n_seqs - 1;
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (cum_s[mid] * n_kv <= first_unit) lo = mid; else hi = mid - 1;
+        }
+        first_seq = lo;
+    }
+    plan->run = run;
+    plan->first_unit = first_unit;
+    plan->end_unit = end_unit;
+    plan->first_seq = first_seq;
+}
+
+// CL: CTAs per thread-block cluster of the launch (1: no clusters).  A kernel of its own for each, so that the
+// merge inside a cluster is compiled once, for one size, with its shares of the columns divided by constants.
+template <int CL>
 __global__ void __launch_bounds__(kThreads)
 attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                         const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, int out_stride,
@@ -502,7 +634,10 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                         const int* __restrict__ block_table, int table_width, const int* __restrict__ seq_start,
                         int n_seqs, int n_q, int n_kv, int ring_tokens, int window, float scale_log2,
                         float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters,
-                        DecodePrep prep, int cluster_size) {
+                        DecodePrep prep) {
+    constexpr int cluster_size = CL;
+    // the merge in the cluster needs a CTA's share of the head's columns in fours
+    constexpr bool kClusterMerge = CL > 1 && (D / (CL > 1 ? CL : 1)) % 4 == 0;
     atrace(0);
     pdl_launch_next();
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -582,90 +717,15 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         if (threadIdx.x == kThreads - 1) cum_s[n_seqs] = before;
         __syncthreads();
     }
-    DecodeRun run;
-    run.total = cum_s[n_seqs] * n_kv;
-    // A CTA takes at least four pages, and enough of them that no sequence is spread over more than
-    // kMaxGroupParts CTAs.
-    const int longest = max(max(warp_max_s[0], warp_max_s[1]), max(warp_max_s[2], warp_max_s[3]));
-    const int shortest = min(min(warp_min_s[0], warp_min_s[1]), min(warp_min_s[2], warp_min_s[3]));
-    const int least = max(4, (longest + kMaxGroupParts - 3) / (kMaxGroupParts - 2));
-    run.n_ctas = max(1, min((int)gridDim.x, run.total / least));
-    run.parts = 0;
-    run.whole = 0;
-    run.uneven = 0;
-    run.tiles = longest;
-    if (shortest == longest) {
-        // every group has the same number of pages: the same number of parts for each, none crossing over
-        const int per_cta = max(least, (run.total + (int)gridDim.x - 1) / (int)gridDim.x);
-        int parts = max(1, longest / per_cta);
-        // Short groups with CTAs to spare: four parts each, although that leaves a CTA fewer than four pages.
-        // Four parts meet in a cluster, which costs less than the pages saved (at batch 1 and 8 with some 700
-        // keys a sequence the kernel took 20 us with two parts of five or six pages that met through scratch
-        // memory and a ticket).
-        if (parts < kDecodeCluster && longest >= kDecodeCluster && cluster_size == kDecodeCluster &&
-            n_seqs * n_kv * kDecodeCluster <= (int)gridDim.x)
-            parts = kDecodeCluster;
-        // A launch in clusters of eight (few groups of up to four query heads): eight parts each as long as a
-        // part stays at ten pages or fewer, so that they meet in the cluster and not through scratch memory
-        // and a ticket.
-        bool by_cluster = false;          // fewer CTAs than equal runs would use, on purpose
-        if (cluster_size == kDecodeClusterWide && longest >= kDecodeClusterWide && longest <= kWideMostPages &&
-            n_seqs * n_kv * kDecodeClusterWide <= (int)gridDim.x) {
-            parts = kDecodeClusterWide;
-            by_cluster = true;
-        }
-        // (not if there are more parts than CTAs, nor if they would keep fewer than 80 % of the CTAs busy
-        // that equal runs crossing from group to group would: then those runs are used)
-        if (n_seqs * n_kv * parts <= (int)gridDim.x && (by_cluster || n_seqs * n_kv * parts * 100 >= run.n_ctas * 80)) {
-            run.parts = parts;
-            run.n_ctas = n_seqs * n_kv * parts;
-        } else if (n_seqs * n_kv >= (int)gridDim.x) {
-            // more groups than CTAs (many short sequences): equal runs would cut most groups in two, and every
-            // cut costs a preparation of the queries, two stores of partial results, a ticket and a merge,
-            // about three pages' worth of time.  Whole groups per CTA cost the busiest CTA a few pages more.
-            const int groups = n_seqs * n_kv;
-            const int busiest = (groups + (int)gridDim.x - 1) / (int)gridDim.x;
-            if (busiest * longest <= run.total / (int)gridDim.x + 3) {
-                run.whole = groups;
-                run.n_ctas = (int)gridDim.x;
-            }
-        }
+    __shared__ DecodePlan plan_s;
+    const int cta = blockIdx.x;
+    if (threadIdx.x == 0) {
+        const int longest = max(max(warp_max_s[0], warp_max_s[1]), max(warp_max_s[2], warp_max_s[3]));
+        const int shortest = min(min(warp_min_s[0], warp_min_s[1]), min(warp_min_s[2], warp_min_s[3]));
+        dec_plan<CL>(&plan_s, cum_s, longest, shortest, n_seqs, n_kv, group, (int)gridDim.x, cta);
     }
-    else if (cluster_size > 1 && n_seqs * n_kv * cluster_size <= (int)gridDim.x && group <= dec_cluster_rows(cluster_size) &&
-             (D / kDecodeCluster) % 4 == 0 && (cluster_size != kDecodeClusterWide || kWideClusterFits)) {
-        // Sequences of different lengths and few groups: every group is cut into as many parts as a cluster has
-        // CTAs, each part a share of its own group's pages (none, for a group with fewer pages than parts), and
-        // the parts meet in the cluster.  The CTAs of the longest sequence then hold more pages than an equal
-        // share; equal runs over all pages instead cut groups wherever a run ends, and every cut costs a second
-        // preparation of queries, a second start of the page ring, partial results through scratch memory and a
-        // ticket: about kCutCost pages' worth (batch 8 near 3,900 keys: 3.42 ms a step with equal runs, 2.85 ms
-        // with sequences of one length).
-        const int per_part = (longest + cluster_size - 1) / cluster_size;
-        if (per_part <= run.total / run.n_ctas + kCutCost) {
-            run.parts = cluster_size;
-            run.uneven = 1;
-            run.n_ctas = n_seqs * n_kv * cluster_size;
-        }
-    }
-    // The same with whole groups, one a CTA, where there are too many groups to cut each (and no more than CTAs):
-    // nothing is merged, and the longest group is the kernel's length.
-    if (shortest != longest && run.parts == 0 && n_seqs * n_kv <= (int)gridDim.x &&
-        longest <= run.total / run.n_ctas + kCutCost) {
-        run.parts = 1;
-        run.uneven = 1;
-        run.n_ctas = n_seqs * n_kv;
-    }
-    // More groups than CTAs: the same number of whole groups for every CTA (one more for some), if the busiest
-    // CTA's pages stay within the cost of the cuts that equal runs would make.
-    if (shortest != longest && run.parts == 0 && n_seqs * n_kv > (int)gridDim.x) {
-        const int groups = n_seqs * n_kv;
-        const int busiest = (groups + (int)gridDim.x - 1) / (int)gridDim.x;
-        if (busiest * longest <= run.total / (int)gridDim.x + kCutCost) {
-            run.whole = groups;
-            run.uneven = 1;
-            run.n_ctas = (int)gridDim.x;
-        }
-    }
+    __syncthreads();
+    const DecodeRun run = plan_s.run;
     // When the launch groups CTAs into clusters and every group of this step is cut into exactly that
     // many parts, the CTAs of a cluster hold the parts of one group and merge them through distributed
     // shared memory: each owns a share of the head's columns and receives the others' sums for them in
@@ -673,37 +733,10 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     // says so), and a second barrier tells it that all parts have arrived.  All CTAs of a cluster
     // take the same decision, since they compute it from the same numbers.
     // (the cluster's size is a constant of this file, so that the shares of the columns below are divided by a constant)
-    const bool clustered = cluster_size > 1 && run.parts == cluster_size && group <= dec_cluster_rows(cluster_size) &&
-                           (D / kDecodeCluster) % 4 == 0 && (cluster_size != kDecodeClusterWide || kWideClusterFits);
-    const int cta = blockIdx.x;
+    const bool clustered = kClusterMerge && run.parts == cluster_size && group <= dec_cluster_rows(cluster_size);
     const bool idle = cta >= run.n_ctas;
-    int u_begin = idle ? 0 : dec_run_begin(run, cta), u_end = idle ? 0 : dec_run_begin(run, cta + 1);
-
-    // the sequence that holds unit u_begin: the last one whose first unit is not past it
-    int seq;
-    if (run.uneven && run.whole > 0 && !idle) {
-        // whole groups g_a .. g_b - 1 of different lengths: from the first unit of the one to that of the other
-        const int g_a = (int)((long long)cta * run.whole / run.n_ctas), g_b = (int)((long long)(cta + 1) * run.whole / run.n_ctas);
-        seq = g_a / n_kv;
-        u_begin = cum_s[seq] * n_kv + (g_a % n_kv) * (cum_s[seq + 1] - cum_s[seq]);
-        const int seq_b = g_b / n_kv;
-        u_end = g_b >= run.whole ? run.total : cum_s[seq_b] * n_kv + (g_b % n_kv) * (cum_s[seq_b + 1] - cum_s[seq_b]);
-    } else if (run.uneven && !idle) {
-        // part `cta % parts` of group `cta / parts`: a share of that group's own pages (it may be empty)
-        const int gi = cta / run.parts, part = cta % run.parts;
-        seq = gi / n_kv;
-        const int seq_tiles = cum_s[seq + 1] - cum_s[seq];
-        const int first = cum_s[seq] * n_kv + (gi % n_kv) * seq_tiles;
-        u_begin = first + seq_tiles * part / run.parts;
-        u_end = first + seq_tiles * (part + 1) / run.parts;
-    } else {
-        int lo = 0, hi = n_seqs - 1;
-        while (lo < hi) {
-            const int mid = (lo + hi + 1) >> 1;
-            if (cum_s[mid] * n_kv <= u_begin) lo = mid; else hi = mid - 1;
-        }
-        seq = lo;
-    }
+    const int u_begin = plan_s.first_unit, u_end = plan_s.end_unit;
+    int seq = plan_s.first_seq;
     // Pages that lie wholly before this step's token were written by earlier steps: the first of them
     // are asked for now, while the kernel before (which writes the new token's keys and values and
     // the queries) may still be running.
@@ -730,12 +763,24 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     pdl_wait();        // from here on the queries and the new keys and values are read
     if (idle) return;
     atrace(2);
+    if constexpr (kClusterMerge) {
+        if (run.uneven && run.parts > 0 && u_begin == u_end) {
+            // A part without pages (its group has fewer pages than the cluster has CTAs) still takes its place in
+            // the cluster's merge: it has nothing to send but "no keys seen", and finishes its share of the columns.
+            const int gi = cta / run.parts;
+            dec_cluster_arrive();
+            dec_cluster_wait();
+            for (int i = threadIdx.x; i < group * (D / 4); i += kThreads)
+                dec_cluster_send<CL>(q_s, i / (D / 4), (i % (D / 4)) * 4, make_float4(0.f, 0.f, 0.f, 0.f), -INFINITY, 0.f);
+            dec_cluster_arrive();
+            dec_cluster_wait();
+            dec_cluster_finish<CL>(q_s, out + (size_t)(gi / n_kv) * out_stride + (size_t)((gi % n_kv) * group) * D, group);
+            return;
+        }
+    }
     int u = u_begin;
     bool first_segment = true;
-    // (a part without pages still takes its place in the cluster's merge: one pass with nothing to attend to)
-    bool empty_part = run.uneven && run.parts > 0 && u_begin == u_end;
-    while (u < u_end || empty_part) {
-        empty_part = false;
+    while (u < u_end) {
         while (cum_s[seq + 1] * n_kv <= u) ++seq;
         const int seq_tiles = cum_s[seq + 1] - cum_s[seq];
         const int in_seq = u - cum_s[seq] * n_kv;
@@ -920,13 +965,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                 sum += c * red_ml[(w * 16 + row) * 2 + 1];
             }
             if (clustered) {
-                if (run.parts == kDecodeClusterPair) {
-                    dec_cluster_send<kDecodeClusterPair>(q_s, row, d, acc, mx, sum);
-                } else if (kWideClusterFits && run.parts == kDecodeClusterWide) {
-                    if constexpr (kWideClusterFits) dec_cluster_send<kDecodeClusterWide>(q_s, row, d, acc, mx, sum);
-                } else {
-                    dec_cluster_send<kDecodeCluster>(q_s, row, d, acc, mx, sum);
-                }
+                if constexpr (kClusterMerge) dec_cluster_send<CL>(q_s, row, d, acc, mx, sum);
             } else if (whole) {
                 const float inv = sum > 0.f ? 1.0f / sum : 0.f;
                 bf16* dst = out + (size_t)seq * out_stride + (size_t)(kv_head * group + row) * D + d;
@@ -942,13 +981,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
             dec_cluster_arrive();
             dec_cluster_wait();
             bf16* dst = out + (size_t)seq * out_stride + (size_t)(kv_head * group) * D;
-            if (run.parts == kDecodeClusterPair) {
-                dec_cluster_finish<kDecodeClusterPair>(q_s, dst, group);
-            } else if (kWideClusterFits && run.parts == kDecodeClusterWide) {
-                if constexpr (kWideClusterFits) dec_cluster_finish<kDecodeClusterWide>(q_s, dst, group);
-            } else {
-                dec_cluster_finish<kDecodeCluster>(q_s, dst, group);
-            }
+            if constexpr (kClusterMerge) dec_cluster_finish<CL>(q_s, dst, group);
         } else if (!whole) {
             __syncthreads();
             atrace(5);
@@ -1071,8 +1104,8 @@ DFI_EXPORT int dfi_attention_decode_wave() {
     int device = 0, sms = 0, per_sm = 0;
     if (cudaGetDevice(&device) != cudaSuccess) return 0;
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return 0;
-    cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecodeSmem);
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_decode_kernel, kThreads, kDecodeSmem) != cudaSuccess)
+    cudaFuncSetAttribute(attention_decode_kernel<kDecodeCluster>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecodeSmem);
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_decode_kernel<kDecodeCluster>, kThreads, kDecodeSmem) != cudaSuccess)
         return 0;
     int ctas = sms * per_sm;
     if (decode_clusters_enabled()) {
@@ -1089,7 +1122,7 @@ DFI_EXPORT int dfi_attention_decode_wave() {
         config.attrs = attr;
         config.numAttrs = 1;
         int clusters = 0;
-        if (cudaOccupancyMaxActiveClusters(&clusters, attention_decode_kernel, &config) == cudaSuccess && clusters > 0)
+        if (cudaOccupancyMaxActiveClusters(&clusters, attention_decode_kernel<kDecodeCluster>, &config) == cudaSuccess && clusters > 0)
             ctas = min(ctas / kDecodeCluster, clusters) * kDecodeCluster;
         else
             cudaGetLastError();
@@ -1139,7 +1172,10 @@ static int attention_decode(const void* q, int q_stride, void* out, int out_stri
     if (out_stride % 2 || (reinterpret_cast<uintptr_t>(out) & 3)) return DFI_ERR_ALIGN;      // outputs are stored in pairs
     static bool configured = false;
     if (!configured) {
-        if (cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecodeSmem) != cudaSuccess)
+        if (cudaFuncSetAttribute(attention_decode_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecodeSmem) != cudaSuccess ||
+            cudaFuncSetAttribute(attention_decode_kernel<kDecodeClusterPair>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecodeSmem) != cudaSuccess ||
+            cudaFuncSetAttribute(attention_decode_kernel<kDecodeCluster>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecodeSmem) != cudaSuccess ||
+            cudaFuncSetAttribute(attention_decode_kernel<kDecodeClusterWide>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecodeSmem) != cudaSuccess)
             return DFI_ERR_LAUNCH;
         configured = true;
     }
@@ -1198,9 +1234,13 @@ static int attention_decode(const void* q, int q_stride, void* out, int out_stri
     }
     config.attrs = attr;
     config.numAttrs = n_attr;
-    if (cudaLaunchKernelEx(&config, attention_decode_kernel, map_k, map_v, (const bf16*)q, q_stride, (bf16*)out, out_stride,
+    auto kernel = cluster == kDecodeClusterWide ? attention_decode_kernel<kDecodeClusterWide>
+                  : cluster == kDecodeCluster   ? attention_decode_kernel<kDecodeCluster>
+                  : cluster == kDecodeClusterPair ? attention_decode_kernel<kDecodeClusterPair>
+                                                  : attention_decode_kernel<1>;
+    if (cudaLaunchKernelEx(&config, kernel, map_k, map_v, (const bf16*)q, q_stride, (bf16*)out, out_stride,
                            (const bf16*)k_cache, (const bf16*)v_cache, block_table, table_width, seq_start, n_seqs, n_q,
-                           n_kv, ring_tokens, window, scale * kLog2e, part_o, part_ml, counters, prep, cluster) != cudaSuccess) {
+                           n_kv, ring_tokens, window, scale * kLog2e, part_o, part_ml, counters, prep) != cudaSuccess) {
         cudaGetLastError();
         return DFI_ERR_LAUNCH;
     }
