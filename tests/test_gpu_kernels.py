@@ -209,8 +209,11 @@ def test_argmax_and_sampling():
     wide = torch.randn(4, 1000, generator=g)[:, :700]                   # rows with a stride
     assert kernels.argmax(wide.cuda()[:, :700]).cpu().tolist() == wide.argmax(-1).tolist()
     # sampling: the token's CDF interval holds its uniform number
-    for vocab, temperature in ((320, 0.8), (151936, 1.3), (5, 0.1)):
+    for vocab, temperature in ((320, 0.8), (151936, 1.3), (5, 0.1), (4097, 0.7), (12289, 2.0)):
         logits = torch.randn(64, vocab, generator=g) * 3
+        if vocab == 12289:
+            logits[:, 4096:8192] = float("-inf")                     # a whole segment without weight
+            logits[3, :12288] = float("-inf")                        # all the weight on the last element
         u = torch.rand(64, generator=g)
         u[0], u[1] = 0.0, 1.0 - 2 ** -24
         got = kernels.sample_temperature(logits.cuda(), u.cuda(), temperature).cpu()
@@ -222,6 +225,16 @@ def test_argmax_and_sampling():
     # a row's draw does not depend on the other rows
     alone = kernels.sample_temperature(logits[5:6].cuda(), u[5:6].cuda(), temperature).cpu()
     assert int(alone[0]) == int(got[5])
+    assert int(got[3]) == 12288
+    # more rows than one launch holds, rows with a stride, and the same call twice
+    many = torch.randn(300, 1000, generator=g)[:, :777] * 2
+    u = torch.rand(300, generator=g)
+    got = kernels.sample_temperature(many.cuda()[:, :777], u.cuda(), 0.9).cpu()
+    cdf = torch.cumsum(plain_model.temperature_probabilities(many, 0.9), -1)
+    for r in range(300):
+        t = int(got[r])
+        assert (float(cdf[r, t - 1]) if t else 0.0) - 2e-5 <= float(u[r]) <= float(cdf[r, t]) + 2e-5, r
+    assert torch.equal(kernels.sample_temperature(many.cuda()[:, :777], u.cuda(), 0.9).cpu(), got)
 
 
 def test_sizes_a_kernel_does_not_take_are_refused():
