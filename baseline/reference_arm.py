@@ -2,7 +2,7 @@
 """Times the unmodified reference engine (M4cr0Chen/dryft-flash-infer, ``engine/engine.py``) on the
 benchmark's decode step, in a process of its own.
 
-    python baseline/reference_arm.py --model DIR --steps K --warmup W [--points] [--prefill]
+    python baseline/reference_arm.py --model DIR --steps K --warmup W [--points] [--prefill] [--workloads]
 
 ``--model`` is a folder with ``config.json`` and ``model.safetensors`` in the checkpoint's tensor names (the
 folder that ``python -m dryft_flash_infer_b200 random-model`` writes).  The reference is the copy of its
@@ -111,6 +111,41 @@ def time_prefill(engine, tokens: int, vocab: int):
     return sorted(times)[1]
 
 
+#: the reference's own public workloads (bench/harness.py:26-30): name, batch, prompt tokens, output tokens
+PUBLIC_WORKLOADS = (("public-0", 1, 512, 32), ("public-1", 4, 2048, 32), ("public-2", 16, 512, 128))
+
+
+def time_workload(generate, batch: int, length: int, steps: int, vocab: int, samples: int = 5):
+    """Generation as the reference's harness measures it (bench/harness.py:81-110): one untimed call, then
+    ``samples`` calls by the wall clock; tokens/s = batch x output tokens / median seconds of a whole call
+    (prefill included), TTFT the median time to the first row, TPOT the rest divided by the other rows."""
+    import statistics
+
+    import torch
+
+    def once(seed):
+        prompts = _prompts(batch, length, vocab, seed)
+        torch.cuda.synchronize()
+        begin = time.perf_counter()
+        first, rows = None, 0
+        for row in generate(prompts, steps):
+            if first is None:
+                first = time.perf_counter() - begin
+            rows += 1
+        torch.cuda.synchronize()
+        total = time.perf_counter() - begin
+        if rows != steps or len(row) != batch:
+            raise RuntimeError(f"{rows} rows of {len(row)} tokens where {steps} of {batch} were asked for")
+        return first, total
+
+    once(100)
+    records = [once(101 + i) for i in range(samples)]
+    median = statistics.median(t for _, t in records)
+    return {"tps": round(batch * steps / median, 1),
+            "ttft_ms": round(statistics.median(f for f, _ in records) * 1e3, 2),
+            "tpot_ms": round(statistics.median((t - f) / max(1, steps - 1) for f, t in records) * 1e3, 3)}
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--model", required=True)
@@ -118,6 +153,7 @@ def main() -> int:
     parser.add_argument("--warmup", type=int, default=4)
     parser.add_argument("--points", action="store_true", help="also batch 1 and 64, and the 512-token prompts")
     parser.add_argument("--prefill", action="store_true", help="also one prompt of 2,048 tokens")
+    parser.add_argument("--workloads", action="store_true", help="also the reference's three public workloads")
     args = parser.parse_args()
     out: dict = {"impl": "reference", "settings": {k: v for k, v in os.environ.items() if k.startswith("DRYFT_")}}
     tee = _Tee(sys.stderr)
@@ -154,6 +190,13 @@ def main() -> int:
             prefill_ms = time_prefill(engine, PREFILL_TOKENS, vocab)
             out["prefill"] = {"value": round(PREFILL_TOKENS / prefill_ms * 1e3, 1), "tokens": PREFILL_TOKENS,
                               "ms": round(prefill_ms, 3), "timed": "wall clock to the first token, upload included"}
+        if args.workloads:
+            out["workloads"] = {}
+            for name, batch, length, steps in PUBLIC_WORKLOADS:
+                try:
+                    out["workloads"][name] = time_workload(engine.generate, batch, length, steps, vocab)
+                except Exception as exc:
+                    out["workloads"][name] = f"failed: {type(exc).__name__}: {exc}"[:200]
         out["fast_path"] = bool(engine._fast)
         torch.cuda.synchronize()
     except Exception as exc:

@@ -163,6 +163,37 @@ def time_decode(engine, n_seqs: int, context: int, steps: int, warmup: int, samp
     return ms, per_step
 
 
+#: the reference's public workloads (bench/harness.py:26-30): name, batch, prompt tokens, output tokens
+PUBLIC_WORKLOADS = (("public-0", 1, 512, 32), ("public-1", 4, 2048, 32), ("public-2", 16, 512, 128))
+
+
+def time_workload(engine, batch: int, length: int, steps: int, vocab: int, g, samples: int = 5) -> dict:
+    """A whole ``Engine.generate`` call as the reference's harness times it (bench/harness.py:81-110): one untimed
+    call, then ``samples`` by the wall clock with host token lists in and out; tokens/s = batch x output tokens /
+    median seconds (prefill included), TTFT = median time to the first row, TPOT = the rest per further row."""
+    import torch
+
+    def once():
+        prompts = [torch.randint(0, vocab, (length,), generator=g).tolist() for _ in range(batch)]
+        torch.cuda.synchronize()
+        begin = time.perf_counter()
+        first, rows = None, 0
+        for _ in engine.generate(prompts, steps):
+            if first is None:
+                first = time.perf_counter() - begin
+            rows += 1
+        torch.cuda.synchronize()
+        assert rows == steps
+        return first, time.perf_counter() - begin
+
+    once()
+    records = [once() for _ in range(samples)]
+    median = statistics.median(t for _, t in records)
+    return {"tps": round(batch * steps / median, 1),
+            "ttft_ms": round(statistics.median(f for f, _ in records) * 1e3, 2),
+            "tpot_ms": round(statistics.median((t - f) / max(1, steps - 1) for f, t in records) * 1e3, 3)}
+
+
 def long_engine(engine, context: int):
     """``engine`` with its cache made anew for one sequence of ``context`` tokens (the weights stay)."""
     engine._make_cache(context, 1, context)
@@ -266,8 +297,8 @@ def reference_run(steps: int, warmup: int, quick: bool) -> int:
             torch.cuda.empty_cache()
             results = {}
             with ClockSampler() as clocks:
-                for name, env, extra in (("stock", {}, [] if quick else ["--points", "--prefill"]),
-                                         ("bf16", {"DRYFT_FP8": "off"}, [])):
+                for name, env, extra in (("stock", {}, [] if quick else ["--points", "--prefill", "--workloads"]),
+                                         ("bf16", {"DRYFT_FP8": "off"}, [] if quick else ["--workloads"])):
                     environment = {k: v for k, v in os.environ.items() if not k.startswith("DRYFT_")}
                     environment.update(env)
                     print(f"reference arm: running the reference with {env or 'its stock settings'}", file=sys.stderr,
@@ -299,9 +330,10 @@ def reference_run(steps: int, warmup: int, quick: bool) -> int:
         "e2e": {"value": stock["e2e_value"], "unit": "tokens/s", "h2d_bytes_per_step": 0,
                 "d2h_bytes_per_step": BATCH * 8},
         "bf16_weights": ({"value": bf16["value"], "ms_per_step": bf16["ms_per_step"], "e2e_value": bf16["e2e_value"],
-                          "fast_path": bf16.get("fast_path"), "settings": bf16.get("settings")}
+                          "fast_path": bf16.get("fast_path"), "settings": bf16.get("settings"),
+                          "workloads": bf16.get("workloads")}
                          if "unavailable" not in bf16 else {"unavailable": bf16["unavailable"]}),
-        "points": stock.get("points", {}), "prefill": stock.get("prefill"),
+        "points": stock.get("points", {}), "prefill": stock.get("prefill"), "workloads": stock.get("workloads"),
         "engine_lines": stock.get("engine_lines", [])[-6:], "clocks": clocks.summary(),
     }
     print(json.dumps(line))
@@ -418,7 +450,7 @@ def main() -> int:
     roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak["hbm_gbs"], "unit": "GB/s",
                 "frac": round(achieved / peak["hbm_gbs"], 4), "peaks": peak["source"]}
 
-    points, e2e = {}, None
+    points, e2e, workloads = {}, None, {}
     if not args.quick:
         # ---- end to end through Engine.generate: host token lists in, host token lists out; directly after
         # `value`, as in the reference arm, whose two numbers come from one timed region
@@ -448,6 +480,10 @@ def main() -> int:
         for name, n in (("decode_b1_prompt512", 1), ("decode_b8_prompt512", BATCH), ("decode_b64_prompt512", 64)):
             point_ms, _ = time_decode(engine, n, PROMPT_OF_POINTS + steps + warmup + 1, steps, warmup)
             points[name] = round(n / point_ms * 1e3, 1)
+        # the reference's own public workloads, measured as its harness measures them (bench/harness.py:26-30,
+        # :81-110): a whole generate call by the wall clock, prefill included
+        for name, batch, length, out_tokens in PUBLIC_WORKLOADS:
+            workloads[name] = time_workload(engine, batch, length, out_tokens, cfg["vocab_size"], g)
         # last, because they make the cache anew: one sequence at 16,384 and at 32,768 tokens
         for name, context in (("decode_b1_context16k", 16384), ("decode_b1_context32k", 32768)):
             point_ms, _ = time_decode(long_engine(engine, context), 1, context, max(8, steps // 8), warmup)
@@ -460,7 +496,7 @@ def main() -> int:
         "dtype": "bf16", "data": "synthetic: random weights, random token ids, random cache content",
         "impl": "ours",
         "config": headline_config(args.layers),
-        "prefill": prefill, "roofline": roofline, "points": points, "e2e": e2e,
+        "prefill": prefill, "roofline": roofline, "points": points, "e2e": e2e, "workloads": workloads,
         "gpu_launches": int(launches * steps), "clocks": clocks.summary(),
     }
     print(json.dumps(line))
