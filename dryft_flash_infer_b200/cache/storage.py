@@ -93,12 +93,15 @@ class SequenceCache:
             for position, cache_id in enumerate(ids):
                 self.group_of[cache_id] = (index, position)
         self.book = SlotBook(max_seqs, [g.pages for g in self.groups], max_context)
+        #: a slot that no sequence ever holds: the state of places that only fill a step's buffers (one row
+        #: more in every state area, which nothing reads for a result)
+        self.spare_slot = max_seqs
         self.state: dict[int, torch.Tensor] = {}
         self.state_init: dict[int, float] = {}
         for position, need in state_needs.items():
             if need.dtype not in _STATE_DTYPES:
                 raise ValueError(f"a state is held in one of {sorted(_STATE_DTYPES)}, not {need.dtype!r}")
-            self.state[position] = torch.full((max_seqs,) + tuple(need.shape), float(need.init),
+            self.state[position] = torch.full((max_seqs + 1,) + tuple(need.shape), float(need.init),
                                               dtype=_STATE_DTYPES[need.dtype], device=device)
             self.state_init[position] = float(need.init)
 

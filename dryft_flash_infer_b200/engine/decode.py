@@ -23,11 +23,17 @@ def _pad4(n: int) -> int:
 
 
 class DecodeBatch:
-    """Fixed buffers (and the graph) for decode steps of ``n`` sequences.
+    """Fixed buffers (and the graph) for decode steps of up to ``n`` sequences.
 
     It looks like a ``StepContext`` to the model: the same attributes, all views of one
     device buffer.  ``run`` refreshes the numbers that change and runs one step; the
     chosen tokens stay on the device as the next step's input and come back as a list.
+
+    A step of fewer than ``n`` sequences fills the places past its own with sequences of one token at
+    position 0 whose block tables name the null page only and whose state is the cache's spare slot:
+    they cost a row of every product and a page of attention, reach nothing that lives, and what is
+    chosen for them is thrown away.  So a live set that shrinks by a sequence keeps its buffers and its
+    graph instead of running a step launch by launch and capturing a graph for every size on its way down.
     """
 
     all_decode = True
@@ -67,6 +73,7 @@ class DecodeBatch:
         self.status_host = [torch.zeros(kernels.STATUS_WORDS, dtype=torch.int32).pin_memory() for _ in range(2)]
         self.status_device = kernels.status_words(device)
         self.result_event = [torch.cuda.Event() for _ in range(2)]
+        self.live_of = [0, 0]             # sequences of the steps whose results the two buffers hold
         self.launched = 0
         #: float32 logits ``[n, vocab]`` of the step launched last (a fixed buffer once the graph exists)
         self.logits: torch.Tensor | None = None
@@ -89,6 +96,7 @@ class DecodeBatch:
         self.graph = None
         self.slots: list[int] = []
         self.starts: list[int] = []
+        self.live = 0                     # sequences of the step launched last (the rest of the n places are filling)
         self.launches_per_step = 0
         self.last_out: list[int] | None = None
 
@@ -104,19 +112,26 @@ class DecodeBatch:
         if self.staging_event[turn] is not None:
             self.staging_event[turn].synchronize()          # the copy that last read this buffer has run
         if tokens is not None:
-            self.tokens_staging[turn][:] = torch.tensor(tokens, dtype=torch.int32)
+            self.tokens_staging[turn][: len(tokens)] = torch.tensor(tokens, dtype=torch.int32)
+            self.tokens_staging[turn][len(tokens):] = 0
             self.tokens.copy_(self.tokens_staging[turn], non_blocking=True)
         n, h, off = self.n, self.staging_np[turn], self.offsets
-        self.slots = slots
-        self.starts = starts = [self.cache.length(s) for s in slots]
+        live = self.live = len(slots)
+        filling = n - live
+        starts = [self.cache.length(s) for s in slots]
+        # as a StepContext shows them, the filling included: its sequences sit at position 0 of the spare slot
+        self.slots = slots + [self.cache.spare_slot] * filling
+        self.starts = starts = starts + [0] * filling
         h[off["row_pos"]: off["row_pos"] + n] = starts
         h[off["seq_start"]: off["seq_start"] + n] = starts
-        h[off["seq_slot"]: off["seq_slot"] + n] = slots
+        h[off["seq_slot"]: off["seq_slot"] + n] = self.slots
         if uniforms is not None:
-            h[off["uniforms"]: off["uniforms"] + n] = np.asarray(uniforms, dtype=np.float32).view(np.int32)
+            h[off["uniforms"]: off["uniforms"] + live] = np.asarray(uniforms, dtype=np.float32).view(np.int32)
+            h[off["uniforms"] + live: off["uniforms"] + n] = 0
         for g, width in enumerate(self.table_widths):
-            self.cache.fill_block_table(h[off[f"table{g}"]: off[f"table{g}"] + n * width].reshape(n, width),
-                                        slots, g, width)
+            table = h[off[f"table{g}"]: off[f"table{g}"] + n * width].reshape(n, width)
+            self.cache.fill_block_table(table[:live], slots, g, width)
+            table[live:] = 0                                   # the null page
         first = self.first_refreshed
         self.device_buffer[first:].copy_(self.staging[turn][first:], non_blocking=True)
         if self.staging_event[turn] is None:
@@ -152,6 +167,7 @@ class DecodeBatch:
             book.advance(slot, 1)
         ticket = self.launched
         self.launched += 1
+        self.live_of[ticket & 1] = len(slots)
         self.result_host[ticket & 1].copy_(self.tokens, non_blocking=True)
         self.status_host[ticket & 1].copy_(self.status_device, non_blocking=True)
         self.result_event[ticket & 1].record()
@@ -165,15 +181,25 @@ class DecodeBatch:
         self.result_event[ticket & 1].synchronize()
         # a bounded wait that ran out in one of the step's kernels: the tokens are not to be trusted
         kernels.raise_for_status(self.status_host[ticket & 1].tolist(), self.model.device)
-        return self.result_host[ticket & 1].tolist()
+        return self.result_host[ticket & 1][: self.live_of[ticket & 1]].tolist()
 
     def run(self, slots: list[int], tokens: list[int] | None, uniforms=None) -> list[int]:
         """One decode step for ``slots``, waited for."""
         return self.fetch(self.launch(slots, tokens, uniforms))
 
 
+def decode_places(n: int) -> int:
+    """The size of the buffers that a decode step of ``n`` sequences runs on: ``n`` itself up to 8, then the
+    next multiple of 2 (up to 16), 4 (up to 32), 8 (up to 64) or 16, so that a large live set that loses
+    sequences one by one passes through few sizes."""
+    if n <= 8:
+        return n
+    step = 2 if n <= 16 else 4 if n <= 32 else 8 if n <= 64 else 16
+    return -(-n // step) * step
+
+
 class Decoder:
-    """Keeps one ``DecodeBatch`` per batch size and remembers which slots ran last, so that a
+    """Keeps one ``DecodeBatch`` per size of buffers and remembers which slots ran last, so that a
     batch that goes on unchanged feeds its tokens back without a trip through the host."""
 
     def __init__(self, model, cache, use_graph: bool):
@@ -185,12 +211,13 @@ class Decoder:
     def _batch_for(self, n: int, params: SamplingParams) -> tuple[tuple, DecodeBatch]:
         cache = self.cache
         widths = [max(1, -(-(g.ring_tokens or cache.max_context) // cache.page_size)) for g in cache.groups]
-        key = (n, tuple(widths), params.temperature)
+        places = decode_places(n)
+        key = (places, tuple(widths), params.temperature)
         batch = self.batches.get(key)
         if batch is None:
-            if len(self.batches) >= 16:
+            if len(self.batches) >= 32:
                 self.batches.pop(next(iter(self.batches)))
-            batch = self.batches[key] = DecodeBatch(self.model, cache, n, widths, cache.max_context,
+            batch = self.batches[key] = DecodeBatch(self.model, cache, places, widths, cache.max_context,
                                                     params.temperature, self.use_graph)
         return key, batch
 
@@ -216,7 +243,7 @@ class Decoder:
         batch.fetch(batch.launch(list(slots), list(tokens)))
         self.last = None                  # the next decode step is fed from the host again
         batch.last_out = None
-        return batch.logits
+        return batch.logits[: len(slots)]
 
     def decode(self, slots: list[int], tokens: list[int], requests: list[int], step_index: int,
                params: SamplingParams) -> list[int]:

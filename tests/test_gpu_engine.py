@@ -761,3 +761,44 @@ def test_widths_that_are_no_multiples_of_eight(tmp_path, dtype, hidden, inter, g
         for i, p in enumerate(prompts):
             assert_close(logits[i], want[i][len(p) - t], dtype, f"decode {i} -{t}")
     engine.check_status()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_a_live_set_of_more_than_eight_runs_on_buffers_with_places_to_spare(folders, name, dtype):
+    """Eleven requests at once with unequal lengths of output: decode steps of 11, 10, 9 sequences run on
+    buffers of 12 and 10 places (``decode_places``), the places past the live sequences filled with sequences
+    of one token on the null page.  Every request's tokens are the plain implementation's, the filling's are
+    never seen, and a toy check that the sizes of buffers are the few expected ones."""
+    from dryft_flash_infer_b200 import Request
+    from dryft_flash_infer_b200.engine.decode import decode_places
+
+    assert [decode_places(n) for n in (1, 7, 8, 9, 10, 11, 16, 17, 20, 33, 64, 65, 100)] == \
+        [1, 7, 8, 10, 10, 12, 16, 20, 20, 40, 64, 80, 112]
+    folder, cfg, weights = folders[name]
+    ref_w = reference_weights(weights, dtype)
+    engine = make_engine(folder, dtype, max_tokens=64 * 2 * 11, max_seqs=11, cuda_graph=True)
+    lengths = [5, 70, 9, 17, 1, 64, 33, 2, 40, 3, 65]
+    news = [3, 14, 5, 8, 2, 7, 14, 4, 9, 11, 6]
+    prompts = prompts_for(cfg, lengths, seed=77)
+    requests = [Request(p, n, request_id=i) for i, (p, n) in enumerate(zip(prompts, news))]
+    engine.generate_requests(requests, max_batch=11)
+    assert engine.cache.live_slots == 0
+    engine.cache.book.check()
+    sizes = sorted({b.n for b in engine.decoder.batches.values()})
+    assert set(sizes) <= {1, 2, 3, 4, 5, 6, 7, 8, 10, 12} and 12 in sizes and 10 in sizes, sizes
+    for r, n in zip(requests, news):
+        assert len(r.output) == n
+        if dtype == "float32":
+            assert r.output == plain_model.greedy_continue(cfg, ref_w, r.prompt, n), f"request {r.request_id}"
+        else:
+            assert _teacher_forced_gap(cfg, ref_w, r.prompt, r.output) <= BF16_TIE_GAP, f"request {r.request_id}"
+    # the step function on the same buffers: nine single-token steps' logits against the plain implementation
+    from dryft_flash_infer_b200 import StepEntry
+    nine = prompts_for(cfg, [12, 3, 30, 8, 64, 65, 2, 19, 7], seed=78)
+    slots = [engine.open_slot() for _ in nine]
+    engine.step([StepEntry(s, p[:-1], []) for s, p in zip(slots, nine)])
+    rows = engine.step([StepEntry(s, [p[-1]], [0]) for s, p in zip(slots, nine)])
+    assert rows.shape[0] == 9
+    for i, p in enumerate(nine):
+        assert_close(rows[i], plain_model.forward(cfg, ref_w, p)[-1], dtype, f"nine at once, sequence {i}")
