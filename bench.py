@@ -156,7 +156,7 @@ def time_decode(engine, n_seqs: int, context: int, steps: int, warmup: int, samp
     handle.result()
     torch.cuda.synchronize()
     ms = start.elapsed_time(end) / steps
-    batch = next(iter(b for b in engine.decoder.batches.values() if b.n == n_seqs))
+    batch = next(iter(b for b in engine.decoder.batches.values() if b.n >= n_seqs))
     per_step = batch.launches_per_step if batch.graph else (kernels.LAUNCHES - launches_before) // max(1, steps)
     for slot in slots:
         engine.close_slot(slot)

@@ -306,6 +306,7 @@ struct DecodeRun {
     int tiles;
     int whole;      // > 0: every group has `tiles` pages, there are this many groups, and a CTA takes whole groups
     int uneven;     // with parts > 0: the groups differ in length; each is cut into `parts` parts of its own pages
+    int group_cost; // equal runs: units that stand for a group's fixed cost in front of its pages (see dec_plan)
 };
 // First unit of a CTA's run: equal contiguous runs over all units, or (when every sequence brings
 // the same number of pages) the same number of parts for every group, so that no run crosses from
@@ -346,6 +347,7 @@ __device__ __forceinline__ uint32_t dec_cluster_map(const void* own, uint32_t ra
 constexpr int kDecodeClusterWide = 8;   // ... or eight, when the groups are few and small (up to four query heads each)
 constexpr int kDecodeClusterPair = 2;   // ... or two, when there are too many groups for four CTAs each
 constexpr bool kWideClusterFits = (D / kDecodeClusterWide) % 4 == 0;     // a CTA's share of the columns in fours
+constexpr int kGroupCost = 4;           // what a group costs a CTA that touches it besides its pages, in pages
 constexpr int kCutCost = 12;            // what a group cut by the end of an equal run costs, in pages of a CTA's time
 constexpr int kWideMostPages = 80;      // a group of more pages than this is cut into more than eight parts
 __device__ __forceinline__ void dec_cluster_arrive() { asm volatile("barrier.cluster.arrive.aligned;\n" ::: "memory"); }
@@ -508,11 +510,17 @@ __device__ __noinline__ void dec_plan(DecodePlan* plan, const int* cum_s, int lo
     constexpr int cluster_size = CL;
     constexpr bool kClusterMerge = CL > 1 && (D / (CL > 1 ? CL : 1)) % 4 == 0;
     DecodeRun run;
-    run.total = cum_s[n_seqs] * n_kv;
-    // A CTA takes at least four pages, and enough of them that no sequence is spread over more than
+    // Equal runs are dealt in units of which every group brings kGroupCost more than it has pages: a CTA pays
+    // for every group it touches (its queries prepared, the page ring started, a result stored) about what
+    // that many pages cost, and a run of pages alone would hand one CTA dozens of one-page groups where they
+    // lie side by side (measured: 24 sequences of 4,096 keys took 66 us, with 8 of one key beside them 130 us).
+    run.group_cost = kGroupCost;
+    run.total = (cum_s[n_seqs] + n_seqs * kGroupCost) * n_kv;
+    // A CTA takes at least four units, and enough of them that no sequence is spread over more than
     // kMaxGroupParts CTAs.
-    const int least = max(4, (longest + kMaxGroupParts - 3) / (kMaxGroupParts - 2));
+    const int least = max(4, (longest + kGroupCost + kMaxGroupParts - 3) / (kMaxGroupParts - 2));
     run.n_ctas = max(1, min(grid, run.total / least));
+    const int equal_share = run.total / run.n_ctas + kCutCost;      // what the busiest CTA of equal runs costs, in pages
     run.parts = 0;
     run.whole = 0;
     run.uneven = 0;
@@ -537,9 +545,9 @@ __device__ __noinline__ void dec_plan(DecodePlan* plan, const int* cum_s, int lo
             parts = kDecodeClusterWide;
             by_cluster = true;
         }
-        // (not if there are more parts than CTAs, nor if they would keep fewer than 80 % of the CTAs busy
-        // that equal runs crossing from group to group would: then those runs are used)
-        if (n_seqs * n_kv * parts <= grid && (by_cluster || n_seqs * n_kv * parts * 100 >= run.n_ctas * 80)) {
+        // (not if there are more parts than CTAs, nor if a part is longer than the busiest CTA of equal runs
+        // would be, cuts included: then those runs are used)
+        if (n_seqs * n_kv * parts <= grid && (by_cluster || (longest + parts - 1) / parts + kGroupCost <= equal_share)) {
             run.parts = parts;
             run.n_ctas = n_seqs * n_kv * parts;
         } else if (n_seqs * n_kv >= grid) {
@@ -548,7 +556,7 @@ __device__ __noinline__ void dec_plan(DecodePlan* plan, const int* cum_s, int lo
             // about three pages' worth of time.  Whole groups per CTA cost the busiest CTA a few pages more.
             const int groups = n_seqs * n_kv;
             const int busiest = (groups + grid - 1) / grid;
-            if (busiest * longest <= run.total / grid + 3) {
+            if (busiest * (longest + kGroupCost) <= equal_share) {
                 run.whole = groups;
                 run.n_ctas = grid;
             }
@@ -562,8 +570,8 @@ __device__ __noinline__ void dec_plan(DecodePlan* plan, const int* cum_s, int lo
         // preparation of queries, a second start of the page ring, partial results through scratch memory and a
         // ticket: about kCutCost pages' worth (batch 8 near 3,900 keys: 3.42 ms a step with equal runs, 2.85 ms
         // with sequences of one length).
-        const int per_part = (longest + cluster_size - 1) / cluster_size;
-        if (per_part <= run.total / run.n_ctas + kCutCost) {
+        const int per_part = (longest + cluster_size - 1) / cluster_size + kGroupCost;
+        if (per_part <= equal_share) {
             run.parts = cluster_size;
             run.uneven = 1;
             run.n_ctas = n_seqs * n_kv * cluster_size;
@@ -571,8 +579,7 @@ __device__ __noinline__ void dec_plan(DecodePlan* plan, const int* cum_s, int lo
     }
     // The same with whole groups, one a CTA, where there are too many groups to cut each (and no more than CTAs):
     // nothing is merged, and the longest group is the kernel's length.
-    if (shortest != longest && run.parts == 0 && n_seqs * n_kv <= grid &&
-        longest <= run.total / run.n_ctas + kCutCost) {
+    if (shortest != longest && run.parts == 0 && n_seqs * n_kv <= grid && longest + kGroupCost <= equal_share) {
         run.parts = 1;
         run.uneven = 1;
         run.n_ctas = n_seqs * n_kv;
@@ -582,11 +589,15 @@ __device__ __noinline__ void dec_plan(DecodePlan* plan, const int* cum_s, int lo
     if (shortest != longest && run.parts == 0 && n_seqs * n_kv > grid) {
         const int groups = n_seqs * n_kv;
         const int busiest = (groups + grid - 1) / grid;
-        if (busiest * longest <= run.total / grid + kCutCost) {
+        if (busiest * (longest + kGroupCost) <= equal_share) {
             run.whole = groups;
             run.uneven = 1;
             run.n_ctas = grid;
         }
+    }
+    if (run.parts > 0 || run.whole > 0) {
+        run.group_cost = 0;                     // groups are cut or kept one by one: the units are their pages
+        run.total = cum_s[n_seqs] * n_kv;
     }
     const bool idle = cta >= run.n_ctas;
     // this CTA's units and the sequence that holds the first of them
@@ -614,7 +625,7 @@ __device__ __noinline__ void dec_plan(DecodePlan* plan, const int* cum_s, int lo
         int lo = 0, hi = n_seqs - 1;
         while (lo < hi) {
             const int mid = (lo + hi + 1) >> 1;
-            if (cum_s[mid] * n_kv <= first_unit) lo = mid; else hi = mid - 1;
+            if ((cum_s[mid] + mid * run.group_cost) * n_kv <= first_unit) lo = mid; else hi = mid - 1;
         }
         first_seq = lo;
     }
@@ -742,10 +753,13 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     // the queries) may still be running.
     unsigned preloaded = 0;
     if (!idle) {
+        // (in equal runs a group's first `gc` units stand for its fixed cost and hold no pages)
+        const int gc = run.group_cost;
         const int seq_tiles = cum_s[seq + 1] - cum_s[seq];
-        const int in_seq = u_begin - cum_s[seq] * n_kv;
-        const int kv_head = in_seq / seq_tiles, t_a = in_seq % seq_tiles;
-        const int t_b = min(seq_tiles, t_a + (u_end - u_begin));
+        const int in_seq = u_begin - (cum_s[seq] + seq * gc) * n_kv;
+        const int kv_head = in_seq / (seq_tiles + gc), off = in_seq % (seq_tiles + gc);
+        const int t_a = max(0, off - gc);
+        const int t_b = max(0, min(seq_tiles + gc, off + (u_end - u_begin)) - gc);
         const int pos = seq_start[seq];
         const int first_key = window > 0 ? max(0, pos - window + 1) : 0;
         const int t_begin = first_key / kPage + t_a, t_end = first_key / kPage + t_b - 1;
@@ -780,14 +794,21 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     }
     int u = u_begin;
     bool first_segment = true;
+    const int gc = run.group_cost;       // equal runs: a group's first `gc` units stand for its fixed cost, no pages
     while (u < u_end) {
-        while (cum_s[seq + 1] * n_kv <= u) ++seq;
+        while ((cum_s[seq + 1] + (seq + 1) * gc) * n_kv <= u) ++seq;
         const int seq_tiles = cum_s[seq + 1] - cum_s[seq];
-        const int in_seq = u - cum_s[seq] * n_kv;
-        const int kv_head = in_seq / seq_tiles, t_a = in_seq % seq_tiles;
-        const int t_b = min(seq_tiles, t_a + (u_end - u));            // tiles [t_a, t_b) of this group
+        const int in_seq = u - (cum_s[seq] + seq * gc) * n_kv;
+        const int kv_head = in_seq / (seq_tiles + gc), off = in_seq % (seq_tiles + gc);
+        const int end_off = min(seq_tiles + gc, off + (u_end - u));
+        const int t_a = max(0, off - gc), t_b = max(0, end_off - gc);  // tiles [t_a, t_b) of this group
+        const int units_here = end_off - off;
+        if (t_b == t_a) {
+            u += units_here;             // the run ends inside the group's cost units: its pages are the next CTA's
+            continue;
+        }
         const bool whole = t_a == 0 && t_b == seq_tiles;
-        const int group_first_unit = cum_s[seq] * n_kv + kv_head * seq_tiles;
+        const int group_first_unit = (cum_s[seq] + seq * gc) * n_kv + kv_head * (seq_tiles + gc);
 
         const int pos = seq_start[seq];
         const int kv_len = pos + 1;
@@ -855,8 +876,8 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                 c_first = (seq * n_kv + kv_head) * run.parts;
                 c_last = c_first + run.parts - 1;
             } else {
-                c_first = dec_cta_of_unit(run, group_first_unit);
-                c_last = dec_cta_of_unit(run, group_first_unit + seq_tiles - 1);
+                c_first = dec_cta_of_unit(run, group_first_unit + gc);                  // who holds the first page
+                c_last = dec_cta_of_unit(run, group_first_unit + gc + seq_tiles - 1);
                 first_slot = dec_run_begin(run, c_first) >= group_first_unit ? 0 : 1;
             }
         }
@@ -1043,7 +1064,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         // (the next group's pages come through the async proxy into memory this group's merge wrote)
         if (kTmaPages) asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
         __syncthreads();     // the reduction buffers alias the tile buffers of the next group
-        u += t_b - t_a;
+        u += units_here;
         first_segment = false;
     }
 }

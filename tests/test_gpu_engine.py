@@ -767,14 +767,14 @@ def test_widths_that_are_no_multiples_of_eight(tmp_path, dtype, hidden, inter, g
 @pytest.mark.parametrize("name", ["A", "B"])
 def test_a_live_set_of_more_than_eight_runs_on_buffers_with_places_to_spare(folders, name, dtype):
     """Eleven requests at once with unequal lengths of output: decode steps of 11, 10, 9 sequences run on
-    buffers of 12 and 10 places (``decode_places``), the places past the live sequences filled with sequences
+    buffers of 16 places (``decode_places``), the places past the live sequences filled with sequences
     of one token on the null page.  Every request's tokens are the plain implementation's, the filling's are
     never seen, and a toy check that the sizes of buffers are the few expected ones."""
     from dryft_flash_infer_b200 import Request
     from dryft_flash_infer_b200.engine.decode import decode_places
 
-    assert [decode_places(n) for n in (1, 7, 8, 9, 10, 11, 16, 17, 20, 33, 64, 65, 100)] == \
-        [1, 7, 8, 10, 10, 12, 16, 20, 20, 40, 64, 80, 112]
+    assert [decode_places(n) for n in (1, 2, 3, 7, 8, 9, 11, 16, 17, 33, 64, 65, 100)] == \
+        [1, 2, 3, 7, 8, 16, 16, 16, 32, 64, 64, 96, 128]
     folder, cfg, weights = folders[name]
     ref_w = reference_weights(weights, dtype)
     engine = make_engine(folder, dtype, max_tokens=64 * 2 * 11, max_seqs=11, cuda_graph=True)
@@ -786,7 +786,7 @@ def test_a_live_set_of_more_than_eight_runs_on_buffers_with_places_to_spare(fold
     assert engine.cache.live_slots == 0
     engine.cache.book.check()
     sizes = sorted({b.n for b in engine.decoder.batches.values()})
-    assert set(sizes) <= {1, 2, 3, 4, 5, 6, 7, 8, 10, 12} and 12 in sizes and 10 in sizes, sizes
+    assert set(sizes) <= {1, 2, 3, 4, 5, 6, 7, 8, 16} and {8, 16} <= set(sizes), sizes
     for r, n in zip(requests, news):
         assert len(r.output) == n
         if dtype == "float32":
