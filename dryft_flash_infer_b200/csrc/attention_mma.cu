@@ -562,6 +562,16 @@ __device__ __noinline__ void dec_plan(DecodePlan* plan, const int* cum_s, int lo
             }
         }
     }
+    else if (const int many = max(1, longest / max(least, (run.total + grid - 1) / grid));
+             many > cluster_size && shortest >= many && n_seqs * n_kv * many <= grid &&
+             (longest + many - 1) / many + kGroupCost <= equal_share) {
+        // Sequences of different lengths, none shorter than the number of parts that sequences of the longest's
+        // length would be cut into: every group in that many parts of its own pages, which meet through scratch
+        // memory and a ticket (more and shorter parts than a cluster has CTAs: the few groups of a small batch)
+        run.parts = many;
+        run.uneven = 1;
+        run.n_ctas = n_seqs * n_kv * many;
+    }
     else if (kClusterMerge && n_seqs * n_kv * cluster_size <= grid && group <= dec_cluster_rows(cluster_size)) {
         // Sequences of different lengths and few groups: every group is cut into as many parts as a cluster has
         // CTAs, each part a share of its own group's pages (none, for a group with fewer pages than parts), and
