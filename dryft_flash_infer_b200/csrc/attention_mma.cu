@@ -506,9 +506,14 @@ struct DecodePlan {
 };
 template <int CL>
 __device__ __noinline__ void dec_plan(DecodePlan* plan, const int* cum_s, int longest, int shortest, int n_seqs, int n_kv,
-                                      int group, int grid, int cta) {
+                                      int group, int launched, int cta) {
     constexpr int cluster_size = CL;
     constexpr bool kClusterMerge = CL > 1 && (D / (CL > 1 ? CL : 1)) % 4 == 0;
+    // CTAs that the plan may give pages to.  A launch in clusters runs fewer CTAs at once than the occupancy
+    // calculation promises (measured on a B200: 284 promised for clusters of four, the kernel at full speed up to
+    // 272 CTAs with pages and a quarter slower from 280 on, when the last clusters wait for a place), so a
+    // sixteenth of the launch is left without pages.
+    const int grid = CL > 1 ? (launched - launched / 16) / CL * CL : launched;
     DecodeRun run;
     // Equal runs are dealt in units of which every group brings kGroupCost more than it has pages: a CTA pays
     // for every group it touches (its queries prepared, the page ring started, a result stored) about what
@@ -527,8 +532,8 @@ __device__ __noinline__ void dec_plan(DecodePlan* plan, const int* cum_s, int lo
     run.tiles = longest;
     if (shortest == longest) {
         // every group has the same number of pages: the same number of parts for each, none crossing over
-        const int per_cta = max(least, (run.total + grid - 1) / grid);
-        int parts = max(1, longest / per_cta);
+        // (as many as there are CTAs for, none shorter than the least a CTA takes)
+        int parts = max(1, min(grid / (n_seqs * n_kv), longest / least));
         // Short groups with CTAs to spare: four parts each, although that leaves a CTA fewer than four pages.
         // Four parts meet in a cluster, which costs less than the pages saved (at batch 1 and 8 with some 700
         // keys a sequence the kernel took 20 us with two parts of five or six pages that met through scratch
@@ -565,7 +570,7 @@ __device__ __noinline__ void dec_plan(DecodePlan* plan, const int* cum_s, int lo
             }
         }
     }
-    else if (const int many = max(1, longest / max(least, (run.total + grid - 1) / grid));
+    else if (const int many = max(1, min(grid / (n_seqs * n_kv), longest / least));
              many > cluster_size && shortest >= many && n_seqs * n_kv * many <= grid &&
              (longest + many - 1) / many + kGroupCost <= equal_share) {
         // Sequences of different lengths, none shorter than the number of parts that sequences of the longest's
