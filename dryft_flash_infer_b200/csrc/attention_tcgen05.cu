@@ -340,12 +340,20 @@ __device__ __forceinline__ unsigned long long fa_now() {
 // last fixed, which after the first pages of a row happens rarely.  The probabilities never touch
 // shared memory: a thread writes its row's bfloat16 pairs into tensor memory (tcgen05.st), and the
 // product with V takes them from there as its first operand.  A tcgen05.commit arrives only
-// when every MMA issued before it is complete, so "scores of page j+1 are ready" also tells the
-// softmax threads that the product of page j has finished reading P and writing the output.
+// when every MMA issued before it is complete, so "the next scores are ready" also tells the
+// softmax threads that the products issued before them have finished reading P and writing the output.
+//
+// Pages are taken two at a time: the keys of a pair of pages lie in shared memory as one tile of 128 keys,
+// and the scores of a query tile against both come from one group of MMAs with N = 128 (the query operand,
+// 4 KB of shared memory per MMA, is fetched once for 128 keys instead of once for 64: an MMA of 128 x 64 x 16
+// took 84 clocks for 32 clocks of arithmetic).  The softmax still goes page by page (64 scores a row at a
+// time), and the second page's scores are there while the first page's product with V runs.  The
+// probabilities of a page overwrite the first half of that page's scores.
 constexpr int kFa2Threads = 320;                                   // producer, issuer, 2 x 4 softmax warps
-constexpr int kFa2Stages = 4;                                      // pages of keys and values in flight
-constexpr int kFa2Smem = 2 * kFaQBytes + kFa2Stages * 2 * kFaKBytes + 1024;
-constexpr int kFa2TmemCols = 512;      // S of tile X at 64 X, output of tile X at 128 + 128 X, P of tile X at 384 + 32 X
+constexpr int kFa2Stages = 2;                                      // pairs of pages of keys and values in flight
+constexpr int kFa2PairBytes = 4 * kFaKBytes;                       // keys of two pages as one tile, values page by page
+constexpr int kFa2Smem = 2 * kFaQBytes + kFa2Stages * kFa2PairBytes + 1024;
+constexpr int kFa2TmemCols = 512;      // S of tile X at 128 X (page p of the pair at + 64 p, its P over its first 32), output at 256 + 128 X
 constexpr float kFaRescaleStep = 8.0f;                             // in log2 units
 
 __global__ void __launch_bounds__(kFa2Threads, 1)
@@ -357,12 +365,12 @@ attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __
     pdl_launch_next();
     extern __shared__ unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t q_full, kv_full[kFa2Stages], kv_empty[kFa2Stages];
-    __shared__ __align__(8) uint64_t s_full[2], p_full[2], all_done;
+    __shared__ __align__(8) uint64_t s_full[2], p_full[2][2], pv_first[2], all_done;
     __shared__ uint32_t tmem_base_s;
 
     unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     unsigned char* q_s = base;                                   // [tile][blocks][128 rows][128 bytes]
-    unsigned char* kv_s = q_s + 2 * kFaQBytes;
+    unsigned char* kv_s = q_s + 2 * kFaQBytes;                   // [stage][K: blocks x 128 keys x 128 B | V: 2 pages x blocks x 64 x 128 B]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // CTAs start in the order of blockIdx.x, then y: the head is x and the rows are y, latest rows
@@ -397,7 +405,9 @@ attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(&s_full[i], 1);
-            mbar_init(&p_full[i], 128);
+            mbar_init(&p_full[i][0], 128);     // one barrier for each page of a pair: the softmax threads go from a pair's
+            mbar_init(&p_full[i][1], 128);     // first page to its second without waiting, and a barrier must not be two phases ahead of its waiter
+            mbar_init(&pv_first[i], 1);
         }
         mbar_init(&all_done, 1);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -420,39 +430,46 @@ attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __
                 for (int b = 0; b < kFaBlocks; ++b)
                     tma_load_2d(q_s + x * kFaQBytes + b * (kFaRows * 128), &map_q, head * kFaD + b * 64,
                                 row0 + r0 + x * kFaRows, &q_full);
-            for (int j = 0; j < n_tiles; ++j) {
-                const int st = j % kFa2Stages;
-                const uint32_t round = j / kFa2Stages;
+            const int n_pairs = (n_tiles + 1) / 2;
+            for (int pr = 0; pr < n_pairs; ++pr) {
+                const int st = pr % kFa2Stages;
+                const uint32_t round = pr / kFa2Stages;
                 if (round > 0 && !mbar_wait(&kv_empty[st], (round - 1) & 1, 21)) break;
-                const int place = place_of((t_begin + j) * kFaKeys, ring_tokens);
-                const int page = table[place / kFaKeys];
-                const int cache_row = (page * n_kv + kv_head) * kFaKeys;
-                unsigned char* k_tile = kv_s + (size_t)st * 2 * kFaKBytes;
-                unsigned char* v_tile = k_tile + kFaKBytes;
-                mbar_expect_tx(&kv_full[st], 2 * kFaKBytes);
+                const int pages = min(2, n_tiles - 2 * pr);
+                unsigned char* k_pair = kv_s + (size_t)st * kFa2PairBytes;
+                unsigned char* v_pair = k_pair + 2 * kFaKBytes;
+                mbar_expect_tx(&kv_full[st], pages * 2 * kFaKBytes);
+                for (int p = 0; p < pages; ++p) {
+                    const int place = place_of((t_begin + 2 * pr + p) * kFaKeys, ring_tokens);
+                    const int page = table[place / kFaKeys];
+                    const int cache_row = (page * n_kv + kv_head) * kFaKeys;
 #pragma unroll
-                for (int b = 0; b < kFaBlocks; ++b) {
-                    tma_load_2d(k_tile + b * (kFaKeys * 128), &map_k, b * 64, cache_row, &kv_full[st]);
-                    tma_load_2d(v_tile + b * (kFaKeys * 128), &map_v, b * 64, cache_row, &kv_full[st]);
+                    for (int b = 0; b < kFaBlocks; ++b) {
+                        // keys: rows 64 p .. 64 p + 63 of the pair's tile of 128 keys; values: the page's own tile
+                        tma_load_2d(k_pair + b * (2 * kFaKeys * 128) + p * (kFaKeys * 128), &map_k, b * 64, cache_row, &kv_full[st]);
+                        tma_load_2d(v_pair + p * kFaKBytes + b * (kFaKeys * 128), &map_v, b * 64, cache_row, &kv_full[st]);
+                    }
                 }
             }
         }
     } else if (warp == 1) {
-        constexpr uint32_t idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kFaKeys >> 3) << 17) | ((uint32_t)(kFaRows >> 4) << 24);
+        // S = Q K^T for a pair of pages: N = 128 keys.  O += P V page by page: N = head size, V MN-major.
+        constexpr uint32_t idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)((2 * kFaKeys) >> 3) << 17) | ((uint32_t)(kFaRows >> 4) << 24);
         constexpr uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(kFaD >> 3) << 17) | ((uint32_t)(kFaRows >> 4) << 24);
         bool ok = mbar_wait(&q_full, 0, 22);
         auto n_of = [&](int x) { return x == 0 ? n_a : n_b; };
-        auto issue_qk = [&](int x, int j) {        // lane 0 only
-            const unsigned char* k_tile = kv_s + (size_t)(j % kFa2Stages) * 2 * kFaKBytes;
+        const int n_pairs = (n_tiles + 1) / 2;
+        auto issue_qk = [&](int x, int pr) {        // lane 0 only: the scores of tile x against the pair's 128 keys
+            const unsigned char* k_pair = kv_s + (size_t)(pr % kFa2Stages) * kFa2PairBytes;
 #pragma unroll
             for (int kk = 0; kk < kFaD / kUmmaK; ++kk) {
                 const uint64_t a = umma_desc(q_s + x * kFaQBytes + (kk / 4) * (kFaRows * 128)) + 2 * (kk % 4);
-                const uint64_t b = umma_desc(k_tile + (kk / 4) * (kFaKeys * 128)) + 2 * (kk % 4);
-                umma_bf16(tmem_base + x * 64, a, b, idesc_qk, kk > 0 ? 1u : 0u);
+                const uint64_t b = umma_desc(k_pair + (kk / 4) * (2 * kFaKeys * 128)) + 2 * (kk % 4);
+                umma_bf16(tmem_base + x * 128, a, b, idesc_qk, kk > 0 ? 1u : 0u);
             }
             umma_commit(&s_full[x]);
         };
-        // page 0: scores of both tiles
+        // pair 0: scores of both tiles
         if (ok) ok = mbar_wait(&kv_full[0], 0, 23);
         if (ok) {
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
@@ -462,45 +479,57 @@ attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __
             }
             __syncwarp();
         }
-        for (int j = 0; j < n_tiles && ok; ++j) {
-            const int st = j % kFa2Stages;
-            unsigned char* v_tile = kv_s + (size_t)st * 2 * kFaKBytes + kFaKBytes;
+        for (int pr = 0; pr < n_pairs && ok; ++pr) {
+            const int st = pr % kFa2Stages;
+            unsigned char* v_pair = kv_s + (size_t)st * kFa2PairBytes + 2 * kFaKBytes;
             // value rows of keys that were never written (only in the sequence's last page) are zeroed
-            const int dead_from = max(kv_len - (t_begin + j) * kFaKeys, 0);
-            if (dead_from < kFaKeys) {
-                const int n_dead = kFaKeys - dead_from;
-                for (int i = lane; i < n_dead * 8 * kFaBlocks; i += 32) {
-                    const int b = i / (n_dead * 8), rest = i % (n_dead * 8);
-                    *reinterpret_cast<uint4*>(v_tile + b * (kFaKeys * 128) + (dead_from + rest / 8) * 128 + (rest % 8) * 16) = make_uint4(0, 0, 0, 0);
+            for (int p = 0; p < 2; ++p) {
+                const int dead_from = max(kv_len - (t_begin + 2 * pr + p) * kFaKeys, 0);
+                if (2 * pr + p < n_tiles && dead_from < kFaKeys) {
+                    const int n_dead = kFaKeys - dead_from;
+                    for (int i = lane; i < n_dead * 8 * kFaBlocks; i += 32) {
+                        const int b = i / (n_dead * 8), rest = i % (n_dead * 8);
+                        *reinterpret_cast<uint4*>(v_pair + p * kFaKBytes + b * (kFaKeys * 128) + (dead_from + rest / 8) * 128 + (rest % 8) * 16) = make_uint4(0, 0, 0, 0);
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                    __syncwarp();
                 }
-                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-                __syncwarp();
             }
-            if (j + 1 < n_tiles) {
-                ok = mbar_wait(&kv_full[(j + 1) % kFa2Stages], ((j + 1) / kFa2Stages) & 1, 24);
-                if (!ok) break;
-            }
-            for (int x = 0; x < 2 && ok; ++x) {
-                if (j >= n_of(x)) continue;
-                FA_T(ti0);
-                ok = mbar_wait(&p_full[x], j & 1, 25);        // P of page j is in shared memory, S has been read
-                if (!ok) break;
-                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                FA_T(ti1);
-                if (lane == 0) FA_ADD(6, ti1 - ti0);
-                if (lane == 0) {
-                    // P comes from tensor memory: 16 keys of a row are 8 columns of packed bfloat16 pairs
+            bool next_landed = false;                          // the next pair's keys, needed by the first scores against them
+            for (int p = 0; p < 2 && ok; ++p) {
+                const int j = 2 * pr + p;
+                for (int x = 0; x < 2 && ok; ++x) {
+                    if (j >= n_of(x)) continue;
+                    const bool last_of_pair = !(p == 0 && j + 1 < n_of(x));
+                    if (last_of_pair && 2 * (pr + 1) < n_of(x) && !next_landed) {
+                        ok = mbar_wait(&kv_full[(pr + 1) % kFa2Stages], ((pr + 1) / kFa2Stages) & 1, 24);
+                        if (!ok) break;
+                        next_landed = true;
+                    }
+                    FA_T(ti0);
+                    ok = mbar_wait(&p_full[x][p], pr & 1, 25);    // P of page j is in tensor memory, its scores have been read
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                    FA_T(ti1);
+                    if (lane == 0) FA_ADD(6, ti1 - ti0);
+                    if (lane == 0) {
+                        // P lies over the first 32 columns of the page's scores: 16 keys of a row are 8 columns of pairs
 #pragma unroll
-                    for (int k = 0; k < kFaKeys / kUmmaK; ++k)
-                        umma_bf16_ts(tmem_base + 128 + x * 128, tmem_base + 384 + x * 32 + 8 * k,
-                                     umma_desc_mn(v_tile + k * 2048, kFaKeys * 128), idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
-                    if (j + 1 < n_of(x)) issue_qk(x, j + 1);  // its commit also covers the product just issued
-                    FA_T(ti2);
-                    FA_ADD(7, ti2 - ti1);
+                        for (int k = 0; k < kFaKeys / kUmmaK; ++k)
+                            umma_bf16_ts(tmem_base + 256 + x * 128, tmem_base + x * 128 + p * 64 + 8 * k,
+                                         umma_desc_mn(v_pair + p * kFaKBytes + k * 2048, kFaKeys * 128), idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+                        if (p == 0 && j + 1 < n_of(x)) {
+                            umma_commit(&pv_first[x]);             // the softmax of the pair's second page may rescale the output after this
+                        } else if (2 * (pr + 1) < n_of(x)) {
+                            issue_qk(x, pr + 1);                   // the tile is through with this pair; its commit also covers the product just issued
+                        }
+                        FA_T(ti2);
+                        FA_ADD(7, ti2 - ti1);
+                    }
+                    __syncwarp();
                 }
-                __syncwarp();
             }
-            if (lane == 0) umma_commit(&kv_empty[st]);         // the page's last user has been issued
+            if (lane == 0) umma_commit(&kv_empty[st]);         // the pair's last user has been issued
             __syncwarp();
         }
         if (lane == 0) umma_commit(&all_done);
@@ -513,7 +542,7 @@ attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __
         const int n_mine = x == 0 ? n_a : n_b;
         const int pos = start + r0 + x * kFaRows + t;
         const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-        const uint32_t s_addr = lane_addr + x * 64, o_addr = lane_addr + 128 + x * 128;
+        const uint32_t s_pair = lane_addr + x * 128, o_addr = lane_addr + 256 + x * 128;
         float m_ref = -INFINITY, l = 0.f;
         bool ok = true;
 #ifdef DFI_TRACE
@@ -522,9 +551,13 @@ attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __
 #endif
         for (int j = 0; j < n_mine && ok; ++j) {
             FA_T(ts0);
-            ok = mbar_wait(&s_full[x], j & 1, 26);
-            if (!ok) break;
-            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            const int pr = j >> 1, p = j & 1;                  // page p of pair pr: its scores at + 64 p
+            const uint32_t s_addr = s_pair + p * 64;
+            if (p == 0) {
+                ok = mbar_wait(&s_full[x], pr & 1, 26);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            }
             FA_T(ts1);
             uint32_t sv[64];
             {
@@ -560,7 +593,14 @@ attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __
                 m_ref = mx;
             }
             if (j > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
-                // the product of the page before is complete (s_full came after it): rescale this row's output
+                // The product of the page before must be complete before the output is touched.  For a pair's first
+                // page it is: the pair's scores were issued after it.  For the second page the issuing thread
+                // commits the first page's product to a barrier of its own.
+                if (p == 1) {
+                    ok = mbar_wait(&pv_first[x], pr & 1, 30);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                }
 #pragma unroll
                 for (int c = 0; c < kFaD; c += 32) {
                     uint32_t v[32];
@@ -592,12 +632,13 @@ attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __
                 packed[e >> 1] = *reinterpret_cast<uint32_t*>(&pair);
             }
             l = l * corr + sum;
-            // the probabilities go to tensor memory as the first operand of the product with V
+            // the probabilities go over the first half of the page's scores (all 64 are in registers by now), where the
+            // product with V takes them as its first operand
             asm volatile(
                 "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
                 "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
                 "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};\n"
-                ::"r"(lane_addr + 384 + x * 32), "r"(packed[0]), "r"(packed[1]), "r"(packed[2]), "r"(packed[3]), "r"(packed[4]),
+                ::"r"(s_addr), "r"(packed[0]), "r"(packed[1]), "r"(packed[2]), "r"(packed[3]), "r"(packed[4]),
                   "r"(packed[5]), "r"(packed[6]), "r"(packed[7]), "r"(packed[8]), "r"(packed[9]), "r"(packed[10]), "r"(packed[11]),
                   "r"(packed[12]), "r"(packed[13]), "r"(packed[14]), "r"(packed[15]), "r"(packed[16]), "r"(packed[17]),
                   "r"(packed[18]), "r"(packed[19]), "r"(packed[20]), "r"(packed[21]), "r"(packed[22]), "r"(packed[23]),
@@ -607,7 +648,7 @@ attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __
             asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
             FA_T(ts3);
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-            fa_arrive(&p_full[x]);
+            fa_arrive(&p_full[x][p]);
 #ifdef DFI_TRACE
             if (tracer) {
                 const unsigned long long ts4 = fa_now();
