@@ -201,3 +201,32 @@ def test_lookahead_stops_where_a_sequence_ends_and_with_stop_tokens():
         backend.decode_launch(slots, tokens, requests, step_index, params).result()
     list(generate_batch(backend, [Request([1, 2, 3], 4, stop_token_ids=(49,))], SamplingParams()))
     assert all(kind != "launch-from-device" for kind, _ in backend.log)
+
+
+def test_sizes_of_decode_buffers_and_hints_without_a_gpu():
+    """Decisions that need no device: which size of buffers a live set of n sequences decodes on, and that a
+    hint about the next weights is nothing where the decode kernels would not run (and keeps no matrix alive)."""
+    import gc
+
+    import torch
+
+    from dryft_flash_infer_b200.engine.decode import decode_places
+    from dryft_flash_infer_b200.ops import kernels
+
+    sizes = [decode_places(n) for n in range(1, 130)]
+    assert sizes[:8] == list(range(1, 9))                                    # small batches keep their own size
+    assert all(a <= b for a, b in zip(sizes, sizes[1:]))                      # never fewer places for more sequences
+    assert all(size >= n for n, size in enumerate(sizes, start=1))
+    assert sorted(set(sizes[8:64])) == [16, 32, 64]                           # the sizes at which the products change their tile
+    assert sorted(set(sizes[64:])) == [96, 128, 160]                          # beyond 64: multiples of 32
+    assert all(size - n < max(32, n) for n, size in enumerate(sizes, start=1))    # never more filling than sequences (or 32 places)
+
+    weight = torch.zeros(16, 32, dtype=torch.bfloat16)
+    hint = kernels.next_weights(weight, swiglu=True)
+    assert hint is kernels.next_weights(weight, swiglu=True) and hint is not kernels.next_weights(weight)
+    assert hint.hint(8) is None                     # not on a device: the decode kernels would not run there
+    assert kernels.next_weights(None) is None
+    held = len(kernels._NEXT_WEIGHTS)
+    del weight
+    gc.collect()
+    assert hint.weight is None and len(kernels._NEXT_WEIGHTS) == held - 2
