@@ -712,7 +712,32 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
 
     // ---- how many pages each sequence brings: known before this step's kernels ran, so this part
     // overlaps the kernel before (the positions were uploaded ahead of the step)
-    {
+    __shared__ DecodePlan plan_s;
+    const int cta = blockIdx.x;
+    if (n_seqs <= 32) {
+        // Up to 32 sequences: one warp counts, scans and plans, and the CTA meets once.  (For the CTAs that get their
+        // place on an SM only when the kernel before leaves it, all of this is on the way to their first page.)
+        if (warp == 0) {
+            int tiles = 0;
+            if (lane < n_seqs) {
+                const int pos = seq_start[lane];
+                const int first_key = window > 0 ? max(0, pos - window + 1) : 0;
+                tiles = pos / kPage - first_key / kPage + 1;
+            }
+            int incl = tiles;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int up = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += up;
+            }
+            const int longest = __reduce_max_sync(0xffffffffu, tiles);
+            const int shortest = __reduce_min_sync(0xffffffffu, lane < n_seqs ? tiles : 0x7fffffff);
+            if (lane < n_seqs) cum_s[lane] = incl - tiles;
+            if (lane == n_seqs - 1) cum_s[n_seqs] = incl;
+            __syncwarp();
+            if (lane == 0) dec_plan<CL>(&plan_s, cum_s, longest, shortest, n_seqs, n_kv, group, (int)gridDim.x, cta);
+        }
+    } else {
         const int per = (n_seqs + kThreads - 1) / kThreads;
         const int lo = min(n_seqs, (int)threadIdx.x * per), hi = min(n_seqs, lo + per);
         int mine = 0, longest = 0, shortest = 0x7fffffff;
@@ -745,13 +770,11 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         }
         if (threadIdx.x == kThreads - 1) cum_s[n_seqs] = before;
         __syncthreads();
-    }
-    __shared__ DecodePlan plan_s;
-    const int cta = blockIdx.x;
-    if (threadIdx.x == 0) {
-        const int longest = max(max(warp_max_s[0], warp_max_s[1]), max(warp_max_s[2], warp_max_s[3]));
-        const int shortest = min(min(warp_min_s[0], warp_min_s[1]), min(warp_min_s[2], warp_min_s[3]));
-        dec_plan<CL>(&plan_s, cum_s, longest, shortest, n_seqs, n_kv, group, (int)gridDim.x, cta);
+        if (threadIdx.x == 0) {
+            const int longest = max(max(warp_max_s[0], warp_max_s[1]), max(warp_max_s[2], warp_max_s[3]));
+            const int shortest = min(min(warp_min_s[0], warp_min_s[1]), min(warp_min_s[2], warp_min_s[3]));
+            dec_plan<CL>(&plan_s, cum_s, longest, shortest, n_seqs, n_kv, group, (int)gridDim.x, cta);
+        }
     }
     __syncthreads();
     const DecodeRun run = plan_s.run;
