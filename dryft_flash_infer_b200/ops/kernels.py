@@ -571,7 +571,8 @@ PREFILL_GEMM = os.environ.get("DRYFT_PREFILL_GEMM", "library")
 class ScaledRows:
     """Rows ``w (.) r`` of an RMS norm that still lack their factor ``1 / rms(r)``: the product that
     reads them applies it to its result.  ``ssq [parts, stride]`` holds partial sums of squares of
-    ``r`` per row; ``dim`` and ``eps`` are the norm's."""
+    ``r`` per row; ``dim`` and ``eps`` are the norm's.  With ``ssq`` None the rows are complete (the
+    factor is in them): what a product over many rows hands on, where a kernel of its own normalises."""
 
     __slots__ = ("rows", "ssq", "dim", "eps")
 
@@ -588,10 +589,11 @@ class ScaledRows:
 
 
 def add_norm_fusable(rows: torch.Tensor) -> bool:
-    """True if a product over ``rows`` runs the decode kernel, whose epilogue can add a residual and
-    prepare the next norm (``decode_linear(..., add_norm=...)``)."""
-    return (rows.is_cuda and rows.dtype == torch.bfloat16 and rows.dim() == 2 and rows.shape[0] <= SKINNY_MAX_ROWS
-            and rows.shape[1] % 8 == 0 and rows.is_contiguous())
+    """True if a product whose result is a delta of the residual ``rows`` can add it there itself and hand on
+    the rows of the next norm (``linear(..., add_norm=...)``): the decode kernel in its epilogue, the
+    library's product over many rows with the residual as its addend."""
+    return (rows.is_cuda and rows.dtype == torch.bfloat16 and rows.dim() == 2 and rows.shape[1] % 8 == 0
+            and rows.is_contiguous())
 
 
 class NextWeights:
@@ -662,6 +664,8 @@ def decode_linear(x, weight: torch.Tensor, out_dtype: torch.dtype | None = None,
     scaled = x if isinstance(x, ScaledRows) else None
     if scaled is not None:
         x = scaled.rows
+        if scaled.ssq is None:
+            scaled = None                        # complete rows: nothing left to apply
     _need_cuda(x, weight)
     m, k = x.shape
     assert x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and weight.shape[1] == k
@@ -733,12 +737,27 @@ def linear(x, weight: torch.Tensor, out_dtype: torch.dtype | None = None, add_no
     take), run the plain float32-pipe kernel of this package: true 32-bit, no library, no
     reduced-precision mode.  ``out_dtype=torch.float32`` keeps bfloat16 products unrounded (used for
     logits).  ``ScaledRows`` in, ``add_norm`` and ``then`` are those of ``decode_linear``; the other
-    kernels ignore ``then``.
+    kernels ignore ``then``.  ``add_norm`` over more than 64 bfloat16 rows: the library's product takes the
+    residual as its addend and the norm kernel follows; the ``ScaledRows`` returned are complete.
     """
-    if isinstance(x, ScaledRows) or add_norm is not None:
+    if isinstance(x, ScaledRows) and x.ssq is None:
+        x = x.rows
+    if isinstance(x, ScaledRows) or (add_norm is not None and x.shape[0] <= SKINNY_MAX_ROWS):
         # only made and asked for where the decode kernel runs (add_norm_fusable)
         return decode_linear(x, weight, out_dtype, add_norm=add_norm, then=then)
     _need_cuda(x, weight)
+    if add_norm is not None:
+        # Many rows: the residual is the product's addend (float32 sum on the accumulator, rounded once), so the
+        # delta is never written and the norm reads one tensor.
+        residual, norm_weight, eps = add_norm
+        assert x.dtype == torch.bfloat16 and residual.dtype == torch.bfloat16 and residual.is_contiguous()
+        assert residual.shape == (x.shape[0], weight.shape[0]) and x.shape[1] == weight.shape[1]
+        if PREFILL_GEMM == "own" and x.is_contiguous() and weight.is_contiguous():
+            normed = add_rms_norm(residual, pair_linear(x, weight), norm_weight, eps)
+        else:
+            residual.addmm_(x, weight.t())
+            normed = rms_norm(residual, norm_weight, eps)
+        return ScaledRows(normed, None, weight.shape[0], float(eps))
     assert x.dim() == 2 and weight.dim() == 2 and x.shape[1] == weight.shape[1] and x.dtype == weight.dtype
     if x.dtype == torch.float32 or x.shape[1] % 8:
         return simt_linear(x, weight, out_dtype)
@@ -755,6 +774,8 @@ def linear_swiglu(x, gate_up: torch.Tensor, then: NextWeights | None = None) -> 
     """``silu(x @ gate.T) * (x @ up.T)`` for the fused matrix ``gate_up = [gate; up]``: one kernel
     for bfloat16 (the decode kernel for few rows, the pair kernel for many), else the product followed by
     the SwiGLU kernel."""
+    if isinstance(x, ScaledRows) and x.ssq is None:
+        x = x.rows
     if isinstance(x, ScaledRows):
         return decode_linear(x, gate_up, swiglu=True, then=then)
     if x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and x.is_contiguous():

@@ -68,8 +68,9 @@ class Part:
     #: numbers (no host read-back, no shape that depends on values), so that a decode step through
     #: it can be captured in a CUDA graph.  A model decodes through a graph only if all its parts say so.
     graph_safe = False
-    #: True if ``forward`` takes its rows as ``kernels.ScaledRows`` too (normalised rows that still
-    #: lack their 1/rms factor, which the part's first product applies)
+    #: True if ``forward`` takes its rows as ``kernels.ScaledRows`` too (normalised rows that may still
+    #: lack their 1/rms factor, which the part's first product applies: it hands them to
+    #: ``kernels.linear`` as they are)
     accepts_scaled_rows = False
     #: True if ``forward`` takes ``add_norm=(residual, weight, eps)``: its last product then adds its
     #: result to ``residual`` in place and returns the ``ScaledRows`` of the norm that follows

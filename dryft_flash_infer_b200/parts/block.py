@@ -13,7 +13,9 @@ class PreNormBlock(Block):
     normalises in one pass, as the reference's chain does (engine/engine.py:918-961).
     When decoding (few bfloat16 rows) and the parts on both sides of a norm can, even that
     pass disappears: the product before the norm adds its result to the residual and leaves
-    the rows scaled by the norm's weight, and the product after it applies 1/rms.
+    the rows scaled by the norm's weight, and the product after it applies 1/rms.  Over a prompt's
+    many bfloat16 rows the product takes the residual as its addend, so that the delta is never
+    written, and the norm reads the sum alone.
     """
 
     kind = "pre_norm"

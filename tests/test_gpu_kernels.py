@@ -21,7 +21,8 @@ def rounded(x, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("rows, dim", [(1, 8), (7, 100), (33, 2560), (5, 3001), (70, 2560), (64, 40), (65, 8192), (66, 4100)])
+@pytest.mark.parametrize("rows, dim", [(1, 8), (7, 100), (33, 2560), (5, 3001), (70, 2560), (64, 40), (65, 8192), (66, 4100),
+                                       (67, 1032), (130, 4096), (259, 264), (2049, 1536)])
 def test_rms_norm_and_add(dtype, rows, dim):
     from dryft_flash_infer_b200.ops import kernels
 
@@ -537,6 +538,44 @@ def test_tcgen05_decode_gemm_with_the_norm_fused_around_it(m, hidden, k, n2):
         assert torch.allclose(z.float().cpu(), want, atol=0.03 * float(want.abs().max()), rtol=2e-2)
     with pytest.raises(kernels.KernelError, match="plain bfloat16"):
         kernels.decode_linear(x.cuda(), w.cuda(), torch.float32, add_norm=(residual.cuda(), norm_w.cuda(), eps))
+
+
+@pytest.mark.parametrize("m, hidden, k, n2", [(65, 200, 96, 72), (300, 2560, 512, 136), (129, 40, 40, 40)])
+def test_product_over_many_rows_with_the_residual_as_its_addend(m, hidden, k, n2, monkeypatch):
+    """More rows than the decode kernel takes: ``linear(..., add_norm=...)`` adds the product to the residual
+    in place and hands on the complete rows of the norm, which the products after it take as they are."""
+    from dryft_flash_infer_b200.ops import kernels
+
+    g = torch.Generator().manual_seed(m + hidden + k)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    w = (torch.randn(hidden, k, generator=g) * 0.1).to(torch.bfloat16)
+    residual = (torch.randn(m, hidden, generator=g) * 3).to(torch.bfloat16)
+    norm_w = 1 + 0.3 * torch.randn(hidden, generator=g)
+    w2 = (torch.randn(n2, hidden, generator=g) * 0.1).to(torch.bfloat16)
+    gate_up = (torch.randn(2 * n2, hidden, generator=g) * 0.1).to(torch.bfloat16)
+    eps = 1e-5
+    assert kernels.add_norm_fusable(residual.cuda()) and not kernels.add_norm_fusable(residual.float().cuda())
+    for gemm in ("library", "own"):
+        monkeypatch.setattr(kernels, "PREFILL_GEMM", gemm)
+        res = residual.clone().cuda()
+        normed = kernels.linear(x.cuda(), w.cuda(), add_norm=(res, norm_w.cuda(), eps))
+        assert isinstance(normed, kernels.ScaledRows) and normed.ssq is None and normed.rows.shape == (m, hidden)
+        want_res = residual.float() + x.float() @ w.float().T
+        got_res = res.float().cpu()
+        assert torch.allclose(got_res, want_res, atol=0.04, rtol=1e-2), gemm     # one rounding of the float32 sum
+        want = plain_model.rms_norm(got_res, norm_w, eps)
+        assert torch.allclose(normed.rows.float().cpu(), want, atol=tol(torch.bfloat16, 4), rtol=tol(torch.bfloat16)), gemm
+        rows = normed.rows.float().cpu()
+        y = kernels.linear(normed, w2.cuda())
+        want = rows @ w2.float().T
+        assert torch.allclose(y.float().cpu(), want, atol=0.02 * float(want.abs().max()), rtol=1e-2), gemm
+        z = kernels.linear_swiglu(normed, gate_up.cuda())
+        gu = rows @ gate_up.float().T
+        want = gu[:, :n2] / (1 + torch.exp(-gu[:, :n2])) * gu[:, n2:]
+        assert torch.allclose(z.float().cpu(), want, atol=0.03 * float(want.abs().max()), rtol=2e-2), gemm
+        few = kernels.ScaledRows(normed.rows[:5].contiguous(), None, hidden, eps)
+        y = kernels.decode_linear(few, w2.cuda(), torch.float32)            # the decode kernel takes complete rows too
+        assert torch.allclose(y.cpu(), (rows[:5] @ w2.float().T), atol=0.02 * float(want.abs().max()) + 0.02, rtol=1e-2)
 
 
 @pytest.mark.parametrize("n_q, n_kv, dim", [(8, 2, 128), (3, 1, 64), (4, 4, 128), (32, 8, 128)])
