@@ -346,17 +346,21 @@ __device__ __forceinline__ uint32_t dec_cluster_map(const void* own, uint32_t ra
 }
 constexpr int kDecodeClusterWide = 8;   // ... or eight, when the groups are few and small (up to four query heads each)
 constexpr int kDecodeClusterPair = 2;   // ... or two, when there are too many groups for four CTAs each
+constexpr int kDecodeClusterFull = 16;  // ... or sixteen (the most a launch may ask for), for the groups of one sequence
+constexpr bool kFullClusterFits = (D / kDecodeClusterFull) % 4 == 0;
+constexpr int kFullLeastKeys = 2048;    // a launch whose sequences cannot outgrow this many keys gains nothing from sixteen
 constexpr bool kWideClusterFits = (D / kDecodeClusterWide) % 4 == 0;     // a CTA's share of the columns in fours
 constexpr int kGroupCost = 4;           // what a group costs a CTA that touches it besides its pages, in pages
 constexpr int kCutCost = 12;            // what a group cut by the end of an equal run costs, in pages of a CTA's time
 constexpr int kWideMostPages = 80;      // a group of more pages than this is cut into more than eight parts
+constexpr int kPartMostPages = kWideMostPages / kDecodeClusterWide;       // (so: ten pages a part in the cluster)
 __device__ __forceinline__ void dec_cluster_arrive() { asm volatile("barrier.cluster.arrive.aligned;\n" ::: "memory"); }
 __device__ __forceinline__ void dec_cluster_wait() { asm volatile("barrier.cluster.wait.aligned;\n" ::: "memory"); }
-// The merge of a group's parts inside a cluster of CL CTAs (2, 4 or 8).  Every CTA owns D / CL columns of the
+// The merge of a group's parts inside a cluster of CL CTAs (2, 4, 8 or 16).  Every CTA owns D / CL columns of the
 // head and receives, in the space of its query tile, [sender][row][its columns] of the others' sums and then
 // [sender][row][maximum, sum]; the space holds dec_cluster_rows(CL) rows of a group (8 query heads, 4 with
-// eight CTAs), kRows * D * 4 + CL * kRows * 8 bytes, which the query tile's 16 rows always cover.
-__host__ __device__ constexpr int dec_cluster_rows(int cl) { return cl == 8 ? 4 : 8; }
+// eight CTAs or more), kRows * D * 4 + CL * kRows * 8 bytes, which the query tile's 16 rows always cover.
+__host__ __device__ constexpr int dec_cluster_rows(int cl) { return cl >= 8 ? 4 : 8; }
 template <int CL>
 __device__ __forceinline__ void dec_cluster_send(const bf16* q_s, int row, int d, float4 acc, float mx, float sum) {
     constexpr int kRows = dec_cluster_rows(CL);
@@ -541,13 +545,13 @@ __device__ __noinline__ void dec_plan(DecodePlan* plan, const int* cum_s, int lo
         if (parts < kDecodeCluster && longest >= kDecodeCluster && cluster_size == kDecodeCluster &&
             n_seqs * n_kv * kDecodeCluster <= grid)
             parts = kDecodeCluster;
-        // A launch in clusters of eight (few groups of up to four query heads): eight parts each as long as a
-        // part stays at ten pages or fewer, so that they meet in the cluster and not through scratch memory
-        // and a ticket.
+        // A launch in clusters of eight or sixteen (few groups of up to four query heads): that many parts each,
+        // as long as a part stays at ten pages or fewer, so that they meet in the cluster and not through
+        // scratch memory and a ticket.
         bool by_cluster = false;          // fewer CTAs than equal runs would use, on purpose
-        if (cluster_size == kDecodeClusterWide && longest >= kDecodeClusterWide && longest <= kWideMostPages &&
-            n_seqs * n_kv * kDecodeClusterWide <= grid) {
-            parts = kDecodeClusterWide;
+        if (cluster_size >= kDecodeClusterWide && longest >= cluster_size && longest <= kPartMostPages * cluster_size &&
+            n_seqs * n_kv * cluster_size <= grid) {
+            parts = cluster_size;
             by_cluster = true;
         }
         // (not if there are more parts than CTAs, nor if they keep fewer than 80 % of the CTAs busy and a part is
@@ -1154,7 +1158,7 @@ static int decode_clusters_enabled() {
 static int wide_clusters_enabled() {
     static int enabled = -1;
     if (enabled < 0) {
-        const char* text = getenv("DRYFT_ATTENTION_CLUSTER");      // "4": never clusters of eight
+        const char* text = getenv("DRYFT_ATTENTION_CLUSTER");      // "4": clusters of four only
         enabled = (text != nullptr && text[0] == '4') ? 0 : 1;
     }
     return enabled;
@@ -1216,6 +1220,36 @@ DFI_EXPORT int dfi_attention_prefill(const void* q, int q_stride, void* out, int
     return DFI_OK;
 }
 
+// How many clusters of sixteen CTAs of the decode kernel the device runs at once (0: none, or switched off).  A
+// cluster of more than eight CTAs is one the kernel has to ask for by an attribute of its own.
+static int full_clusters_at_once() {
+    static int clusters = -1;
+    if (clusters >= 0) return clusters;
+    clusters = 0;
+    if (!kFullClusterFits || !decode_clusters_enabled() || !wide_clusters_enabled()) return clusters;
+    auto kernel = attention_decode_kernel<kDecodeClusterFull>;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecodeSmem) != cudaSuccess ||
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) {
+        cudaGetLastError();
+        return clusters;
+    }
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(kDecodeClusterFull * 16);
+    config.blockDim = dim3(kThreads);
+    config.dynamicSmemBytes = kDecodeSmem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = kDecodeClusterFull;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    config.attrs = attr;
+    config.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kernel, &config) == cudaSuccess && n > 0) clusters = n;
+    else cudaGetLastError();
+    return clusters;
+}
+
 // One query row per sequence (row i belongs to sequence i).  `scratch` holds
 // dfi_attention_decode_scratch_floats(n_ctas) floats; `counters` holds n_seqs * n_kv ints, zero
 // before the first call and left zero by every call.  n_ctas <= 0: as many as run at once.
@@ -1275,6 +1309,19 @@ static int attention_decode(const void* q, int q_stride, void* out, int out_stri
         cluster = kDecodeClusterWide;
         grid = wide_grid;
     }
+    // Sixteen CTAs a cluster for the groups of one sequence (fewer groups than sixteen) that may grow past
+    // kFullLeastKeys keys but not past ten pages a part: a CTA alone on its SM takes about a microsecond a page (three
+    // pages in flight), so half the pages a CTA are worth more than the wider meeting costs.
+    if (cluster >= kDecodeCluster && kFullClusterFits && wide_clusters_enabled() && n_q / n_kv <= dec_cluster_rows(kDecodeClusterFull) &&
+        n_seqs * n_kv < 16 && max_kv_len > kFullLeastKeys &&
+        max_kv_len <= kPartMostPages * kDecodeClusterFull * kPage && n_seqs * n_kv <= full_clusters_at_once()) {
+        const int full_grid = n_ctas / kDecodeClusterFull * kDecodeClusterFull;
+        // (what the plan keeps of a cluster launch: see dec_plan)
+        if ((long long)n_seqs * n_kv * kDecodeClusterFull <= (full_grid - full_grid / 16) / kDecodeClusterFull * kDecodeClusterFull) {
+            cluster = kDecodeClusterFull;
+            grid = full_grid;
+        }
+    }
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3(grid);
     config.blockDim = dim3(kThreads);
@@ -1296,7 +1343,8 @@ static int attention_decode(const void* q, int q_stride, void* out, int out_stri
     }
     config.attrs = attr;
     config.numAttrs = n_attr;
-    auto kernel = cluster == kDecodeClusterWide ? attention_decode_kernel<kDecodeClusterWide>
+    auto kernel = cluster == kDecodeClusterFull ? attention_decode_kernel<kDecodeClusterFull>
+                  : cluster == kDecodeClusterWide ? attention_decode_kernel<kDecodeClusterWide>
                   : cluster == kDecodeCluster   ? attention_decode_kernel<kDecodeCluster>
                   : cluster == kDecodeClusterPair ? attention_decode_kernel<kDecodeClusterPair>
                                                   : attention_decode_kernel<1>;
@@ -1321,6 +1369,13 @@ DFI_EXPORT int dfi_attention_decode(const void* q, int q_stride, void* out, int 
     return attention_decode(q, q_stride, out, out_stride, k_cache, v_cache, cache_pages, block_table, table_width,
                             seq_start, n_seqs, n_q, n_kv, page_size, ring_tokens, window, scale, n_ctas, scratch, counters,
                             none, max_kv_len, stream);
+}
+
+// The lengths (in keys) at which the launch shape chosen by `max_kv_len` changes, in rising order; 0 past the
+// last.  A caller that knows how long its sequences are picks the smallest of them that covers the longest.
+DFI_EXPORT int dfi_attention_decode_kv_step(int i) {
+    const int steps[3] = {kFullLeastKeys, kWideMostPages * kPage, kPartMostPages * kDecodeClusterFull * kPage};
+    return i >= 0 && i < 3 ? steps[i] : 0;
 }
 
 // 1 if this build (head size) has the variant that prepares the step's token itself.

@@ -36,6 +36,12 @@ class DecodeBatch:
     they cost a row of every product and a page of attention, reach nothing that lives, and what is
     chosen for them is thrown away.  So a live set that shrinks by a sequence keeps its buffers and its
     graph instead of running a step launch by launch and capturing a graph for every size on its way down.
+
+    The attention kernel chooses its launch shape by how long a sequence may get (``max_kv_len``), and a
+    graph holds the shape it was captured with.  The host knows every sequence's length, so a step says the
+    smallest of ``kernels.DECODE_KV_STEPS`` that covers its longest sequence, and the batch keeps a graph for
+    each limit it has met: all on the same buffers, so the tokens stay where they are when a batch grows
+    past a limit.
     """
 
     all_decode = True
@@ -51,7 +57,8 @@ class DecodeBatch:
         self.temperature = temperature
         self.use_graph = use_graph
         self.q_lens = [1] * n
-        self.max_kv_len = max_context
+        self.max_context = max_context
+        self.max_kv_len = max_context     # of the step being launched: see ``launch``
         device = model.device
         sections = {"tokens": n, "row_seq": n, "row_pos": n, "seq_start": n, "seq_qlen": n, "seq_slot": n,
                     "cu_rows": n + 1, "wanted_rows": n, "uniforms": n}
@@ -95,7 +102,8 @@ class DecodeBatch:
             h[self.offsets["wanted_rows"]: self.offsets["wanted_rows"] + n] = np.arange(n)
         self.first_refreshed = self.offsets["row_seq"]
         self.h2d_bytes_per_step = (total - self.first_refreshed) * 4
-        self.graph = None
+        self.graph = None                 # of the limit used last: None (never run), False (run once), or the graph
+        self.graphs: dict[int, tuple] = {}          # kv limit -> (graph or False, its logits)
         self.slots: list[int] = []
         self.starts: list[int] = []
         self.live = 0                     # sequences of the step launched last (the rest of the n places are filling)
@@ -147,23 +155,28 @@ class DecodeBatch:
         for slot in slots:
             book.reserve(slot, 1)
         self._refresh(slots, tokens, uniforms)
+        limit = self.max_kv_len = kernels.decode_kv_limit(max(self.starts) + 1, self.max_context)
+        held = self.graphs.get(limit)
         if not self.use_graph:
             self._body()
-        elif self.graph is None:
-            # the first step runs as it is (it also sizes every scratch buffer); the second is captured
+        elif held is None:
+            # the first step under a limit runs as it is (it also sizes every scratch buffer); the second is captured
             before = kernels.LAUNCHES
             self._body()
             self.launches_per_step = kernels.LAUNCHES - before
+            self.graphs[limit] = (False, None)
             self.graph = False
-        elif self.graph is False:
+        elif held[0] is False:
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
                 self._body()
             # capturing does not run the kernels: replay once for this step
             graph.replay()
+            self.graphs[limit] = (graph, self.logits)
             self.graph = graph
         else:
+            self.graph, self.logits = held
             self.graph.replay()
         for slot in slots:
             book.advance(slot, 1)

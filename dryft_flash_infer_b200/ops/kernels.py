@@ -403,6 +403,21 @@ def decode_prepares_tokens(qkv: torch.Tensor, ctx, n_q: int, n_kv: int, head_dim
             and qkv.stride(0) % 4 == 0 and bool(_attention_library(head_dim).dfi_attention_decode_prepares()))
 
 
+#: Lengths (in keys) at which the decode attention's launch shape changes with ``ctx.max_kv_len`` (the
+#: kernel library names the same ones: ``dfi_attention_decode_kv_step``)
+DECODE_KV_STEPS = (2048, 5120, 10240)
+
+
+def decode_kv_limit(longest: int, max_context: int) -> int:
+    """What a decode step whose longest sequence holds ``longest`` keys says as its ``max_kv_len``: the
+    smallest of ``DECODE_KV_STEPS`` that covers it, at most ``max_context``.  A step launched (or a graph
+    captured) under a limit serves every step whose sequences stay within it."""
+    for step in DECODE_KV_STEPS:
+        if longest <= step:
+            return min(step, max_context)
+    return max_context
+
+
 def attention_decode(q, cache, ctx, n_q: int, n_kv: int, head_dim: int, scale: float, window: int = 0,
                      n_ctas: int | None = None, prep: TokenPrep | None = None):
     """Tensor-core attention (bfloat16) for steps with one query row per sequence: the pages of

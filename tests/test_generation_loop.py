@@ -221,6 +221,18 @@ def test_sizes_of_decode_buffers_and_hints_without_a_gpu():
     assert sorted(set(sizes[64:])) == [96, 128, 160]                          # beyond 64: multiples of 32
     assert all(size - n < max(32, n) for n, size in enumerate(sizes, start=1))    # never more filling than sequences (or 32 places)
 
+    # what a decode step says about how long its sequences may get: the smallest limit that covers the longest,
+    # never more than the cache's own, never less than the longest
+    steps = kernels.DECODE_KV_STEPS
+    assert list(steps) == sorted(steps)
+    for max_context in (64, 2048, 4096, 6000, 40960):
+        limits = [kernels.decode_kv_limit(n, max_context) for n in range(1, max_context + 1, 61)]
+        assert all(a <= b for a, b in zip(limits, limits[1:])) and limits[-1] <= max_context
+        assert all(limit >= n for limit, n in zip(limits, range(1, max_context + 1, 61)))
+        assert set(limits) <= set(steps) | {max_context}
+    assert kernels.decode_kv_limit(1, 40960) == steps[0] and kernels.decode_kv_limit(steps[0] + 1, 40960) == steps[1]
+    assert kernels.decode_kv_limit(steps[-1] + 1, 40960) == 40960
+
     weight = torch.zeros(16, 32, dtype=torch.bfloat16)
     hint = kernels.next_weights(weight, swiglu=True)
     assert hint is kernels.next_weights(weight, swiglu=True) and hint is not kernels.next_weights(weight)

@@ -802,3 +802,48 @@ def test_a_live_set_of_more_than_eight_runs_on_buffers_with_places_to_spare(fold
     assert rows.shape[0] == 9
     for i, p in enumerate(nine):
         assert_close(rows[i], plain_model.forward(cfg, ref_w, p)[-1], dtype, f"nine at once, sequence {i}")
+
+
+TINY_F = {
+    "architectures": ["Qwen3ForCausalLM"], "num_hidden_layers": 1, "hidden_size": 96, "num_attention_heads": 4,
+    "num_key_value_heads": 2, "head_dim": 128, "intermediate_size": 136, "vocab_size": 157, "rope_theta": 30000.0,
+    "rms_norm_eps": 1e-5, "tie_word_embeddings": True, "hidden_act": "silu", "max_position_embeddings": 4096,
+}
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_decoding_across_a_length_at_which_the_attention_launch_changes(tmp_path, dtype):
+    """One sequence decoded from 2,040 to 2,056 keys on the fixed buffers: at 2,048 the step says another
+    limit, the attention kernel is launched in another shape (clusters of sixteen CTAs in bfloat16) and a
+    second graph is captured on the same buffers.  Every token's logits against the plain implementation;
+    then a second, short sequence goes back to the first limit's graph."""
+    from dryft_flash_infer_b200 import Engine, StepEntry
+    from dryft_flash_infer_b200.ops import kernels
+
+    cfg = TINY_F
+    weights = plain_model.random_weights(cfg, seed=21, matrix_std=0.05, norm_std=0.1)
+    folder = write_model(tmp_path, cfg, weights)
+    ref_w = reference_weights(weights, dtype)
+    engine = Engine(folder, dtype=dtype, max_tokens=4096, max_context=4096)
+    prompt = prompts_for(cfg, [2056], seed=8)[0]
+    short = prompts_for(cfg, [70], seed=9)[0]
+    want = plain_model.forward(cfg, ref_w, prompt, places=list(range(2039, 2056)))
+    want_short = plain_model.forward(cfg, ref_w, short, places=[68, 69])
+    slot = engine.open_slot()
+    logits = engine.step([StepEntry(slot, prompt[:2040], [2039])])
+    assert_close(logits[0], want[0], dtype, "the prompt's last place")
+    for i in range(2040, 2056):
+        logits = engine.step([StepEntry(slot, [prompt[i]], [0])])
+        assert_close(logits[0], want[i - 2039], dtype, f"token {i}")
+    batch = next(iter(engine.decoder.batches.values()))
+    if batch.use_graph:
+        assert sorted(batch.graphs) == [kernels.DECODE_KV_STEPS[0], 4096]
+        assert all(graph is not False for graph, _ in batch.graphs.values())
+    engine.close_slot(slot)
+    slot = engine.open_slot()
+    engine.step([StepEntry(slot, short[:68], [])])
+    for i in (68, 69):
+        logits = engine.step([StepEntry(slot, [short[i]], [0])])
+        assert_close(logits[0], want_short[i - 68], dtype, f"short sequence, token {i}")
+    engine.close_slot(slot)
+    engine.check_status()

@@ -742,3 +742,47 @@ def test_attention_decode_of_sequences_of_different_lengths(n_seqs, n_kv, group,
         assert torch.allclose(one.k.float(), two.k.float(), atol=tol(dtype), rtol=tol(dtype), equal_nan=True)
         assert torch.equal(one.v.float().nan_to_num(7.0), two.v.float().nan_to_num(7.0))
     kernels.check_status()
+
+
+@pytest.mark.parametrize("n_seqs, n_kv, group, dim", [(1, 8, 4, 128), (1, 4, 2, 64), (3, 2, 4, 128), (1, 8, 4, 96), (1, 15, 1, 32)])
+def test_attention_decode_in_clusters_of_sixteen(n_seqs, n_kv, group, dim):
+    """The groups of one sequence (fewer than sixteen) whose cache may grow past 2,048 keys, but not past ten
+    pages for each of sixteen parts, are launched in clusters of sixteen CTAs: sixteen parts that meet in the
+    cluster from 16 pages on, and the other ways of dealing where that does not apply (fewer pages; sequences
+    of different lengths; a head size whose columns sixteen CTAs cannot share, which stays with eight).  With
+    token preparation inside and without."""
+    from dryft_flash_infer_b200.ops import kernels
+    from dryft_flash_infer_b200.parts.rotary import RotaryEmbedding
+
+    dtype = torch.bfloat16
+    n_q = n_kv * group
+    g = torch.Generator().manual_seed(dim + n_kv)
+    lib = kernels._attention_library(dim)
+    assert tuple(lib.dfi_attention_decode_kv_step(i) for i in range(4)) == kernels.DECODE_KV_STEPS + (0,)
+    for longest, limit in ((2100, 2100), (4096, 4096), (9001, 10240), (600, 4096), (1023, 8000), (65, 4096), (40, 4096),
+                           (1025, 2049)):
+        lengths = [longest] + [max(1, longest // (3 * i + 2)) for i in range(n_seqs - 1)]
+        new = [1] * n_seqs
+        q, cache, row_seq, row_pos, scale, want = attention_case(dtype, n_q, n_kv, dim, lengths, new, seed=dim + longest,
+                                                                 sharp=max(1, longest // 3))
+        ctx = step_like(lengths, new)
+        ctx.max_kv_len = limit
+        for ctas in (None, 64):
+            got = kernels.attention_decode(q, cache, ctx, n_q, n_kv, dim, scale, n_ctas=ctas)
+            assert torch.isfinite(got).all()
+            assert torch.allclose(got.float().cpu(), want, atol=tol(dtype, 2), rtol=tol(dtype)), (longest, limit, ctas)
+            assert torch.equal(kernels.attention_decode(q, cache, ctx, n_q, n_kv, dim, scale, n_ctas=ctas), got)
+        if dim in (32, 64, 128):
+            qkv = torch.randn(n_seqs, (n_q + 2 * n_kv) * dim, generator=g).to(dtype).cuda()
+            qw, kw = (1 + 0.3 * torch.randn(dim, generator=g)).cuda(), (1 + 0.3 * torch.randn(dim, generator=g)).cuda()
+            rot = RotaryEmbedding(0, dim, 4321.0)
+            rot.prepare(10240, "cuda")
+            two = LayerCache(cache.k.clone(), cache.v.clone(), cache.block_table, 64, 0, True)
+            prepared = kernels.qk_norm_rope_write(qkv.clone(), n_q, n_kv, dim, qw, kw, 1e-5, rot.cos, rot.sin, row_pos, row_seq, two)
+            want2 = kernels.attention_decode(prepared, two, ctx, n_q, n_kv, dim, scale, n_ctas=7)
+            one = LayerCache(cache.k.clone(), cache.v.clone(), cache.block_table, 64, 0, True)
+            got2 = kernels.attention_decode(None, one, ctx, n_q, n_kv, dim, scale,
+                                            prep=kernels.TokenPrep(qkv, qw, kw, 1e-5, rot.cos, rot.sin))
+            assert torch.allclose(got2.float(), want2.float(), atol=tol(dtype, 2), rtol=tol(dtype)), (longest, limit)
+            assert torch.equal(one.v.float().nan_to_num(7.0), two.v.float().nan_to_num(7.0))
+    kernels.check_status()
