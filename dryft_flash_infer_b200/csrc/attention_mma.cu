@@ -444,22 +444,37 @@ struct HeadInput {
     uint2 raw;
     float4 weight, cosine, sine;
 };
-__device__ __forceinline__ HeadInput head_load(const bf16* src, const float* weight, const float* cos_t,
-                                               const float* sin_t, int pos, int lane) {
+// What the preparation of a head at position `pos` needs besides the head itself: the same for every head of a
+// kind at that position, and known before the step's projection has run.
+struct HeadTables {
+    float4 weight, cosine, sine;
+};
+__device__ __forceinline__ HeadTables head_tables(const float* weight, const float* cos_t, const float* sin_t, int pos, int lane) {
     constexpr int kLanes = D / 4;
-    HeadInput in;
-    in.raw = make_uint2(0u, 0u);
-    in.weight = in.cosine = in.sine = make_float4(0.f, 0.f, 0.f, 0.f);
+    HeadTables tb;
+    tb.weight = tb.cosine = tb.sine = make_float4(0.f, 0.f, 0.f, 0.f);
     if (lane < kLanes) {
-        if (src != nullptr) in.raw = *reinterpret_cast<const uint2*>(src + 4 * lane);
-        if (weight != nullptr) in.weight = *reinterpret_cast<const float4*>(weight + 4 * lane);
+        if (weight != nullptr) tb.weight = *reinterpret_cast<const float4*>(weight + 4 * lane);
         if (cos_t != nullptr) {
             const int at = (4 * lane) % (D / 2);
-            in.cosine = *reinterpret_cast<const float4*>(cos_t + (size_t)pos * (D / 2) + at);
-            in.sine = *reinterpret_cast<const float4*>(sin_t + (size_t)pos * (D / 2) + at);
+            tb.cosine = *reinterpret_cast<const float4*>(cos_t + (size_t)pos * (D / 2) + at);
+            tb.sine = *reinterpret_cast<const float4*>(sin_t + (size_t)pos * (D / 2) + at);
         }
     }
+    return tb;
+}
+__device__ __forceinline__ HeadInput head_load(const bf16* src, const HeadTables& tb, int lane) {
+    HeadInput in;
+    in.raw = make_uint2(0u, 0u);
+    in.weight = tb.weight;
+    in.cosine = tb.cosine;
+    in.sine = tb.sine;
+    if (lane < D / 4 && src != nullptr) in.raw = *reinterpret_cast<const uint2*>(src + 4 * lane);
     return in;
+}
+__device__ __forceinline__ HeadInput head_load(const bf16* src, const float* weight, const float* cos_t,
+                                               const float* sin_t, int pos, int lane) {
+    return head_load(src, head_tables(weight, cos_t, sin_t, pos, lane), lane);
 }
 // `sw_row` >= 0: dst is a swizzled tile (see tile_chunk) and the vector is its row sw_row.
 __device__ __forceinline__ void head_finish(const HeadInput& in, bool norm, float eps, bool rotate, bf16* dst, bf16* dst2,
@@ -504,10 +519,12 @@ constexpr int kMaxDecodeSeqs = 1024;    // sequences per launch (their page coun
 // How a launch deals its pages, and what this CTA gets: worked out by one thread of the CTA (in a function of
 // its own, so that its divisions and branches stay out of the registers and the schedule of the page loop) and
 // handed to the others through shared memory.
-struct DecodePlan {
+struct alignas(16) DecodePlan {
     DecodeRun run;
     int first_unit, end_unit, first_seq;
+    int reserved[2];
 };
+static_assert(sizeof(DecodePlan) == 48, "a CTA reads its plan as three 16-byte words");
 template <int CL>
 __device__ __noinline__ void dec_plan(DecodePlan* plan, const int* cum_s, int longest, int shortest, int n_seqs, int n_kv,
                                       int group, int launched, int cta) {
@@ -657,6 +674,49 @@ __device__ __noinline__ void dec_plan(DecodePlan* plan, const int* cum_s, int lo
     plan->first_seq = first_seq;
 }
 
+// The plans of every CTA of a launch, worked out once: by one CTA, for the launches of all layers of a step that
+// deal the same pages (same sequences, heads, window and launch shape).  Working the plan out costs a CTA that
+// starts on an SM where another kernel ran until then one to two microseconds (its divisions, and above all its
+// instructions, none of which the SM holds yet), every layer, on the way to its first page; reading it costs
+// one load.  This kernel lets no later kernel start before it has ended (it never says launch_dependents), so
+// that every reader finds the plans complete, and it waits for everything before it, so that no reader of the
+// step before is still looking at them.
+template <int CL>
+__global__ void __launch_bounds__(kThreads)
+attention_decode_plan_kernel(DecodePlan* __restrict__ plans, const int* __restrict__ seq_start, int n_seqs, int n_kv,
+                             int group, int window, int launched) {
+    __shared__ int cum_s[kMaxDecodeSeqs + 1];
+    __shared__ int longest_s, shortest_s;
+    for (int i = threadIdx.x; i < n_seqs; i += kThreads) {
+        const int pos = seq_start[i];
+        const int first_key = window > 0 ? max(0, pos - window + 1) : 0;
+        cum_s[i + 1] = pos / kPage - first_key / kPage + 1;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        // (a thousand sequences at most, once a step: one thread sums)
+        int total = 0, longest = 0, shortest = 0x7fffffff;
+        cum_s[0] = 0;
+        for (int i = 1; i <= n_seqs; ++i) {
+            const int tiles = cum_s[i];
+            total += tiles;
+            cum_s[i] = total;
+            longest = max(longest, tiles);
+            shortest = min(shortest, tiles);
+        }
+        longest_s = longest;
+        shortest_s = shortest;
+    }
+    __syncthreads();
+    pdl_wait();
+    for (int cta = threadIdx.x; cta < launched; cta += kThreads) {
+        DecodePlan plan;
+        dec_plan<CL>(&plan, cum_s, longest_s, shortest_s, n_seqs, n_kv, group, launched, cta);
+        plan.reserved[0] = plan.reserved[1] = 0;
+        plans[cta] = plan;
+    }
+}
+
 // CL: CTAs per thread-block cluster of the launch (1: no clusters).  A kernel of its own for each, so that the
 // merge inside a cluster is compiled once, for one size, with its shares of the columns divided by constants.
 template <int CL>
@@ -667,7 +727,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                         const int* __restrict__ block_table, int table_width, const int* __restrict__ seq_start,
                         int n_seqs, int n_q, int n_kv, int ring_tokens, int window, float scale_log2,
                         float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters,
-                        DecodePrep prep) {
+                        DecodePrep prep, const DecodePlan* __restrict__ plans) {
     constexpr int cluster_size = CL;
     // the merge in the cluster needs a CTA's share of the head's columns in fours
     constexpr bool kClusterMerge = CL > 1 && (D / (CL > 1 ? CL : 1)) % 4 == 0;
@@ -739,7 +799,11 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
             if (lane < n_seqs) cum_s[lane] = incl - tiles;
             if (lane == n_seqs - 1) cum_s[n_seqs] = incl;
             __syncwarp();
-            if (lane == 0) dec_plan<CL>(&plan_s, cum_s, longest, shortest, n_seqs, n_kv, group, (int)gridDim.x, cta);
+            if (lane == 0 && plans == nullptr)
+                dec_plan<CL>(&plan_s, cum_s, longest, shortest, n_seqs, n_kv, group, (int)gridDim.x, cta);
+        } else if (warp == 1 && lane < 3 && plans != nullptr) {
+            // worked out before this launch (attention_decode_plan_kernel): three 16-byte words
+            reinterpret_cast<int4*>(&plan_s)[lane] = reinterpret_cast<const int4*>(plans + cta)[lane];
         }
     } else {
         const int per = (n_seqs + kThreads - 1) / kThreads;
@@ -774,10 +838,12 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         }
         if (threadIdx.x == kThreads - 1) cum_s[n_seqs] = before;
         __syncthreads();
-        if (threadIdx.x == 0) {
+        if (threadIdx.x == 0 && plans == nullptr) {
             const int longest = max(max(warp_max_s[0], warp_max_s[1]), max(warp_max_s[2], warp_max_s[3]));
             const int shortest = min(min(warp_min_s[0], warp_min_s[1]), min(warp_min_s[2], warp_min_s[3]));
             dec_plan<CL>(&plan_s, cum_s, longest, shortest, n_seqs, n_kv, group, (int)gridDim.x, cta);
+        } else if (threadIdx.x >= 32 && threadIdx.x < 35 && plans != nullptr) {
+            reinterpret_cast<int4*>(&plan_s)[threadIdx.x - 32] = reinterpret_cast<const int4*>(plans + cta)[threadIdx.x - 32];
         }
     }
     __syncthreads();
@@ -797,6 +863,9 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     // are asked for now, while the kernel before (which writes the new token's keys and values and
     // the queries) may still be running.
     unsigned preloaded = 0;
+    HeadTables tables_q = {};
+    float4 tables_kw = make_float4(0.f, 0.f, 0.f, 0.f);
+    int tables_pos = -1;          // the position that tables_q and tables_kw were loaded for
     if (!idle) {
         // (in equal runs a group's first `gc` units stand for its fixed cost and hold no pages)
         const int gc = run.group_cost;
@@ -816,6 +885,14 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                 fetch_page(i, table, t, kv_head, pos + 1);
                 preloaded |= 1u << i;
             }
+        }
+        // The norm's weights and the rotation's row of the token's position do not wait for the projection either.
+        // (After the wait every CTA of the launch asks for the same few lines at once; these are off that queue.)
+        if (kPrepHeadDim && prep.qkv != nullptr) {
+            tables_q = head_tables(prep.q_weight, prep.cos_table, prep.sin_table, pos, lane);
+            if (warp == 0 && prep.k_weight != nullptr && lane < D / 4)
+                tables_kw = *reinterpret_cast<const float4*>(prep.k_weight + 4 * lane);
+            tables_pos = pos;
         }
     }
     atrace(1);
@@ -874,17 +951,24 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         if (kPrepHeadDim && prep.qkv != nullptr) {
             // the group's query heads come raw from the projection: a warp prepares rows warp, warp + 4, ...
             HeadInput rows_in[4];
+            if (pos != tables_pos) {
+                tables_q = head_tables(prep.q_weight, prep.cos_table, prep.sin_table, pos, lane);
+                if (warp == 0 && prep.k_weight != nullptr && lane < D / 4)
+                    tables_kw = *reinterpret_cast<const float4*>(prep.k_weight + 4 * lane);
+                tables_pos = pos;
+            }
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const int row = warp + 4 * i;
                 rows_in[i] = head_load(row < group ? prep.qkv + (size_t)seq * prep.qkv_stride + (size_t)(kv_head * group + row) * D : nullptr,
-                                       prep.q_weight, prep.cos_table, prep.sin_table, pos, lane);
+                                       tables_q, lane);
             }
             // the step's own key and value, if this share of the group holds their page
             if (prep.write_cache && warp < 2 && t_end == pos / kPage) {
                 const bf16* raw = prep.qkv + (size_t)seq * prep.qkv_stride + (size_t)(warp == 0 ? n_q + kv_head : n_q + n_kv + kv_head) * D;
-                token_in = warp == 0 ? head_load(raw, prep.k_weight, prep.cos_table, prep.sin_table, pos, lane)
-                                     : head_load(raw, nullptr, nullptr, nullptr, pos, lane);
+                HeadTables tables_k = tables_q;
+                tables_k.weight = tables_kw;
+                token_in = head_load(raw, tables_k, lane);
             }
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -1257,8 +1341,10 @@ static int attention_decode(const void* q, int q_stride, void* out, int out_stri
                             const void* v_cache, long long cache_pages, const int* block_table, int table_width,
                             const int* seq_start, int n_seqs, int n_q, int n_kv, int page_size,
                             int ring_tokens, int window, float scale, int n_ctas, float* scratch,
-                            int* counters, const DecodePrep& prep, int max_kv_len, void* stream) {
+                            int* counters, const DecodePrep& prep, int max_kv_len, void* plans, int plans_fresh,
+                            void* stream) {
     if (n_seqs <= 0) return DFI_OK;
+    if (plans != nullptr && !aligned16(plans)) return DFI_ERR_ALIGN;
     if (page_size != kPage || n_q <= 0 || n_kv <= 0 || n_q % n_kv || n_q / n_kv > 16 || ring_tokens % kPage)
         return DFI_ERR_SHAPE;
     if (n_seqs > kMaxDecodeSeqs) return DFI_ERR_LIMIT;
@@ -1343,6 +1429,19 @@ static int attention_decode(const void* q, int q_stride, void* out, int out_stri
     }
     config.attrs = attr;
     config.numAttrs = n_attr;
+    if (plans != nullptr && plans_fresh) {
+        // the plans of this launch shape, for this launch and those that say they deal the same pages
+        auto planner = cluster == kDecodeClusterFull ? attention_decode_plan_kernel<kDecodeClusterFull>
+                       : cluster == kDecodeClusterWide ? attention_decode_plan_kernel<kDecodeClusterWide>
+                       : cluster == kDecodeCluster   ? attention_decode_plan_kernel<kDecodeCluster>
+                       : cluster == kDecodeClusterPair ? attention_decode_plan_kernel<kDecodeClusterPair>
+                                                       : attention_decode_plan_kernel<1>;
+        if (launch(planner, 1, kThreads, 0, (cudaStream_t)stream, (DecodePlan*)plans, seq_start, n_seqs, n_kv, n_q / n_kv,
+                   window, grid) != cudaSuccess) {
+            cudaGetLastError();
+            return DFI_ERR_LAUNCH;
+        }
+    }
     auto kernel = cluster == kDecodeClusterFull ? attention_decode_kernel<kDecodeClusterFull>
                   : cluster == kDecodeClusterWide ? attention_decode_kernel<kDecodeClusterWide>
                   : cluster == kDecodeCluster   ? attention_decode_kernel<kDecodeCluster>
@@ -1350,7 +1449,8 @@ static int attention_decode(const void* q, int q_stride, void* out, int out_stri
                                                   : attention_decode_kernel<1>;
     if (cudaLaunchKernelEx(&config, kernel, map_k, map_v, (const bf16*)q, q_stride, (bf16*)out, out_stride,
                            (const bf16*)k_cache, (const bf16*)v_cache, block_table, table_width, seq_start, n_seqs, n_q,
-                           n_kv, ring_tokens, window, scale * kLog2e, part_o, part_ml, counters, prep) != cudaSuccess) {
+                           n_kv, ring_tokens, window, scale * kLog2e, part_o, part_ml, counters, prep,
+                           (const DecodePlan*)plans) != cudaSuccess) {
         cudaGetLastError();
         return DFI_ERR_LAUNCH;
     }
@@ -1358,17 +1458,27 @@ static int attention_decode(const void* q, int q_stride, void* out, int out_stri
     return DFI_OK;
 }
 
+// Bytes of the plans of a launch of up to n_ctas CTAs (n_ctas <= 0: as many as run at once).
+DFI_EXPORT long long dfi_attention_decode_plan_bytes(int n_ctas) {
+    if (n_ctas <= 0) n_ctas = dfi_attention_decode_wave();
+    return (long long)sizeof(DecodePlan) * (n_ctas > 4096 ? 4096 : n_ctas < 1 ? 1 : n_ctas);
+}
+
 // max_kv_len: no sequence of this launch, or of any later replay of it in a CUDA graph, holds more keys than this
 // (0: not known).  It only chooses between launch shapes.
+// plans: null, or dfi_attention_decode_plan_bytes(n_ctas) bytes on the device that hold how the launch deals its
+// pages.  With plans_fresh they are worked out now, by a kernel before the launch; without, the launch reads what
+// an earlier call with the same seq_start, n_seqs, n_q, n_kv, window, n_ctas and max_kv_len left there (the layers
+// of one step).  Null: every CTA works its plan out itself.
 DFI_EXPORT int dfi_attention_decode(const void* q, int q_stride, void* out, int out_stride, const void* k_cache,
                                     const void* v_cache, long long cache_pages, const int* block_table, int table_width,
                                     const int* seq_start, int n_seqs, int n_q, int n_kv, int page_size,
                                     int ring_tokens, int window, float scale, int n_ctas, float* scratch,
-                                    int* counters, int max_kv_len, void* stream) {
+                                    int* counters, int max_kv_len, void* plans, int plans_fresh, void* stream) {
     DecodePrep none = {};
     return attention_decode(q, q_stride, out, out_stride, k_cache, v_cache, cache_pages, block_table, table_width,
                             seq_start, n_seqs, n_q, n_kv, page_size, ring_tokens, window, scale, n_ctas, scratch, counters,
-                            none, max_kv_len, stream);
+                            none, max_kv_len, plans, plans_fresh, stream);
 }
 
 // The lengths (in keys) at which the launch shape chosen by `max_kv_len` changes, in rising order; 0 past the
@@ -1392,7 +1502,7 @@ DFI_EXPORT int dfi_attention_decode_prepared(const void* qkv, int qkv_stride, co
                                              const int* block_table, int table_width,
                                              const int* seq_start, int n_seqs, int n_q, int n_kv, int page_size,
                                              int ring_tokens, int window, float scale, int n_ctas, float* scratch,
-                                             int* counters, int max_kv_len, void* stream) {
+                                             int* counters, int max_kv_len, void* plans, int plans_fresh, void* stream) {
     if (!kPrepHeadDim) return DFI_ERR_SHAPE;
     if (qkv == nullptr || qkv_stride % 4 || (reinterpret_cast<uintptr_t>(qkv) & 7)) return DFI_ERR_ALIGN;
     if (!aligned16(q_weight) || !aligned16(k_weight) || !aligned16(cos_table) || !aligned16(sin_table)) return DFI_ERR_ALIGN;
@@ -1410,5 +1520,5 @@ DFI_EXPORT int dfi_attention_decode_prepared(const void* qkv, int qkv_stride, co
     prep.write_cache = write_cache;
     return attention_decode(nullptr, 0, out, out_stride, k_cache, v_cache, cache_pages, block_table, table_width,
                             seq_start, n_seqs, n_q, n_kv, page_size, ring_tokens, window, scale, n_ctas, scratch, counters,
-                            prep, max_kv_len, stream);
+                            prep, max_kv_len, plans, plans_fresh, stream);
 }

@@ -44,6 +44,7 @@ class StepContext:
         #: ``kernels.NextWeights`` of the matrix that the step streams after the part that is running, or
         #: None: the model and the blocks keep it up to date, a part may give it to its last kernel
         self.upcoming = None
+        self.decode_plans = None          # set by the model for the length of one pass (see kernels.attention_decode)
         self.slots = [e.slot for e in entries]
         self.q_lens = [len(e.tokens) for e in entries]
         self.starts = [cache.length(e.slot) for e in entries]

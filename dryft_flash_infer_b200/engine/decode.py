@@ -48,6 +48,7 @@ class DecodeBatch:
     wants_every_row = True
     max_q_len = 1
     upcoming = None          # as in StepContext: what the step streams after the part that is running
+    decode_plans = None      # as in StepContext: what the kernels of one pass share between layers
 
     def __init__(self, model, cache, n: int, table_widths: list[int], max_context: int, temperature: float,
                  use_graph: bool):

@@ -143,6 +143,7 @@ class DecoderModel:
 
     def _forward(self, ctx, cache) -> torch.Tensor | None:
         spec = self.spec
+        ctx.decode_plans = {}       # what the kernels of this pass work out once and share between layers
         residual = kernels.embedding(self.embedding, ctx.tokens, scale=spec.embedding_scale)
         pending = None
         schedule = self.spec.schedule
@@ -168,6 +169,7 @@ class DecoderModel:
             else:
                 residual, pending = block.forward(residual, pending, ctx, view, state)
         ctx.upcoming = None
+        ctx.decode_plans = None
         if ctx.n_wanted == 0:
             return None
         if isinstance(pending, kernels.ScaledRows):

@@ -426,7 +426,11 @@ def attention_decode(q, cache, ctx, n_q: int, n_kv: int, head_dim: int, scale: f
 
     With ``prep`` (and ``q`` None) the kernel also does what ``qk_norm_rope_write`` does for the step's
     tokens: per-head norm and rotation of q and k, and (if ``cache.writes``) the new key and value
-    into the cache."""
+    into the cache.
+
+    ``ctx.decode_plans`` (a dict that lives as long as one pass through the model, or absent): how the
+    launch deals its pages is then worked out once, by a small kernel before the first launch that deals
+    these pages, and the launches of the other layers read it instead of working it out CTA by CTA."""
     if prep is not None:
         q = prep.qkv
         _need_cuda(q, cache.k)
@@ -442,20 +446,31 @@ def attention_decode(q, cache, ctx, n_q: int, n_kv: int, head_dim: int, scale: f
     floats, n_counters = lib.dfi_attention_decode_scratch_floats(n_ctas), ctx.n_seqs * n_kv
     held = _scratch(_ATTENTION_SCRATCH, q.device, floats, n_counters)
     out = torch.empty((q.shape[0], n_q * head_dim), dtype=q.dtype, device=q.device)
+    max_kv_len = int(getattr(ctx, "max_kv_len", 0) or 0)
+    plans, fresh = None, 0
+    shared = getattr(ctx, "decode_plans", None)
+    if shared is not None:
+        # everything the plans depend on: the launches of one pass that agree in it deal the same pages
+        key = ("attention_decode", head_dim, ctx.seq_start.data_ptr(), ctx.n_seqs, n_q, n_kv, window, n_ctas, max_kv_len)
+        plans = shared.get(key)
+        if plans is None:
+            lib.dfi_attention_decode_plan_bytes.restype = ctypes.c_longlong
+            plans = shared[key] = torch.empty(lib.dfi_attention_decode_plan_bytes(n_ctas), dtype=torch.uint8, device=q.device)
+            fresh = 1
     if prep is not None:
         _check(lib.dfi_attention_decode_prepared(
             _ptr(q), q.stride(0), _ptr(prep.q_weight), _ptr(prep.k_weight), _f(prep.eps), _ptr(prep.cos), _ptr(prep.sin),
             int(cache.writes), _ptr(out), out.stride(0), _ptr(cache.k), _ptr(cache.v), ctypes.c_longlong(cache.k.shape[0]),
             _ptr(cache.block_table),
             cache.block_table.shape[1], _ptr(ctx.seq_start), ctx.n_seqs, n_q, n_kv, cache.page_size, cache.ring_tokens,
-            window, _f(scale), n_ctas, _ptr(held[0]), _ptr(held[1]), int(getattr(ctx, "max_kv_len", 0) or 0), _stream()),
+            window, _f(scale), n_ctas, _ptr(held[0]), _ptr(held[1]), max_kv_len, _ptr(plans), fresh, _stream()),
             "attention_decode", f"head_dim {head_dim}, {n_q}/{n_kv} heads, tokens prepared inside")
         return out
     _check(lib.dfi_attention_decode(
         _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cache.k), _ptr(cache.v), ctypes.c_longlong(cache.k.shape[0]),
         _ptr(cache.block_table),
         cache.block_table.shape[1], _ptr(ctx.seq_start), ctx.n_seqs, n_q, n_kv, cache.page_size, cache.ring_tokens,
-        window, _f(scale), n_ctas, _ptr(held[0]), _ptr(held[1]), int(getattr(ctx, "max_kv_len", 0) or 0), _stream()),
+        window, _f(scale), n_ctas, _ptr(held[0]), _ptr(held[1]), max_kv_len, _ptr(plans), fresh, _stream()),
         "attention_decode", f"head_dim {head_dim}, {n_q}/{n_kv} heads")
     return out
 

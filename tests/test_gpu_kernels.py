@@ -786,3 +786,37 @@ def test_attention_decode_in_clusters_of_sixteen(n_seqs, n_kv, group, dim):
             assert torch.allclose(got2.float(), want2.float(), atol=tol(dtype, 2), rtol=tol(dtype)), (longest, limit)
             assert torch.equal(one.v.float().nan_to_num(7.0), two.v.float().nan_to_num(7.0))
     kernels.check_status()
+
+
+@pytest.mark.parametrize("n_seqs, n_kv, group, dim, lengths", [
+    (1, 8, 4, 128, [4096]), (8, 8, 4, 128, [1500] * 8), (3, 2, 4, 64, [3000, 700, 65]), (40, 4, 2, 64, None),
+    (70, 5, 3, 48, None), (9, 8, 4, 128, None), (2, 1, 16, 32, [200, 200])])
+def test_attention_decode_with_plans_worked_out_once_for_all_layers(n_seqs, n_kv, group, dim, lengths):
+    """``ctx.decode_plans``: the first launch of a pass works the plans of all CTAs out in a kernel of its own, later
+    launches (other layers: other queries and caches, the same sequences) read them.  Same results, bit for bit,
+    as launches whose CTAs plan for themselves; and a second pass with other lengths gets plans of its own."""
+    from dryft_flash_infer_b200.ops import kernels
+
+    dtype = torch.bfloat16
+    n_q = n_kv * group
+    g = torch.Generator().manual_seed(n_seqs * 7 + dim)
+    for round_ in range(2):
+        if lengths is None or round_ == 1:
+            lens = [int(x) for x in torch.randint(1, 1400, (n_seqs,), generator=g)]
+        else:
+            lens = list(lengths)
+        new = [1] * n_seqs
+        layers = [attention_case(dtype, n_q, n_kv, dim, lens, new, seed=dim + n_seqs + layer) for layer in range(3)]
+        ctx = step_like(lens, new)
+        for ctas in (None, 40):
+            alone = [kernels.attention_decode(q, cache, ctx, n_q, n_kv, dim, scale, n_ctas=ctas)
+                     for q, cache, _, _, scale, _ in layers]
+            ctx.decode_plans = {}
+            shared = [kernels.attention_decode(q, cache, ctx, n_q, n_kv, dim, scale, n_ctas=ctas)
+                      for q, cache, _, _, scale, _ in layers]
+            assert len(ctx.decode_plans) == 1
+            ctx.decode_plans = None
+            for layer, (a, b) in enumerate(zip(alone, shared)):
+                assert torch.equal(a, b), (round_, ctas, layer)
+                assert torch.allclose(b.float().cpu(), layers[layer][5], atol=tol(dtype, 2), rtol=tol(dtype)), (round_, ctas, layer)
+    kernels.check_status()
