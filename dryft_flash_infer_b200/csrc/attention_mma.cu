@@ -715,6 +715,10 @@ attention_decode_plan_kernel(DecodePlan* __restrict__ plans, const int* __restri
         plan.reserved[0] = plan.reserved[1] = 0;
         plans[cta] = plan;
     }
+    // The launch behind this kernel starts when this CTA has ended and reads the plans before its own
+    // griddepcontrol.wait: they are in L2 before the CTA ends (and are read from there, not through an SM's L1,
+    // which may still hold the plans of the step before).
+    __threadfence();
 }
 
 // CL: CTAs per thread-block cluster of the launch (1: no clusters).  A kernel of its own for each, so that the
@@ -803,7 +807,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                 dec_plan<CL>(&plan_s, cum_s, longest, shortest, n_seqs, n_kv, group, (int)gridDim.x, cta);
         } else if (warp == 1 && lane < 3 && plans != nullptr) {
             // worked out before this launch (attention_decode_plan_kernel): three 16-byte words
-            reinterpret_cast<int4*>(&plan_s)[lane] = reinterpret_cast<const int4*>(plans + cta)[lane];
+            reinterpret_cast<int4*>(&plan_s)[lane] = __ldcg(reinterpret_cast<const int4*>(plans + cta) + lane);
         }
     } else {
         const int per = (n_seqs + kThreads - 1) / kThreads;
@@ -843,7 +847,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
             const int shortest = min(min(warp_min_s[0], warp_min_s[1]), min(warp_min_s[2], warp_min_s[3]));
             dec_plan<CL>(&plan_s, cum_s, longest, shortest, n_seqs, n_kv, group, (int)gridDim.x, cta);
         } else if (threadIdx.x >= 32 && threadIdx.x < 35 && plans != nullptr) {
-            reinterpret_cast<int4*>(&plan_s)[threadIdx.x - 32] = reinterpret_cast<const int4*>(plans + cta)[threadIdx.x - 32];
+            reinterpret_cast<int4*>(&plan_s)[threadIdx.x - 32] = __ldcg(reinterpret_cast<const int4*>(plans + cta) + (threadIdx.x - 32));
         }
     }
     __syncthreads();
