@@ -457,6 +457,8 @@ def attention_decode(q, cache, ctx, n_q: int, n_kv: int, head_dim: int, scale: f
             lib.dfi_attention_decode_plan_bytes.restype = ctypes.c_longlong
             plans = shared[key] = torch.empty(lib.dfi_attention_decode_plan_bytes(n_ctas), dtype=torch.uint8, device=q.device)
             fresh = 1
+            global LAUNCHES
+            LAUNCHES += 1                        # the call then launches the planning kernel too
     if prep is not None:
         _check(lib.dfi_attention_decode_prepared(
             _ptr(q), q.stride(0), _ptr(prep.q_weight), _ptr(prep.k_weight), _f(prep.eps), _ptr(prep.cos), _ptr(prep.sin),
