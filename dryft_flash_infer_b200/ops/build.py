@@ -37,6 +37,8 @@ ATTENTION_SOURCES = ["attention_mma.cu", "attention_tcgen05.cu"]
 PREBUILT_HEAD_DIMS = (16, 32, 64, 128)
 #: host-only code (no CUDA calls, not linked against the driver): the safetensors reader
 IO_SOURCES = ["safetensors_reader.cpp"]
+#: host-only: the decode attention's plan by the kernels' own function, for tests without a device
+PLAN_SOURCES = ["decode_plan_host.cpp"]
 
 
 class BuildError(RuntimeError):
@@ -82,7 +84,7 @@ def _host_only(sources: list[str]) -> bool:
 
 def _digest(sources: list[str], defines: list[str]) -> str:
     h = hashlib.sha256()
-    for path in [CSRC / s for s in sources] + ([] if _host_only(sources) else _headers()):
+    for path in [CSRC / s for s in sources] + (sorted(CSRC.glob("*.h")) if _host_only(sources) else _headers()):
         if not path.is_file():
             raise BuildError(f"kernel source missing: {path}")
         h.update(path.name.encode())
@@ -143,7 +145,7 @@ def compile_library(name: str, sources: list[str], defines: list[str] | None = N
 
 def all_libraries() -> list[tuple[str, list[str], list[str]]]:
     """Every library the package can load: ``(name, sources, defines)``."""
-    out = [("dfi_io", IO_SOURCES, []), ("dfi_core", CORE_SOURCES, [])]
+    out = [("dfi_io", IO_SOURCES, []), ("dfi_plan", PLAN_SOURCES, []), ("dfi_core", CORE_SOURCES, [])]
     for dim in PREBUILT_HEAD_DIMS:
         out.append((f"dfi_attention_d{dim}", ATTENTION_SOURCES, [f"-DDFI_HEAD_DIM={dim}"]))
     return out
